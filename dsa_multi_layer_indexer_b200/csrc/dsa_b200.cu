@@ -1,0 +1,473 @@
+// libdsa_b200.so: the C ABI declared in include/dsa_b200.h. One translation
+// unit so the kernels share the per-device status word without relocatable
+// device code. Host code here only validates arguments, encodes tensor maps
+// and launches; it never allocates device memory and never synchronises,
+// except dsa_check_device_status which exists to do exactly that.
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "indexer_scan.cuh"
+#include "sparse_mla.cuh"
+#include "topk_select.cuh"
+
+namespace dsa {
+
+namespace {
+thread_local char tl_error[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int sm_count() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(DSA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  CUresult res = fn(map, dtype, rank, const_cast<void*>(base), gdim, gstr, bx, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS)
+    return fail(DSA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(res));
+  return DSA_OK;
+}
+
+static int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : fallback;
+}
+
+// Raises a kernel's dynamic shared-memory limit, once per device.
+template <typename K>
+static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
+  int dev = 0;
+  DSA_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && done[dev]) return DSA_OK;
+  DSA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
+  if (dev >= 0 && dev < 64) done[dev] = true;
+  return DSA_OK;
+}
+static bool g_opt_scan[64], g_opt_mla[64], g_opt_scan_f32[64];
+
+}  // namespace dsa
+
+namespace dsa {
+__global__ void __launch_bounds__(128)
+quantize_rowwise_kernel(const float* __restrict__ x, uint8_t* __restrict__ q,
+                        float* __restrict__ scale, int64_t rows, int cols, float clamp_min) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = int64_t(blockIdx.x) * 4 + warp;
+  if (row >= rows) return;
+  const float* xr = x + row * cols;
+  float amax = 0.f;
+  for (int c = lane; c < cols; c += 32) amax = fmaxf(amax, fabsf(xr[c]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float s = fmaxf(amax, clamp_min) / 448.0f;
+  if (lane == 0) scale[row] = s;
+  for (int c = lane; c < cols; c += 32) {
+    float v = xr[c] / s;
+    v = fminf(fmaxf(v, -448.f), 448.f);
+    q[row * cols + c] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+  }
+}
+}  // namespace dsa
+
+using namespace dsa;
+
+extern "C" {
+
+int dsa_abi_version(void) { return DSA_ABI_VERSION; }
+
+const char* dsa_last_error(void) { return tl_error; }
+
+const char* dsa_status_string(int status) {
+  switch (status) {
+    case DSA_OK: return "ok";
+    case DSA_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case DSA_ERR_UNSUPPORTED: return "unsupported geometry";
+    case DSA_ERR_CUDA: return "CUDA error";
+    case DSA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+int dsa_check_device_status(uint32_t* detail) {
+  unsigned int word = 0, zero = 0;
+  DSA_CUDA(cudaDeviceSynchronize());
+  DSA_CUDA(cudaMemcpyFromSymbol(&word, g_device_status, sizeof(word)));
+  if (word) DSA_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
+  if (detail) *detail = word;
+  if (word) return fail(DSA_ERR_DEVICE_TIMEOUT, "device status word 0x%x", word);
+  return DSA_OK;
+}
+
+// ------------------------------------------------------------------ indexer scan
+static int scan_common_checks(const uint8_t* index_q, const float* index_w, const float* logits,
+                              int R, int n_heads, int64_t ctx, int64_t slab_stride) {
+  DSA_REQUIRE(index_q && index_w && logits, "indexer scan: null pointer");
+  DSA_REQUIRE(aligned16(index_q) && aligned16(logits), "indexer scan: pointers must be 16-byte aligned");
+  DSA_REQUIRE(R > 0 && R <= 65535, "indexer scan: R=%d out of range [1, 65535]", R);
+  DSA_REQUIRE(n_heads > 0 && n_heads <= DSA_INDEX_MAX_HEADS && n_heads % 16 == 0,
+              "indexer scan: n_heads=%d must be a multiple of 16 and <= %d", n_heads,
+              DSA_INDEX_MAX_HEADS);
+  DSA_REQUIRE(ctx > 0 && ctx < (int64_t(1) << 31), "indexer scan: ctx=%lld out of range",
+              (long long)ctx);
+  DSA_REQUIRE(slab_stride >= ctx, "indexer scan: slab_stride=%lld < ctx=%lld",
+              (long long)slab_stride, (long long)ctx);
+  return DSA_OK;
+}
+
+static int scan_grid_x(int R, int tiles_per_row) {
+  // about two CTAs per SM in total, never more CTAs than tiles in a row
+  int per_row = env_int("DSA_SCAN_CTAS_PER_ROW", 0);
+  if (per_row <= 0) per_row = (2 * sm_count() + R - 1) / R;
+  if (per_row > tiles_per_row) per_row = tiles_per_row;
+  if (per_row < 1) per_row = 1;
+  return per_row;
+}
+
+int dsa_indexer_scan_fp8(const uint8_t* index_q, const float* index_w, const uint8_t* index_k,
+                         const float* k_scale, const int32_t* seq_lens, float* logits,
+                         uint32_t* hist, int R, int rows_per_seq, int n_heads, int64_t ctx,
+                         int64_t n_seq, int64_t k_seq_stride, int64_t scale_seq_stride,
+                         int64_t slab_stride, int impl, void* stream) {
+  int rc = scan_common_checks(index_q, index_w, logits, R, n_heads, ctx, slab_stride);
+  if (rc) return rc;
+  DSA_REQUIRE(index_k && k_scale, "indexer scan: null key cache");
+  DSA_REQUIRE(aligned16(index_k), "indexer scan: index_k must be 16-byte aligned");
+  DSA_REQUIRE(rows_per_seq > 0 && R % rows_per_seq == 0,
+              "indexer scan: R=%d is not a multiple of rows_per_seq=%d", R, rows_per_seq);
+  DSA_REQUIRE(n_seq == R / rows_per_seq, "indexer scan: n_seq=%lld but R / rows_per_seq = %d",
+              (long long)n_seq, R / rows_per_seq);
+  DSA_REQUIRE(k_seq_stride >= ctx && scale_seq_stride >= ctx,
+              "indexer scan: sequence strides must be >= ctx");
+  DSA_REQUIRE(n_seq * k_seq_stride < (int64_t(1) << 31), "indexer scan: key cache too large");
+  DSA_REQUIRE(impl == 0 || impl == 1, "indexer scan: impl must be 0 (tcgen05) or 1 (legacy)");
+
+  scan::Params p{};
+  p.q = index_q;
+  p.w = index_w;
+  p.keys = index_k;
+  p.k_scale = k_scale;
+  p.seq_lens = seq_lens;
+  p.logits = logits;
+  p.hist = hist;
+  p.ctx = ctx;
+  p.k_seq_stride = k_seq_stride;
+  p.scale_seq_stride = scale_seq_stride;
+  p.slab_stride = slab_stride;
+  p.rows_per_seq = rows_per_seq;
+  p.n_heads = n_heads;
+  p.tiles_per_row = int((ctx + scan::kTileKeys - 1) / scan::kTileKeys);
+  p.paged = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (impl == 1) {
+    int gx = int((ctx + 63) / 64);
+    int cap = (8 * sm_count() + R - 1) / R;
+    if (gx > cap) gx = cap < 1 ? 1 : cap;
+    scan::indexer_scan_legacy_kernel<<<dim3(gx, R), scan::kLegacyThreads, 0, st>>>(p);
+    DSA_CUDA(cudaGetLastError());
+    return DSA_OK;
+  }
+
+  CUtensorMap tmap;
+  // the map covers exactly the rows the scan may touch, so nothing past them is read
+  const uint64_t rows = uint64_t(n_seq - 1) * uint64_t(k_seq_stride) + uint64_t(ctx);
+  const uint64_t dims[2] = {uint64_t(scan::kKeyBytes), rows};
+  const uint64_t strides[1] = {uint64_t(scan::kKeyBytes)};
+  const uint32_t box[2] = {uint32_t(scan::kKeyBytes), uint32_t(scan::kTileKeys)};
+  rc = encode_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, index_k, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = opt_in_smem(scan::indexer_scan_tc_kernel, scan::kSmemBytes, g_opt_scan);
+  if (rc) return rc;
+  scan::indexer_scan_tc_kernel<<<dim3(scan_grid_x(R, p.tiles_per_row), R), scan::kThreads,
+                                 scan::kSmemBytes, st>>>(tmap, p);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+int dsa_indexer_scan_fp8_paged(const uint8_t* index_q, const float* index_w,
+                               const uint8_t* index_k_pages, int64_t num_pages,
+                               const int32_t* page_table, int64_t pt_stride,
+                               const int32_t* seq_lens, float* logits, uint32_t* hist, int R,
+                               int n_heads, int64_t ctx, int64_t slab_stride, void* stream) {
+  int rc = scan_common_checks(index_q, index_w, logits, R, n_heads, ctx, slab_stride);
+  if (rc) return rc;
+  DSA_REQUIRE(index_k_pages && page_table && seq_lens, "paged indexer scan: null pointer");
+  DSA_REQUIRE(aligned16(index_k_pages), "paged indexer scan: page pool must be 16-byte aligned");
+  DSA_REQUIRE(num_pages > 0 && num_pages < (int64_t(1) << 31), "paged indexer scan: bad num_pages");
+  DSA_REQUIRE(pt_stride * DSA_PAGE_TOKENS >= ctx,
+              "paged indexer scan: pt_stride=%lld pages cannot cover ctx=%lld", (long long)pt_stride,
+              (long long)ctx);
+
+  scan::Params p{};
+  p.q = index_q;
+  p.w = index_w;
+  p.seq_lens = seq_lens;
+  p.logits = logits;
+  p.hist = hist;
+  p.pages = index_k_pages;
+  p.page_table = page_table;
+  p.pt_stride = pt_stride;
+  p.ctx = ctx;
+  p.slab_stride = slab_stride;
+  p.rows_per_seq = 1;
+  p.n_heads = n_heads;
+  p.tiles_per_row = int((ctx + scan::kTileKeys - 1) / scan::kTileKeys);
+  p.paged = 1;
+
+  CUtensorMap tmap;
+  // a page is 66 rows of 128 B: 64 key rows, then 2 rows holding the 64 fp32 scales
+  const uint64_t dims[3] = {uint64_t(scan::kKeyBytes), uint64_t(DSA_INDEX_PAGE_BYTES / scan::kKeyBytes),
+                            uint64_t(num_pages)};
+  const uint64_t strides[2] = {uint64_t(scan::kKeyBytes), uint64_t(DSA_INDEX_PAGE_BYTES)};
+  const uint32_t box[3] = {uint32_t(scan::kKeyBytes), uint32_t(DSA_PAGE_TOKENS), 1u};
+  rc = encode_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, index_k_pages, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = opt_in_smem(scan::indexer_scan_tc_kernel, scan::kSmemBytes, g_opt_scan);
+  if (rc) return rc;
+  scan::indexer_scan_tc_kernel<<<dim3(scan_grid_x(R, p.tiles_per_row), R), scan::kThreads,
+                                 scan::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmap, p);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+int dsa_indexer_scan_f32(const float* index_q, const float* index_w, const float* index_k,
+                         const int32_t* seq_lens, float* logits, int R, int rows_per_seq,
+                         int n_heads, int head_dim, int64_t ctx, int64_t k_seq_stride,
+                         int64_t slab_stride, void* stream) {
+  DSA_REQUIRE(index_q && index_w && index_k && logits, "f32 indexer scan: null pointer");
+  DSA_REQUIRE(R > 0 && R <= 65535 && rows_per_seq > 0 && R % rows_per_seq == 0,
+              "f32 indexer scan: bad R=%d / rows_per_seq=%d", R, rows_per_seq);
+  DSA_REQUIRE(n_heads > 0 && head_dim > 0 && ctx > 0, "f32 indexer scan: bad geometry");
+  DSA_REQUIRE(k_seq_stride >= ctx && slab_stride >= ctx, "f32 indexer scan: strides must be >= ctx");
+  const size_t smem = (size_t(n_heads) * head_dim + n_heads) * sizeof(float);
+  DSA_REQUIRE(smem <= 200 * 1024, "f32 indexer scan: n_heads * head_dim too large for shared memory");
+  if (smem > 48 * 1024) {
+    int rc = opt_in_smem(scan::indexer_scan_f32_kernel, 200 * 1024, g_opt_scan_f32);
+    if (rc) return rc;
+  }
+  int gx = int((ctx + 7) / 8);
+  int cap = (16 * sm_count() + R - 1) / R;
+  if (gx > cap) gx = cap < 1 ? 1 : cap;
+  scan::indexer_scan_f32_kernel<<<dim3(gx, R), 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      index_q, index_w, index_k, seq_lens, logits, rows_per_seq, n_heads, head_dim, ctx,
+      k_seq_stride, slab_stride);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+// ------------------------------------------------------------------ top-k
+}  // extern "C"
+
+template <int ITEMS>
+static int launch_topk(const topk::Params& p, int R, cudaStream_t st) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(topk::kCluster, R, 1);
+  cfg.blockDim = dim3(topk::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = topk::kCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_select_kernel<ITEMS>, p));
+  return DSA_OK;
+}
+
+extern "C" {
+
+int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist,
+                    const int32_t* index_map, int32_t* out_idx, float* out_val, int R, int64_t n,
+                    int64_t slab_stride, int topk_k, int32_t pad_value, int32_t index_offset,
+                    void* stream) {
+  DSA_REQUIRE(logits && out_idx, "topk: null pointer");
+  DSA_REQUIRE(aligned16(logits), "topk: logits must be 16-byte aligned");
+  DSA_REQUIRE(R > 0 && R <= 65535, "topk: R=%d out of range", R);
+  DSA_REQUIRE(n > 0 && slab_stride >= n, "topk: need 0 < n <= slab_stride");
+  DSA_REQUIRE(topk_k > 0 && topk_k <= 32768, "topk: k=%d out of range [1, 32768]", topk_k);
+  if (n > int64_t(topk::kCluster) * topk::kThreads * 32)
+    return fail(DSA_ERR_UNSUPPORTED, "topk: n=%lld exceeds the 262144-per-row limit", (long long)n);
+  topk::Params p{};
+  p.logits = logits;
+  p.seq_lens = seq_lens;
+  p.hist = hist;
+  p.index_map = index_map;
+  p.out_idx = out_idx;
+  p.out_val = out_val;
+  p.n = n;
+  p.slab_stride = slab_stride;
+  p.topk = topk_k;
+  p.pad = pad_value;
+  p.index_offset = index_offset;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t per_thread = (n + int64_t(topk::kCluster) * topk::kThreads - 1) /
+                             (int64_t(topk::kCluster) * topk::kThreads);
+  if (per_thread <= 4) return launch_topk<4>(p, R, st);
+  if (per_thread <= 8) return launch_topk<8>(p, R, st);
+  if (per_thread <= 16) return launch_topk<16>(p, R, st);
+  return launch_topk<32>(p, R, st);
+}
+
+// ------------------------------------------------------------------ sparse MLA
+int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
+                            const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
+                            int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
+                            int64_t kv_seq_stride, int kv_fp8, void* stream) {
+  DSA_REQUIRE(q && kv && part_acc && part_m && part_l, "sparse MLA: null pointer");
+  DSA_REQUIRE(aligned16(q) && aligned16(kv) && aligned16(part_acc),
+              "sparse MLA: pointers must be 16-byte aligned");
+  DSA_REQUIRE(R > 0 && R <= 65535 && rows_per_seq > 0 && R % rows_per_seq == 0,
+              "sparse MLA: bad R=%d / rows_per_seq=%d", R, rows_per_seq);
+  DSA_REQUIRE(H > 0 && H % DSA_HEAD_BLOCK == 0, "sparse MLA: H=%d must be a multiple of %d", H,
+              DSA_HEAD_BLOCK);
+  DSA_REQUIRE(topk_k > 0, "sparse MLA: topk must be positive");
+  DSA_REQUIRE(nsplit > 0 && nsplit <= 65535, "sparse MLA: nsplit=%d out of range", nsplit);
+  DSA_REQUIRE(kv_seq_stride > 0, "sparse MLA: kv_seq_stride must be positive");
+  DSA_REQUIRE(kv_fp8 == 0 || kv_fp8 == 1, "sparse MLA: kv_fp8 must be 0 or 1");
+  mla::Params p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.kv = static_cast<const uint8_t*>(kv);
+  p.indices = indices;
+  p.seq_lens = seq_lens;
+  p.part_acc = part_acc;
+  p.part_m = part_m;
+  p.part_l = part_l;
+  p.kv_seq_stride = kv_seq_stride;
+  p.ctx = kv_seq_stride;
+  p.rows_per_seq = rows_per_seq;
+  p.H = H;
+  p.topk = topk_k;
+  p.nsplit = nsplit;
+  int kps = (topk_k + nsplit - 1) / nsplit;
+  kps = (kps + 15) / 16 * 16;
+  p.keys_per_split = kps;
+  p.kv_fp8 = kv_fp8;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  const size_t smem = kv_fp8 ? mla::SmemLayout::bytes_fp8 : mla::SmemLayout::bytes_bf16;
+  {
+    int rc = opt_in_smem(mla::sparse_mla_partials_kernel, mla::SmemLayout::bytes_fp8, g_opt_mla);
+    if (rc) return rc;
+  }
+  mla::sparse_mla_partials_kernel<<<dim3(nsplit, H / DSA_HEAD_BLOCK, R), mla::kThreads, smem,
+                                    static_cast<cudaStream_t>(stream)>>>(p);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+int dsa_sparse_mla_combine(const float* part_acc, const float* part_m, const float* part_l,
+                           void* out, int R, int H, int nsplit, void* stream) {
+  DSA_REQUIRE(part_acc && part_m && part_l && out, "sparse MLA combine: null pointer");
+  DSA_REQUIRE(aligned16(part_acc) && aligned16(out), "sparse MLA combine: misaligned pointer");
+  DSA_REQUIRE(R > 0 && R <= 65535 && H > 0 && nsplit > 0, "sparse MLA combine: bad geometry");
+  mla::sparse_mla_combine_kernel<<<dim3(H, R), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      part_acc, part_m, part_l, static_cast<__nv_bfloat16*>(out), H, nsplit);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
+                          const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
+                          void* out, int R, int rows_per_seq, int H, int topk_k, int nsplit,
+                          float sm_scale, int64_t kv_seq_stride, int kv_fp8, void* stream) {
+  int rc = dsa_sparse_mla_partials(q, kv, indices, seq_lens, part_acc, part_m, part_l, R,
+                                   rows_per_seq, H, topk_k, nsplit, sm_scale, kv_seq_stride, kv_fp8,
+                                   stream);
+  if (rc) return rc;
+  return dsa_sparse_mla_combine(part_acc, part_m, part_l, out, R, H, nsplit, stream);
+}
+
+int dsa_sparse_mla_f32(const float* q, const float* kv, const int32_t* indices,
+                       const int32_t* seq_lens, float* out, int R, int rows_per_seq, int H,
+                       int qk_dim, int v_dim, int topk_k, float sm_scale, int64_t kv_seq_stride,
+                       void* stream) {
+  DSA_REQUIRE(q && kv && out, "f32 sparse MLA: null pointer");
+  DSA_REQUIRE(R > 0 && R <= 65535 && rows_per_seq > 0 && R % rows_per_seq == 0,
+              "f32 sparse MLA: bad R=%d / rows_per_seq=%d", R, rows_per_seq);
+  DSA_REQUIRE(H > 0 && qk_dim > 0 && v_dim > 0 && v_dim <= qk_dim && v_dim <= 512,
+              "f32 sparse MLA: need 0 < v_dim <= min(qk_dim, 512)");
+  DSA_REQUIRE(indices == nullptr || topk_k > 0, "f32 sparse MLA: topk must be positive");
+  const size_t smem = (size_t(qk_dim) + 128 + 128 + 8) * sizeof(float);
+  DSA_REQUIRE(smem <= 48 * 1024, "f32 sparse MLA: qk_dim too large");
+  mla::sparse_mla_f32_kernel<<<dim3(H, R), 128, smem, static_cast<cudaStream_t>(stream)>>>(
+      q, kv, indices, seq_lens, out, rows_per_seq, H, qk_dim, v_dim, topk_k, sm_scale,
+      kv_seq_stride, kv_seq_stride);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+// ------------------------------------------------------------------ quantisation
+int dsa_quantize_e4m3_rowwise(const float* x, uint8_t* q_out, float* scale_out, int64_t rows,
+                              int cols, float clamp_min, void* stream) {
+  DSA_REQUIRE(x && q_out && scale_out, "quantize: null pointer");
+  DSA_REQUIRE(rows > 0 && cols > 0, "quantize: bad shape");
+  const int64_t blocks = (rows + 3) / 4;
+  DSA_REQUIRE(blocks < (int64_t(1) << 31), "quantize: too many rows");
+  dsa::quantize_rowwise_kernel<<<unsigned(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, q_out, scale_out, rows, cols, clamp_min);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,398 @@
+// Lightning-indexer scan over an FP8-e4m3 index-key cache.
+//
+//   logit[r, s] = (sum_h w[r,h] * relu(q[r,h,:] . k[s,:])) * k_scale[s]
+//
+// Same arithmetic as the reference's indexer blocks
+// (kernels/cuda_fused_sparse_splitk.py:531-647 dense, :1677-1903 paged; host
+// form ref_indexer_logits_fp8 :2990-2992), laid out for sm_100a:
+//
+//   * keys stream HBM -> shared memory through a TMA tensor map in 128-key x
+//     128-byte tiles with the 128-byte swizzle, into a ring of kStages slots;
+//   * one elected thread issues tcgen05.mma kind::f8f6f4 (M = 128 keys,
+//     N = 64 heads, K = 4 x 32) per tile, accumulating in tensor memory, two
+//     accumulators so the next tile's MMA overlaps this tile's epilogue;
+//   * four epilogue warps read the accumulator with tcgen05.ld: one thread owns
+//     one key and all 64 head products, so ReLU, the head weights, the head sum
+//     and the per-key scale never leave registers, and the logit store (and the
+//     optional 4096-bin histogram used by the top-k) is coalesced.
+//
+// No inter-CTA waits; every mbarrier wait is bounded and reports through
+// g_device_status.
+#pragma once
+
+#include "common.cuh"
+
+namespace dsa {
+namespace scan {
+
+constexpr int kTileKeys = 128;
+constexpr int kKeyBytes = DSA_INDEX_DIM;  // 128 e4m3 per key
+constexpr int kTileBytes = kTileKeys * kKeyBytes;
+constexpr int kStages = 4;
+constexpr int kMaxHeads = DSA_INDEX_MAX_HEADS;
+constexpr int kThreads = 192;    // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kTmemCols = 128;   // two 64-column fp32 accumulators
+constexpr int kHistBins = DSA_TOPK_HIST_BINS;
+
+struct Params {
+  const uint8_t* q;
+  const float* w;
+  const uint8_t* keys;         // dense only (the tcgen05 path reads them through the tensor map)
+  const float* k_scale;
+  const int32_t* seq_lens;
+  float* logits;
+  uint32_t* hist;
+  const uint8_t* pages;        // paged only
+  const int32_t* page_table;   // paged only
+  int64_t pt_stride;
+  int64_t ctx;
+  int64_t k_seq_stride;
+  int64_t scale_seq_stride;
+  int64_t slab_stride;
+  int rows_per_seq;
+  int n_heads;
+  int tiles_per_row;
+  int paged;
+};
+
+struct __align__(8) Barriers {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
+constexpr size_t kSmemQ = size_t(kMaxHeads) * kKeyBytes;
+constexpr size_t kSmemBytes =
+    1024 /*alignment slack*/ + kSmemStages + kSmemQ + kHistBins * 4 + kMaxHeads * 4 + sizeof(Barriers);
+
+__device__ __forceinline__ int row_len(const Params& p, int r) {
+  int64_t len = p.seq_lens ? static_cast<int64_t>(p.seq_lens[r]) : p.ctx;
+  if (len < 0) len = 0;
+  if (len > p.ctx) len = p.ctx;
+  return static_cast<int>(len);
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* s_tiles = smem;
+  uint8_t* s_q = smem + kSmemStages;
+  uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_q + kSmemQ);
+  float* s_w = reinterpret_cast<float*>(s_hist + kHistBins);
+  Barriers* bars = reinterpret_cast<Barriers*>(s_w + kMaxHeads);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int r = blockIdx.y;
+  const int seq = r / p.rows_per_seq;
+  const int len = row_len(p, r);
+  const int G = gridDim.x;
+  const bool want_hist = p.hist != nullptr;
+
+  // ---- set-up: barriers, tensor memory, swizzled query tile, head weights
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bars->full[s]), 1);
+      mbar_init(smem_u32(&bars->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bars->acc_full[b]), 1);
+      mbar_init(smem_u32(&bars->acc_empty[b]), 4);
+    }
+    bars->abort = 0;
+    mbar_fence_init();
+    prefetch_tensor_map(&tmap);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  {
+    // q[r] is [n_heads][128 B]; shared copy is K-major with the 128-B swizzle
+    // (16-byte chunk c of row h lands in chunk c ^ (h & 7)); rows past
+    // n_heads are zero so they contribute relu(0) * 0.
+    const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + size_t(r) * p.n_heads * kKeyBytes);
+    for (int i = tid; i < kMaxHeads * 8; i += kThreads) {
+      const int h = i >> 3, c = i & 7;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h < p.n_heads) v = qsrc[h * 8 + c];
+      *reinterpret_cast<uint4*>(s_q + h * kKeyBytes + ((c ^ (h & 7)) << 4)) = v;
+    }
+    for (int i = tid; i < kMaxHeads; i += kThreads)
+      s_w[i] = i < p.n_heads ? p.w[size_t(r) * p.n_heads + i] : 0.f;
+    if (want_hist)
+      for (int i = tid; i < kHistBins; i += kThreads) s_hist[i] = 0;
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  volatile uint32_t* abort_flag = &bars->abort;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      int it = 0;
+      for (int t = blockIdx.x; t < p.tiles_per_row; t += G, ++it) {
+        if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
+          atomicOr(&g_device_status, kStatusScanTimeout);
+          *abort_flag = 1;
+          break;
+        }
+        const uint32_t dst = smem_u32(s_tiles + size_t(s) * kTileBytes);
+        const uint32_t bar = smem_u32(&bars->full[s]);
+        if (!p.paged) {
+          mbar_arrive_expect_tx(bar, kTileBytes);
+          tma_load_2d(dst, &tmap, 0, static_cast<int>(int64_t(seq) * p.k_seq_stride +
+                                                       int64_t(t) * kTileKeys), bar);
+        } else {
+          const int32_t* pt = p.page_table + int64_t(r) * p.pt_stride + 2 * t;
+          const bool second = int64_t(2 * t + 1) * DSA_PAGE_TOKENS < len;
+          mbar_arrive_expect_tx(bar, second ? kTileBytes : kTileBytes / 2);
+          tma_load_3d(dst, &tmap, 0, 0, pt[0], bar);
+          if (second) tma_load_3d(dst + kTileBytes / 2, &tmap, 0, 0, pt[1], bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = idesc_f8_f32(kTileKeys, kMaxHeads);
+      const uint64_t b_desc = smem_desc_k128(smem_u32(s_q));
+      int it = 0;
+      for (int t = blockIdx.x; t < p.tiles_per_row; t += G, ++it) {
+        if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        const int b = it & 1;
+        const uint32_t bph = (it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&bars->acc_empty[b]), bph ^ 1) ||
+            !mbar_wait(smem_u32(&bars->full[s]), ph)) {
+          atomicOr(&g_device_status, kStatusScanTimeout);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t a_desc = smem_desc_k128(smem_u32(s_tiles + size_t(s) * kTileBytes));
+#pragma unroll
+        for (int k = 0; k < kKeyBytes / 32; ++k)  // 32 e4m3 per MMA step = 32 B = 2 x 16-B units
+          tc_mma_f8(tmem_base + b * kMaxHeads, a_desc + 2 * k, b_desc + 2 * k, idesc, k > 0);
+        tc_commit(smem_u32(&bars->empty[s]));
+        tc_commit(smem_u32(&bars->acc_full[b]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;  // tcgen05.ld: warp w may touch lanes 32 (w % 4) ..
+    const float* kscale_row = p.k_scale;
+    float* out_row = p.logits + int64_t(r) * p.slab_stride;
+    const float neg_inf = __int_as_float(0xff800000);
+    int it = 0;
+    bool dead = false;
+    for (int t = blockIdx.x; t < p.tiles_per_row; t += G) {
+      const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
+      if (int64_t(t) * kTileKeys >= len || dead) {  // no visible key in this tile
+        if (g < p.ctx) out_row[g] = neg_inf;
+        continue;
+      }
+      const bool valid = g < len;
+      float scale = 0.f;
+      if (valid) {
+        if (!p.paged) {
+          scale = kscale_row[int64_t(seq) * p.scale_seq_stride + g];
+        } else {
+          const int page = p.page_table[int64_t(r) * p.pt_stride + (g >> 6)];
+          scale = *reinterpret_cast<const float*>(p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES +
+                                                  DSA_PAGE_TOKENS * kKeyBytes + (g & 63) * 4);
+        }
+      }
+      const int b = it & 1;
+      const uint32_t bph = (it >> 1) & 1;
+      ++it;
+      if (!mbar_wait(smem_u32(&bars->acc_full[b]), bph)) {
+        atomicOr(&g_device_status, kStatusScanTimeout);
+        *abort_flag = 1;
+        dead = true;
+        if (g < p.ctx) out_row[g] = neg_inf;
+        continue;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + b * kMaxHeads;
+      float sum = 0.f;
+      uint32_t v[32];
+      tmem_ld_32x32(taddr, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < 32; ++h) sum = fmaf(s_w[h], fmaxf(__uint_as_float(v[h]), 0.f), sum);
+      tmem_ld_32x32(taddr + 32, v);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[b]));
+#pragma unroll
+      for (int h = 0; h < 32; ++h)
+        sum = fmaf(s_w[32 + h], fmaxf(__uint_as_float(v[h]), 0.f), sum);
+      const float logit = valid ? sum * scale : neg_inf;
+      if (g < p.ctx) out_row[g] = logit;
+      if (want_hist && valid) atomicAdd(&s_hist[ordered_key(logit) >> 20], 1u);
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // let copies that may still be in flight land before the CTA's shared memory is reused
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  if (want_hist) {
+    uint32_t* gh = p.hist + size_t(r) * kHistBins;
+    for (int i = tid; i < kHistBins; i += kThreads) {
+      const uint32_t c = s_hist[i];
+      if (c) atomicAdd(&gh[i], c);
+    }
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------
+// Legacy tensor-core path (mma.sync m16n8k32 e4m3), dense caches only. Kept as a
+// diagnostic cross-check of the tcgen05 path, like the reference keeps its HMMA
+// scan beside wgmma (kernels/cuda_fused_sparse_splitk.py:1851-1880).
+constexpr int kLegacyThreads = 128;
+
+__device__ __forceinline__ void mma_e4m3_16832(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kLegacyThreads)
+indexer_scan_legacy_kernel(const Params p) {
+  __shared__ __align__(16) uint8_t s_q[kMaxHeads * kKeyBytes];
+  __shared__ float s_w[kMaxHeads];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = blockIdx.y;
+  const int seq = r / p.rows_per_seq;
+  const int len = row_len(p, r);
+  {
+    const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + size_t(r) * p.n_heads * kKeyBytes);
+    for (int i = tid; i < kMaxHeads * 8; i += kLegacyThreads) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if ((i >> 3) < p.n_heads) v = qsrc[i];
+      reinterpret_cast<uint4*>(s_q)[i] = v;
+    }
+    for (int i = tid; i < kMaxHeads; i += kLegacyThreads)
+      s_w[i] = i < p.n_heads ? p.w[size_t(r) * p.n_heads + i] : 0.f;
+  }
+  __syncthreads();
+  const uint8_t* keys = p.keys + int64_t(seq) * p.k_seq_stride * kKeyBytes;
+  const float* kscale = p.k_scale + int64_t(seq) * p.scale_seq_stride;
+  float* out_row = p.logits + int64_t(r) * p.slab_stride;
+  const float neg_inf = __int_as_float(0xff800000);
+  const int gr = lane >> 2, gc = lane & 3;
+  const int64_t n_groups = (p.ctx + 15) / 16;
+  for (int64_t grp = int64_t(blockIdx.x) * 4 + warp; grp < n_groups; grp += int64_t(gridDim.x) * 4) {
+    const int64_t k0 = grp * 16;
+    const int64_t ra = k0 + gr, rb = k0 + gr + 8;
+    float sa = 0.f, sb = 0.f;
+    if (k0 < len) {
+      uint32_t a[4][4];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const int off = kk * 32 + gc * 4;
+        a[kk][0] = ra < p.ctx ? *reinterpret_cast<const uint32_t*>(keys + ra * kKeyBytes + off) : 0u;
+        a[kk][1] = rb < p.ctx ? *reinterpret_cast<const uint32_t*>(keys + rb * kKeyBytes + off) : 0u;
+        a[kk][2] = ra < p.ctx ? *reinterpret_cast<const uint32_t*>(keys + ra * kKeyBytes + off + 16) : 0u;
+        a[kk][3] = rb < p.ctx ? *reinterpret_cast<const uint32_t*>(keys + rb * kKeyBytes + off + 16) : 0u;
+      }
+#pragma unroll
+      for (int nt = 0; nt < kMaxHeads / 8; ++nt) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint8_t* qh = s_q + (nt * 8 + gr) * kKeyBytes + gc * 4;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_e4m3_16832(c, a[kk], *reinterpret_cast<const uint32_t*>(qh + kk * 32),
+                         *reinterpret_cast<const uint32_t*>(qh + kk * 32 + 16));
+        const float w0 = s_w[nt * 8 + gc * 2], w1 = s_w[nt * 8 + gc * 2 + 1];
+        sa = fmaf(w0, fmaxf(c[0], 0.f), sa);
+        sa = fmaf(w1, fmaxf(c[1], 0.f), sa);
+        sb = fmaf(w0, fmaxf(c[2], 0.f), sb);
+        sb = fmaf(w1, fmaxf(c[3], 0.f), sb);
+      }
+      sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+      sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+      sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+      sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+    }
+    if (gc == 0) {
+      if (ra < p.ctx) {
+        const float v = ra < len ? sa * kscale[ra] : neg_inf;
+        out_row[ra] = v;
+        if (p.hist && ra < len) atomicAdd(&p.hist[size_t(r) * kHistBins + (ordered_key(v) >> 20)], 1u);
+      }
+      if (rb < p.ctx) {
+        const float v = rb < len ? sb * kscale[rb] : neg_inf;
+        out_row[rb] = v;
+        if (p.hist && rb < len) atomicAdd(&p.hist[size_t(r) * kHistBins + (ordered_key(v) >> 20)], 1u);
+      }
+    }
+  }
+}
+
+// fp32 scan for any head count / key width: one warp per key, lanes stride the
+// key dimension per head. Accuracy path of the full-sequence layer API.
+__global__ void __launch_bounds__(256)
+indexer_scan_f32_kernel(const float* __restrict__ q, const float* __restrict__ w,
+                        const float* __restrict__ k, const int32_t* __restrict__ seq_lens,
+                        float* __restrict__ logits, int rows_per_seq, int n_heads, int head_dim,
+                        int64_t ctx, int64_t k_seq_stride, int64_t slab_stride) {
+  extern __shared__ float s_qf[];  // [n_heads][head_dim] then w[n_heads]
+  const int r = blockIdx.y;
+  const int seq = r / rows_per_seq;
+  float* s_wf = s_qf + size_t(n_heads) * head_dim;
+  for (int i = threadIdx.x; i < n_heads * head_dim; i += blockDim.x)
+    s_qf[i] = q[size_t(r) * n_heads * head_dim + i];
+  for (int i = threadIdx.x; i < n_heads; i += blockDim.x) s_wf[i] = w[size_t(r) * n_heads + i];
+  __syncthreads();
+  int64_t len = seq_lens ? seq_lens[r] : ctx;
+  len = len < 0 ? 0 : (len > ctx ? ctx : len);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const float neg_inf = __int_as_float(0xff800000);
+  for (int64_t s = int64_t(blockIdx.x) * wpb + warp; s < ctx; s += int64_t(gridDim.x) * wpb) {
+    if (s >= len) {
+      if (lane == 0) logits[int64_t(r) * slab_stride + s] = neg_inf;
+      continue;
+    }
+    const float* kr = k + (int64_t(seq) * k_seq_stride + s) * head_dim;
+    float total = 0.f;
+    for (int h = 0; h < n_heads; ++h) {
+      float dot = 0.f;
+      for (int d = lane; d < head_dim; d += 32) dot = fmaf(s_qf[h * head_dim + d], kr[d], dot);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      total = fmaf(s_wf[h], fmaxf(dot, 0.f), total);
+    }
+    if (lane == 0) logits[int64_t(r) * slab_stride + s] = total;
+  }
+}
+
+}  // namespace scan
+}  // namespace dsa

@@ -1,0 +1,325 @@
+"""Tensor-level entry points over the C ABI: checks shapes and dtypes, hands raw
+device pointers and the current CUDA stream to libdsa_b200.so.
+
+torch is used here for device memory and streams only. Nothing in this module
+computes on the host or falls back to torch kernels; a missing library raises
+at the first call (``_lib.lib()``).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+LATENT_DIM = 576
+VALUE_DIM = 512
+INDEX_DIM = 128
+HEAD_BLOCK = 16
+PAGE_TOKENS = 64
+INDEX_PAGE_BYTES = 8448
+FP8_LATENT_ROW = 656
+HIST_BINS = 4096
+
+_FP8 = torch.float8_e4m3fn
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _cuda_contig(t: torch.Tensor, name: str, dtypes) -> None:
+    _need(t.is_cuda, f"{name} must be a CUDA tensor")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    _need(t.dtype in dtypes, f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+
+
+def _lens(seq_lens: Optional[torch.Tensor], rows: int) -> Optional[torch.Tensor]:
+    if seq_lens is not None:
+        _cuda_contig(seq_lens, "seq_lens", (torch.int32,))
+        _need(seq_lens.numel() == rows, f"seq_lens has {seq_lens.numel()} entries, expected {rows}")
+    return seq_lens
+
+
+# --------------------------------------------------------------------------- a7
+def quantize_e4m3_rowwise(x: torch.Tensor, clamp_min: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row absmax e4m3 quantisation: ``(q, scale)`` with ``x ~ q * scale[..., None]``
+    (reference kernels/cuda_fused_sparse_splitk.py:2969-2974)."""
+    _cuda_contig(x, "x", (torch.float32,))
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().dsa_quantize_e4m3_rowwise(_ptr(x), _ptr(q), _ptr(scale), rows, cols,
+                                                   float(clamp_min), _stream()))
+    return q.view(_FP8), scale
+
+
+# --------------------------------------------------------------------------- a1
+def indexer_scan_fp8(
+    index_q: torch.Tensor,
+    index_w: torch.Tensor,
+    index_k: torch.Tensor,
+    k_scale: torch.Tensor,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    rows_per_seq: int = 1,
+    ctx: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+    hist: Optional[torch.Tensor] = None,
+    impl: int = 0,
+) -> torch.Tensor:
+    """Indexer logits ``[R, ctx]`` (fp32) from e4m3 queries/keys.
+
+    index_q ``[R, Hidx, 128]`` e4m3 (or uint8 bytes), index_w ``[R, Hidx]`` fp32
+    with the query scale folded in, index_k ``[n_seq, cap, 128]`` (or ``[cap, 128]``),
+    k_scale ``[n_seq, cap]`` fp32. Row r reads sequence ``r // rows_per_seq``.
+    """
+    _cuda_contig(index_q, "index_q", (_FP8, torch.uint8))
+    _cuda_contig(index_w, "index_w", (torch.float32,))
+    _cuda_contig(index_k, "index_k", (_FP8, torch.uint8))
+    _cuda_contig(k_scale, "k_scale", (torch.float32,))
+    _need(index_q.dim() == 3 and index_q.shape[-1] == INDEX_DIM, "index_q must be [R, Hidx, 128]")
+    R, n_heads = index_q.shape[0], index_q.shape[1]
+    _need(tuple(index_w.shape) == (R, n_heads), "index_w must be [R, Hidx]")
+    if index_k.dim() == 2:
+        index_k = index_k.unsqueeze(0)
+        k_scale = k_scale.reshape(1, -1)
+    _need(index_k.dim() == 3 and index_k.shape[-1] == INDEX_DIM, "index_k must be [n_seq, cap, 128]")
+    n_seq, cap = index_k.shape[0], index_k.shape[1]
+    _need(tuple(k_scale.shape) == (n_seq, cap), "k_scale must be [n_seq, cap]")
+    _need(R == n_seq * rows_per_seq, f"R={R} must equal n_seq={n_seq} * rows_per_seq={rows_per_seq}")
+    ctx = cap if ctx is None else int(ctx)
+    _need(0 < ctx <= cap, "ctx must be in (0, cap]")
+    seq_lens = _lens(seq_lens, R)
+    if out is None:
+        out = torch.empty(R, (ctx + 3) // 4 * 4, dtype=torch.float32, device=index_q.device)
+    _cuda_contig(out, "out", (torch.float32,))
+    _need(out.dim() == 2 and out.shape[0] == R and out.shape[1] >= ctx, "out must be [R, >= ctx]")
+    if hist is not None:
+        _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+        _need(hist.numel() == R * HIST_BINS, "hist must be [R, 4096]")
+    _lib.check(_lib.lib().dsa_indexer_scan_fp8(
+        _ptr(index_q), _ptr(index_w), _ptr(index_k), _ptr(k_scale), _ptr(seq_lens), _ptr(out),
+        _ptr(hist), R, rows_per_seq, n_heads, ctx, n_seq, cap, cap, out.shape[1], impl, _stream()))
+    return out[:, :ctx]
+
+
+def indexer_scan_fp8_paged(
+    index_q: torch.Tensor,
+    index_w: torch.Tensor,
+    index_k_pages: torch.Tensor,
+    page_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    ctx: int,
+    *,
+    out: Optional[torch.Tensor] = None,
+    hist: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Paged form: index_k_pages ``[num_pages, 8448]`` uint8, page_table ``[R, pt_stride]`` int32."""
+    _cuda_contig(index_q, "index_q", (_FP8, torch.uint8))
+    _cuda_contig(index_w, "index_w", (torch.float32,))
+    _cuda_contig(index_k_pages, "index_k_pages", (torch.uint8,))
+    _cuda_contig(page_table, "page_table", (torch.int32,))
+    _need(index_q.dim() == 3 and index_q.shape[-1] == INDEX_DIM, "index_q must be [R, Hidx, 128]")
+    R, n_heads = index_q.shape[0], index_q.shape[1]
+    _need(index_k_pages.dim() == 2 and index_k_pages.shape[1] == INDEX_PAGE_BYTES,
+          "index_k_pages must be [num_pages, 8448]")
+    _need(page_table.dim() == 2 and page_table.shape[0] == R, "page_table must be [R, pt_stride]")
+    seq_lens = _lens(seq_lens, R)
+    _need(seq_lens is not None, "paged scan needs seq_lens")
+    if out is None:
+        out = torch.empty(R, (ctx + 3) // 4 * 4, dtype=torch.float32, device=index_q.device)
+    _cuda_contig(out, "out", (torch.float32,))
+    if hist is not None:
+        _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+        _need(hist.numel() == R * HIST_BINS, "hist must be [R, 4096]")
+    _lib.check(_lib.lib().dsa_indexer_scan_fp8_paged(
+        _ptr(index_q), _ptr(index_w), _ptr(index_k_pages), index_k_pages.shape[0], _ptr(page_table),
+        page_table.shape[1], _ptr(seq_lens), _ptr(out), _ptr(hist), R, n_heads, int(ctx),
+        out.shape[1], _stream()))
+    return out[:, :ctx]
+
+
+def indexer_scan_f32(
+    index_q: torch.Tensor,
+    index_w: torch.Tensor,
+    index_k: torch.Tensor,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    rows_per_seq: int = 1,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """fp32 logits for any head count / key width: q ``[R, H, D]``, k ``[n_seq, ctx, D]``."""
+    for t, n in ((index_q, "index_q"), (index_w, "index_w"), (index_k, "index_k")):
+        _cuda_contig(t, n, (torch.float32,))
+    R, n_heads, d = index_q.shape
+    if index_k.dim() == 2:
+        index_k = index_k.unsqueeze(0)
+    n_seq, ctx = index_k.shape[0], index_k.shape[1]
+    _need(index_k.shape[2] == d, "index_k width differs from index_q")
+    _need(R == n_seq * rows_per_seq, "R must equal n_seq * rows_per_seq")
+    seq_lens = _lens(seq_lens, R)
+    if out is None:
+        out = torch.empty(R, (ctx + 3) // 4 * 4, dtype=torch.float32, device=index_q.device)
+    _lib.check(_lib.lib().dsa_indexer_scan_f32(
+        _ptr(index_q), _ptr(index_w), _ptr(index_k), _ptr(seq_lens), _ptr(out), R, rows_per_seq,
+        n_heads, d, ctx, ctx, out.shape[1], _stream()))
+    return out[:, :ctx]
+
+
+# --------------------------------------------------------------------------- a3
+def topk_select(
+    logits: torch.Tensor,
+    topk: int,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    hist: Optional[torch.Tensor] = None,
+    index_map: Optional[torch.Tensor] = None,
+    pad_value: int = -1,
+    index_offset: int = 0,
+    out_idx: Optional[torch.Tensor] = None,
+    out_val: Optional[torch.Tensor] = None,
+    return_values: bool = False,
+):
+    """Exact top-k per row of ``logits[R, n]`` (a view of a wider slab is fine):
+    int32 positions in ascending order, ties to the lower position, padded with
+    ``pad_value``."""
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2, "logits must be CUDA fp32 [R, n]")
+    _need(logits.stride(1) == 1, "logits rows must be dense")
+    R, n = logits.shape
+    slab_stride = logits.stride(0) if R > 1 else max(logits.stride(0), n)
+    seq_lens = _lens(seq_lens, R)
+    if index_map is not None:
+        _cuda_contig(index_map, "index_map", (torch.int32,))
+        _need(tuple(index_map.shape) == (R, n), "index_map must be [R, n]")
+    if out_idx is None:
+        out_idx = torch.empty(R, topk, dtype=torch.int32, device=logits.device)
+    _cuda_contig(out_idx, "out_idx", (torch.int32,))
+    if out_val is None and return_values:
+        out_val = torch.empty(R, topk, dtype=torch.float32, device=logits.device)
+    if hist is not None:
+        _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+    _lib.check(_lib.lib().dsa_topk_select(
+        _ptr(logits), _ptr(seq_lens), _ptr(hist), _ptr(index_map), _ptr(out_idx), _ptr(out_val),
+        R, n, slab_stride, int(topk), int(pad_value), int(index_offset), _stream()))
+    if return_values or out_val is not None:
+        return out_idx, out_val
+    return out_idx
+
+
+# --------------------------------------------------------------------------- a4, a5
+class MlaScratch:
+    """Caller-owned split-K partials (the reference's PartAcc / PartM / PartL,
+    kernels/cuda_fused_sparse_splitk.py:3005-3009), sized once and reused."""
+
+    def __init__(self, rows: int, heads: int, nsplit: int, device) -> None:
+        self.rows, self.heads, self.nsplit = rows, heads, nsplit
+        self.acc = torch.empty(rows, nsplit, heads, VALUE_DIM, dtype=torch.float32, device=device)
+        self.m = torch.empty(rows, nsplit, heads, dtype=torch.float32, device=device)
+        self.l = torch.empty(rows, nsplit, heads, dtype=torch.float32, device=device)
+
+
+def default_nsplit(rows: int, heads: int, topk: int, sm_count: int = 148) -> int:
+    """Splits so that rows x head blocks x splits is about two CTAs per SM,
+    each split a whole number of 64-key tiles."""
+    blocks = max(1, rows * (heads // HEAD_BLOCK))
+    want = max(1, (2 * sm_count) // blocks)
+    tiles = max(1, math.ceil(topk / 64))
+    return max(1, min(want, tiles))
+
+
+def sparse_mla_decode(
+    q: torch.Tensor,
+    kv: torch.Tensor,
+    indices: Optional[torch.Tensor],
+    sm_scale: float,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    rows_per_seq: int = 1,
+    nsplit: Optional[int] = None,
+    scratch: Optional[MlaScratch] = None,
+    out: Optional[torch.Tensor] = None,
+    dense_keys: Optional[int] = None,
+) -> torch.Tensor:
+    """Sparse MLA decode: q ``[R, H, 576]`` bf16, kv ``[n_seq, cap, 576]`` bf16 or
+    ``[n_seq, cap, 656]`` uint8 (fp8-packed rows), indices ``[R, topk]`` int32 or
+    None for dense attention over ``dense_keys`` positions. Returns ``[R, H, 512]`` bf16."""
+    _cuda_contig(q, "q", (torch.bfloat16,))
+    _need(q.dim() == 3 and q.shape[2] == LATENT_DIM, "q must be [R, H, 576]")
+    R, H = q.shape[0], q.shape[1]
+    _need(H % HEAD_BLOCK == 0, f"H={H} must be a multiple of {HEAD_BLOCK} (pad heads with zero queries)")
+    if kv.dim() == 2:
+        kv = kv.unsqueeze(0)
+    _need(kv.is_cuda and kv.is_contiguous() and kv.dim() == 3, "kv must be a contiguous CUDA [n_seq, cap, w] tensor")
+    if kv.dtype == torch.bfloat16:
+        _need(kv.shape[2] == LATENT_DIM, "bf16 kv rows must be 576 wide")
+        kv_fp8 = 0
+    else:
+        _need(kv.dtype == torch.uint8 and kv.shape[2] == FP8_LATENT_ROW, "fp8 kv rows must be 656 bytes of uint8")
+        kv_fp8 = 1
+    n_seq, cap = kv.shape[0], kv.shape[1]
+    _need(R == n_seq * rows_per_seq, "R must equal n_seq * rows_per_seq")
+    if indices is not None:
+        _cuda_contig(indices, "indices", (torch.int32,))
+        _need(indices.dim() == 2 and indices.shape[0] == R, "indices must be [R, topk]")
+        topk = indices.shape[1]
+    else:
+        topk = int(dense_keys if dense_keys is not None else cap)
+    seq_lens = _lens(seq_lens, R)
+    if nsplit is None:
+        nsplit = scratch.nsplit if scratch is not None else default_nsplit(R, H, topk)
+    if scratch is None:
+        scratch = MlaScratch(R, H, nsplit, q.device)
+    _need(scratch.rows >= R and scratch.heads == H and scratch.nsplit == nsplit, "scratch does not match the launch")
+    if out is None:
+        out = torch.empty(R, H, VALUE_DIM, dtype=torch.bfloat16, device=q.device)
+    _cuda_contig(out, "out", (torch.bfloat16,))
+    _lib.check(_lib.lib().dsa_sparse_mla_decode(
+        _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),
+        _ptr(scratch.l), _ptr(out), R, rows_per_seq, H, topk, nsplit, float(sm_scale), cap, kv_fp8,
+        _stream()))
+    return out
+
+
+def sparse_mla_f32(
+    q: torch.Tensor,
+    kv: torch.Tensor,
+    indices: Optional[torch.Tensor],
+    value_dim: int,
+    sm_scale: float,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    rows_per_seq: int = 1,
+) -> torch.Tensor:
+    """fp32 attention for any width: q ``[R, H, Dqk]``, kv ``[n_seq, ctx, Dqk]``;
+    indices None = dense causal over ``seq_lens``."""
+    _cuda_contig(q, "q", (torch.float32,))
+    _cuda_contig(kv, "kv", (torch.float32,))
+    if kv.dim() == 2:
+        kv = kv.unsqueeze(0)
+    R, H, dqk = q.shape
+    n_seq, ctx = kv.shape[0], kv.shape[1]
+    _need(kv.shape[2] == dqk and R == n_seq * rows_per_seq, "q / kv shapes disagree")
+    topk = 0
+    if indices is not None:
+        _cuda_contig(indices, "indices", (torch.int32,))
+        topk = indices.shape[1]
+    seq_lens = _lens(seq_lens, R)
+    out = torch.empty(R, H, value_dim, dtype=torch.float32, device=q.device)
+    _lib.check(_lib.lib().dsa_sparse_mla_f32(
+        _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(out), R, rows_per_seq, H, dqk,
+        value_dim, topk, float(sm_scale), ctx, _stream()))
+    return out

@@ -1,0 +1,177 @@
+/*
+ * dsa_b200 -- C ABI of the B200 (sm_100a) DSA decode kernels.
+ *
+ * One shared library, libdsa_b200.so, replaces the torch extension that the
+ * reference JIT-builds from kernels/cuda_fused_sparse_splitk.py (export list
+ * :2922-2941, declarations :2228-2303). Every entry point takes raw device
+ * pointers, plain sizes and a CUDA stream; nothing here allocates, synchronises
+ * with the host or reads a length on the host, so each call can be captured in
+ * a CUDA graph (the reference's contract: kernels/cuda_fused_sparse_splitk.py
+ * :2399-2499 argument checks, :2531 current stream, caller-owned scratch
+ * src/lagged_indexer_dsa/inference/modeling/fused_decode.py:46-119).
+ *
+ * Conventions
+ *   - return value: DSA_OK (0) or a negative dsa_status; dsa_last_error()
+ *     returns the message of the calling thread's last failure.
+ *   - "row" = one query token. R rows share `rows_per_seq` consecutive rows per
+ *     cached sequence: rows_per_seq == 1 is batched decode, rows_per_seq == S
+ *     is the reference's S-row single-sequence launch.
+ *   - seq_lens[r] (device int32, may be NULL = `ctx`) is the number of causally
+ *     visible keys of row r; keys at positions >= seq_lens[r] are masked.
+ *   - stream is a cudaStream_t passed as void*.
+ *   - all device pointers must be 16-byte aligned.
+ */
+#ifndef DSA_B200_H_
+#define DSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSA_ABI_VERSION 1
+
+enum dsa_status {
+  DSA_OK = 0,
+  DSA_ERR_INVALID_ARGUMENT = -1, /* shape / stride / alignment contract broken  */
+  DSA_ERR_UNSUPPORTED = -2,      /* valid request outside the compiled geometry */
+  DSA_ERR_CUDA = -3,             /* a CUDA runtime/driver call failed           */
+  DSA_ERR_DEVICE_TIMEOUT = -4    /* a bounded in-kernel wait gave up            */
+};
+
+/* Geometry fixed at compile time, as in the reference kernel
+ * (kernels/cuda_fused_sparse_splitk.py:53-55, :2498-2499, :2550). */
+#define DSA_LATENT_DIM 576      /* 512 latent + 64 rope, bf16                    */
+#define DSA_VALUE_DIM 512
+#define DSA_INDEX_DIM 128       /* index key width, e4m3                         */
+#define DSA_INDEX_MAX_HEADS 64
+#define DSA_HEAD_BLOCK 16       /* MLA heads per attention CTA                   */
+#define DSA_PAGE_TOKENS 64
+#define DSA_INDEX_PAGE_BYTES 8448 /* 64 x 128 B keys, then 64 x fp32 scales      */
+#define DSA_FP8_LATENT_ROW 656  /* 512 e4m3 | 4 x fp32 group scale | 64 bf16     */
+#define DSA_TOPK_HIST_BINS 4096 /* first-level histogram bins per row            */
+
+int dsa_abi_version(void);
+const char* dsa_last_error(void);
+const char* dsa_status_string(int status);
+
+/* Reads and clears the per-device status word that kernels set when one of
+ * their bounded waits ran out. Synchronises the device. Returns DSA_OK or
+ * DSA_ERR_DEVICE_TIMEOUT; *detail (optional) receives the raw word. */
+int dsa_check_device_status(uint32_t* detail);
+
+/* ---- (a1) lightning-indexer scan ------------------------------------------
+ * logits[r, s] = (sum_h w[r,h] * relu(q[r,h,:] . k[s,:])) * k_scale[s],
+ * -inf for s >= seq_lens[r]. Replaces the indexer half of
+ * launch_fused_sparse_splitk* with with_select=1
+ * (kernels/cuda_fused_sparse_splitk.py:531-647, :1677-1903; host reference
+ * ref_indexer_logits_fp8 :2990-2992).
+ *
+ *   index_q   [R, n_heads, 128] e4m3        index_w  [R, n_heads] fp32
+ *   index_k   [n_seq, k_seq_stride, 128] e4m3  (sequence of row r = r / rows_per_seq)
+ *   k_scale   [n_seq, scale_seq_stride] fp32
+ *   logits    [R, slab_stride] fp32, columns [0, ctx) written
+ *   hist      NULL, or [R, DSA_TOPK_HIST_BINS] uint32 that the scan increments
+ *             with the top-12-bit bucket of every valid logit (must be zero on
+ *             entry; dsa_topk_select re-zeroes it after use)
+ *   impl      0 = TMA + tcgen05 FP8 MMA, 1 = legacy mma.sync path (diagnostic,
+ *             like the reference's hp_diag_mode bit 2, :1851-1880)
+ */
+int dsa_indexer_scan_fp8(const uint8_t* index_q, const float* index_w,
+                         const uint8_t* index_k, const float* k_scale,
+                         const int32_t* seq_lens, float* logits, uint32_t* hist,
+                         int R, int rows_per_seq, int n_heads, int64_t ctx,
+                         int64_t n_seq, int64_t k_seq_stride, int64_t scale_seq_stride,
+                         int64_t slab_stride, int impl, void* stream);
+
+/* Paged form: index keys live in 64-token pages of DSA_INDEX_PAGE_BYTES
+ * ([64 x 128 B keys][64 x fp32 scales], kernels/cuda_fused_sparse_splitk.py
+ * :540-546, :2428-2429); page_table[r, j] is the pool page of tokens
+ * [64 j, 64 j + 64) of row r (rows_per_seq is 1). Replaces the indexer half of
+ * launch_fused_sparse_splitk_paged (:2770-2808). */
+int dsa_indexer_scan_fp8_paged(const uint8_t* index_q, const float* index_w,
+                               const uint8_t* index_k_pages, int64_t num_pages,
+                               const int32_t* page_table, int64_t pt_stride,
+                               const int32_t* seq_lens, float* logits, uint32_t* hist,
+                               int R, int n_heads, int64_t ctx, int64_t slab_stride,
+                               void* stream);
+
+/* fp32 form for any head count / key width (src/lagged_indexer_dsa/
+ * attention_core.py:27-49 arithmetic, used by the full-sequence layer API). */
+int dsa_indexer_scan_f32(const float* index_q, const float* index_w, const float* index_k,
+                         const int32_t* seq_lens, float* logits,
+                         int R, int rows_per_seq, int n_heads, int head_dim, int64_t ctx,
+                         int64_t k_seq_stride, int64_t slab_stride, void* stream);
+
+/* ---- (a3) exact top-k selection -------------------------------------------
+ * Indices of the `topk` largest logits[r, 0:min(n, seq_lens[r])), ties broken
+ * by lower position, written in ascending position order and padded with
+ * `pad_value` (also written for a selected entry whose logit is -inf). Replaces
+ * torch.topk on the slab (src/lagged_indexer_dsa/attention_core.py:66-91;
+ * inference/modeling/transformer.py:1156) and the in-kernel select
+ * (kernels/cuda_fused_sparse_splitk.py:2017-2154).
+ *
+ *   hist       NULL, or the histogram dsa_indexer_scan_fp8 filled for these
+ *              rows (skips the first radix pass; re-zeroed on exit)
+ *   index_map  NULL, or [R, n] int32: the value written for position p is
+ *              index_map[r, p] (used to merge per-GPU candidate lists)
+ *   out_idx    [R, topk] int32        out_val  NULL or [R, topk] fp32
+ *   index_offset is added to positions when index_map is NULL.
+ * Limit: n <= 262144 per row.
+ */
+int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist,
+                    const int32_t* index_map, int32_t* out_idx, float* out_val,
+                    int R, int64_t n, int64_t slab_stride, int topk,
+                    int32_t pad_value, int32_t index_offset, void* stream);
+
+/* ---- (a4, a5) split-K sparse MLA decode ------------------------------------
+ * out[r,h,:] = softmax_j(sm_scale * q[r,h,:] . kv[idx_j,:]) . kv[idx_j,:512]
+ * over the entries of indices[r,:] with 0 <= idx < seq_lens[r]. Replaces the
+ * attention half of launch_fused_sparse_splitk* and combine_kernel
+ * (kernels/cuda_fused_sparse_splitk.py:282-530, :996-1045; host reference
+ * ref_sparse_mla :2950-2966).
+ *
+ *   q        [R, H, 576] bf16 (absorbed queries), H a multiple of 16
+ *   kv       kv_fp8 == 0: [n_seq, kv_seq_stride, 576] bf16
+ *            kv_fp8 == 1: [n_seq, kv_seq_stride, 656] bytes, rows laid out as
+ *            512 e4m3 | 4 fp32 scales (one per 128 dims) | 64 bf16 rope
+ *            (:1098-1104), dequantised fp8->f32 * scale -> bf16 RN (:1181-1196)
+ *   indices  [R, topk] int32, or NULL to attend every key below seq_lens[r]
+ *            (dense cold start; topk is then the key capacity to cover)
+ *   part_acc [R, nsplit, H, 512] fp32, part_m / part_l [R, nsplit, H] fp32
+ *   out      [R, H, 512] bf16
+ * dsa_sparse_mla_decode = partials + combine; the two halves are exported for
+ * callers that schedule them separately, as the reference does.
+ */
+int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
+                            const int32_t* seq_lens, float* part_acc, float* part_m,
+                            float* part_l, int R, int rows_per_seq, int H, int topk,
+                            int nsplit, float sm_scale, int64_t kv_seq_stride, int kv_fp8,
+                            void* stream);
+int dsa_sparse_mla_combine(const float* part_acc, const float* part_m, const float* part_l,
+                           void* out, int R, int H, int nsplit, void* stream);
+int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
+                          const int32_t* seq_lens, float* part_acc, float* part_m,
+                          float* part_l, void* out, int R, int rows_per_seq, int H, int topk,
+                          int nsplit, float sm_scale, int64_t kv_seq_stride, int kv_fp8,
+                          void* stream);
+
+/* fp32 form for any head / latent width (src/lagged_indexer_dsa/
+ * attention_core.py:94-160): one pass, no split. indices NULL = dense causal. */
+int dsa_sparse_mla_f32(const float* q, const float* kv, const int32_t* indices,
+                       const int32_t* seq_lens, float* out, int R, int rows_per_seq, int H,
+                       int qk_dim, int v_dim, int topk, float sm_scale,
+                       int64_t kv_seq_stride, void* stream);
+
+/* ---- (a7) per-token e4m3 quantisation of index keys / queries --------------
+ * scale = max(amax(row), clamp_min) / 448, q = sat(x / scale) -> e4m3 RN
+ * (kernels/cuda_fused_sparse_splitk.py:2969-2974). x is fp32 [rows, cols]. */
+int dsa_quantize_e4m3_rowwise(const float* x, uint8_t* q_out, float* scale_out,
+                              int64_t rows, int cols, float clamp_min, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSA_B200_H_ */

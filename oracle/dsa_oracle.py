@@ -1,0 +1,280 @@
+"""CPU oracle for the DSA decode hot path. TEST INFRASTRUCTURE, NOT PRODUCT.
+
+A restatement, in plain torch-CPU / numpy, of the reference's algorithm for the
+indexer scan, the top-k selection, the sparse MLA decode, the split-K merge, the
+FP8 formats and the lagged schedule. Every function names the reference lines
+it follows. Only tests, the smoke check and the bench's CPU-baseline leg may
+import this module; the product package never does.
+
+Parity status: PINNED. ``tests/golden/`` holds outputs of the reference's own
+functions (imported from its source tree by ``tests/golden/make_golden.py``) on
+seeded inputs, and ``tests/test_oracle_golden.py`` checks this module against
+them, so the oracle travels to machines where the reference is absent.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+E4M3_MAX = 448.0
+
+
+# ----------------------------------------------------------------------- FP8 e4m3
+def e4m3_table() -> np.ndarray:
+    """All 256 e4m3fn values as float32, built from the format definition
+    (1 sign, 4 exponent bits with bias 7, 3 mantissa bits, no infinities,
+    S.1111.111 = NaN). The reference relies on torch's float8_e4m3fn cast
+    (kernels/cuda_fused_sparse_splitk.py:2969-2974); the tests check this table
+    against that cast."""
+    out = np.zeros(256, dtype=np.float32)
+    for b in range(256):
+        sign = -1.0 if b & 0x80 else 1.0
+        e = (b >> 3) & 0xF
+        m = b & 0x7
+        if e == 0xF and m == 0x7:
+            v = np.nan
+        elif e == 0:
+            v = sign * (m / 8.0) * 2.0 ** (-6)
+        else:
+            v = sign * (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        out[b] = v
+    return out
+
+
+_E4M3 = torch.from_numpy(e4m3_table())
+
+
+def e4m3_to_f32(bytes_u8: torch.Tensor) -> torch.Tensor:
+    """Decode e4m3 bytes (uint8 or float8_e4m3fn tensor) to float32 exactly."""
+    if bytes_u8.dtype == torch.float8_e4m3fn:
+        bytes_u8 = bytes_u8.view(torch.uint8)
+    return _E4M3[bytes_u8.long()]
+
+
+def quantize_e4m3_rowwise(x: torch.Tensor, clamp_min: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric e4m3 quantisation -> (uint8 bytes, fp32 scale).
+    Follows quantize_e4m3_rowwise, kernels/cuda_fused_sparse_splitk.py:2969-2974:
+    amax clamped at 1e-6, scale = amax / 448, round-to-nearest-even cast."""
+    x = x.float()
+    amax = x.abs().amax(dim=-1, keepdim=True).clamp_min(clamp_min)
+    scale = amax / E4M3_MAX
+    q = (x / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.view(torch.uint8), scale.squeeze(-1)
+
+
+def make_fp8_indexer_inputs(iq: torch.Tensor, ik: torch.Tensor, w: torch.Tensor):
+    """(iq8, ik8, w_folded, k_scale): the operand form the scan consumes, with
+    the per-(row, head) query scale folded into the head weights. Follows
+    make_fp8_indexer_inputs, kernels/cuda_fused_sparse_splitk.py:2977-2987
+    (which draws its own randn; here the caller supplies iq [S,H,D], ik [N,D],
+    w [S,H])."""
+    iq8, sq = quantize_e4m3_rowwise(iq)
+    ik8, sk = quantize_e4m3_rowwise(ik)
+    return iq8.contiguous(), ik8.contiguous(), (sq * w.float()).contiguous(), sk.contiguous()
+
+
+# ----------------------------------------------------------------------- a1 indexer
+def indexer_logits_f32(index_q: torch.Tensor, index_k: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """I[b,t,s] = sum_h w[b,t,h] relu(q[b,t,h].k[b,s]).
+    Follows indexer_logits, src/lagged_indexer_dsa/attention_core.py:27-49.
+    index_q [B,S,H,D], index_k [B,N,D], weights [B,S,H] -> [B,S,N]."""
+    score = torch.einsum("bshd,bnd->bshn", index_q.float(), index_k.float())
+    return (torch.relu(score) * weights.float().unsqueeze(-1)).sum(dim=2)
+
+
+def indexer_logits_fp8(iq8: torch.Tensor, ik8: torch.Tensor, w_folded: torch.Tensor, k_scale: torch.Tensor,
+                       chunk: int = 16384) -> torch.Tensor:
+    """Logits from the same e4m3 bytes the GPU reads: [S,H,D] x [N,D] -> [S,N].
+    Follows ref_indexer_logits_fp8, kernels/cuda_fused_sparse_splitk.py:2990-2992
+    (decode to fp32, bilinear, relu, weighted head sum, per-key scale); keys are
+    processed in chunks only to bound memory."""
+    q = e4m3_to_f32(iq8)
+    out = torch.empty(q.shape[0], ik8.shape[0], dtype=torch.float32)
+    for s0 in range(0, ik8.shape[0], chunk):
+        k = e4m3_to_f32(ik8[s0:s0 + chunk])
+        bil = torch.einsum("shd,gd->shg", q, k)
+        out[:, s0:s0 + chunk] = (bil.relu() * w_folded.float().unsqueeze(-1)).sum(1) * k_scale[s0:s0 + chunk].view(1, -1)
+    return out
+
+
+def mask_beyond(logits: torch.Tensor, seq_lens: Sequence[int]) -> torch.Tensor:
+    """-inf for key positions >= seq_lens[row]: the decode form of the causal gate
+    (kernel `g <= q_pos`, kernels/cuda_fused_sparse_splitk.py:627, :1702-1711;
+    full-sequence form apply_causal_mask, attention_core.py:52-63)."""
+    out = logits.clone()
+    pos = torch.arange(logits.shape[-1])
+    for r, n in enumerate(seq_lens):
+        out[r, pos >= int(n)] = float("-inf")
+    return out
+
+
+# ----------------------------------------------------------------------- a3 top-k
+def select_topk(logits: torch.Tensor, topk: int, pad_value: int) -> torch.Tensor:
+    """Positions of the top-k finite logits per row, as a SORTED int64 [R, topk]
+    padded with ``pad_value``. Set semantics of select_topk,
+    src/lagged_indexer_dsa/attention_core.py:66-91 (non-finite values become the
+    sentinel, short rows are padded); ties are resolved toward the lower
+    position (the kernels' convention, kernels/cuda_fused_sparse_splitk.py:919-921),
+    which torch.topk leaves unspecified."""
+    R, n = logits.shape
+    out = torch.full((R, topk), pad_value, dtype=torch.int64)
+    for r in range(R):
+        row = logits[r].double()
+        order = torch.sort(row, descending=True, stable=True).indices  # stable: lower index first among ties
+        take = order[: min(topk, n)]
+        take = take[torch.isfinite(row[take])]
+        take = torch.sort(take).values
+        out[r, : take.numel()] = take
+    return out
+
+
+# ----------------------------------------------------------------------- a4 sparse MLA
+def sparse_mla_decode(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, seq_lens: Sequence[int],
+                      sm_scale: float, value_dim: int = 512) -> torch.Tensor:
+    """out[r,h] = softmax_j(scale q[r,h].kv[idx_j]) . kv[idx_j,:value_dim] over
+    the entries 0 <= idx < seq_lens[r]. q [R,H,D], kv [N,D] (shared by all rows),
+    indices [R,topk]. Follows ref_sparse_mla, kernels/cuda_fused_sparse_splitk.py
+    :2950-2966 (q_pos = seq_len - 1), equivalently _selection_mask + _attend,
+    attention_core.py:94-118. fp32 math on the given values."""
+    R, H, _ = q.shape
+    out = torch.zeros(R, H, value_dim, dtype=torch.float32)
+    kvf = kv.float()
+    for r in range(R):
+        idx = indices[r].long()
+        sel = idx[(idx >= 0) & (idx < int(seq_lens[r]))]
+        if sel.numel() == 0:
+            continue
+        k = kvf[sel]
+        p = torch.softmax((q[r].float() @ k.t()) * sm_scale, dim=-1)
+        out[r] = p @ k[:, :value_dim]
+    return out
+
+
+def dense_mla_decode(q: torch.Tensor, kv: torch.Tensor, seq_lens: Sequence[int], sm_scale: float,
+                     value_dim: int = 512) -> torch.Tensor:
+    """Dense causal attention of the cold start (dense_mla_core, attention_core.py:149-160)."""
+    R = q.shape[0]
+    idx = torch.arange(kv.shape[0]).unsqueeze(0).expand(R, -1)
+    return sparse_mla_decode(q, kv, idx, seq_lens, sm_scale, value_dim)
+
+
+def splitk_merge(acc: torch.Tensor, m: torch.Tensor, l: torch.Tensor) -> torch.Tensor:
+    """Log-sum-exp merge of split partials: acc [S,H,V] unnormalised, m/l [S,H]
+    (m in base-2 exponent units). Follows combine_kernel,
+    kernels/cuda_fused_sparse_splitk.py:996-1045 including the -inf skip."""
+    mx = m.max(dim=0).values
+    e = torch.where(torch.isinf(m) & (m < 0), torch.zeros_like(m), torch.exp2(m - mx))
+    lsum = (l * e).sum(0)
+    o = (acc * e.unsqueeze(-1)).sum(0)
+    return torch.where(lsum.unsqueeze(-1) > 0, o / lsum.unsqueeze(-1).clamp_min(1e-38), torch.zeros_like(o))
+
+
+# ----------------------------------------------------------------------- FP8 latent rows
+def pack_fp8_latent(kv: torch.Tensor) -> torch.Tensor:
+    """[N,576] -> [N,656] uint8 rows: 512 e4m3 | 4 fp32 scales (one per 128
+    dims) | 64 bf16 rope. Layout of the serving pool,
+    kernels/cuda_fused_sparse_splitk.py:1098-1104; scale = amax/448 per group."""
+    n = kv.shape[0]
+    nope = kv[:, :512].float().reshape(n, 4, 128)
+    amax = nope.abs().amax(-1, keepdim=True).clamp_min(1e-4)
+    scale = amax / E4M3_MAX
+    q = (nope / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8).reshape(n, 512)
+    rope = kv[:, 512:].to(torch.bfloat16).contiguous().view(torch.uint8).reshape(n, 128)
+    sc = scale.reshape(n, 4).contiguous().view(torch.uint8).reshape(n, 16)
+    return torch.cat([q, sc, rope], dim=1).contiguous()
+
+
+def unpack_fp8_latent(rows: torch.Tensor) -> torch.Tensor:
+    """[N,656] uint8 -> [N,576] bf16 exactly as the kernels dequantise:
+    fp8 -> f32, x group scale (f32), round to bf16
+    (hp_dequant4, kernels/cuda_fused_sparse_splitk.py:1181-1196)."""
+    n = rows.shape[0]
+    vals = e4m3_to_f32(rows[:, :512]).reshape(n, 4, 128)
+    scale = rows[:, 512:528].contiguous().view(torch.float32).reshape(n, 4, 1)
+    nope = (vals * scale).to(torch.bfloat16).reshape(n, 512)
+    rope = rows[:, 528:].contiguous().view(torch.bfloat16).reshape(n, 64)
+    return torch.cat([nope, rope], dim=1)
+
+
+# ----------------------------------------------------------------------- paged index keys
+def pack_index_pages(ik8: torch.Tensor, k_scale: torch.Tensor, page_ids: Sequence[int], num_pages: int,
+                     pool: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Scatter a sequence's e4m3 keys [N,128] + scales [N] into 64-token pages of
+    8448 bytes ([64 x 128 B keys][64 x fp32 scales]); layout from
+    kernels/cuda_fused_sparse_splitk.py:540-546, :2428-2429."""
+    if pool is None:
+        pool = torch.zeros(num_pages, 8448, dtype=torch.uint8)
+    n = ik8.shape[0]
+    for j, pid in enumerate(page_ids):
+        lo, hi = j * 64, min(n, j * 64 + 64)
+        if lo >= n:
+            break
+        page = pool[pid]
+        page[: (hi - lo) * 128] = ik8[lo:hi].reshape(-1)
+        sc = torch.zeros(64, dtype=torch.float32)
+        sc[: hi - lo] = k_scale[lo:hi]
+        page[8192:] = sc.view(torch.uint8)
+    return pool
+
+
+# ----------------------------------------------------------------------- inputs with a margin
+def enforce_topk_margin(logits: torch.Tensor, k_scale: torch.Tensor, topk: int, band: float = 2e-2,
+                        max_iter: int = 50) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rescale per-key scales so no logit lies within ``band * max|logit|`` of
+    the rank-topk cutoff; the logit is linear in k_scale[s]
+    (kernels/cuda_fused_sparse_splitk.py:630, :2992), so logits scale with it.
+    Returns (new_scale, new_logits) for one row of logits [N]. With such inputs
+    any implementation whose logits are within band/2 selects the same set."""
+    logits = logits.clone().double()
+    scale = k_scale.clone().double()
+    for _ in range(max_iter):
+        srt = torch.sort(logits, descending=True).values
+        tau = 0.5 * (srt[topk - 1] + srt[topk])
+        width = band * logits.abs().max()
+        near = (logits - tau).abs() < width
+        if not bool(near.any()):
+            break
+        above = near & (logits >= tau)
+        below = near & (logits < tau)
+        # push away from the cutoff multiplicatively (sign-aware)
+        for sel, up in ((above, True), (below, False)):
+            if bool(sel.any()):
+                target = tau + (2.0 * width if up else -2.0 * width)
+                lv = logits[sel]
+                safe = lv.abs() > 1e-12
+                f = torch.where(safe, target / torch.where(safe, lv, torch.ones_like(lv)), torch.ones_like(lv))
+                f = torch.where(f > 0, f, torch.ones_like(f))
+                scale[sel] = scale[sel] * f
+                logits[sel] = lv * f
+    return scale.float(), logits.float()
+
+
+# ----------------------------------------------------------------------- a9 schedule
+def lagged_producers(is_dsa: Sequence[bool]) -> List[bool]:
+    """Layer L runs an indexer under the lagged schedule iff layer L+1 attends
+    sparsely (src/lagged_indexer_dsa/model.py:61-71)."""
+    n = len(is_dsa)
+    return [(i + 1 < n and bool(is_dsa[i + 1])) for i in range(n)]
+
+
+def schedule_plan(is_dsa: Sequence[bool], mode: str, cold_start: str) -> List[dict]:
+    """Per layer: which selection attention consumes ('own', 'prev', 'dense') and
+    whether the layer's indexer runs. Restates DSAModel.forward's control flow
+    (src/lagged_indexer_dsa/model.py:93-136) without tensors."""
+    plan = []
+    prod = lagged_producers(is_dsa)
+    for i, dsa in enumerate(is_dsa):
+        if mode == "baseline":
+            plan.append({"attend": "own" if dsa else "dense", "produce": bool(dsa)})
+        else:
+            if not dsa:
+                attend = "dense"
+            elif i == 0:
+                attend = "dense" if cold_start == "dense" else "own"
+            else:
+                attend = "prev"
+            plan.append({"attend": attend, "produce": prod[i]})
+    return plan

@@ -1,0 +1,130 @@
+"""Generates the golden fixtures in this directory FROM THE REFERENCE ITSELF.
+
+Run where the reference source tree is mounted (it is not needed to run the
+tests):
+
+    python tests/golden/make_golden.py --reference /path/to/dsa-multi-layer-indexer
+
+It imports the reference's pure-PyTorch package (src/lagged_indexer_dsa) and the
+host-side helpers of its kernel file (kernels/cuda_fused_sparse_splitk.py:
+quantize_e4m3_rowwise, ref_indexer_logits_fp8, ref_sparse_mla, make_indices),
+feeds them seeded inputs and stores inputs + outputs as small .npz files. The
+reference code is only called, never copied. bf16 / fp8 tensors are stored as
+their raw uint16 / uint8 bit patterns.
+"""
+
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.bfloat16:
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    if t.dtype == torch.float8_e4m3fn:
+        return t.contiguous().view(torch.uint8).numpy()
+    return t.contiguous().numpy()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    ref = Path(args.reference)
+    sys.path.insert(0, str(ref / "src"))
+    sys.path.insert(0, str(ref / "kernels"))
+
+    import cuda_fused_sparse_splitk as K  # noqa: E402  (host helpers only; nothing is built)
+    import lagged_indexer_dsa as L  # noqa: E402
+    from lagged_indexer_dsa import attention_core as AC  # noqa: E402
+
+    torch.set_num_threads(4)
+    dev = torch.device("cpu")
+
+    # ---- FP8 formats: every e4m3 byte through torch's cast, and the row quantiser
+    all_bytes = torch.arange(256, dtype=torch.uint8)
+    table = all_bytes.view(torch.float8_e4m3fn).float()
+    torch.manual_seed(0)
+    x = torch.randn(37, 128) * torch.logspace(-3, 2, 37).unsqueeze(1)
+    xq, xs = K.quantize_e4m3_rowwise(x)
+    np.savez_compressed(HERE / "fp8_formats.npz", e4m3_table=table.numpy(), x=x.numpy(),
+                        xq=_bits(xq), xs=xs.numpy())
+
+    # ---- indexer logits on e4m3 operands (ref_indexer_logits_fp8)
+    torch.manual_seed(0)
+    S, Hidx, D, N = 2, 64, 128, 768
+    iq = torch.randn(S, Hidx, D)
+    ik = torch.randn(N, D)
+    w = torch.randn(S, Hidx) / 8
+    iq8, sq = K.quantize_e4m3_rowwise(iq)
+    ik8, sk = K.quantize_e4m3_rowwise(ik)
+    wp = (sq * w).contiguous()
+    logits = K.ref_indexer_logits_fp8(iq8, ik8, wp, sk)
+    np.savez_compressed(HERE / "indexer_fp8.npz", iq=iq.numpy(), ik=ik.numpy(), w=w.numpy(),
+                        iq8=_bits(iq8), ik8=_bits(ik8), wp=wp.numpy(), sk=sk.numpy(),
+                        logits=logits.numpy())
+
+    # ---- sparse MLA decode (ref_sparse_mla) with the reference's causal random indices
+    torch.manual_seed(0)
+    S, H, N, topk = 2, 16, 160, 64
+    q = torch.randn(1, S, H, 576, dtype=torch.bfloat16)
+    kv = torch.randn(1, N, 1, 576, dtype=torch.bfloat16)
+    indices = K.make_indices(S, N, topk, dev)
+    sm_scale = 576 ** -0.5
+    out = K.ref_sparse_mla(q, kv, indices, sm_scale, dev)
+    np.savez_compressed(HERE / "sparse_mla.npz", q=_bits(q), kv=_bits(kv), indices=indices.numpy(),
+                        sm_scale=np.float64(sm_scale), out=out.numpy())
+
+    # ---- fp32 core ops of the pure-PyTorch layer (attention_core.py)
+    torch.manual_seed(0)
+    b, s, h, d, skv = 2, 12, 8, 16, 12
+    cq = torch.randn(b, s, h, d)
+    ck = torch.randn(b, skv, d)
+    cw = torch.randn(b, s, h)
+    c_logits = AC.indexer_logits(cq, ck, cw)
+    c_masked = AC.apply_causal_mask(c_logits)
+    c_idx = AC.select_topk(c_masked, 4)
+    vdim, rope = 64, 16
+    mq = torch.randn(b, s, h, vdim + rope)
+    mkv = torch.randn(b, s, vdim + rope)
+    m_sparse = AC.sparse_mla_core(mq, mkv, c_idx, value_dim=vdim)
+    m_dense = AC.dense_mla_core(mq, mkv, value_dim=vdim)
+    np.savez_compressed(HERE / "attention_core_f32.npz", q=cq.numpy(), k=ck.numpy(), w=cw.numpy(),
+                        logits=c_logits.numpy(), masked=c_masked.numpy(), idx=c_idx.numpy(),
+                        mq=mq.numpy(), mkv=mkv.numpy(), sparse=m_sparse.numpy(), dense=m_dense.numpy())
+
+    # ---- the three schedules on the SMALL preset (weights are re-created from the seed)
+    cfg = L.SMALL_CONFIG
+    rec = {}
+    for seed in (0, 7):
+        torch.manual_seed(seed)
+        model = L.DSAModel(cfg).eval()
+        torch.manual_seed(1000 + seed)
+        x = torch.randn(1, 40, cfg.hidden_size)
+        rec[f"x_{seed}"] = x.numpy()
+        for mode in L.ScheduleMode:
+            for cold in L.ColdStartPolicy:
+                with torch.no_grad():
+                    tr = model(x, mode, cold_start=cold, record=True)
+                key = f"{seed}_{mode.value}_{cold.value}"
+                rec[f"hidden_{key}"] = tr.final_hidden.numpy()
+                for li, (u, p) in enumerate(zip(tr.indices_used, tr.indices_produced)):
+                    if u is not None:
+                        rec[f"used_{key}_{li}"] = u.numpy().astype(np.int32)
+                    if p is not None:
+                        rec[f"produced_{key}_{li}"] = p.numpy().astype(np.int32)
+    np.savez_compressed(HERE / "model_small.npz", **rec)
+
+    for f in sorted(HERE.glob("*.npz")):
+        print(f.name, f.stat().st_size, "bytes")
+
+
+if __name__ == "__main__":
+    main()

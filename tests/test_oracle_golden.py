@@ -1,0 +1,127 @@
+"""Pins the CPU oracle against outputs of the reference's own functions
+(tests/golden/*.npz, produced by tests/golden/make_golden.py)."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from conftest import bf16_from_bits, load_golden
+from oracle import dsa_oracle as O
+
+
+def test_e4m3_table_matches_torch_cast():
+    g = load_golden("fp8_formats.npz")
+    ours = O.e4m3_table()
+    ref = g["e4m3_table"]
+    assert np.array_equal(np.isnan(ours), np.isnan(ref))
+    ok = ~np.isnan(ref)
+    assert np.array_equal(ours[ok], ref[ok])
+
+
+def test_rowwise_quantiser_bit_exact():
+    g = load_golden("fp8_formats.npz")
+    q, s = O.quantize_e4m3_rowwise(torch.from_numpy(g["x"]))
+    assert np.array_equal(q.numpy(), g["xq"])
+    assert np.array_equal(s.numpy(), g["xs"])
+
+
+def test_indexer_fp8_operands_and_logits():
+    g = load_golden("indexer_fp8.npz")
+    iq8, ik8, wp, sk = O.make_fp8_indexer_inputs(
+        torch.from_numpy(g["iq"]), torch.from_numpy(g["ik"]), torch.from_numpy(g["w"]))
+    assert np.array_equal(iq8.numpy(), g["iq8"])
+    assert np.array_equal(ik8.numpy(), g["ik8"])
+    assert np.array_equal(wp.numpy(), g["wp"])
+    assert np.array_equal(sk.numpy(), g["sk"])
+    logits = O.indexer_logits_fp8(iq8, ik8, wp, sk, chunk=256)
+    assert torch.allclose(logits, torch.from_numpy(g["logits"]), rtol=1e-5, atol=1e-5)
+
+
+def test_sparse_mla_decode():
+    g = load_golden("sparse_mla.npz")
+    q = bf16_from_bits(g["q"])[0]            # [S,H,576]
+    kv = bf16_from_bits(g["kv"])[0, :, 0]    # [N,576]
+    idx = torch.from_numpy(g["indices"])
+    S, N = q.shape[0], kv.shape[0]
+    lens = [(N - S) + s + 1 for s in range(S)]
+    out = O.sparse_mla_decode(q, kv, idx, lens, float(g["sm_scale"]))
+    assert torch.allclose(out, torch.from_numpy(g["out"])[0], rtol=1e-5, atol=1e-6)
+
+
+def test_fp32_core_ops():
+    g = load_golden("attention_core_f32.npz")
+    q, k, w = (torch.from_numpy(g[n]) for n in ("q", "k", "w"))
+    logits = O.indexer_logits_f32(q, k, w)
+    assert torch.allclose(logits, torch.from_numpy(g["logits"]), rtol=1e-5, atol=1e-5)
+    B, S, N = logits.shape
+    ref_idx = g["idx"]
+    mq, mkv = torch.from_numpy(g["mq"]), torch.from_numpy(g["mkv"])
+    for b in range(B):
+        lens = list(range(1, S + 1))
+        masked = O.mask_beyond(logits[b], lens)
+        assert np.array_equal(np.isinf(masked.numpy()), np.isinf(g["masked"][b]))
+        ours = O.select_topk(masked, 4, pad_value=N)
+        for s in range(S):
+            assert sorted(ours[s].tolist()) == sorted(ref_idx[b, s].tolist())
+        sm = mq.shape[-1] ** -0.5
+        sp = O.sparse_mla_decode(mq[b], mkv[b], torch.from_numpy(ref_idx[b]), lens, sm, value_dim=64)
+        assert torch.allclose(sp, torch.from_numpy(g["sparse"])[b], rtol=1e-5, atol=1e-6)
+        de = O.dense_mla_decode(mq[b], mkv[b], lens, sm, value_dim=64)
+        assert torch.allclose(de, torch.from_numpy(g["dense"])[b], rtol=1e-5, atol=1e-6)
+
+
+def test_topk_ties_go_to_lower_position():
+    logits = torch.tensor([[1.0, 3.0, 3.0, 3.0, 0.5, 3.0, float("-inf")]])
+    assert O.select_topk(logits, 3, pad_value=-1).tolist() == [[1, 2, 3]]
+    assert O.select_topk(logits, 7, pad_value=-1).tolist() == [[0, 1, 2, 3, 4, 5, -1]]
+
+
+def test_splitk_merge_equals_single_pass():
+    torch.manual_seed(0)
+    H, V, n, S = 4, 8, 96, 3
+    s = torch.randn(H, n) * 3
+    v = torch.randn(n, V)
+    full = torch.softmax(s, -1) @ v
+    acc, m, l = [], [], []
+    for c in torch.chunk(torch.arange(n), S):
+        sc = s[:, c] * 1.4426950408889634
+        mm = sc.max(-1).values
+        p = torch.exp2(sc - mm[:, None])
+        acc.append(p @ v[c]); m.append(mm); l.append(p.sum(-1))
+    # one empty split must be skipped
+    acc.append(torch.zeros(H, V)); m.append(torch.full((H,), float("-inf"))); l.append(torch.zeros(H))
+    got = O.splitk_merge(torch.stack(acc), torch.stack(m), torch.stack(l))
+    assert torch.allclose(got, full, rtol=1e-5, atol=1e-6)
+
+
+def test_fp8_latent_round_trip():
+    torch.manual_seed(0)
+    kv = torch.randn(33, 576)
+    rows = O.pack_fp8_latent(kv)
+    assert rows.shape == (33, 656) and rows.dtype == torch.uint8
+    back = O.unpack_fp8_latent(rows).float()
+    assert torch.equal(back[:, 512:], kv[:, 512:].to(torch.bfloat16).float())
+    assert float((back[:, :512] - kv[:, :512]).abs().max()) < 0.25  # e4m3 step at |x| < 4.5 after scaling
+
+
+def test_margin_enforcement():
+    torch.manual_seed(0)
+    logits = torch.randn(4096)
+    scale = torch.rand(4096) + 0.5
+    s2, l2 = O.enforce_topk_margin(logits, scale, 512, band=2e-2)
+    srt = torch.sort(l2, descending=True).values
+    gap = float(srt[511] - srt[512])
+    assert gap >= 2 * 2e-2 * float(l2.abs().max()) * 0.99
+    assert torch.allclose(l2, logits * (s2 / scale), rtol=1e-5, atol=1e-6)
+
+
+def test_schedule_plan():
+    plan = O.schedule_plan([True] * 4, "lagged_fused", "dense")
+    assert [p["attend"] for p in plan] == ["dense", "prev", "prev", "prev"]
+    assert [p["produce"] for p in plan] == [True, True, True, False]
+    plan = O.schedule_plan([False, False, True, True], "lagged_reference", "eager")
+    assert [p["attend"] for p in plan] == ["dense", "dense", "prev", "prev"]
+    assert [p["produce"] for p in plan] == [False, True, True, False]
+    plan = O.schedule_plan([True, True], "baseline", "dense")
+    assert all(p["attend"] == "own" and p["produce"] for p in plan)
