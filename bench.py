@@ -1,0 +1,404 @@
+"""Benchmark of the DSA decode hot path (indexer scan -> top-2048 -> split-K
+sparse MLA) at the DeepSeek-V3.2 single-layer decode shape: batch 1, context
+131072, FP8 index keys, 128 MLA heads over a bf16 latent cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one layer's hot path for one decode token. Steps cycle over
+`--layers` distinct per-layer caches so a step never finds its keys in L2.
+Prints ONE JSON line (rank 0). With --impl reference the CPU oracle (a port of
+the reference's PyTorch path) is timed on the host cores instead.
+
+Under torchrun (N > 1) MLA heads are split tensor-parallel across ranks and the
+indexer is replicated, as the reference does under TP
+(src/lagged_indexer_dsa/inference/modeling/transformer.py:673-677, :1323); with
+--seq-shard the scan is split by KV range instead and the per-rank top-2048
+candidates are merged after an NCCL all-gather.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+CTX = 131072
+HEADS = 128
+INDEX_HEADS = 64
+TOPK = 2048
+SM_SCALE = 192 ** -0.5
+SCAN_BYTES_PER_KEY = 132          # 128 B e4m3 key + 4 B fp32 scale
+METRIC = "dsa_decode_layer_tokens_per_s_ctx128k"
+UNIT = "tok/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=32)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=CTX)
+    ap.add_argument("--layers", type=int, default=16, help="distinct per-layer caches cycled through")
+    ap.add_argument("--seq-shard", action="store_true", help="N>1: shard the scan by KV range + all-gather merge")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scan-impl", type=int, default=0, help="0 tcgen05, 1 legacy mma.sync")
+    return ap.parse_args()
+
+
+def workload_config(args, world):
+    return {
+        "workload": "deepseek_v3.2_single_layer_decode (BASELINE config 2)",
+        "batch": 1, "context": args.ctx, "index_heads": INDEX_HEADS, "index_dim": 128,
+        "index_key_dtype": "e4m3+fp32 scale", "topk": TOPK, "mla_heads": HEADS, "latent_dim": 576,
+        "latent_dtype": "bf16", "sm_scale": "1/sqrt(192)",
+        "parallelism": ("tp%d_heads" % world) + ("+seq_sharded_indexer" if args.seq_shard and world > 1 else "+replicated_indexer" if world > 1 else ""),
+        "l2": "%d distinct per-layer caches cycled (%.0f MB of index keys + %.0f MB of latent rows): "
+              "inputs larger than the 126 MB L2" % (args.layers, args.layers * args.ctx * 132 / 1e6,
+                                                    args.layers * args.ctx * 1152 / 1e6),
+        "launch": "one CUDA graph per layer (4 kernels: scan, select, attention partials, combine)",
+    }
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_step_inputs(ctx, seed=0):
+    from oracle import dsa_oracle as O
+
+    g = torch.Generator().manual_seed(seed)
+    iq8, ik8, wp, sk = O.make_fp8_indexer_inputs(torch.randn(1, INDEX_HEADS, 128, generator=g),
+                                                 torch.randn(ctx, 128, generator=g),
+                                                 torch.randn(1, INDEX_HEADS, generator=g) / 8)
+    q = torch.randn(1, HEADS, 576, generator=g).to(torch.bfloat16)
+    kv = torch.randn(ctx, 576, generator=g).to(torch.bfloat16)
+    return iq8, ik8, wp, sk, q, kv
+
+
+def cpu_one_step(inputs, ctx):
+    """The oracle's hot path: fp32 logits from the e4m3 bytes, torch.topk, sparse MLA."""
+    from oracle import dsa_oracle as O
+
+    iq8, ik8, wp, sk, q, kv = inputs
+    logits = O.indexer_logits_fp8(iq8, ik8, wp, sk, chunk=32768)
+    idx = torch.topk(logits, TOPK, dim=-1).indices
+    return O.sparse_mla_decode(q, kv, idx, [ctx], SM_SCALE)
+
+
+def time_cpu(ctx, steps, warmup):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    inputs = cpu_step_inputs(ctx)
+    for _ in range(warmup):
+        cpu_one_step(inputs, ctx)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_one_step(inputs, ctx)
+    dt = (time.perf_counter() - t0) / steps
+    return dt, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    warmup = max(1, min(args.warmup, 3))
+    dt, cores = time_cpu(args.ctx, steps, warmup)
+    val = 1.0 / dt
+    sample = f"{steps} full steps (ctx {args.ctx}, all 128 heads) after {warmup} warm-ups; torch CPU, {cores} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (e4m3/bf16 operands decoded on the host)",
+        "data": "synthetic", "config": workload_config(args, 1),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+def event_time_ms(fn, iters):
+    st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    st.record()
+    for i in range(iters):
+        fn(i)
+    en.record()
+    torch.cuda.synchronize()
+    return st.elapsed_time(en) / iters
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    from dsa_multi_layer_indexer_b200 import _lib, ops
+    from dsa_multi_layer_indexer_b200.decode import HostDecoder, HotPathState, LayerCache
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+    assert HEADS % world == 0
+    heads_local = HEADS // world
+    ctx, L = args.ctx, args.layers
+    seq_shard = args.seq_shard and world > 1
+    ctx_local = ctx // world if seq_shard else ctx
+    key_lo = rank * ctx_local if seq_shard else 0
+
+    # ---- per-layer caches, generated and quantised on the device (seeded)
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    caches = []
+    for _ in range(L):
+        ik = torch.randn(ctx, 128, device=dev, generator=gen)
+        ik8, sk = ops.quantize_e4m3_rowwise(ik)
+        kv = torch.randn(ctx, 576, device=dev, generator=gen).to(torch.bfloat16)
+        caches.append(LayerCache(ik8[key_lo:key_lo + ctx_local].unsqueeze(0).contiguous(),
+                                 sk[key_lo:key_lo + ctx_local].unsqueeze(0).contiguous(), kv.unsqueeze(0)))
+        del ik
+    # ---- the step's query operands come from (pinned) host memory
+    hgen = torch.Generator().manual_seed(99)
+    iq = torch.randn(1, INDEX_HEADS, 128, generator=hgen)
+    w = torch.randn(1, INDEX_HEADS, generator=hgen) / 8
+    q_all = torch.randn(1, HEADS, 576, generator=hgen).to(torch.bfloat16)
+    iq8, sq = ops.quantize_e4m3_rowwise(iq.to(dev))
+    h_iq8 = iq8.view(torch.uint8).cpu()
+    h_w = (sq.cpu() * w).contiguous()
+    h_q = q_all[:, rank * heads_local:(rank + 1) * heads_local].contiguous()
+
+    states, graphs = [], []
+    cand_idx = cand_val = gath_idx = gath_val = None
+    if seq_shard:
+        cand_idx = torch.empty(1, TOPK, dtype=torch.int32, device=dev)
+        cand_val = torch.empty(1, TOPK, dtype=torch.float32, device=dev)
+        gath_idx = torch.empty(1, world * TOPK, dtype=torch.int32, device=dev)
+        gath_val = torch.empty(1, world * TOPK, dtype=torch.float32, device=dev)
+
+    def hot_path(state, cache):
+        if not seq_shard:
+            state.run(cache, SM_SCALE, impl=args.scan_impl)
+            return
+        logits = ops.indexer_scan_fp8(state.index_q, state.index_w, cache.index_k, cache.k_scale, None,
+                                      ctx=ctx_local, out=state.logits, hist=state.hist, impl=args.scan_impl)
+        ops.topk_select(logits, TOPK, None, hist=state.hist, out_idx=cand_idx, out_val=cand_val,
+                        index_offset=key_lo)
+        dist.all_gather_into_tensor(gath_idx.view(-1), cand_idx.view(-1))
+        dist.all_gather_into_tensor(gath_val.view(-1), cand_val.view(-1))
+        ops.topk_select(gath_val, TOPK, None, index_map=gath_idx, out_idx=state.indices)
+        state.run_attention(cache, state.indices, SM_SCALE)
+
+    for l in range(L):
+        st = HotPathState(1, heads_local, INDEX_HEADS, ctx_local, TOPK, dev)
+        st.index_q.copy_(h_iq8)
+        st.index_w.copy_(h_w)
+        st.q.copy_(h_q)
+        if seq_shard:
+            st.seq_lens.fill_(ctx)  # attention sees the whole (replicated) latent cache
+        states.append(st)
+    torch.cuda.synchronize()
+    # eager warm-up (also the NCCL communicator), then one graph per layer
+    for l in range(L):
+        hot_path(states[l], caches[l])
+    torch.cuda.synchronize()
+    for l in range(L):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            hot_path(states[l], caches[l])
+        graphs.append(g)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        graphs[i % L].replay()
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    st_ev, en_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    st_ev.record()
+    for i in range(args.steps):
+        graphs[i % L].replay()
+    en_ev.record()
+    barrier()
+    ms_step = st_ev.elapsed_time(en_ev) / args.steps
+
+    # ---- the dominant kernel alone, same rotation: average launch duration with CUDA events
+    scan_graphs = []
+    for l in range(L):
+        g = torch.cuda.CUDAGraph()
+        s = states[l]
+        with torch.cuda.graph(g):
+            ops.indexer_scan_fp8(s.index_q, s.index_w, caches[l].index_k, caches[l].k_scale, None,
+                                 ctx=ctx_local, out=s.logits, hist=None, impl=args.scan_impl)
+        scan_graphs.append(g)
+    n_scan = max(args.steps, 64)
+    for i in range(L):
+        scan_graphs[i].replay()
+    scan_ms = event_time_ms(lambda i: scan_graphs[i % L].replay(), n_scan)
+    # the other kernels, for the breakdown (each its own graph, rotating caches)
+    def time_graphs(build):
+        gs = []
+        for l in range(L):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                build(l)
+            gs.append(g)
+        for i in range(L):
+            gs[i].replay()
+        return event_time_ms(lambda i: gs[i % L].replay(), n_scan)
+
+    topk_ms = time_graphs(lambda l: ops.topk_select(states[l].logits[:, :ctx_local], TOPK, None,
+                                                    out_idx=states[l].indices))
+    attn_ms = time_graphs(lambda l: states[l].run_attention(caches[l], states[l].indices, SM_SCALE))
+    clocks = sampler.stop()
+
+    # ---- end to end with host buffers (rank-local operands in pinned memory)
+    e2e = None
+    if not seq_shard:
+        dec = [HostDecoder(states[l], caches[l], SM_SCALE) for l in range(min(L, 4))]
+        for d in dec:
+            d.h_index_q.copy_(h_iq8)
+            d.h_index_w.copy_(h_w)
+            d.h_q.copy_(h_q)
+        for i in range(8):
+            dec[i % len(dec)].step()
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            dec[i % len(dec)].step()
+        barrier()
+        e2e_dt = (time.perf_counter() - t0) / args.steps
+        e2e = {"value": 1.0 / e2e_dt, "unit": UNIT, "ms_per_step": e2e_dt * 1e3,
+               "h2d_bytes_per_step": dec[0].h2d_bytes, "d2h_bytes_per_step": dec[0].d2h_bytes,
+               "note": "pinned host operands -> device, graph replay, output + selection -> host, sync every step"}
+
+    _lib.check_device_status()
+    times = torch.tensor([ms_step, scan_ms, topk_ms, attn_ms, e2e["ms_per_step"] if e2e else 0.0],
+                         dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_step, scan_ms, topk_ms, attn_ms, e2e_ms = times.tolist()
+    if e2e:
+        e2e["ms_per_step"] = e2e_ms
+        e2e["value"] = 1e3 / e2e_ms
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        scan_bytes = ctx_local * SCAN_BYTES_PER_KEY
+        achieved = scan_bytes / (scan_ms * 1e-3) / 1e9
+        out = {
+            "metric": METRIC, "value": 1e3 / ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8 e4m3 (indexer MMA) + bf16 (MLA), fp32 accumulate",
+            "data": "synthetic", "config": workload_config(args, world),
+            "layer_us": ms_step * 1e3,
+            "breakdown_us": {"indexer_scan": scan_ms * 1e3, "topk_select": topk_ms * 1e3,
+                             "sparse_mla_partials_plus_combine": attn_ms * 1e3},
+            "roofline": {"kernel": "indexer_scan_tc_kernel" if args.scan_impl == 0 else "indexer_scan_legacy_kernel",
+                         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": peak_src,
+                         "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "algorithmic_bytes_per_launch": scan_bytes,
+                         "traffic": None},
+            "gpu_launches": args.steps * (6 if seq_shard else 4),
+            "clocks": clocks,
+        }
+        if e2e:
+            out["e2e"] = e2e
+        if not args.no_cpu_baseline and world == 1:
+            dt, cores = time_cpu(ctx, 10, 2)
+            out["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, "cores": cores, "kind": "port",
+                                   "sample": f"10 full steps (ctx {ctx}, 128 heads) after 2 warm-ups, torch CPU"}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

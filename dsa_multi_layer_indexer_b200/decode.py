@@ -1,0 +1,133 @@
+"""Decode-time driver of the hot path: persistent buffers, the three launches
+(indexer scan -> top-k -> split-K sparse MLA) and CUDA-graph capture.
+
+The reference's pure-PyTorch layer has no decode entry; its serving overlay
+keeps per-shape persistent scratch and replays a captured graph
+(sglang_overlay/mli-sglang-v0.5.16.patch:1274-1279, :1490-1505;
+src/lagged_indexer_dsa/inference/modeling/fused_decode.py:46-119). This module
+is that contract on top of the C ABI: every buffer is allocated once, lengths
+are read on the device, and a step makes no allocation and no host sync.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+
+from . import ops
+
+
+@dataclasses.dataclass
+class LayerCache:
+    """One layer's decode caches for ``n_seq`` sequences of capacity ``cap``.
+
+    index_k ``[n_seq, cap, 128]`` e4m3 with k_scale ``[n_seq, cap]`` fp32, and
+    the latent cache kv ``[n_seq, cap, 576]`` bf16 (or ``[n_seq, cap, 656]``
+    uint8 fp8-packed rows)."""
+
+    index_k: torch.Tensor
+    k_scale: torch.Tensor
+    kv: torch.Tensor
+
+    @property
+    def n_seq(self) -> int:
+        return self.index_k.shape[0]
+
+    @property
+    def capacity(self) -> int:
+        return self.index_k.shape[1]
+
+
+class HotPathState:
+    """Buffers of one decode step for ``rows`` query tokens (one per sequence).
+
+    Inputs a caller fills before a step: ``index_q`` (e4m3 bytes), ``index_w``,
+    ``q`` and ``seq_lens``. Outputs after a step: ``indices`` (the selection the
+    indexer produced) and ``out`` (attention over ``attend`` indices)."""
+
+    def __init__(self, rows: int, heads: int, index_heads: int, capacity: int, topk: int,
+                 device, nsplit: Optional[int] = None, use_hist: bool = True) -> None:
+        self.rows, self.heads, self.index_heads = rows, heads, index_heads
+        self.capacity, self.topk = capacity, topk
+        dev = torch.device(device)
+        self.index_q = torch.zeros(rows, index_heads, ops.INDEX_DIM, dtype=torch.uint8, device=dev)
+        self.index_w = torch.zeros(rows, index_heads, dtype=torch.float32, device=dev)
+        self.q = torch.zeros(rows, heads, ops.LATENT_DIM, dtype=torch.bfloat16, device=dev)
+        self.seq_lens = torch.full((rows,), capacity, dtype=torch.int32, device=dev)
+        slab = (capacity + 3) // 4 * 4
+        self.logits = torch.empty(rows, slab, dtype=torch.float32, device=dev)
+        # zero once; the select kernel re-zeroes it after every use
+        self.hist = torch.zeros(rows, ops.HIST_BINS, dtype=torch.int32, device=dev) if use_hist else None
+        self.indices = torch.full((rows, topk), -1, dtype=torch.int32, device=dev)
+        self.nsplit = nsplit or ops.default_nsplit(rows, heads, topk)
+        self.scratch = ops.MlaScratch(rows, heads, self.nsplit, dev)
+        self.out = torch.empty(rows, heads, ops.VALUE_DIM, dtype=torch.bfloat16, device=dev)
+
+    # -- the three launches, on the current stream -----------------------------
+    def run_indexer(self, cache: LayerCache, impl: int = 0) -> torch.Tensor:
+        """Scan + select: fills and returns ``self.indices``."""
+        logits = ops.indexer_scan_fp8(self.index_q, self.index_w, cache.index_k, cache.k_scale,
+                                      self.seq_lens, ctx=self.capacity, out=self.logits,
+                                      hist=self.hist, impl=impl)
+        ops.topk_select(logits, self.topk, self.seq_lens, hist=self.hist, out_idx=self.indices)
+        return self.indices
+
+    def run_attention(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float) -> torch.Tensor:
+        """Sparse MLA over ``attend`` (any ``[rows, topk]`` int32 selection)."""
+        return ops.sparse_mla_decode(self.q, cache.kv, attend, sm_scale, self.seq_lens,
+                                     scratch=self.scratch, out=self.out)
+
+    def run(self, cache: LayerCache, sm_scale: float, impl: int = 0) -> torch.Tensor:
+        """Baseline order: the layer attends its own fresh selection."""
+        self.run_indexer(cache, impl)
+        return self.run_attention(cache, self.indices, sm_scale)
+
+    def capture(self, cache: LayerCache, sm_scale: float, impl: int = 0) -> torch.cuda.CUDAGraph:
+        """Captures ``run`` into a CUDA graph (after one eager warm-up launch)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.run(cache, sm_scale, impl)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.run(cache, sm_scale, impl)
+        return graph
+
+
+class HostDecoder:
+    """End-to-end form with HOST buffers: copies a step's query operands from
+    pinned host memory, replays the captured hot path and copies the attention
+    output (and the selection) back. This is the call a host-side integrator
+    makes when its tensors are not already on the device."""
+
+    def __init__(self, state: HotPathState, cache: LayerCache, sm_scale: float) -> None:
+        self.state, self.cache = state, cache
+        self.graph = state.capture(cache, sm_scale)
+        s = state
+        self.h_index_q = torch.zeros(s.index_q.shape, dtype=torch.uint8).pin_memory()
+        self.h_index_w = torch.zeros(s.index_w.shape, dtype=torch.float32).pin_memory()
+        self.h_q = torch.zeros(s.q.shape, dtype=torch.bfloat16).pin_memory()
+        self.h_out = torch.zeros(s.out.shape, dtype=torch.bfloat16).pin_memory()
+        self.h_indices = torch.zeros(s.indices.shape, dtype=torch.int32).pin_memory()
+
+    @property
+    def h2d_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.h_index_q, self.h_index_w, self.h_q))
+
+    @property
+    def d2h_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.h_out, self.h_indices))
+
+    def step(self) -> torch.Tensor:
+        s = self.state
+        s.index_q.copy_(self.h_index_q, non_blocking=True)
+        s.index_w.copy_(self.h_index_w, non_blocking=True)
+        s.q.copy_(self.h_q, non_blocking=True)
+        self.graph.replay()
+        self.h_out.copy_(s.out, non_blocking=True)
+        self.h_indices.copy_(s.indices, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_out
