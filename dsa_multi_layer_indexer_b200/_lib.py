@@ -12,8 +12,11 @@ import ctypes as C
 from pathlib import Path
 from typing import Dict, List, Tuple
 
+import os
+
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libdsa_b200.so"
+# DSA_B200_LIB selects another build of the same ABI (e.g. the tracing build).
+LIB_PATH = Path(os.environ.get("DSA_B200_LIB") or (_PKG / "libdsa_b200.so"))
 
 _p = C.c_void_p
 _i = C.c_int
@@ -26,10 +29,12 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_last_error": (C.c_char_p, []),
     "dsa_status_string": (C.c_char_p, [_i]),
     "dsa_check_device_status": (_i, [C.POINTER(C.c_uint32)]),
+    "dsa_debug_read_stamps": (_i, [_p, _i]),
     "dsa_indexer_scan_fp8": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _l, _l, _l, _l, _l, _i, _p]),
     "dsa_indexer_scan_fp8_paged": (_i, [_p, _p, _p, _l, _p, _l, _p, _p, _p, _i, _i, _l, _l, _p]),
     "dsa_indexer_scan_f32": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _l, _l, _l, _p]),
-    "dsa_topk_select": (_i, [_p, _p, _p, _p, _p, _p, _i, _l, _l, _i, C.c_int32, C.c_int32, _p]),
+    "dsa_topk_workspace_bytes": (_l, [_i, _l]),
+    "dsa_topk_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _l, _i, _l, _l, _i, C.c_int32, C.c_int32, _p]),
     "dsa_sparse_mla_partials": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _l, _i, _p]),
     "dsa_sparse_mla_combine": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "dsa_sparse_mla_decode": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _l, _i, _p]),
@@ -37,7 +42,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_quantize_e4m3_rowwise": (_i, [_p, _p, _p, _l, _i, _f, _p]),
 }
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 
 class DsaError(RuntimeError):

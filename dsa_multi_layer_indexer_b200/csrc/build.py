@@ -42,6 +42,17 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > built for d in deps)
 
 
+def build_trace(out: Path) -> Path:
+    """Tracing build: same ABI plus per-CTA phase stamps (dsa_debug_read_stamps).
+    Select it at run time with DSA_B200_LIB=<out>."""
+    cmd = [_nvcc(), *NVCC_FLAGS, "-DDSA_STAMPS", "-o", str(out), *[str(CSRC / s) for s in SOURCES]]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError(f"nvcc failed ({proc.returncode})")
+    return out
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and not is_stale():
         return LIB
@@ -58,4 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build_trace(Path(sys.argv[sys.argv.index("--trace") + 1])))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -52,6 +52,43 @@ constexpr unsigned int kStatusAttnTimeout = 2u;
 constexpr unsigned int kStatusSelectOverflow = 4u;
 
 #ifdef __CUDACC__
+// ---------------------------------------------------------------- device: phase stamps
+// Tracing build only (-DDSA_STAMPS): thread 0 of a CTA records its SM cycle
+// counter at numbered phases, read back with dsa_debug_read_stamps. The
+// reference has the same facility (kernels/cuda_fused_sparse_splitk.py
+// :1076-1090 stamps, :2329-2349 read-back). Compiled out of the normal build.
+constexpr int kStampSlots = 16;
+constexpr int kStampCtas = 1024;
+#ifdef DSA_STAMPS
+__device__ unsigned long long g_stamps[kStampCtas * kStampSlots];
+#define DSA_STAMP_IF(cond, cta, slot)                                                \
+  do {                                                                               \
+    if ((cond) && (cta) < ::dsa::kStampCtas)                                         \
+      ::dsa::g_stamps[(cta) * ::dsa::kStampSlots + (slot)] = clock64();              \
+  } while (0)
+// Kernel begin / end wall times (global nanosecond timer), min / max over CTAs,
+// stored after the per-CTA stamps: words [kStampCtas*kStampSlots + 2*id, +1].
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ unsigned long long g_ktime[32];
+#define DSA_KTIME_BEGIN(id)                                                          \
+  do {                                                                               \
+    if (threadIdx.x == 0) atomicMin(&::dsa::g_ktime[2 * (id)], ::dsa::global_ns());  \
+  } while (0)
+#define DSA_KTIME_END(id)                                                                \
+  do {                                                                                   \
+    if (threadIdx.x == 0) atomicMax(&::dsa::g_ktime[2 * (id) + 1], ::dsa::global_ns());  \
+  } while (0)
+#else
+#define DSA_STAMP_IF(cond, cta, slot) do { } while (0)
+#define DSA_KTIME_BEGIN(id) do { } while (0)
+#define DSA_KTIME_END(id) do { } while (0)
+#endif
+#define DSA_STAMP(cta, slot) DSA_STAMP_IF(threadIdx.x == 0, cta, slot)
+
 // ---------------------------------------------------------------- device: misc
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -101,7 +101,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_scan[64], g_opt_mla[64], g_opt_scan_f32[64];
+static bool g_opt_scan[64], g_opt_mla[64], g_opt_scan_f32[64], g_opt_topk[64];
 
 }  // namespace dsa
 
@@ -154,6 +154,28 @@ int dsa_check_device_status(uint32_t* detail) {
   if (detail) *detail = word;
   if (word) return fail(DSA_ERR_DEVICE_TIMEOUT, "device status word 0x%x", word);
   return DSA_OK;
+}
+
+int dsa_debug_read_stamps(uint64_t* host_out, int max_words) {
+#ifdef DSA_STAMPS
+  const int n = max_words < kStampCtas * kStampSlots ? max_words : kStampCtas * kStampSlots;
+  DSA_CUDA(cudaDeviceSynchronize());
+  DSA_CUDA(cudaMemcpyFromSymbol(host_out, g_stamps, size_t(n) * sizeof(uint64_t)));
+  static unsigned long long zeros[kStampCtas * kStampSlots];
+  DSA_CUDA(cudaMemcpyToSymbol(g_stamps, zeros, sizeof(zeros)));
+  if (max_words >= kStampCtas * kStampSlots + 32) {
+    DSA_CUDA(cudaMemcpyFromSymbol(host_out + kStampCtas * kStampSlots, g_ktime, sizeof(g_ktime)));
+    unsigned long long init[32];
+    for (int i = 0; i < 32; ++i) init[i] = (i & 1) ? 0ull : ~0ull;
+    DSA_CUDA(cudaMemcpyToSymbol(g_ktime, init, sizeof(init)));
+    return kStampCtas * kStampSlots + 32;
+  }
+  return n;
+#else
+  (void)host_out;
+  (void)max_words;
+  return fail(DSA_ERR_UNSUPPORTED, "this build has no phase stamps (compile with -DDSA_STAMPS)");
+#endif
 }
 
 // ------------------------------------------------------------------ indexer scan
@@ -316,58 +338,61 @@ int dsa_indexer_scan_f32(const float* index_q, const float* index_w, const float
 }
 
 // ------------------------------------------------------------------ top-k
-}  // extern "C"
-
-template <int ITEMS>
-static int launch_topk(const topk::Params& p, int R, cudaStream_t st) {
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(topk::kCluster, R, 1);
-  cfg.blockDim = dim3(topk::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = topk::kCluster;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_select_kernel<ITEMS>, p));
-  return DSA_OK;
+int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
+  if (R <= 0 || n <= 0) return 0;
+  return topk::workspace_words(R, n) * 4;
 }
 
-extern "C" {
-
 int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist,
-                    const int32_t* index_map, int32_t* out_idx, float* out_val, int R, int64_t n,
-                    int64_t slab_stride, int topk_k, int32_t pad_value, int32_t index_offset,
-                    void* stream) {
-  DSA_REQUIRE(logits && out_idx, "topk: null pointer");
-  DSA_REQUIRE(aligned16(logits), "topk: logits must be 16-byte aligned");
+                    const int32_t* index_map, int32_t* out_idx, float* out_val, void* workspace,
+                    int64_t workspace_bytes, int R, int64_t n, int64_t slab_stride, int topk_k,
+                    int32_t pad_value, int32_t index_offset, void* stream) {
+  DSA_REQUIRE(logits && out_idx && workspace, "topk: null pointer");
+  DSA_REQUIRE(aligned16(logits) && aligned16(workspace), "topk: logits / workspace must be 16-byte aligned");
   DSA_REQUIRE(R > 0 && R <= 65535, "topk: R=%d out of range", R);
   DSA_REQUIRE(n > 0 && slab_stride >= n, "topk: need 0 < n <= slab_stride");
-  DSA_REQUIRE(topk_k > 0 && topk_k <= 32768, "topk: k=%d out of range [1, 32768]", topk_k);
-  if (n > int64_t(topk::kCluster) * topk::kThreads * 32)
-    return fail(DSA_ERR_UNSUPPORTED, "topk: n=%lld exceeds the 262144-per-row limit", (long long)n);
+  DSA_REQUIRE(topk_k > 0 && topk_k <= 65536, "topk: k=%d out of range [1, 65536]", topk_k);
+  if (n > topk::kMaxN)
+    return fail(DSA_ERR_UNSUPPORTED, "topk: n=%lld exceeds the %lld-per-row limit", (long long)n,
+                (long long)topk::kMaxN);
+  DSA_REQUIRE(workspace_bytes >= dsa_topk_workspace_bytes(R, n),
+              "topk: workspace of %lld bytes is smaller than dsa_topk_workspace_bytes = %lld",
+              (long long)workspace_bytes, (long long)dsa_topk_workspace_bytes(R, n));
+  const int64_t words = topk::mask_words(n), slots = words / 4;
+  uint32_t* ws = static_cast<uint32_t*>(workspace);
   topk::Params p{};
   p.logits = logits;
   p.seq_lens = seq_lens;
-  p.hist = hist;
+  p.above_mask = ws;
+  p.slot_cnt = p.above_mask + int64_t(R) * words;
+  p.header = p.slot_cnt + int64_t(R) * slots;
+  uint32_t* ws_hist = p.header + int64_t(R) * 4;
+  p.slot_cand = reinterpret_cast<uint2*>(ws_hist + int64_t(R) * topk::kBins);
+  p.hist = hist ? hist : ws_hist;
   p.index_map = index_map;
   p.out_idx = out_idx;
   p.out_val = out_val;
   p.n = n;
   p.slab_stride = slab_stride;
+  p.words = int(words);
+  p.slots = int(slots);
   p.topk = topk_k;
   p.pad = pad_value;
   p.index_offset = index_offset;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t per_thread = (n + int64_t(topk::kCluster) * topk::kThreads - 1) /
-                             (int64_t(topk::kCluster) * topk::kThreads);
-  if (per_thread <= 4) return launch_topk<4>(p, R, st);
-  if (per_thread <= 8) return launch_topk<8>(p, R, st);
-  if (per_thread <= 16) return launch_topk<16>(p, R, st);
-  return launch_topk<32>(p, R, st);
+  const dim3 grid(unsigned(words / (topk::kChunk / 32)), R);
+  if (!hist) {
+    topk::topk_hist_kernel<<<grid, topk::kThreads, 0, st>>>(p);
+    DSA_CUDA(cudaGetLastError());
+  }
+  topk::topk_classify_kernel<<<grid, topk::kThreads, 0, st>>>(p);
+  DSA_CUDA(cudaGetLastError());
+  int rc = opt_in_smem(topk::topk_finish_kernel,
+                       topk::fin_smem_bytes(int(topk::mask_words(topk::kMaxN))), g_opt_topk);
+  if (rc) return rc;
+  topk::topk_finish_kernel<<<R, topk::kFinThreads, topk::fin_smem_bytes(p.words), st>>>(p);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
 }
 
 // ------------------------------------------------------------------ sparse MLA

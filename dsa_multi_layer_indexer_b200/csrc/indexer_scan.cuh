@@ -62,6 +62,8 @@ struct __align__(8) Barriers {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort;
+  uint32_t bin_lo;  // range of histogram bins this CTA touched
+  uint32_t bin_hi;
 };
 
 constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
@@ -95,8 +97,30 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   const int len = row_len(p, r);
   const int G = gridDim.x;
   const bool want_hist = p.hist != nullptr;
+  const int stamp_cta = blockIdx.y * gridDim.x + blockIdx.x;
+  DSA_STAMP(stamp_cta, 0);
+  DSA_KTIME_BEGIN(0);
 
-  // ---- set-up: barriers, tensor memory, swizzled query tile, head weights
+  // One tile's TMA load into ring slot (it % kStages); the caller has made sure the slot is free.
+  auto issue_tile = [&](int it, int t) {
+    const int s = it % kStages;
+    const uint32_t dst = smem_u32(s_tiles + size_t(s) * kTileBytes);
+    const uint32_t bar = smem_u32(&bars->full[s]);
+    if (!p.paged) {
+      mbar_arrive_expect_tx(bar, kTileBytes);
+      tma_load_2d(dst, &tmap, 0, static_cast<int>(int64_t(seq) * p.k_seq_stride + int64_t(t) * kTileKeys), bar);
+    } else {
+      const int32_t* pt = p.page_table + int64_t(r) * p.pt_stride + 2 * t;
+      const bool second = int64_t(2 * t + 1) * DSA_PAGE_TOKENS < len;
+      mbar_arrive_expect_tx(bar, second ? kTileBytes : kTileBytes / 2);
+      tma_load_3d(dst, &tmap, 0, 0, pt[0], bar);
+      if (second) tma_load_3d(dst + kTileBytes / 2, &tmap, 0, 0, pt[1], bar);
+    }
+  };
+
+  // ---- set-up. Thread 0 arms the barriers and at once starts the first kStages
+  // tile loads, so the HBM latency of the keys overlaps the rest of the set-up
+  // (tensor memory, swizzled query tile, head weights, histogram clear).
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bars->full[s]), 1);
@@ -107,8 +131,14 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
       mbar_init(smem_u32(&bars->acc_empty[b]), 4);
     }
     bars->abort = 0;
+    bars->bin_lo = kHistBins;
+    bars->bin_hi = 0;
     mbar_fence_init();
-    prefetch_tensor_map(&tmap);
+    int it = 0;
+    for (int t = blockIdx.x; t < p.tiles_per_row && it < kStages; t += G, ++it) {
+      if (int64_t(t) * kTileKeys >= len) break;
+      issue_tile(it, t);
+    }
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
@@ -128,7 +158,8 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     for (int i = tid; i < kMaxHeads; i += kThreads)
       s_w[i] = i < p.n_heads ? p.w[size_t(r) * p.n_heads + i] : 0.f;
     if (want_hist)
-      for (int i = tid; i < kHistBins; i += kThreads) s_hist[i] = 0;
+      for (int i = tid; i < kHistBins / 4; i += kThreads)
+        reinterpret_cast<uint4*>(s_hist)[i] = make_uint4(0, 0, 0, 0);
   }
   fence_proxy_async_smem();
   tc_fence_before();
@@ -136,33 +167,23 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
   volatile uint32_t* abort_flag = &bars->abort;
+  DSA_STAMP(stamp_cta, 1);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (elect_one()) {
+    // (tiles beyond the first kStages: wait for the MMA to release a ring slot)
+    if (lane == 0) {
       int it = 0;
       for (int t = blockIdx.x; t < p.tiles_per_row; t += G, ++it) {
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
-        const int s = it % kStages;
+        if (it < kStages) continue;
         const uint32_t ph = (it / kStages) & 1;
-        if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) {
+        if (!mbar_wait(smem_u32(&bars->empty[it % kStages]), ph ^ 1)) {
           atomicOr(&g_device_status, kStatusScanTimeout);
           *abort_flag = 1;
           break;
         }
-        const uint32_t dst = smem_u32(s_tiles + size_t(s) * kTileBytes);
-        const uint32_t bar = smem_u32(&bars->full[s]);
-        if (!p.paged) {
-          mbar_arrive_expect_tx(bar, kTileBytes);
-          tma_load_2d(dst, &tmap, 0, static_cast<int>(int64_t(seq) * p.k_seq_stride +
-                                                       int64_t(t) * kTileKeys), bar);
-        } else {
-          const int32_t* pt = p.page_table + int64_t(r) * p.pt_stride + 2 * t;
-          const bool second = int64_t(2 * t + 1) * DSA_PAGE_TOKENS < len;
-          mbar_arrive_expect_tx(bar, second ? kTileBytes : kTileBytes / 2);
-          tma_load_3d(dst, &tmap, 0, 0, pt[0], bar);
-          if (second) tma_load_3d(dst + kTileBytes / 2, &tmap, 0, 0, pt[1], bar);
-        }
+        issue_tile(it, t);
       }
     }
   } else if (warp == 1) {
@@ -200,6 +221,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     const float neg_inf = __int_as_float(0xff800000);
     int it = 0;
     bool dead = false;
+    uint32_t bin_lo = kHistBins, bin_hi = 0;
     for (int t = blockIdx.x; t < p.tiles_per_row; t += G) {
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
       if (int64_t(t) * kTileKeys >= len || dead) {  // no visible key in this tile
@@ -228,6 +250,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
         continue;
       }
       tc_fence_after();
+      DSA_STAMP_IF(tid == 64 && it <= 4, stamp_cta, 2 + it);  // accumulator of live tile it-1 is ready
       const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + b * kMaxHeads;
       float sum = 0.f;
       uint32_t v[32];
@@ -245,24 +268,43 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
         sum = fmaf(s_w[32 + h], fmaxf(__uint_as_float(v[h]), 0.f), sum);
       const float logit = valid ? sum * scale : neg_inf;
       if (g < p.ctx) out_row[g] = logit;
-      if (want_hist && valid) atomicAdd(&s_hist[ordered_key(logit) >> 20], 1u);
+      if (want_hist) {
+        const uint32_t bin = ordered_key(logit) >> 20;
+        if (valid) atomicAdd(&s_hist[bin], 1u);
+        bin_lo = min(bin_lo, valid ? bin : uint32_t(kHistBins));
+        bin_hi = max(bin_hi, valid ? bin : 0u);
+      }
+    }
+    if (want_hist) {
+      bin_lo = __reduce_min_sync(0xffffffffu, bin_lo);
+      bin_hi = __reduce_max_sync(0xffffffffu, bin_hi);
+      if (lane == 0) {
+        atomicMin(&bars->bin_lo, bin_lo);
+        atomicMax(&bars->bin_hi, bin_hi);
+      }
     }
   }
 
   // ---- teardown
+  DSA_STAMP_IF(tid == 64, stamp_cta, 8);
   tc_fence_before();
   __syncthreads();
+  DSA_STAMP(stamp_cta, 9);
   if (*abort_flag) {
     // let copies that may still be in flight land before the CTA's shared memory is reused
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
   if (want_hist) {
+    // only the bins this CTA touched (a narrow band around the logits' magnitude)
     uint32_t* gh = p.hist + size_t(r) * kHistBins;
-    for (int i = tid; i < kHistBins; i += kThreads) {
+    const int hi = int(bars->bin_hi);
+    for (int i = int(bars->bin_lo) + tid; i <= hi; i += kThreads) {
       const uint32_t c = s_hist[i];
       if (c) atomicAdd(&gh[i], c);
     }
   }
+  DSA_STAMP(stamp_cta, 10);
+  DSA_KTIME_END(0);
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);

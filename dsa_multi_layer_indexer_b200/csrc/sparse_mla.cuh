@@ -109,6 +109,7 @@ sparse_mla_partials_kernel(const Params p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, hg = blockIdx.y, r = blockIdx.z;
+  DSA_KTIME_BEGIN(2);
   const int seq = r / p.rows_per_seq;
   int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.ctx;
   len = len < 0 ? 0 : (len > p.ctx ? p.ctx : len);
@@ -323,6 +324,7 @@ sparse_mla_partials_kernel(const Params p) {
     p.part_l[pbase + g] = l_run[0];
     p.part_l[pbase + g + 8] = l_run[1];
   }
+  DSA_KTIME_END(2);
 }
 
 // out = sum_s acc_s 2^(m_s - m) / sum_s l_s 2^(m_s - m); splits with m = -inf
@@ -332,22 +334,27 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
                           const float* __restrict__ part_l, __nv_bfloat16* __restrict__ out, int H,
                           int nsplit) {
   const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
+  DSA_KTIME_BEGIN(3);
+  const float* pm = part_m + int64_t(r) * nsplit * H + h;
+  const float* pl = part_l + int64_t(r) * nsplit * H + h;
+  const float* pa = part_acc + (int64_t(r) * nsplit * H + h) * kDV + tid * 4;
+  // all loads of a loop are independent, so unrolling keeps many of them in flight
   float m = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_m[(int64_t(r) * nsplit + s) * H + h]);
+#pragma unroll 8
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, pm[int64_t(s) * H]);
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
   float l = 0.f;
   if (m != -INFINITY) {
+#pragma unroll 8
     for (int s = 0; s < nsplit; ++s) {
-      const int64_t pb = (int64_t(r) * nsplit + s) * H + h;
-      const float ms = part_m[pb];
-      if (ms == -INFINITY) continue;
-      const float e = exp2f(ms - m);
-      l += part_l[pb] * e;
-      const float4 a = *reinterpret_cast<const float4*>(part_acc + pb * kDV + tid * 4);
-      o.x += a.x * e;
-      o.y += a.y * e;
-      o.z += a.z * e;
-      o.w += a.w * e;
+      const float ms = pm[int64_t(s) * H];
+      const float e = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+      const float4 a = *reinterpret_cast<const float4*>(pa + int64_t(s) * H * kDV);
+      l = fmaf(pl[int64_t(s) * H], e, l);
+      o.x = fmaf(a.x, e, o.x);
+      o.y = fmaf(a.y, e, o.y);
+      o.z = fmaf(a.z, e, o.z);
+      o.w = fmaf(a.w, e, o.w);
     }
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -357,6 +364,7 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
   pk.x = *reinterpret_cast<uint32_t*>(&lo);
   pk.y = *reinterpret_cast<uint32_t*>(&hi);
   *reinterpret_cast<uint2*>(out + (int64_t(r) * H + h) * kDV + tid * 4) = pk;
+  DSA_KTIME_END(3);
 }
 
 // fp32 attention for any head / latent width: one CTA per (row, head), keys in

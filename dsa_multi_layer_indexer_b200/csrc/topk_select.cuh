@@ -1,65 +1,82 @@
-// Exact top-k of one row of fp32 logits, ties to the lower position, output in
+// Exact top-k of each row of fp32 logits, ties to the lower position, output in
 // ascending position order.
 //
 // Replaces torch.topk on the logit slab (src/lagged_indexer_dsa/
-// attention_core.py:66-91) and the reference's in-kernel select, whose row
-// barrier is an unbounded spin on a global counter
-// (kernels/cuda_fused_sparse_splitk.py:2017-2154). Here one thread-block
-// cluster of 8 CTAs owns a row and its CTAs meet only at hardware cluster
-// barriers:
+// attention_core.py:66-91) and the reference's in-kernel select, which walks a
+// 10-bit coarse histogram to a threshold bin and resolves that bin exactly, but
+// synchronises a row's blocks with an unbounded spin on a global counter
+// (kernels/cuda_fused_sparse_splitk.py:2017-2154). The same two-level idea is
+// laid out here as launches in stream order, so no block ever waits for another:
 //
-//   * every thread keeps ITEMS consecutive logits as order-preserving u32 keys
-//     in registers for the whole kernel (the row is read once);
-//   * an MSB-first radix select narrows the k-th largest key: per round each
-//     CTA histograms the digit of its still-matching keys in shared memory, the
-//     cluster sums the eight histograms through distributed shared memory, and
-//     every CTA derives the same threshold digit. With the 4096-bin histogram
-//     that the scan epilogue already filled, the first round is free;
-//   * the last step ranks ties by position with block scans plus one exchange of
-//     per-CTA counts, so the kept set and its order are deterministic.
+//   1. (optional) topk_hist_kernel: 4096-bin histogram of the top 12 bits of the
+//      order-preserving key. Skipped when the indexer scan already produced it
+//      in its epilogue.
+//   2. topk_classify_kernel, all SMs: every CTA finds the threshold bin T from
+//      the histogram and classifies its 2048 logits with warp ballots: bin > T
+//      goes into a bit mask (certainly kept), bin == T is a candidate whose
+//      (key, position) each warp compacts, in position order, into its own slot
+//      of a candidate buffer.
+//   3. topk_finish_kernel, one CTA per row: gathers the few thousand candidates
+//      into shared memory, runs two 10-bit radix rounds on the low 20 key bits,
+//      ranks exact ties by position, ORs the kept candidates into the mask and
+//      expands the mask into the ascending index list.
+//
+// Scratch per row (caller-owned): mask of n/32 words, per-warp candidate counts
+// and slots, (T, need) header, histogram. Only the histogram must be zero on
+// entry; the finish kernel re-zeroes it.
 #pragma once
-
-#include <cooperative_groups.h>
 
 #include "common.cuh"
 
 namespace dsa {
 namespace topk {
 
-namespace cg = cooperative_groups;
-
-constexpr int kCluster = 8;
-constexpr int kThreads = 1024;
-constexpr int kMaxBins = DSA_TOPK_HIST_BINS;  // 4096: first level when the scan supplies it
-constexpr int kRoundBins = 2048;              // in-kernel rounds use at most 11-bit digits
+constexpr int kThreads = 512;                   // classify / histogram CTAs
+constexpr int kItems = 4;                       // logits per thread in the classify phase
+constexpr int kChunk = kThreads * kItems;       // 2048 logits per CTA
+constexpr int kWarpSpan = 32 * kItems;          // 128 consecutive logits per warp = one candidate slot
+constexpr int kBins = DSA_TOPK_HIST_BINS;       // 4096 = top 12 key bits
+constexpr int kLowBits = 20;
+constexpr int kRoundBins = 1024;                // two 10-bit rounds over the low 20 bits
+constexpr int kFinThreads = 1024;               // finish CTA
+constexpr int kFinWarps = kFinThreads / 32;
+constexpr int kCandCap = 8192;                  // candidates held in shared memory (more: re-read from L2)
+constexpr int64_t kMaxN = 1 << 20;              // the selection mask of one row lives in shared memory
 
 struct Params {
   const float* logits;
   const int32_t* seq_lens;
-  uint32_t* hist;
+  uint32_t* hist;        // [R][4096]: from the scan, or the workspace copy filled by topk_hist_kernel
+  uint32_t* above_mask;  // [R][words]
+  uint32_t* slot_cnt;    // [R][slots]        candidates in each warp slot
+  uint2* slot_cand;      // [R][slots][128]   (key, position), position order
+  uint32_t* header;      // [R][4]            T, need
   const int32_t* index_map;
   int32_t* out_idx;
   float* out_val;
   int64_t n;
   int64_t slab_stride;
+  int words;             // mask words per row, rounded up to whole chunks
+  int slots;             // warp slots per row = words / 4
   int topk;
   int32_t pad;
   int32_t index_offset;
 };
 
-struct Shared {
-  uint32_t tot[kMaxBins];
-  uint32_t hist[2][kRoundBins];
-  uint32_t warp_tot[32];
-  uint32_t sel_bin;
-  uint32_t k_next;
-  uint32_t block_total;
-  uint32_t cta_tot;  // published to the cluster: above | ties << 16
-};
+// Workspace layout in 32-bit words: [R][words] mask | [R][slots] counts |
+// [R][4] header | [R][4096] histogram | [R][slots][128][2] candidates.
+__host__ __device__ inline int64_t mask_words(int64_t n) {
+  const int64_t chunks = (n + kChunk - 1) / kChunk;
+  return chunks * (kChunk / 32);
+}
+__host__ __device__ inline int64_t workspace_words(int64_t R, int64_t n) {
+  const int64_t words = mask_words(n), slots = words / 4;
+  return R * (words + slots + 4 + kBins + slots * kWarpSpan * 2) + 32;
+}
 
-// Exclusive prefix of v over the 1024 threads of the block; *total (optional)
-// receives the block sum. Two barriers; safe to call back to back.
-__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, Shared& sh, uint32_t* total) {
+// Exclusive prefix of v over the block's threads (NW warps); *total = block sum.
+template <int NW>
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* warp_tot, uint32_t* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t inc = v;
 #pragma unroll
@@ -67,196 +84,324 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, Shared& sh,
     const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
     if (lane >= o) inc += up;
   }
-  __syncthreads();  // previous users of warp_tot are done
-  if (lane == 31) sh.warp_tot[warp] = inc;
+  __syncthreads();  // earlier readers of warp_tot are done
+  if (lane == 31) warp_tot[warp] = inc;
   __syncthreads();
-  uint32_t wsum = sh.warp_tot[lane];
+  const uint32_t wsum = lane < NW ? warp_tot[lane] : 0u;
   uint32_t winc = wsum;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
+  for (int o = 1; o < NW; o <<= 1) {
     const uint32_t up = __shfl_up_sync(0xffffffffu, winc, o);
     if (lane >= o) winc += up;
   }
   const uint32_t before = __shfl_sync(0xffffffffu, winc - wsum, warp);
-  if (total) *total = __shfl_sync(0xffffffffu, winc, 31);
+  if (total) *total = __shfl_sync(0xffffffffu, winc, NW - 1);
   return before + inc - v;
 }
 
-// Walks sh.tot[0..nb) from the highest bin down and finds the bin holding the
-// k-th largest element; leaves the bin in sh.sel_bin and the rank inside that
-// bin in sh.k_next. nb is 1024, 2048 or 4096. Ends with a barrier.
-__device__ __forceinline__ void find_threshold_bin(Shared& sh, int nb, uint32_t k) {
-  const int per = nb >> 10;
-  const int first = nb - 1 - int(threadIdx.x) * per;  // this thread's highest bin
+// Given this thread's PER bin counts c[] (thread t owns the PER bins just below
+// nb - PER t, highest first), finds the bin holding the k-th largest element.
+// res[0] = bin, res[1] = rank inside the bin. Ends with a barrier.
+template <int NW, int PER>
+__device__ __forceinline__ void find_threshold_bin(const uint32_t (&c)[PER], int nb, uint32_t k,
+                                                   uint32_t* warp_tot, uint32_t* res) {
+  const int first = nb - 1 - int(threadIdx.x) * PER;
   uint32_t s = 0;
-  for (int i = 0; i < per; ++i) s += sh.tot[first - i];
-  uint32_t running = block_exclusive_scan(s, sh, nullptr);
-  for (int i = 0; i < per; ++i) {
-    const uint32_t c = sh.tot[first - i];
-    if (running < k && k <= running + c) {
-      sh.sel_bin = uint32_t(first - i);
-      sh.k_next = k - running;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) s += c[i];
+  uint32_t running = block_exclusive_scan<NW>(s, warp_tot, nullptr);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    if (running < k && k <= running + c[i]) {
+      res[0] = uint32_t(first - i);
+      res[1] = k - running;
     }
-    running += c;
+    running += c[i];
   }
   __syncthreads();
 }
 
-template <int ITEMS>
-__global__ void __launch_bounds__(kThreads, 1)
-topk_select_kernel(const Params p) {
-  __shared__ Shared sh;
-  cg::cluster_group cluster = cg::this_cluster();
-  const unsigned crank = cluster.block_rank();
-  const int tid = threadIdx.x;
+// 4096-bin histogram of one row chunk (only needed when the scan did not build it).
+__global__ void __launch_bounds__(kThreads)
+topk_hist_kernel(const Params p) {
+  __shared__ uint32_t s_hist[kBins];
+  __shared__ uint32_t s_lo, s_hi;
+  const int tid = threadIdx.x, r = blockIdx.y;
+  for (int i = tid; i < kBins; i += kThreads) s_hist[i] = 0;
+  if (tid == 0) {
+    s_lo = kBins;
+    s_hi = 0;
+  }
+  __syncthreads();
+  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
+  len = len < 0 ? 0 : (len > p.n ? p.n : len);
+  const float* row = p.logits + int64_t(r) * p.slab_stride;
+  uint32_t lo = kBins, hi = 0;
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const int64_t i = int64_t(blockIdx.x) * kChunk + j * kThreads + tid;
+    if (i < len) {
+      const uint32_t bin = ordered_key(row[i]) >> kLowBits;
+      atomicAdd(&s_hist[bin], 1u);
+      lo = min(lo, bin);
+      hi = max(hi, bin);
+    }
+  }
+  lo = __reduce_min_sync(0xffffffffu, lo);
+  hi = __reduce_max_sync(0xffffffffu, hi);
+  if ((tid & 31) == 0) {
+    atomicMin(&s_lo, lo);
+    atomicMax(&s_hi, hi);
+  }
+  __syncthreads();
+  uint32_t* gh = p.hist + size_t(r) * kBins;
+  const int top = int(s_hi);
+  for (int i = int(s_lo) + tid; i <= top; i += kThreads) {
+    const uint32_t c = s_hist[i];
+    if (c) atomicAdd(&gh[i], c);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+topk_classify_kernel(const Params p) {
+  __shared__ uint32_t s_warp_tot[kThreads / 32];
+  __shared__ uint32_t s_res[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = blockIdx.y;
+  DSA_KTIME_BEGIN(1);
   const float* row = p.logits + int64_t(r) * p.slab_stride;
   int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len = len < 0 ? 0 : (len > p.n ? p.n : len);
-  const int64_t base = (int64_t(crank) * kThreads + tid) * ITEMS;
-
-  uint32_t key[ITEMS];
-  if (ITEMS % 4 == 0 && base + ITEMS <= len && ((p.slab_stride & 3) == 0)) {
-#pragma unroll
-    for (int j = 0; j < ITEMS; j += 4) {
-      const float4 v = *reinterpret_cast<const float4*>(row + base + j);
-      key[j] = ordered_key(v.x);
-      key[j + 1] = ordered_key(v.y);
-      key[j + 2] = ordered_key(v.z);
-      key[j + 3] = ordered_key(v.w);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < ITEMS; ++j) key[j] = (base + j < len) ? ordered_key(row[base + j]) : 0u;
-  }
-  const int n_valid = len - base >= ITEMS ? ITEMS : (len > base ? int(len - base) : 0);
-
   const bool take_all = len <= p.topk;
-  uint32_t prefix = 0, mask = 0, k_rem = uint32_t(p.topk);
-  bool hist_pending_reset = false;
 
+  // issue the loads of this CTA's 2048 logits, then find the threshold bin
+  const int64_t span0 = int64_t(blockIdx.x) * kChunk + warp * kWarpSpan;
+  float v[kItems];
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const int64_t i = span0 + j * 32 + lane;
+    v[j] = i < len ? row[i] : 0.f;
+  }
+  uint32_t T = 0;
   if (!take_all) {
-    int shift = 32;
-    int round = 0;
-    if (p.hist != nullptr) {
-      // first level from the histogram the scan filled: top 12 key bits
-      const uint32_t* gh = p.hist + size_t(r) * kMaxBins;
-      for (int i = tid; i < kMaxBins; i += kThreads) sh.tot[i] = gh[i];
-      __syncthreads();
-      find_threshold_bin(sh, kMaxBins, k_rem);
-      shift = 20;
-      prefix = sh.sel_bin << shift;
-      mask = 0xFFFu << shift;
-      k_rem = sh.k_next;
-      hist_pending_reset = true;
+    constexpr int PER = kBins / kThreads;  // 8 bins per thread, two 16-byte loads
+    const uint4* gh4 = reinterpret_cast<const uint4*>(p.hist + size_t(r) * kBins + (kBins - PER * (tid + 1)));
+    const uint4 lo = __ldcg(gh4), hi = __ldcg(gh4 + 1);
+    const uint32_t c[PER] = {hi.w, hi.z, hi.y, hi.x, lo.w, lo.z, lo.y, lo.x};  // highest bin first
+    find_threshold_bin<kThreads / 32, PER>(c, kBins, uint32_t(p.topk), s_warp_tot, s_res);
+    T = s_res[0];
+    if (blockIdx.x == 0 && tid == 0) {
+      p.header[r * 4 + 0] = T;
+      p.header[r * 4 + 1] = s_res[1];  // how many of bin T's elements are kept (>= 1)
     }
-    while (shift > 0) {
-      const int bits = shift > 21 ? 11 : (shift > 10 ? shift - 10 : shift);
-      const int nb = 1 << bits;
-      shift -= bits;
-      uint32_t* hb = sh.hist[round & 1];
-      for (int i = tid; i < nb; i += kThreads) hb[i] = 0;
-      __syncthreads();
-#pragma unroll
-      for (int j = 0; j < ITEMS; ++j)
-        if (j < n_valid && (key[j] & mask) == prefix) atomicAdd(&hb[(key[j] >> shift) & (nb - 1)], 1u);
-      cluster.sync();
-      if (hist_pending_reset) {
-        // every CTA of the row has read the scan's histogram: re-arm it for the next launch
-        uint32_t* gh = p.hist + size_t(r) * kMaxBins;
-        for (int i = crank * kThreads + tid; i < kMaxBins; i += kCluster * kThreads) gh[i] = 0;
-        hist_pending_reset = false;
-      }
-      for (int i = tid; i < nb; i += kThreads) {
-        uint32_t t = 0;
-#pragma unroll
-        for (unsigned c = 0; c < kCluster; ++c) t += cluster.map_shared_rank(hb, c)[i];
-        sh.tot[i] = t;
-      }
-      __syncthreads();
-      find_threshold_bin(sh, nb, k_rem);
-      prefix |= sh.sel_bin << shift;
-      mask |= uint32_t(nb - 1) << shift;
-      k_rem = sh.k_next;
-      ++round;
-    }
-  } else if (p.hist != nullptr) {
-    uint32_t* gh = p.hist + size_t(r) * kMaxBins;
-    for (int i = crank * kThreads + tid; i < kMaxBins; i += kCluster * kThreads) gh[i] = 0;
   }
+  // classify with ballots: mask word for bin > T, compacted (key, position) for bin == T
+  const int64_t slot = span0 / kWarpSpan;
+  uint2* cand = p.slot_cand + (int64_t(r) * p.slots + slot) * kWarpSpan;
+  uint32_t* above_mask = p.above_mask + size_t(r) * p.words;
+  uint32_t cnt = 0;
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const int64_t i = span0 + j * 32 + lane;
+    const uint32_t key = ordered_key(v[j]);
+    const uint32_t bin = key >> kLowBits;
+    const bool valid = i < len;
+    const bool is_cand = valid && !take_all && bin == T;
+    const uint32_t a = __ballot_sync(0xffffffffu, valid && (take_all || bin > T));
+    const uint32_t c = __ballot_sync(0xffffffffu, is_cand);
+    if (is_cand) cand[cnt + __popc(c & ((1u << lane) - 1u))] = make_uint2(key, uint32_t(i));
+    cnt += __popc(c);
+    if (lane == 0) above_mask[(span0 >> 5) + j] = a;
+  }
+  if (lane == 0) p.slot_cnt[int64_t(r) * p.slots + slot] = cnt;
+  DSA_KTIME_END(1);
+}
 
-  // ---- rank ties by position and emit
-  uint32_t cnt_above = 0, cnt_tie = 0;
-  if (take_all) {
-    cnt_above = uint32_t(n_valid);
-    k_rem = 0;
-  } else {
-#pragma unroll
-    for (int j = 0; j < ITEMS; ++j) {
-      if (j < n_valid) {
-        cnt_above += key[j] > prefix;
-        cnt_tie += key[j] == prefix;
-      }
-    }
-  }
-  uint32_t block_total = 0;
-  const uint32_t excl = block_exclusive_scan(cnt_above | (cnt_tie << 16), sh, &block_total);
-  if (tid == 0) sh.cta_tot = block_total;
-  cluster.sync();
-  // CTAs of lower rank hold lower positions: their kept entries come first
-  uint32_t ties_before = 0, sel_before = 0;
-#pragma unroll
-  for (unsigned c = 0; c < kCluster; ++c) {
-    const uint32_t t = *cluster.map_shared_rank(&sh.cta_tot, c);
-    if (c < crank) {
-      const uint32_t a_c = t & 0xFFFFu, t_c = t >> 16;
-      const uint32_t kept = k_rem > ties_before ? min(k_rem - ties_before, t_c) : 0u;
-      sel_before += a_c + kept;
-      ties_before += t_c;
-    }
-  }
-  const uint32_t my_tie_base = ties_before + (excl >> 16);
-  const uint32_t my_kept = k_rem > my_tie_base ? min(k_rem - my_tie_base, cnt_tie) : 0u;
-  uint32_t pos = sel_before + block_exclusive_scan(cnt_above + my_kept, sh, nullptr);
+struct FinShared {
+  uint32_t cand_key[kCandCap];
+  uint32_t cand_pos[kCandCap];   // reused as the output position list during emission
+  uint32_t hist[kRoundBins];
+  uint32_t warp_tot[kFinWarps];
+  uint32_t res[2];
+  uint32_t sel_mask[1];          // really p.words entries
+};
+inline size_t fin_smem_bytes(int words) { return sizeof(FinShared) + size_t(words) * 4; }
 
+__global__ void __launch_bounds__(kFinThreads, 1)
+topk_finish_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t topk_smem[];
+  FinShared& sh = *reinterpret_cast<FinShared*>(topk_smem);
+  const int tid = threadIdx.x;
+  const int r = blockIdx.x;
+  DSA_KTIME_BEGIN(4);
+  DSA_STAMP(r, 0);
+  const float* row = p.logits + int64_t(r) * p.slab_stride;
+  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
+  len = len < 0 ? 0 : (len > p.n ? p.n : len);
+  const bool take_all = len <= p.topk;
+  const int words = p.words, slots = p.slots;
+  const uint32_t* above_mask = p.above_mask + size_t(r) * words;
+  const uint32_t* slot_cnt = p.slot_cnt + size_t(r) * slots;
+  const uint2* slot_cand = p.slot_cand + size_t(r) * slots * kWarpSpan;
   int32_t* out_idx = p.out_idx + int64_t(r) * p.topk;
   float* out_val = p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
   const int32_t* imap = p.index_map ? p.index_map + int64_t(r) * p.n : nullptr;
-  uint32_t tie_rank = my_tie_base;
+  const uint32_t T = take_all ? 0u : __ldcg(p.header + r * 4 + 0);
+  const uint32_t need = take_all ? 0u : __ldcg(p.header + r * 4 + 1);
+
+  // ---- masks into shared memory; candidate counts of this thread's slots (contiguous = position order)
+  for (int w = tid; w < words; w += kFinThreads) sh.sel_mask[w] = __ldcg(above_mask + w);
+  const int sper = (slots + kFinThreads - 1) / kFinThreads;
+  const int s0 = min(tid * sper, slots), s1 = min(s0 + sper, slots);
+  uint32_t c_cnt = 0;
+  if (!take_all)
+    for (int s = s0; s < s1; ++s) c_cnt += __ldcg(slot_cnt + s);
+  uint32_t C = 0;
+  const uint32_t c_off = block_exclusive_scan<kFinWarps>(c_cnt, sh.warp_tot, &C);
+  // the histogram has served every classify CTA: clear it for the next scan
+  {
+    uint4* gh4 = reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins);
+    for (int i = tid; i < kBins / 4; i += kFinThreads) gh4[i] = make_uint4(0, 0, 0, 0);
+  }
+  DSA_STAMP(r, 1);
+
+  uint32_t kstar = 0xFFFFFFFFu;
+  if (!take_all && C > 0) {
+    const bool listed = C <= uint32_t(kCandCap);
+    if (listed) {
+      uint32_t at = c_off;
+      for (int s = s0; s < s1; ++s) {
+        const uint32_t cn = __ldcg(slot_cnt + s);
+        const uint2* src = slot_cand + size_t(s) * kWarpSpan;
+        for (uint32_t e = 0; e < cn; e += 4) {  // batches of independent loads
+          uint2 t[4];
 #pragma unroll
-  for (int j = 0; j < ITEMS; ++j) {
-    if (j < n_valid) {
-      bool keep;
-      if (take_all) {
-        keep = true;
-      } else if (key[j] > prefix) {
-        keep = true;
-      } else if (key[j] == prefix) {
-        keep = tie_rank < k_rem;
-        ++tie_rank;
+          for (int u = 0; u < 4; ++u)
+            if (e + u < cn) t[u] = __ldcg(src + e + u);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (e + u < cn) {
+              sh.cand_key[at] = t[u].x;
+              sh.cand_pos[at] = t[u].y;
+              ++at;
+            }
+        }
+      }
+    }
+    __syncthreads();
+    DSA_STAMP(r, 2);
+    // two 10-bit radix rounds on the low 20 bits of the candidates' keys
+    uint32_t prefix = T << kLowBits, pmask = 0xFFFu << kLowBits, k_rem = need;
+    for (int shift = 10; shift >= 0; shift -= 10) {
+      sh.hist[tid] = 0;  // kRoundBins == kFinThreads
+      __syncthreads();
+      if (listed) {
+        for (uint32_t i = tid; i < C; i += kFinThreads) {
+          const uint32_t k = sh.cand_key[i];
+          if ((k & pmask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
+        }
       } else {
-        keep = false;
+        for (int s = s0; s < s1; ++s) {
+          const uint32_t cn = __ldcg(slot_cnt + s);
+          for (uint32_t e = 0; e < cn; ++e) {
+            const uint32_t k = __ldcg(slot_cand + size_t(s) * kWarpSpan + e).x;
+            if ((k & pmask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
+          }
+        }
       }
-      if (keep && pos < uint32_t(p.topk)) {
-        const uint32_t kk = key[j];
-        const uint32_t bits = (kk & 0x80000000u) ? (kk ^ 0x80000000u) : ~kk;
-        const bool is_neg_inf = bits == 0xff800000u;
-        const int64_t at = base + j;
-        int32_t id = imap ? imap[at] : int32_t(at) + p.index_offset;
-        out_idx[pos] = is_neg_inf ? p.pad : id;
-        if (out_val) out_val[pos] = __uint_as_float(bits);
-        ++pos;
+      __syncthreads();
+      const uint32_t c1[1] = {sh.hist[kRoundBins - 1 - tid]};
+      find_threshold_bin<kFinWarps, 1>(c1, kRoundBins, k_rem, sh.warp_tot, sh.res);
+      prefix |= sh.res[0] << shift;
+      pmask |= uint32_t(kRoundBins - 1) << shift;
+      k_rem = sh.res[1];
+    }
+    kstar = prefix;                    // the k-th largest key of the row
+    const uint32_t ties_kept = k_rem;  // elements equal to it that are kept, lowest positions first
+    DSA_STAMP(r, 3);
+    if (listed) {
+      const uint32_t lper = (C + kFinThreads - 1) / kFinThreads;  // contiguous list slice per thread
+      const uint32_t l0 = min(uint32_t(tid) * lper, C), l1 = min(l0 + lper, C);
+      uint32_t ties = 0;
+      for (uint32_t i = l0; i < l1; ++i) ties += sh.cand_key[i] == kstar;
+      uint32_t tie_rank = block_exclusive_scan<kFinWarps>(ties, sh.warp_tot, nullptr);
+      for (uint32_t i = l0; i < l1; ++i) {
+        const uint32_t k = sh.cand_key[i];
+        bool keep = k > kstar;
+        if (k == kstar) keep = tie_rank++ < ties_kept;
+        if (keep) atomicOr(&sh.sel_mask[sh.cand_pos[i] >> 5], 1u << (sh.cand_pos[i] & 31));
+      }
+    } else {
+      uint32_t ties = 0;
+      for (int s = s0; s < s1; ++s) {
+        const uint32_t cn = __ldcg(slot_cnt + s);
+        for (uint32_t e = 0; e < cn; ++e) ties += __ldcg(slot_cand + size_t(s) * kWarpSpan + e).x == kstar;
+      }
+      uint32_t tie_rank = block_exclusive_scan<kFinWarps>(ties, sh.warp_tot, nullptr);
+      for (int s = s0; s < s1; ++s) {
+        const uint32_t cn = __ldcg(slot_cnt + s);
+        for (uint32_t e = 0; e < cn; ++e) {
+          const uint2 kp = __ldcg(slot_cand + size_t(s) * kWarpSpan + e);
+          bool keep = kp.x > kstar;
+          if (kp.x == kstar) keep = tie_rank++ < ties_kept;
+          if (keep) atomicOr(&sh.sel_mask[kp.y >> 5], 1u << (kp.y & 31));
+        }
       }
     }
   }
-  if (take_all && crank == 0) {
-    const float neg_inf = __int_as_float(0xff800000);
-    for (int64_t i = len + tid; i < p.topk; i += kThreads) {
-      out_idx[i] = p.pad;
-      if (out_val) out_val[i] = neg_inf;
+  __syncthreads();
+  DSA_STAMP(r, 4);
+
+  // ---- expand the selection mask into ascending positions
+  const int per = (words + kFinThreads - 1) / kFinThreads;  // contiguous mask words per thread
+  const int w0 = min(tid * per, words), w1 = min(w0 + per, words);
+  uint32_t s_cnt = 0;
+  for (int w = w0; w < w1; ++w) s_cnt += __popc(sh.sel_mask[w]);
+  uint32_t total = 0;
+  uint32_t pos_out = block_exclusive_scan<kFinWarps>(s_cnt, sh.warp_tot, &total);
+  // a selected -inf can only appear when the row has fewer than topk finite logits
+  const bool check_inf = take_all || kstar <= 0x007FFFFFu;
+  const bool simple = !imap && !out_val && !check_inf;
+  const bool staged = p.topk <= kCandCap;
+  const float neg_inf = __int_as_float(0xff800000);
+  for (int w = w0; w < w1; ++w) {
+    uint32_t bits = sh.sel_mask[w];
+    while (bits) {
+      const int b = __ffs(bits) - 1;
+      bits &= bits - 1;
+      const uint32_t pos = uint32_t(w) * 32 + b;
+      if (pos_out < uint32_t(p.topk)) {
+        if (simple) {
+          out_idx[pos_out] = int32_t(pos) + p.index_offset;
+        } else if (staged) {
+          sh.cand_pos[pos_out] = pos;
+        } else {
+          const float val = __ldcg(row + pos);
+          const int32_t id = imap ? imap[pos] : int32_t(pos) + p.index_offset;
+          out_idx[pos_out] = (val == neg_inf) ? p.pad : id;
+          if (out_val) out_val[pos_out] = val;
+        }
+      }
+      ++pos_out;
     }
   }
-  cluster.sync();  // nobody leaves while a peer may still read its shared memory
+  if (!simple && staged) {
+    __syncthreads();
+    const uint32_t cnt = min(total, uint32_t(p.topk));
+    for (uint32_t i = tid; i < cnt; i += kFinThreads) {  // independent loads
+      const uint32_t pos = sh.cand_pos[i];
+      const float val = __ldcg(row + pos);
+      const int32_t id = imap ? imap[pos] : int32_t(pos) + p.index_offset;
+      out_idx[i] = (val == neg_inf) ? p.pad : id;
+      if (out_val) out_val[i] = val;
+    }
+  }
+  for (uint32_t i = total + tid; i < uint32_t(p.topk); i += kFinThreads) {
+    out_idx[i] = p.pad;
+    if (out_val) out_val[i] = neg_inf;
+  }
+  DSA_STAMP(r, 5);
+  DSA_KTIME_END(4);
 }
 
 }  // namespace topk

@@ -61,6 +61,7 @@ class HotPathState:
         # zero once; the select kernel re-zeroes it after every use
         self.hist = torch.zeros(rows, ops.HIST_BINS, dtype=torch.int32, device=dev) if use_hist else None
         self.indices = torch.full((rows, topk), -1, dtype=torch.int32, device=dev)
+        self.topk_ws = ops.topk_workspace(rows, capacity, dev)
         self.nsplit = nsplit or ops.default_nsplit(rows, heads, topk)
         self.scratch = ops.MlaScratch(rows, heads, self.nsplit, dev)
         self.out = torch.empty(rows, heads, ops.VALUE_DIM, dtype=torch.bfloat16, device=dev)
@@ -71,7 +72,8 @@ class HotPathState:
         logits = ops.indexer_scan_fp8(self.index_q, self.index_w, cache.index_k, cache.k_scale,
                                       self.seq_lens, ctx=self.capacity, out=self.logits,
                                       hist=self.hist, impl=impl)
-        ops.topk_select(logits, self.topk, self.seq_lens, hist=self.hist, out_idx=self.indices)
+        ops.topk_select(logits, self.topk, self.seq_lens, hist=self.hist, out_idx=self.indices,
+                        workspace=self.topk_ws)
         return self.indices
 
     def run_attention(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float) -> torch.Tensor:

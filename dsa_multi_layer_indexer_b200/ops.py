@@ -181,6 +181,14 @@ def indexer_scan_f32(
 
 
 # --------------------------------------------------------------------------- a3
+def topk_workspace(rows: int, n: int, device) -> torch.Tensor:
+    """Zeroed scratch for ``topk_select`` on ``rows`` rows of ``n`` logits. It is
+    left re-armed by every call, so one allocation serves a whole decode loop;
+    calls that share it must not overlap on the device."""
+    nbytes = int(_lib.lib().dsa_topk_workspace_bytes(rows, n))
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
 def topk_select(
     logits: torch.Tensor,
     topk: int,
@@ -193,6 +201,7 @@ def topk_select(
     out_idx: Optional[torch.Tensor] = None,
     out_val: Optional[torch.Tensor] = None,
     return_values: bool = False,
+    workspace: Optional[torch.Tensor] = None,
 ):
     """Exact top-k per row of ``logits[R, n]`` (a view of a wider slab is fine):
     int32 positions in ascending order, ties to the lower position, padded with
@@ -212,9 +221,14 @@ def topk_select(
         out_val = torch.empty(R, topk, dtype=torch.float32, device=logits.device)
     if hist is not None:
         _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+    if workspace is None:
+        # a fresh zeroed scratch per call is always safe; steady-state callers pass their own
+        workspace = topk_workspace(R, n, logits.device)
+    _cuda_contig(workspace, "workspace", (torch.uint8,))
     _lib.check(_lib.lib().dsa_topk_select(
         _ptr(logits), _ptr(seq_lens), _ptr(hist), _ptr(index_map), _ptr(out_idx), _ptr(out_val),
-        R, n, slab_stride, int(topk), int(pad_value), int(index_offset), _stream()))
+        _ptr(workspace), workspace.numel(), R, n, slab_stride, int(topk), int(pad_value),
+        int(index_offset), _stream()))
     if return_values or out_val is not None:
         return out_idx, out_val
     return out_idx
@@ -253,6 +267,7 @@ def sparse_mla_decode(
     scratch: Optional[MlaScratch] = None,
     out: Optional[torch.Tensor] = None,
     dense_keys: Optional[int] = None,
+    stage: str = "both",
 ) -> torch.Tensor:
     """Sparse MLA decode: q ``[R, H, 576]`` bf16, kv ``[n_seq, cap, 576]`` bf16 or
     ``[n_seq, cap, 656]`` uint8 (fp8-packed rows), indices ``[R, topk]`` int32 or
@@ -287,10 +302,20 @@ def sparse_mla_decode(
     if out is None:
         out = torch.empty(R, H, VALUE_DIM, dtype=torch.bfloat16, device=q.device)
     _cuda_contig(out, "out", (torch.bfloat16,))
-    _lib.check(_lib.lib().dsa_sparse_mla_decode(
-        _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),
-        _ptr(scratch.l), _ptr(out), R, rows_per_seq, H, topk, nsplit, float(sm_scale), cap, kv_fp8,
-        _stream()))
+    if stage == "both":
+        _lib.check(_lib.lib().dsa_sparse_mla_decode(
+            _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),
+            _ptr(scratch.l), _ptr(out), R, rows_per_seq, H, topk, nsplit, float(sm_scale), cap, kv_fp8,
+            _stream()))
+    elif stage == "partials":  # the two halves separately, as the reference schedules them
+        _lib.check(_lib.lib().dsa_sparse_mla_partials(
+            _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),
+            _ptr(scratch.l), R, rows_per_seq, H, topk, nsplit, float(sm_scale), cap, kv_fp8, _stream()))
+    elif stage == "combine":
+        _lib.check(_lib.lib().dsa_sparse_mla_combine(
+            _ptr(scratch.acc), _ptr(scratch.m), _ptr(scratch.l), _ptr(out), R, H, nsplit, _stream()))
+    else:
+        raise ValueError(f"unknown stage {stage!r}")
     return out
 
 

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 1
+#define DSA_ABI_VERSION 2
 
 enum dsa_status {
   DSA_OK = 0,
@@ -61,6 +61,12 @@ const char* dsa_status_string(int status);
  * their bounded waits ran out. Synchronises the device. Returns DSA_OK or
  * DSA_ERR_DEVICE_TIMEOUT; *detail (optional) receives the raw word. */
 int dsa_check_device_status(uint32_t* detail);
+
+/* Tracing builds only (compiled with -DDSA_STAMPS): copies the per-CTA phase
+ * stamps (SM cycle counters, 16 slots per CTA, first 1024 CTAs) to host_out and
+ * clears them; returns the number of words or DSA_ERR_UNSUPPORTED. Counterpart
+ * of hide_debug_read (kernels/cuda_fused_sparse_splitk.py:2329-2349). */
+int dsa_debug_read_stamps(uint64_t* host_out, int max_words);
 
 /* ---- (a1) lightning-indexer scan ------------------------------------------
  * logits[r, s] = (sum_h w[r,h] * relu(q[r,h,:] . k[s,:])) * k_scale[s],
@@ -114,15 +120,21 @@ int dsa_indexer_scan_f32(const float* index_q, const float* index_w, const float
  * (kernels/cuda_fused_sparse_splitk.py:2017-2154).
  *
  *   hist       NULL, or the histogram dsa_indexer_scan_fp8 filled for these
- *              rows (skips the first radix pass; re-zeroed on exit)
+ *              rows (saves the histogram launch; re-zeroed on exit)
  *   index_map  NULL, or [R, n] int32: the value written for position p is
  *              index_map[r, p] (used to merge per-GPU candidate lists)
  *   out_idx    [R, topk] int32        out_val  NULL or [R, topk] fp32
+ *   workspace  caller-owned scratch of at least dsa_topk_workspace_bytes(R, n)
+ *              bytes, zero before its first use; every call leaves it re-armed
+ *              (the reference's self-resetting SelScratch, :2150-2153). Calls
+ *              that share a workspace must not overlap on the device.
  *   index_offset is added to positions when index_map is NULL.
- * Limit: n <= 262144 per row.
+ * Limit: n <= 1048576 per row.
  */
+int64_t dsa_topk_workspace_bytes(int R, int64_t n);
 int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist,
                     const int32_t* index_map, int32_t* out_idx, float* out_val,
+                    void* workspace, int64_t workspace_bytes,
                     int R, int64_t n, int64_t slab_stride, int topk,
                     int32_t pad_value, int32_t index_offset, void* stream);
 

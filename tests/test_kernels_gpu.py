@@ -142,7 +142,7 @@ def check_topk(ops, logits, topk, lens=None, pad=-1):
 
 
 @pytest.mark.parametrize("n,topk", [(100, 16), (2048, 2048), (4096, 2048), (5000, 64), (32768, 2048),
-                                    (40000, 2048), (131072, 2048), (200000, 2048), (262144, 2048)])
+                                    (40000, 2048), (131072, 2048), (200000, 2048), (262144, 2048), (1 << 20, 4096)])
 def test_topk_random(ops, n, topk):
     torch.manual_seed(n)
     check_topk(ops, torch.randn(2, n), topk)
@@ -308,4 +308,4 @@ def test_bad_arguments_raise(ops):
         ops.sparse_mla_decode(torch.zeros(1, 8, 576, dtype=torch.bfloat16, device="cuda"),
                               torch.zeros(10, 576, dtype=torch.bfloat16, device="cuda"), None, 1.0)
     with pytest.raises(DsaError):
-        ops.topk_select(torch.zeros(1, 300000, device="cuda"), 2048)
+        ops.topk_select(torch.zeros(1, (1 << 20) + 1, device="cuda"), 2048)
