@@ -19,7 +19,16 @@ from .config import (
     named_config,
 )
 
+from .dsa_layer import DSALayer, LayerDecodeCache, RopeCaches
+from .model import DecodeState, DSAModel, ForwardTrace
+
 __all__ = [
+    "DSALayer",
+    "RopeCaches",
+    "LayerDecodeCache",
+    "DSAModel",
+    "ForwardTrace",
+    "DecodeState",
     "GLM5_1_CONFIG",
     "GLM5_CONFIG",
     "SMALL_CONFIG",

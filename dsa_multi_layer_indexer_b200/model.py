@@ -1,0 +1,288 @@
+"""A stack of DSA blocks under the three schedules, full-sequence and decode.
+
+``DSAModel.forward`` keeps the reference's signature and control flow
+(src/lagged_indexer_dsa/model.py:73-144): BASELINE attends the layer's own
+selection; the lagged modes attend the previous layer's, with layer 0 cold
+started, and a layer runs an indexer only if a later layer consumes it.
+
+The decode half has no counterpart in the reference's pure-PyTorch model; it is
+the GPU realisation of what the serving overlay does to SGLang
+(sglang_overlay/mli-sglang-v0.5.16.patch:2942-2997 fork, :1820-1832 and
+:3858-3870 join, :4516-4532 drain, :1785-1802 pre-created stream): in the lagged
+modes layer l's indexer (quantise -> FP8 scan -> top-k) is launched on a second
+CUDA stream and joined just before layer l+1's attention, so it overlaps layer
+l's attention, output projection and MLP; the whole step is capturable in one
+CUDA graph. ``retention`` keeps indexers on a subset of layers ("F") and lets
+the others ("S") reuse the carried selection (overlay :33-51, :4027-4049).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import List, Optional, Sequence
+
+import torch
+from torch import nn
+
+from .config import AttentionType, ColdStartPolicy, DSAConfig, ScheduleMode
+from .dsa_layer import DSALayer, LayerDecodeCache, RMSNorm, RopeCaches
+from .rope import build_rope_cache
+
+
+@dataclasses.dataclass
+class ForwardTrace:
+    """Per-layer record of a forward pass (reference model.py:23-33)."""
+
+    final_hidden: torch.Tensor
+    indices_used: List[Optional[torch.Tensor]]
+    indices_produced: List[Optional[torch.Tensor]]
+
+
+def lagged_producers(types: Sequence[AttentionType]) -> List[bool]:
+    """Layer L runs an indexer under the lag iff layer L+1 is a DSA layer
+    (reference model.py:61-71)."""
+    n = len(types)
+    return [(i + 1 < n and types[i + 1] is AttentionType.DSA) for i in range(n)]
+
+
+def parse_retention(pattern: Optional[str], n_layers: int) -> List[bool]:
+    """'F'/'S' per layer -> runs-an-indexer flags. None keeps every indexer; an
+    integer string 'k' keeps every k-th. Layer 0 always runs one (overlay :37-44)."""
+    if pattern is None:
+        return [True] * n_layers
+    if pattern.isdigit():
+        k = max(1, int(pattern))
+        flags = [(i % k) == 0 for i in range(n_layers)]
+    else:
+        if len(pattern) != n_layers or set(pattern) - {"F", "S"}:
+            raise ValueError(f"retention pattern must be {n_layers} characters of F/S, got {pattern!r}")
+        flags = [ch == "F" for ch in pattern]
+    flags[0] = True
+    return flags
+
+
+@dataclasses.dataclass
+class DecodeState:
+    """Mutable decode state: per-layer caches, device-side lengths, rotary tables,
+    the side stream of the lagged schedule and the selection being carried."""
+
+    caches: List[LayerDecodeCache]
+    rope: RopeCaches
+    positions: torch.Tensor      # int64 [B]: position of the NEXT token
+    seq_lens: torch.Tensor       # int32 [B]: keys visible to the next token (= positions + 1 once appended)
+    batch_index: torch.Tensor    # int64 [B]
+    side_stream: torch.cuda.Stream
+    runs_indexer: List[bool]
+    fp8: bool
+    carried: Optional[torch.Tensor] = None
+
+
+class DSAModel(nn.Module):
+    def __init__(self, config: DSAConfig) -> None:
+        super().__init__()
+        self.config = config
+        self.layers = nn.ModuleList([DSALayer(config) for _ in range(config.num_hidden_layers)])
+        self.final_norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+
+    # ------------------------------------------------------------------ shared helpers
+    def _build_rope(self, seq_len: int, device, dtype) -> RopeCaches:
+        c = self.config
+        mc, ms = build_rope_cache(seq_len, c.qk_rope_head_dim, c.rope_theta, device, dtype)
+        ic, is_ = build_rope_cache(seq_len, c.index_head_dim, c.rope_theta, device, dtype,
+                                   interleave=c.indexer_rope_interleave)
+        return RopeCaches(mc, ms, ic, is_)
+
+    def _cold_start_indices(self, layer: DSALayer, x_norm, rope, cold_start: ColdStartPolicy):
+        if cold_start is ColdStartPolicy.DENSE:
+            return None
+        if cold_start is ColdStartPolicy.EAGER:
+            return layer.indexer_indices(x_norm, rope)
+        raise ValueError(f"unknown cold start policy: {cold_start}")
+
+    def _lagged_indexer_layers(self, types) -> List[bool]:
+        return lagged_producers(types)
+
+    # ------------------------------------------------------------------ reference API
+    def forward(self, inputs_embeds: torch.Tensor, mode: ScheduleMode,
+                cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, record: bool = False):
+        if inputs_embeds.dim() != 3:
+            raise ValueError(f"inputs_embeds must be [B,S,H], got {tuple(inputs_embeds.shape)}")
+        if not inputs_embeds.is_cuda:
+            raise RuntimeError("this implementation runs on a CUDA device only (there is no CPU path)")
+        rope = self._build_rope(inputs_embeds.shape[1], inputs_embeds.device, inputs_embeds.dtype)
+        types = self.config.resolved_attention_types
+        produces = lagged_producers(types)
+        x = inputs_embeds
+        prev: Optional[torch.Tensor] = None
+        used, produced = [], []
+        for li, layer in enumerate(self.layers):
+            x_norm = layer.attn_norm(x)
+            is_dsa = types[li] is AttentionType.DSA
+            if mode is ScheduleMode.BASELINE:
+                made = layer.indexer_indices(x_norm, rope) if is_dsa else None
+                attend = made
+                attn = layer.attention_output(x_norm, rope, attend)
+            elif mode in (ScheduleMode.LAGGED_REFERENCE, ScheduleMode.LAGGED_FUSED):
+                if not is_dsa:
+                    attend = None
+                elif li == 0:
+                    attend = self._cold_start_indices(layer, x_norm, rope, cold_start)
+                else:
+                    attend = prev
+                if mode is ScheduleMode.LAGGED_REFERENCE:
+                    attn = layer.attention_output(x_norm, rope, attend)
+                    made = layer.indexer_indices(x_norm, rope) if produces[li] else None
+                else:
+                    attn, made = layer.fused_attention_and_indices(x_norm, rope, attend,
+                                                                   produce_indexer=produces[li])
+            else:
+                raise ValueError(f"unknown schedule mode: {mode}")
+            h = x + attn
+            x = h + layer.mlp(layer.ffn_norm(h))
+            prev = made
+            if record:
+                used.append(attend)
+                produced.append(made)
+        x = self.final_norm(x)
+        return ForwardTrace(x, used, produced) if record else x
+
+    # ------------------------------------------------------------------ decode
+    def init_decode(self, batch: int, capacity: int, fp8: Optional[bool] = None,
+                    retention: Optional[str] = None) -> DecodeState:
+        """Allocates the caches for ``batch`` sequences of up to ``capacity`` tokens.
+        fp8=True stores e4m3 index keys + bf16 latent rows (needs the production
+        geometry); fp8=False stores fp32 caches of any width."""
+        p = next(self.parameters())
+        if not p.is_cuda:
+            raise RuntimeError("decode needs the model on a CUDA device")
+        if fp8 is None:
+            fp8 = self.config.is_production_geometry and p.dtype == torch.bfloat16
+        if fp8 and not self.config.is_production_geometry:
+            raise ValueError("fp8 caches need the production geometry (576-wide latent, 128-wide index keys)")
+        dev = p.device
+        caches = [layer.new_cache(batch, capacity, dev, fp8) for layer in self.layers]
+        return DecodeState(
+            caches=caches, rope=self._build_rope(capacity, dev, p.dtype),
+            positions=torch.zeros(batch, dtype=torch.int64, device=dev),
+            seq_lens=torch.zeros(batch, dtype=torch.int32, device=dev),
+            batch_index=torch.arange(batch, device=dev), side_stream=torch.cuda.Stream(device=dev),
+            runs_indexer=parse_retention(retention, len(self.layers)), fp8=fp8)
+
+    @torch.no_grad()
+    def prefill(self, state: DecodeState, inputs_embeds: torch.Tensor,
+                mode: ScheduleMode = ScheduleMode.BASELINE,
+                cold_start: ColdStartPolicy = ColdStartPolicy.DENSE) -> torch.Tensor:
+        """Runs the full-sequence forward over a prompt [B,S,hidden], filling every
+        layer's caches on the way; returns the final hidden states."""
+        b, s, _ = inputs_embeds.shape
+        rope = RopeCaches(state.rope.mla_cos[:s], state.rope.mla_sin[:s], state.rope.idx_cos[:s], state.rope.idx_sin[:s])
+        types = self.config.resolved_attention_types
+        produces = lagged_producers(types)
+        x, prev = inputs_embeds, None
+        for li, layer in enumerate(self.layers):
+            x_norm = layer.attn_norm(x)
+            layer.fill_cache(state.caches[li], x_norm, rope)
+            is_dsa = types[li] is AttentionType.DSA
+            if mode is ScheduleMode.BASELINE:
+                made = layer.indexer_indices(x_norm, rope) if is_dsa else None
+                attend = made
+            else:
+                attend = (None if not is_dsa else
+                          self._cold_start_indices(layer, x_norm, rope, cold_start) if li == 0 else prev)
+                made = layer.indexer_indices(x_norm, rope) if produces[li] else None
+            h = x + layer.attention_output(x_norm, rope, attend)
+            x = h + layer.mlp(layer.ffn_norm(h))
+            prev = made
+        state.positions.fill_(s)
+        state.seq_lens.fill_(s)
+        return self.final_norm(x)
+
+    @torch.no_grad()
+    def decode_step(self, state: DecodeState, x: torch.Tensor, mode: ScheduleMode,
+                    cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True,
+                    record: Optional[dict] = None) -> torch.Tensor:
+        """One new token per sequence: x [B,hidden] -> final hidden [B,hidden].
+
+        Appends the token's keys to every layer's caches at ``state.positions``
+        and advances the device-side lengths. In the lagged modes with
+        ``overlap`` the indexers run on ``state.side_stream``. Capturable in a
+        CUDA graph (no host sync, lengths stay on the device)."""
+        types = self.config.resolved_attention_types
+        n = len(self.layers)
+        lagged = mode is not ScheduleMode.BASELINE
+        main = torch.cuda.current_stream()
+        side = state.side_stream if (lagged and overlap) else None
+        state.seq_lens.add_(1)  # the new token sees itself
+        carried: Optional[torch.Tensor] = None
+        pending = False  # an indexer is in flight on the side stream
+        used, produced = [], []
+        for li, layer in enumerate(self.layers):
+            cache = state.caches[li]
+            is_dsa = types[li] is AttentionType.DSA
+            x_norm = layer.attn_norm(x)
+            q, iq, w = layer.decode_project(x_norm, state.rope, state.positions, cache, state.batch_index)
+            made = None
+            if not lagged:
+                if is_dsa and state.runs_indexer[li]:
+                    carried = made = layer.decode_indexer(iq, w, cache, state.seq_lens)
+                attend = carried if is_dsa else None
+            else:
+                if pending:  # join layer li-1's indexer before its selection is read
+                    main.wait_stream(side)
+                    pending = False
+                if not is_dsa:
+                    attend = None
+                elif li == 0:
+                    attend = (None if cold_start is ColdStartPolicy.DENSE
+                              else layer.decode_indexer(iq, w, cache, state.seq_lens))
+                else:
+                    attend = carried
+                # a layer produces iff it keeps its indexer and the next layer attends sparsely
+                if state.runs_indexer[li] and li + 1 < n and types[li + 1] is AttentionType.DSA:
+                    if side is not None:
+                        side.wait_stream(main)  # fork: needs iq, w and the appended key
+                        with torch.cuda.stream(side):
+                            made = layer.decode_indexer(iq, w, cache, state.seq_lens)
+                        pending = True
+                    else:
+                        made = layer.decode_indexer(iq, w, cache, state.seq_lens)
+            attn = layer.decode_attention(q, cache, attend, state.seq_lens)
+            h = x + attn
+            x = h + layer.mlp(layer.ffn_norm(h))
+            if lagged and made is not None:
+                carried = made  # becomes visible to layer li+1 after the join
+            if record is not None:
+                used.append(attend)
+                produced.append(made)
+        if pending:  # never leave a fork dangling (a captured graph must end joined)
+            main.wait_stream(side)
+        state.positions.add_(1)
+        state.carried = carried
+        if record is not None:
+            record["used"], record["produced"] = used, produced
+        return self.final_norm(x)
+
+    def capture_decode(self, state: DecodeState, mode: ScheduleMode,
+                       cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True):
+        """Captures one decode step in a CUDA graph. Returns (graph, x_in, x_out):
+        copy the token's hidden state into x_in, replay, read x_out. The caches
+        and lengths advance on every replay exactly as in eager mode. Warm-up
+        steps run first on a scratch copy of the lengths so the state is left
+        where it was."""
+        p = next(self.parameters())
+        b = state.positions.shape[0]
+        x_in = torch.zeros(b, self.config.hidden_size, dtype=p.dtype, device=p.device)
+        saved = (state.positions.clone(), state.seq_lens.clone())
+        warm = torch.cuda.Stream(device=p.device)
+        warm.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(warm):
+            for _ in range(2):
+                self.decode_step(state, x_in, mode, cold_start, overlap)
+                state.positions.copy_(saved[0])
+                state.seq_lens.copy_(saved[1])
+        torch.cuda.current_stream().wait_stream(warm)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            x_out = self.decode_step(state, x_in, mode, cold_start, overlap)
+        # the capture itself does not execute: lengths are still at their saved values
+        return graph, x_in, x_out

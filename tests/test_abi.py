@@ -1,0 +1,78 @@
+"""The C-ABI library loads without a GPU and exports exactly what
+include/dsa_b200.h declares; the ctypes table mirrors the header."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "dsa_b200.h").read_text()
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER, flags=re.S)
+    out = {}
+    for m in re.finditer(r"\b(?:int|int64_t|const char\*)\s+(dsa_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+        args = m.group(2).strip()
+        n = 0 if args in ("", "void") else len([a for a in args.split(",") if a.strip()])
+        out[m.group(1)] = n
+    return out
+
+
+def test_header_declares_the_hot_path():
+    names = declared_functions()
+    for need in ("dsa_indexer_scan_fp8", "dsa_indexer_scan_fp8_paged", "dsa_topk_select", "dsa_sparse_mla_decode",
+                 "dsa_sparse_mla_partials", "dsa_sparse_mla_combine", "dsa_quantize_e4m3_rowwise",
+                 "dsa_check_device_status"):
+        assert need in names
+
+
+def test_library_exports_every_declared_symbol():
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    handle = _lib.lib()  # raises if the library is missing or a symbol is absent
+    names = declared_functions()
+    assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
+    for name, n_args in names.items():
+        assert hasattr(handle, name)
+        assert len(_lib.SIGNATURES[name][1]) == n_args, name
+    assert handle.dsa_abi_version() == _lib.ABI_VERSION
+    m = re.search(r"#define DSA_ABI_VERSION (\d+)", HEADER)
+    assert int(m.group(1)) == _lib.ABI_VERSION
+    assert handle.dsa_status_string(0) == b"ok"
+    assert int(handle.dsa_topk_workspace_bytes(1, 131072)) > 0
+
+
+def test_bad_arguments_are_rejected_before_any_launch():
+    """Argument checks run on the host: they fail the same way without a GPU."""
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    h = _lib.lib()
+    rc = h.dsa_sparse_mla_combine(None, None, None, None, 1, 16, 1, None)
+    assert rc == -1 and b"null pointer" in h.dsa_last_error()
+    buf = (ctypes.c_char * 64)()
+    addr = ctypes.addressof(buf)
+    addr += (-addr) % 16
+    rc = h.dsa_indexer_scan_fp8(addr, addr, addr, addr, None, addr, None, 1, 1, 24, 128, 1, 128, 128, 128, 0, None)
+    assert rc == -1 and b"multiple of 16" in h.dsa_last_error()
+    rc = h.dsa_topk_select(addr, None, None, None, addr, None, addr, 16, 1, 1 << 21, 1 << 21, 2048, -1, 0, None)
+    assert rc == -2
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    import importlib
+
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    monkeypatch.setenv("DSA_B200_LIB", str(tmp_path / "nope.so"))
+    fresh = importlib.reload(_lib)
+    try:
+        with pytest.raises(ImportError):
+            fresh.lib()
+    finally:
+        monkeypatch.delenv("DSA_B200_LIB")
+        importlib.reload(_lib)

@@ -1,0 +1,200 @@
+"""GPU tests of the layer / model API: the reference's schedules on the SMALL
+preset against reference-generated goldens, the decode path against the
+full-sequence forward, the two-stream lagged schedule and its CUDA graph."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def D():
+    import dsa_multi_layer_indexer_b200 as pkg
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    _lib.lib()
+    yield pkg
+    _lib.check_device_status()
+
+
+def small_model(D, seed):
+    torch.manual_seed(seed)  # same construction order as the reference -> same weights
+    return D.DSAModel(D.SMALL_CONFIG).eval().cuda()
+
+
+def sets_equal(a: torch.Tensor, b: np.ndarray, sentinel: int) -> float:
+    """Fraction of (batch, query) rows whose selected sets agree exactly."""
+    a = a.cpu().numpy().reshape(-1, a.shape[-1])
+    b = b.reshape(-1, b.shape[-1])
+    same = 0
+    for ra, rb in zip(a, b):
+        sa = set(int(v) for v in ra if 0 <= v < sentinel)
+        sb = set(int(v) for v in rb if 0 <= v < sentinel)
+        same += sa == sb
+    return same / len(a)
+
+
+@pytest.mark.parametrize("seed", [0, 7])
+def test_forward_matches_reference_goldens(D, seed):
+    g = load_golden("model_small.npz")
+    model = small_model(D, seed)
+    x = torch.from_numpy(g[f"x_{seed}"]).cuda()
+    S = x.shape[1]
+    for mode in D.ScheduleMode:
+        for cold in D.ColdStartPolicy:
+            with torch.no_grad():
+                tr = model(x, mode, cold_start=cold, record=True)
+            key = f"{seed}_{mode.value}_{cold.value}"
+            ref_h = torch.from_numpy(g[f"hidden_{key}"])
+            assert rel_err(tr.final_hidden.cpu(), ref_h) < 2e-4, key
+            for li, (u, p) in enumerate(zip(tr.indices_used, tr.indices_produced)):
+                assert (u is None) == (f"used_{key}_{li}" not in g.files)
+                assert (p is None) == (f"produced_{key}_{li}" not in g.files)
+                if p is not None:
+                    assert p.dtype == torch.int64 and p.shape == (1, S, D.SMALL_CONFIG.index_topk)
+                    assert sets_equal(p, g[f"produced_{key}_{li}"], S) == 1.0, (key, li)
+                if u is not None:
+                    assert sets_equal(u, g[f"used_{key}_{li}"], S) == 1.0, (key, li)
+
+
+def test_lagged_fused_equals_lagged_reference_and_is_causal(D):
+    model = small_model(D, 1)
+    torch.manual_seed(5)
+    x = torch.randn(2, 24, D.SMALL_CONFIG.hidden_size, device="cuda")
+    with torch.no_grad():
+        a = model(x, D.ScheduleMode.LAGGED_FUSED, record=True)
+        b = model(x, D.ScheduleMode.LAGGED_REFERENCE, record=True)
+        base = model(x, D.ScheduleMode.BASELINE)
+    assert torch.equal(a.final_hidden, b.final_hidden)
+    for ia, ib in zip(a.indices_produced, b.indices_produced):
+        assert (ia is None) == (ib is None)
+        if ia is not None:
+            assert torch.equal(ia, ib)
+    assert not torch.allclose(a.final_hidden, base)  # the lag changes the result
+    S = x.shape[1]
+    pos = torch.arange(S, device="cuda").view(1, S, 1)
+    for u in a.indices_used:
+        if u is not None:
+            real = u < S
+            assert bool((u[real] <= pos.expand_as(u)[real]).all())
+    assert a.indices_produced[-1] is None  # the last layer has no consumer
+
+
+@pytest.mark.parametrize("mode_name", ["BASELINE", "LAGGED_FUSED"])
+def test_decode_equals_full_forward(D, mode_name):
+    mode = D.ScheduleMode[mode_name]
+    cold = D.ColdStartPolicy.EAGER
+    model = small_model(D, 3)
+    torch.manual_seed(8)
+    B, S, S0 = 2, 30, 20
+    x = torch.randn(B, S, D.SMALL_CONFIG.hidden_size, device="cuda")
+    with torch.no_grad():
+        full = model(x, mode, cold_start=cold)
+    st = model.init_decode(B, 64, fp8=False)
+    pre = model.prefill(st, x[:, :S0], mode, cold)
+    assert rel_err(pre.cpu(), full[:, :S0].cpu()) < 1e-4
+    for t in range(S0, S):
+        out = model.decode_step(st, x[:, t], mode, cold)
+        assert rel_err(out.cpu(), full[:, t].cpu()) < 2e-4, t
+    assert st.positions.tolist() == [S, S]
+
+
+def test_lagged_overlap_graph_and_eager_agree(D):
+    model = small_model(D, 4)
+    torch.manual_seed(9)
+    B, S0, steps = 3, 16, 6
+    hid = D.SMALL_CONFIG.hidden_size
+    prompt = torch.randn(B, S0, hid, device="cuda")
+    toks = torch.randn(steps, B, hid, device="cuda")
+    mode, cold = D.ScheduleMode.LAGGED_FUSED, D.ColdStartPolicy.DENSE
+
+    def run(overlap, graph):
+        st = model.init_decode(B, 40, fp8=False)
+        model.prefill(st, prompt, mode, cold)
+        outs = []
+        if graph:
+            g, x_in, x_out = model.capture_decode(st, mode, cold, overlap=overlap)
+            for t in range(steps):
+                x_in.copy_(toks[t])
+                g.replay()
+                outs.append(x_out.clone())
+        else:
+            for t in range(steps):
+                outs.append(model.decode_step(st, toks[t], mode, cold, overlap=overlap).clone())
+        torch.cuda.synchronize()
+        assert st.positions.tolist() == [S0 + steps] * B
+        return torch.stack(outs)
+
+    serial = run(False, False)
+    two_streams = run(True, False)
+    graphed = run(True, True)
+    assert torch.equal(serial, two_streams)
+    assert torch.equal(serial, graphed)
+
+
+def test_retention_pattern_carries_the_selection(D):
+    model = small_model(D, 5)
+    torch.manual_seed(10)
+    B, S0 = 1, 24
+    hid = D.SMALL_CONFIG.hidden_size
+    st = model.init_decode(B, 32, fp8=False, retention="FSSFSS")
+    model.prefill(st, torch.randn(B, S0, hid, device="cuda"))
+    rec = {}
+    model.decode_step(st, torch.randn(B, hid, device="cuda"), D.ScheduleMode.BASELINE, record=rec)
+    used, made = rec["used"], rec["produced"]
+    assert [m is not None for m in made] == [True, False, False, True, False, False]
+    assert torch.equal(used[1], made[0]) and torch.equal(used[2], made[0])
+    assert torch.equal(used[4], made[3]) and torch.equal(used[5], made[3])
+    rec = {}
+    model.decode_step(st, torch.randn(B, hid, device="cuda"), D.ScheduleMode.LAGGED_FUSED,
+                      D.ColdStartPolicy.EAGER, record=rec)
+    used, made = rec["used"], rec["produced"]
+    assert [m is not None for m in made] == [True, False, False, True, False, False]
+    assert torch.equal(used[1], made[0]) and torch.equal(used[3], made[0])  # the F layer attends the carry
+    assert torch.equal(used[4], made[3])
+
+
+def production_config(D, layers=3):
+    return D.DSAConfig(hidden_size=256, num_hidden_layers=layers, num_attention_heads=16, q_lora_rank=96,
+                       kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32,
+                       index_n_heads=16, index_head_dim=128, index_topk=64, intermediate_size=512,
+                       first_k_dense_replace=0)
+
+
+def test_production_geometry_fp8_bf16_path(D):
+    """FP8 scan + bf16 split-K attention behind the same model API: decode
+    follows the fp32 kernels within bf16 tolerance and picks nearly the same keys."""
+    cfg = production_config(D)
+    torch.manual_seed(11)
+    ref_model = D.DSAModel(cfg).eval().cuda()
+    fast = D.DSAModel(cfg).eval().cuda().to(torch.bfloat16)
+    fast.load_state_dict({k: v.to(torch.bfloat16) for k, v in ref_model.state_dict().items()})
+    ref_model.load_state_dict({k: v.float() for k, v in fast.state_dict().items()})  # same rounded weights
+    B, S0, steps = 2, 200, 4
+    torch.manual_seed(12)
+    prompt = torch.randn(B, S0, cfg.hidden_size, device="cuda")
+    toks = torch.randn(steps, B, cfg.hidden_size, device="cuda")
+    mode, cold = D.ScheduleMode.LAGGED_FUSED, D.ColdStartPolicy.EAGER
+    s_ref = ref_model.init_decode(B, 256, fp8=False)
+    s_fast = fast.init_decode(B, 256)
+    assert s_fast.fp8
+    ref_model.prefill(s_ref, prompt, mode, cold)
+    fast.prefill(s_fast, prompt.to(torch.bfloat16), mode, cold)
+    overlaps = []
+    for t in range(steps):
+        ra, rb = {}, {}
+        a = ref_model.decode_step(s_ref, toks[t], mode, cold, record=ra)
+        b = fast.decode_step(s_fast, toks[t].to(torch.bfloat16), mode, cold, record=rb)
+        assert rel_err(b.float().cpu(), a.cpu()) < 6e-2
+        for ia, ib in zip(ra["produced"], rb["produced"]):
+            if ia is not None:
+                for r in range(B):
+                    sa, sb = set(ia[r].tolist()) - {-1}, set(ib[r].tolist()) - {-1}
+                    overlaps.append(len(sa & sb) / max(1, len(sa | sb)))
+    assert min(overlaps) > 0.6 and sum(overlaps) / len(overlaps) > 0.8
