@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "indexer_scan.cuh"
@@ -102,6 +103,27 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   return DSA_OK;
 }
 static bool g_opt_scan[64], g_opt_mla[64], g_opt_scan_f32[64], g_opt_topk[64];
+
+// Launch with programmatic dependent launch allowed: the kernel may be scheduled
+// while its predecessor in the stream is still draining; it calls
+// griddepcontrol.wait (pdl_wait) before it touches anything the predecessor
+// wrote. DSA_PDL=0 turns the attribute off.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t st, Args&&... args) {
+  static const bool enabled = env_int("DSA_PDL", 1) != 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 }  // namespace dsa
 
@@ -259,9 +281,8 @@ int dsa_indexer_scan_fp8(const uint8_t* index_q, const float* index_w, const uin
   if (rc) return rc;
   rc = opt_in_smem(scan::indexer_scan_tc_kernel, scan::kSmemBytes, g_opt_scan);
   if (rc) return rc;
-  scan::indexer_scan_tc_kernel<<<dim3(scan_grid_x(R, p.tiles_per_row), R), scan::kThreads,
-                                 scan::kSmemBytes, st>>>(tmap, p);
-  DSA_CUDA(cudaGetLastError());
+  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel, dim3(scan_grid_x(R, p.tiles_per_row), R),
+                      dim3(scan::kThreads), scan::kSmemBytes, st, tmap, p));
   return DSA_OK;
 }
 
@@ -306,9 +327,8 @@ int dsa_indexer_scan_fp8_paged(const uint8_t* index_q, const float* index_w,
   if (rc) return rc;
   rc = opt_in_smem(scan::indexer_scan_tc_kernel, scan::kSmemBytes, g_opt_scan);
   if (rc) return rc;
-  scan::indexer_scan_tc_kernel<<<dim3(scan_grid_x(R, p.tiles_per_row), R), scan::kThreads,
-                                 scan::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmap, p);
-  DSA_CUDA(cudaGetLastError());
+  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel, dim3(scan_grid_x(R, p.tiles_per_row), R),
+                      dim3(scan::kThreads), scan::kSmemBytes, static_cast<cudaStream_t>(stream), tmap, p));
   return DSA_OK;
 }
 
@@ -382,16 +402,14 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 grid(unsigned(words / (topk::kChunk / 32)), R);
   if (!hist) {
-    topk::topk_hist_kernel<<<grid, topk::kThreads, 0, st>>>(p);
-    DSA_CUDA(cudaGetLastError());
+    DSA_CUDA(launch_pdl(topk::topk_hist_kernel, grid, dim3(topk::kThreads), 0, st, p));
   }
-  topk::topk_classify_kernel<<<grid, topk::kThreads, 0, st>>>(p);
-  DSA_CUDA(cudaGetLastError());
+  DSA_CUDA(launch_pdl(topk::topk_classify_kernel, grid, dim3(topk::kThreads), 0, st, p));
   int rc = opt_in_smem(topk::topk_finish_kernel,
                        topk::fin_smem_bytes(int(topk::mask_words(topk::kMaxN))), g_opt_topk);
   if (rc) return rc;
-  topk::topk_finish_kernel<<<R, topk::kFinThreads, topk::fin_smem_bytes(p.words), st>>>(p);
-  DSA_CUDA(cudaGetLastError());
+  DSA_CUDA(launch_pdl(topk::topk_finish_kernel, dim3(R), dim3(topk::kFinThreads),
+                      topk::fin_smem_bytes(p.words), st, p));
   return DSA_OK;
 }
 
@@ -435,9 +453,8 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
     int rc = opt_in_smem(mla::sparse_mla_partials_kernel, mla::SmemLayout::bytes_fp8, g_opt_mla);
     if (rc) return rc;
   }
-  mla::sparse_mla_partials_kernel<<<dim3(nsplit, H / DSA_HEAD_BLOCK, R), mla::kThreads, smem,
-                                    static_cast<cudaStream_t>(stream)>>>(p);
-  DSA_CUDA(cudaGetLastError());
+  DSA_CUDA(launch_pdl(mla::sparse_mla_partials_kernel, dim3(nsplit, H / DSA_HEAD_BLOCK, R),
+                      dim3(mla::kThreads), smem, static_cast<cudaStream_t>(stream), p));
   return DSA_OK;
 }
 
@@ -446,9 +463,9 @@ int dsa_sparse_mla_combine(const float* part_acc, const float* part_m, const flo
   DSA_REQUIRE(part_acc && part_m && part_l && out, "sparse MLA combine: null pointer");
   DSA_REQUIRE(aligned16(part_acc) && aligned16(out), "sparse MLA combine: misaligned pointer");
   DSA_REQUIRE(R > 0 && R <= 65535 && H > 0 && nsplit > 0, "sparse MLA combine: bad geometry");
-  mla::sparse_mla_combine_kernel<<<dim3(H, R), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      part_acc, part_m, part_l, static_cast<__nv_bfloat16*>(out), H, nsplit);
-  DSA_CUDA(cudaGetLastError());
+  DSA_CUDA(launch_pdl(mla::sparse_mla_combine_kernel, dim3(H, R), dim3(128), 0,
+                      static_cast<cudaStream_t>(stream), part_acc, part_m, part_l,
+                      static_cast<__nv_bfloat16*>(out), H, nsplit));
   return DSA_OK;
 }
 

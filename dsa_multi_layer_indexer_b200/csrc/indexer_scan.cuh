@@ -94,7 +94,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   const int lane = tid & 31;
   const int r = blockIdx.y;
   const int seq = r / p.rows_per_seq;
-  const int len = row_len(p, r);
+  int len = 0;  // read after the dependency wait below
   const int G = gridDim.x;
   const bool want_hist = p.hist != nullptr;
   const int stamp_cta = blockIdx.y * gridDim.x + blockIdx.x;
@@ -118,9 +118,10 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     }
   };
 
-  // ---- set-up. Thread 0 arms the barriers and at once starts the first kStages
-  // tile loads, so the HBM latency of the keys overlaps the rest of the set-up
-  // (tensor memory, swizzled query tile, head weights, histogram clear).
+  // ---- set-up. What needs no input comes first (barriers, tensor memory,
+  // histogram clear) and overlaps the tail of the previous kernel; after the
+  // dependency wait thread 0 at once starts the first kStages tile loads, so the
+  // HBM latency of the keys overlaps the query-tile and weight loads.
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&bars->full[s]), 1);
@@ -134,15 +135,24 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     bars->bin_lo = kHistBins;
     bars->bin_hi = 0;
     mbar_fence_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  if (want_hist)
+    for (int i = tid; i < kHistBins / 4; i += kThreads)
+      reinterpret_cast<uint4*>(s_hist)[i] = make_uint4(0, 0, 0, 0);
+  pdl_wait();  // keys, query, weights and lengths may come from the previous kernel
+  pdl_launch_dependents();
+  len = row_len(p, r);
+  if (tid == 0) {
     int it = 0;
     for (int t = blockIdx.x; t < p.tiles_per_row && it < kStages; t += G, ++it) {
       if (int64_t(t) * kTileKeys >= len) break;
       issue_tile(it, t);
     }
-  }
-  if (warp == 0) {
-    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
-    tmem_relinquish();
   }
   {
     // q[r] is [n_heads][128 B]; shared copy is K-major with the 128-B swizzle
@@ -157,9 +167,6 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     }
     for (int i = tid; i < kMaxHeads; i += kThreads)
       s_w[i] = i < p.n_heads ? p.w[size_t(r) * p.n_heads + i] : 0.f;
-    if (want_hist)
-      for (int i = tid; i < kHistBins / 4; i += kThreads)
-        reinterpret_cast<uint4*>(s_hist)[i] = make_uint4(0, 0, 0, 0);
   }
   fence_proxy_async_smem();
   tc_fence_before();

@@ -111,8 +111,6 @@ sparse_mla_partials_kernel(const Params p) {
   const int split = blockIdx.x, hg = blockIdx.y, r = blockIdx.z;
   DSA_KTIME_BEGIN(2);
   const int seq = r / p.rows_per_seq;
-  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.ctx;
-  len = len < 0 ? 0 : (len > p.ctx ? p.ctx : len);
   const uint32_t bar_q = smem_u32(&s_bar[0]);
   const uint32_t bar_k = smem_u32(&s_bar[1]);
   const int row_bytes = p.kv_fp8 ? kFp8Row : kRowBytes;
@@ -124,6 +122,10 @@ sparse_mla_partials_kernel(const Params p) {
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_wait();  // the selection, the queries and the lengths may come from the previous kernel
+  pdl_launch_dependents();
+  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.ctx;
+  len = len < 0 ? 0 : (len > p.ctx ? p.ctx : len);
 
   // queries of this head block: 16 rows of 1152 B
   if (tid >= kBN && tid < kBN + kHB) {
@@ -335,6 +337,8 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
                           int nsplit) {
   const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
   DSA_KTIME_BEGIN(3);
+  pdl_wait();
+  pdl_launch_dependents();
   const float* pm = part_m + int64_t(r) * nsplit * H + h;
   const float* pl = part_l + int64_t(r) * nsplit * H + h;
   const float* pa = part_acc + (int64_t(r) * nsplit * H + h) * kDV + tid * 4;

@@ -133,6 +133,8 @@ topk_hist_kernel(const Params p) {
     s_hi = 0;
   }
   __syncthreads();
+  pdl_wait();
+  pdl_launch_dependents();
   int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len = len < 0 ? 0 : (len > p.n ? p.n : len);
   const float* row = p.logits + int64_t(r) * p.slab_stride;
@@ -169,6 +171,8 @@ topk_classify_kernel(const Params p) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = blockIdx.y;
   DSA_KTIME_BEGIN(1);
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = p.logits + int64_t(r) * p.slab_stride;
   int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len = len < 0 ? 0 : (len > p.n ? p.n : len);
@@ -235,6 +239,8 @@ topk_finish_kernel(const Params p) {
   const int r = blockIdx.x;
   DSA_KTIME_BEGIN(4);
   DSA_STAMP(r, 0);
+  pdl_wait();
+  pdl_launch_dependents();
   const float* row = p.logits + int64_t(r) * p.slab_stride;
   int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len = len < 0 ? 0 : (len > p.n ? p.n : len);
