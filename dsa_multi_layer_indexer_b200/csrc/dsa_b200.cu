@@ -413,6 +413,56 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
   return DSA_OK;
 }
 
+// ------------------------------------------------------------------ top-k without caller scratch
+}  // extern "C"
+
+// Scratch of dsa_topk_select_static: one fixed array inside the library's device
+// image. Every GPU that loads the library carries these 4 MiB until the process
+// exits. Host code must not hand this symbol to a kernel: on the host the name is
+// only a stand-in, so the device address is looked up once per device below.
+static __device__ __align__(256) unsigned char g_topk_static_scratch[DSA_TOPK_STATIC_SCRATCH_BYTES];
+
+// Device address of the array on the current device (looked up on first use).
+static int topk_static_scratch(void** out) {
+  static void* ptr[64];
+  int dev = 0;
+  DSA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(DSA_ERR_UNSUPPORTED, "topk (static scratch): device ordinal %d", dev);
+  if (ptr[dev] == nullptr) {
+    void* p = nullptr;
+    DSA_CUDA(cudaGetSymbolAddress(&p, g_topk_static_scratch));
+    ptr[dev] = p;
+  }
+  *out = ptr[dev];
+  return DSA_OK;
+}
+
+extern "C" {
+
+int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t* out_idx,
+                           float* out_val, int R, int64_t n, int64_t slab_stride, int topk_k,
+                           int32_t pad_value, int32_t index_offset, void* stream) {
+  DSA_REQUIRE(R > 0 && n > 0, "topk (static scratch): need R > 0 and n > 0");
+  const int64_t need = dsa_topk_workspace_bytes(R, n);
+  if (n > topk::kMaxN || need > int64_t(DSA_TOPK_STATIC_SCRATCH_BYTES))
+    return fail(DSA_ERR_UNSUPPORTED,
+                "topk (static scratch): R=%d rows of n=%lld logits need %lld bytes of scratch, the built-in "
+                "array holds %lld; use dsa_topk_select with caller-owned scratch",
+                R, (long long)n, (long long)need, (long long)DSA_TOPK_STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  int rc = topk_static_scratch(&scratch);
+  if (rc) return rc;
+  // The array still holds whatever the previous call left, possibly laid out for
+  // another (R, n): the histogram of this call's layout has to start at zero.
+  const int64_t words = topk::mask_words(n), slots = words / 4;
+  uint32_t* hist = static_cast<uint32_t*>(scratch) + int64_t(R) * (words + slots + 4);
+  DSA_CUDA(cudaMemsetAsync(hist, 0, size_t(R) * topk::kBins * sizeof(uint32_t),
+                           static_cast<cudaStream_t>(stream)));
+  return dsa_topk_select(logits, seq_lens, nullptr, nullptr, out_idx, out_val, scratch,
+                         DSA_TOPK_STATIC_SCRATCH_BYTES, R, n, slab_stride, topk_k, pad_value,
+                         index_offset, stream);
+}
+
 // ------------------------------------------------------------------ sparse MLA
 int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
                             const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,

@@ -138,6 +138,32 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
                     int R, int64_t n, int64_t slab_stride, int topk,
                     int32_t pad_value, int32_t index_offset, void* stream);
 
+/* ---- top-k for callers that cannot allocate ---------------------------------
+ * This entry point has no counterpart in the reference. It is dsa_topk_select
+ * (no histogram input, no index map) for hosts that have no way to obtain device
+ * memory for scratch: a runtime whose memory pool is closed once serving starts,
+ * a plugin that is handed only its input and output buffers, or code running
+ * where cudaMalloc is forbidden (for example while a stream is being captured).
+ * The scratch is a fixed DSA_TOPK_STATIC_SCRATCH_BYTES array inside the library's
+ * device image, so each GPU that loads the library gives up that much memory
+ * until the process exits; the call itself performs no cudaMalloc / cudaFree
+ * and calls no allocating routine.
+ *   - Limit: dsa_topk_workspace_bytes(R, n) <= DSA_TOPK_STATIC_SCRATCH_BYTES
+ *     (one row of up to ~480k logits, or 4 rows of 114k); larger requests return
+ *     DSA_ERR_UNSUPPORTED with a message naming both sizes.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call before starting any stream
+ *     capture.
+ *   - All calls on a device share the one array and it keeps the previous call's
+ *     contents; the part that must start at zero is cleared on `stream` by every
+ *     call. Two calls that overlap on the GPU (different streams, or graphs
+ *     replayed concurrently) race on it: serialise them.
+ */
+#define DSA_TOPK_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t* out_idx,
+                           float* out_val, int R, int64_t n, int64_t slab_stride, int topk,
+                           int32_t pad_value, int32_t index_offset, void* stream);
+
 /* ---- (a4, a5) split-K sparse MLA decode ------------------------------------
  * out[r,h,:] = softmax_j(sm_scale * q[r,h,:] . kv[idx_j,:]) . kv[idx_j,:512]
  * over the entries of indices[r,:] with 0 <= idx < seq_lens[r]. Replaces the
