@@ -256,7 +256,15 @@ topk_finish_kernel(const Params p) {
   const uint32_t need = take_all ? 0u : __ldcg(p.header + r * 4 + 1);
 
   // ---- masks into shared memory; candidate counts of this thread's slots (contiguous = position order)
-  for (int w = tid; w < words; w += kFinThreads) sh.sel_mask[w] = __ldcg(above_mask + w);
+  for (int w = tid; w < words; w += 4 * kFinThreads) {  // batches of independent loads
+    uint32_t t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (w + u * kFinThreads < words) t[u] = __ldcg(above_mask + w + u * kFinThreads);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (w + u * kFinThreads < words) sh.sel_mask[w + u * kFinThreads] = t[u];
+  }
   const int sper = (slots + kFinThreads - 1) / kFinThreads;
   const int s0 = min(tid * sper, slots), s1 = min(s0 + sper, slots);
   uint32_t c_cnt = 0;

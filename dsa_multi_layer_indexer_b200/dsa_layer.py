@@ -67,6 +67,26 @@ class LayerDecodeCache:
         return self.kv.shape[1]
 
 
+@dataclasses.dataclass
+class IndexerWorkspace:
+    """Persistent buffers of one layer's decode indexer: logits slab, the scan's
+    histogram (zero once, re-armed by the select), top-k scratch and result."""
+
+    logits: torch.Tensor
+    hist: Optional[torch.Tensor]
+    topk_ws: torch.Tensor
+    indices: torch.Tensor
+
+    @staticmethod
+    def create(n_seq: int, capacity: int, topk: int, device, fp8: bool) -> "IndexerWorkspace":
+        slab = (capacity + 3) // 4 * 4
+        return IndexerWorkspace(
+            torch.empty(n_seq, slab, dtype=torch.float32, device=device),
+            torch.zeros(n_seq, ops.HIST_BINS, dtype=torch.int32, device=device) if fp8 else None,
+            ops.topk_workspace(n_seq, capacity, device),
+            torch.full((n_seq, topk), -1, dtype=torch.int32, device=device))
+
+
 def _pad_heads(t: torch.Tensor, multiple: int) -> torch.Tensor:
     """Zero-pads dim 1 (heads) to a multiple; zero queries attend uniformly and
     are dropped by the caller (reference fused_decode.py:38-43)."""
@@ -272,15 +292,26 @@ class DSALayer(nn.Module):
             cache.index_k[batch_index, positions] = ik.float()
         return q_full, iq, w
 
-    def decode_indexer(self, iq, w, cache: LayerDecodeCache, seq_lens, pad_value: int = -1) -> torch.Tensor:
-        """int32 [B, topk] selection over each sequence's first seq_lens keys."""
+    def decode_indexer(self, iq, w, cache: LayerDecodeCache, seq_lens, pad_value: int = -1,
+                       ws: Optional["IndexerWorkspace"] = None) -> torch.Tensor:
+        """int32 [B, topk] selection over each sequence's first seq_lens keys. With
+        a workspace the logits slab, the histogram, the top-k scratch and the
+        result live in persistent buffers (nothing is allocated per step)."""
         topk = self.config.index_topk
         if cache.k_scale is not None:
             iq8, sq = ops.quantize_e4m3_rowwise(iq.float().contiguous())
-            logits = ops.indexer_scan_fp8(iq8, (sq * w.float()).contiguous(), cache.index_k, cache.k_scale, seq_lens)
-        else:
-            logits = ops.indexer_scan_f32(iq.float().contiguous(), w.float().contiguous(), cache.index_k, seq_lens)
-        return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value)
+            wf = (sq * w.float()).contiguous()
+            if ws is None:
+                logits = ops.indexer_scan_fp8(iq8, wf, cache.index_k, cache.k_scale, seq_lens)
+                return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value)
+            logits = ops.indexer_scan_fp8(iq8, wf, cache.index_k, cache.k_scale, seq_lens, out=ws.logits, hist=ws.hist)
+            return ops.topk_select(logits, topk, seq_lens, hist=ws.hist, pad_value=pad_value, out_idx=ws.indices,
+                                   workspace=ws.topk_ws)
+        logits = ops.indexer_scan_f32(iq.float().contiguous(), w.float().contiguous(), cache.index_k, seq_lens,
+                                      out=None if ws is None else ws.logits)
+        if ws is None:
+            return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value)
+        return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value, out_idx=ws.indices, workspace=ws.topk_ws)
 
     def decode_attention(self, q, cache: LayerDecodeCache, indices, seq_lens) -> torch.Tensor:
         """Attention hidden output [B, hidden] of the new tokens; indices None = dense."""

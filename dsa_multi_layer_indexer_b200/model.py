@@ -25,7 +25,7 @@ import torch
 from torch import nn
 
 from .config import AttentionType, ColdStartPolicy, DSAConfig, ScheduleMode
-from .dsa_layer import DSALayer, LayerDecodeCache, RMSNorm, RopeCaches
+from .dsa_layer import DSALayer, IndexerWorkspace, LayerDecodeCache, RMSNorm, RopeCaches
 from .rope import build_rope_cache
 
 
@@ -74,6 +74,7 @@ class DecodeState:
     side_stream: torch.cuda.Stream
     runs_indexer: List[bool]
     fp8: bool
+    workspaces: List[IndexerWorkspace] = dataclasses.field(default_factory=list)
     carried: Optional[torch.Tensor] = None
 
 
@@ -166,7 +167,9 @@ class DSAModel(nn.Module):
             positions=torch.zeros(batch, dtype=torch.int64, device=dev),
             seq_lens=torch.zeros(batch, dtype=torch.int32, device=dev),
             batch_index=torch.arange(batch, device=dev), side_stream=torch.cuda.Stream(device=dev),
-            runs_indexer=parse_retention(retention, len(self.layers)), fp8=fp8)
+            runs_indexer=parse_retention(retention, len(self.layers)), fp8=fp8,
+            workspaces=[IndexerWorkspace.create(batch, capacity, self.config.index_topk, dev, fp8)
+                        for _ in self.layers])
 
     @torch.no_grad()
     def prefill(self, state: DecodeState, inputs_embeds: torch.Tensor,
@@ -224,7 +227,7 @@ class DSAModel(nn.Module):
             made = None
             if not lagged:
                 if is_dsa and state.runs_indexer[li]:
-                    carried = made = layer.decode_indexer(iq, w, cache, state.seq_lens)
+                    carried = made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
                 attend = carried if is_dsa else None
             else:
                 if pending:  # join layer li-1's indexer before its selection is read
@@ -234,7 +237,7 @@ class DSAModel(nn.Module):
                     attend = None
                 elif li == 0:
                     attend = (None if cold_start is ColdStartPolicy.DENSE
-                              else layer.decode_indexer(iq, w, cache, state.seq_lens))
+                              else layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li]))
                 else:
                     attend = carried
                 # a layer produces iff it keeps its indexer and the next layer attends sparsely
@@ -242,10 +245,10 @@ class DSAModel(nn.Module):
                     if side is not None:
                         side.wait_stream(main)  # fork: needs iq, w and the appended key
                         with torch.cuda.stream(side):
-                            made = layer.decode_indexer(iq, w, cache, state.seq_lens)
+                            made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
                         pending = True
                     else:
-                        made = layer.decode_indexer(iq, w, cache, state.seq_lens)
+                        made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
             attn = layer.decode_attention(q, cache, attend, state.seq_lens)
             h = x + attn
             x = h + layer.mlp(layer.ffn_norm(h))
