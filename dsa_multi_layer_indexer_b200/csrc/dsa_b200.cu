@@ -102,7 +102,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_scan[64], g_opt_mla[64], g_opt_scan_f32[64], g_opt_topk[64];
+static bool g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_scan_f32[64], g_opt_topk[64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -216,13 +216,33 @@ static int scan_common_checks(const uint8_t* index_q, const float* index_w, cons
   return DSA_OK;
 }
 
-static int scan_grid_x(int R, int tiles_per_row) {
-  // about two CTAs per SM in total, never more CTAs than tiles in a row
+static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
+  // about ctas_per_sm CTAs per SM in total, never more CTAs than tiles in a row
   int per_row = env_int("DSA_SCAN_CTAS_PER_ROW", 0);
-  if (per_row <= 0) per_row = (2 * sm_count() + R - 1) / R;
+  if (per_row <= 0) per_row = (ctas_per_sm * sm_count() + R - 1) / R;
   if (per_row > tiles_per_row) per_row = tiles_per_row;
   if (per_row < 1) per_row = 1;
   return per_row;
+}
+
+// Two shapes of the same kernel: two CTAs per SM with a 4-slot ring (default), or
+// one CTA per SM with a 10-slot ring (DSA_SCAN_DEEP=1).
+static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p, int R, cudaStream_t st) {
+  static const bool deep = env_int("DSA_SCAN_DEEP", 0) != 0;
+  if (deep) {
+    constexpr size_t smem = scan::smem_bytes<scan::kStagesOnePerSm>();
+    int rc = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesOnePerSm>, smem, g_opt_scan_deep);
+    if (rc) return rc;
+    DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesOnePerSm>,
+                        dim3(scan_grid_x(R, p.tiles_per_row, 1), R), dim3(scan::kThreads), smem, st, tmap, p));
+    return DSA_OK;
+  }
+  constexpr size_t smem = scan::smem_bytes<scan::kStagesTwoPerSm>();
+  int rc = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm>, smem, g_opt_scan);
+  if (rc) return rc;
+  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm>,
+                      dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(scan::kThreads), smem, st, tmap, p));
+  return DSA_OK;
 }
 
 int dsa_indexer_scan_fp8(const uint8_t* index_q, const float* index_w, const uint8_t* index_k,
@@ -279,10 +299,8 @@ int dsa_indexer_scan_fp8(const uint8_t* index_q, const float* index_w, const uin
   rc = encode_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, index_k, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  rc = opt_in_smem(scan::indexer_scan_tc_kernel, scan::kSmemBytes, g_opt_scan);
+  rc = launch_scan_tc(tmap, p, R, st);
   if (rc) return rc;
-  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel, dim3(scan_grid_x(R, p.tiles_per_row), R),
-                      dim3(scan::kThreads), scan::kSmemBytes, st, tmap, p));
   return DSA_OK;
 }
 
@@ -325,10 +343,8 @@ int dsa_indexer_scan_fp8_paged(const uint8_t* index_q, const float* index_w,
   rc = encode_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, index_k_pages, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  rc = opt_in_smem(scan::indexer_scan_tc_kernel, scan::kSmemBytes, g_opt_scan);
+  rc = launch_scan_tc(tmap, p, R, static_cast<cudaStream_t>(stream));
   if (rc) return rc;
-  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel, dim3(scan_grid_x(R, p.tiles_per_row), R),
-                      dim3(scan::kThreads), scan::kSmemBytes, static_cast<cudaStream_t>(stream), tmap, p));
   return DSA_OK;
 }
 

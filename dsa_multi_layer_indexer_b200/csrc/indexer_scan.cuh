@@ -28,7 +28,8 @@ namespace scan {
 constexpr int kTileKeys = 128;
 constexpr int kKeyBytes = DSA_INDEX_DIM;  // 128 e4m3 per key
 constexpr int kTileBytes = kTileKeys * kKeyBytes;
-constexpr int kStages = 4;
+constexpr int kStagesTwoPerSm = 4;   // 92 KB of shared memory: two CTAs per SM
+constexpr int kStagesOnePerSm = 10;  // 190 KB: one CTA per SM with every tile of a 128K row in flight
 constexpr int kMaxHeads = DSA_INDEX_MAX_HEADS;
 constexpr int kThreads = 192;    // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int kTmemCols = 128;   // two 64-column fp32 accumulators
@@ -55,6 +56,7 @@ struct Params {
   int paged;
 };
 
+template <int kStages>
 struct __align__(8) Barriers {
   uint64_t full[kStages];
   uint64_t empty[kStages];
@@ -66,10 +68,12 @@ struct __align__(8) Barriers {
   uint32_t bin_hi;
 };
 
-constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
 constexpr size_t kSmemQ = size_t(kMaxHeads) * kKeyBytes;
-constexpr size_t kSmemBytes =
-    1024 /*alignment slack*/ + kSmemStages + kSmemQ + kHistBins * 4 + kMaxHeads * 4 + sizeof(Barriers);
+template <int kStages>
+constexpr size_t smem_bytes() {
+  return 1024 /*alignment slack*/ + size_t(kStages) * kTileBytes + kSmemQ + kHistBins * 4 + kMaxHeads * 4 +
+         sizeof(Barriers<kStages>);
+}
 
 __device__ __forceinline__ int row_len(const Params& p, int r) {
   int64_t len = p.seq_lens ? static_cast<int64_t>(p.seq_lens[r]) : p.ctx;
@@ -78,8 +82,10 @@ __device__ __forceinline__ int row_len(const Params& p, int r) {
   return static_cast<int>(len);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+template <int kStages>
+__global__ void __launch_bounds__(kThreads, kStages <= kStagesTwoPerSm ? 2 : 1)
 indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
+  constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -87,7 +93,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   uint8_t* s_q = smem + kSmemStages;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_q + kSmemQ);
   float* s_w = reinterpret_cast<float*>(s_hist + kHistBins);
-  Barriers* bars = reinterpret_cast<Barriers*>(s_w + kMaxHeads);
+  Barriers<kStages>* bars = reinterpret_cast<Barriers<kStages>*>(s_w + kMaxHeads);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -100,6 +106,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   const int stamp_cta = blockIdx.y * gridDim.x + blockIdx.x;
   DSA_STAMP(stamp_cta, 0);
   DSA_KTIME_BEGIN(0);
+  if (tid == 0) prefetch_tensor_map(&tmap);
 
   // One tile's TMA load into ring slot (it % kStages); the caller has made sure the slot is free.
   auto issue_tile = [&](int it, int t) {
@@ -136,17 +143,35 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     bars->bin_hi = 0;
     mbar_fence_init();
   }
-  if (warp == 0) {
-    __syncwarp();
-    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
-    tmem_relinquish();
-  }
+  DSA_STAMP(stamp_cta, 11);
   if (want_hist)
     for (int i = tid; i < kHistBins / 4; i += kThreads)
       reinterpret_cast<uint4*>(s_hist)[i] = make_uint4(0, 0, 0, 0);
   pdl_wait();  // keys, query, weights and lengths may come from the previous kernel
   pdl_launch_dependents();
+  DSA_STAMP(stamp_cta, 13);
   len = row_len(p, r);
+  // q[r] is [n_heads][128 B]. Its loads (and the head weights') are issued before
+  // the key tiles' so they are not queued behind 64 KB of TMA traffic per CTA.
+  constexpr int kQChunks = (kMaxHeads * 8 + kThreads - 1) / kThreads;
+  uint4 qv[kQChunks];
+  {
+    const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + size_t(r) * p.n_heads * kKeyBytes);
+#pragma unroll
+    for (int k = 0; k < kQChunks; ++k) {
+      const int i = tid + k * kThreads;
+      qv[k] = make_uint4(0, 0, 0, 0);
+      if (i < kMaxHeads * 8 && (i >> 3) < p.n_heads) qv[k] = qsrc[i];
+    }
+  }
+  const float wv = tid < p.n_heads ? p.w[size_t(r) * p.n_heads + tid] : 0.f;
+  if (warp == 0) {  // tensor-memory allocation overlaps the latency of those loads
+    __syncwarp();
+    tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  DSA_STAMP(stamp_cta, 12);
+  __syncthreads();  // every query load has been issued
   if (tid == 0) {
     int it = 0;
     for (int t = blockIdx.x; t < p.tiles_per_row && it < kStages; t += G, ++it) {
@@ -154,20 +179,19 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
       issue_tile(it, t);
     }
   }
-  {
-    // q[r] is [n_heads][128 B]; shared copy is K-major with the 128-B swizzle
-    // (16-byte chunk c of row h lands in chunk c ^ (h & 7)); rows past
-    // n_heads are zero so they contribute relu(0) * 0.
-    const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + size_t(r) * p.n_heads * kKeyBytes);
-    for (int i = tid; i < kMaxHeads * 8; i += kThreads) {
+  DSA_STAMP(stamp_cta, 15);
+  // shared copy of q: K-major with the 128-B swizzle (16-byte chunk c of row h
+  // lands in chunk c ^ (h & 7)); rows past n_heads are zero -> relu(0) * 0.
+#pragma unroll
+  for (int k = 0; k < kQChunks; ++k) {
+    const int i = tid + k * kThreads;
+    if (i < kMaxHeads * 8) {
       const int h = i >> 3, c = i & 7;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (h < p.n_heads) v = qsrc[h * 8 + c];
-      *reinterpret_cast<uint4*>(s_q + h * kKeyBytes + ((c ^ (h & 7)) << 4)) = v;
+      *reinterpret_cast<uint4*>(s_q + h * kKeyBytes + ((c ^ (h & 7)) << 4)) = qv[k];
     }
-    for (int i = tid; i < kMaxHeads; i += kThreads)
-      s_w[i] = i < p.n_heads ? p.w[size_t(r) * p.n_heads + i] : 0.f;
   }
+  if (tid < kMaxHeads) s_w[tid] = wv;
+  DSA_STAMP(stamp_cta, 14);
   fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();

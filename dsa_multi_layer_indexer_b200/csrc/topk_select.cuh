@@ -314,6 +314,7 @@ topk_finish_kernel(const Params p) {
           const uint32_t k = sh.cand_key[i];
           if ((k & pmask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
         }
+        DSA_STAMP(r, shift == 10 ? 10 : 12);
       } else {
         for (int s = s0; s < s1; ++s) {
           const uint32_t cn = __ldcg(slot_cnt + s);
@@ -326,10 +327,12 @@ topk_finish_kernel(const Params p) {
       __syncthreads();
       const uint32_t c1[1] = {sh.hist[kRoundBins - 1 - tid]};
       find_threshold_bin<kFinWarps, 1>(c1, kRoundBins, k_rem, sh.warp_tot, sh.res);
+      DSA_STAMP(r, shift == 10 ? 11 : 13);
       prefix |= sh.res[0] << shift;
       pmask |= uint32_t(kRoundBins - 1) << shift;
       k_rem = sh.res[1];
     }
+    DSA_STAMP(r, 8 + 0);
     kstar = prefix;                    // the k-th largest key of the row
     const uint32_t ties_kept = k_rem;  // elements equal to it that are kept, lowest positions first
     DSA_STAMP(r, 3);
@@ -339,6 +342,7 @@ topk_finish_kernel(const Params p) {
       uint32_t ties = 0;
       for (uint32_t i = l0; i < l1; ++i) ties += sh.cand_key[i] == kstar;
       uint32_t tie_rank = block_exclusive_scan<kFinWarps>(ties, sh.warp_tot, nullptr);
+      DSA_STAMP(r, 9);
       for (uint32_t i = l0; i < l1; ++i) {
         const uint32_t k = sh.cand_key[i];
         bool keep = k > kstar;
@@ -373,6 +377,7 @@ topk_finish_kernel(const Params p) {
   for (int w = w0; w < w1; ++w) s_cnt += __popc(sh.sel_mask[w]);
   uint32_t total = 0;
   uint32_t pos_out = block_exclusive_scan<kFinWarps>(s_cnt, sh.warp_tot, &total);
+  DSA_STAMP(r, 6);
   // a selected -inf can only appear when the row has fewer than topk finite logits
   const bool check_inf = take_all || kstar <= 0x007FFFFFu;
   const bool simple = !imap && !out_val && !check_inf;
@@ -399,6 +404,7 @@ topk_finish_kernel(const Params p) {
       ++pos_out;
     }
   }
+  DSA_STAMP(r, 7);
   if (!simple && staged) {
     __syncthreads();
     const uint32_t cnt = min(total, uint32_t(p.topk));
