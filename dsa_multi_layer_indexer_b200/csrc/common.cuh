@@ -93,6 +93,19 @@ __device__ unsigned long long g_ktime[32];
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+// Shared-memory reductions in the explicit .shared state space (no return value).
+__device__ __forceinline__ void smem_red_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void smem_red_or(uint32_t* p, uint32_t v) {
+  asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void smem_red_min(uint32_t* p, uint32_t v) {
+  asm volatile("red.shared.min.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void smem_red_max(uint32_t* p, uint32_t v) {
+  asm volatile("red.shared.max.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

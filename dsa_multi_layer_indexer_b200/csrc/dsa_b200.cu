@@ -102,7 +102,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_scan_f32[64], g_opt_topk[64];
+static bool g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -123,6 +123,74 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.attrs = attr;
   cfg.numAttrs = enabled ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// Fused sparse MLA: the splits of one (row, head block) form a thread-block
+// cluster and merge through distributed shared memory. Returns DSA_OK after the
+// launch, or 1 when the fused form is not selected (it is opt-in: DSA_MLA_FUSED=1).
+static int launch_mla_cluster(mla::Params p, void* out, int R, int H, int nsplit, int topk_k,
+                              cudaStream_t st) {
+  static const bool fused = env_int("DSA_MLA_FUSED", 0) != 0;
+  if (!fused) return 1;
+  static int cl16_ok[64];  // 0 unknown, 1 yes, -1 no: a 16-CTA cluster needs an opt-in and room in a GPC
+  int dev = 0;
+  DSA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return 1;
+  const size_t smem = p.kv_fp8 ? mla::ClusterSmem::bytes_fp8 : mla::ClusterSmem::bytes_bf16;
+  int rc = opt_in_smem(mla::sparse_mla_cluster_kernel, mla::ClusterSmem::bytes_fp8, g_opt_mla_cluster);
+  if (rc) return rc;
+  static const int cl_max = env_int("DSA_MLA_CLUSTER_MAX", 16);
+  int cl = 1;
+  while (cl * 2 <= nsplit && cl * 2 <= 16 && cl * 2 <= cl_max) cl *= 2;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[2];
+  auto fill = [&](int c) {
+    cfg.gridDim = dim3(c, H / DSA_HEAD_BLOCK, R);
+    cfg.blockDim = dim3(mla::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = c;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = env_int("DSA_PDL", 1) != 0 ? 2 : 1;
+  };
+  if (cl == 16) {
+    if (cl16_ok[dev] == 0) {
+      cl16_ok[dev] = -1;
+      if (cudaFuncSetAttribute(mla::sparse_mla_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed,
+                               1) == cudaSuccess) {
+        fill(16);
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, mla::sparse_mla_cluster_kernel, &cfg) == cudaSuccess && n >= 1)
+          cl16_ok[dev] = 1;
+      }
+      (void)cudaGetLastError();
+    }
+    if (cl16_ok[dev] != 1) cl = 8;
+  }
+  int kps = (topk_k + cl - 1) / cl;
+  p.keys_per_split = (kps + 15) / 16 * 16;
+  p.nsplit = cl;
+  fill(cl);
+  if (env_int("DSA_VERBOSE", 0)) {
+    for (int c = 1; c <= 16; c *= 2) {
+      fill(c);
+      cfg.numAttrs = 1;
+      int n = -1;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, mla::sparse_mla_cluster_kernel, &cfg);
+      fprintf(stderr, "[dsa] sparse_mla_cluster: cluster size %d, smem %zu: max active clusters %d (%s)\n", c,
+              smem, n, cudaGetErrorString(e));
+    }
+    (void)cudaGetLastError();
+    fill(cl);
+  }
+  DSA_CUDA(cudaLaunchKernelEx(&cfg, mla::sparse_mla_cluster_kernel, p, static_cast<__nv_bfloat16*>(out)));
+  return DSA_OK;
 }
 
 }  // namespace dsa
@@ -480,11 +548,13 @@ int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t
 }
 
 // ------------------------------------------------------------------ sparse MLA
-int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
-                            const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
-                            int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
-                            int64_t kv_seq_stride, int kv_fp8, void* stream) {
-  DSA_REQUIRE(q && kv && part_acc && part_m && part_l, "sparse MLA: null pointer");
+// Argument checks and parameter block shared by the split and the fused launch.
+static int mla_prepare(const void* q, const void* kv, const int32_t* indices, const int32_t* seq_lens,
+                       float* part_acc, float* part_m, float* part_l, int R, int rows_per_seq, int H,
+                       int topk_k, int nsplit, float sm_scale, int64_t kv_seq_stride, int kv_fp8,
+                       bool need_partials, mla::Params* out_p) {
+  DSA_REQUIRE(q && kv, "sparse MLA: null pointer");
+  DSA_REQUIRE(!need_partials || (part_acc && part_m && part_l), "sparse MLA: null split-K scratch");
   DSA_REQUIRE(aligned16(q) && aligned16(kv) && aligned16(part_acc),
               "sparse MLA: pointers must be 16-byte aligned");
   DSA_REQUIRE(R > 0 && R <= 65535 && rows_per_seq > 0 && R % rows_per_seq == 0,
@@ -495,7 +565,8 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   DSA_REQUIRE(nsplit > 0 && nsplit <= 65535, "sparse MLA: nsplit=%d out of range", nsplit);
   DSA_REQUIRE(kv_seq_stride > 0, "sparse MLA: kv_seq_stride must be positive");
   DSA_REQUIRE(kv_fp8 == 0 || kv_fp8 == 1, "sparse MLA: kv_fp8 must be 0 or 1");
-  mla::Params p{};
+  mla::Params& p = *out_p;
+  p = mla::Params{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.kv = static_cast<const uint8_t*>(kv);
   p.indices = indices;
@@ -514,6 +585,17 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   p.keys_per_split = kps;
   p.kv_fp8 = kv_fp8;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
+  return DSA_OK;
+}
+
+int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
+                            const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
+                            int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
+                            int64_t kv_seq_stride, int kv_fp8, void* stream) {
+  mla::Params p;
+  int rc0 = mla_prepare(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
+                        nsplit, sm_scale, kv_seq_stride, kv_fp8, true, &p);
+  if (rc0) return rc0;
   const size_t smem = kv_fp8 ? mla::SmemLayout::bytes_fp8 : mla::SmemLayout::bytes_bf16;
   {
     int rc = opt_in_smem(mla::sparse_mla_partials_kernel, mla::SmemLayout::bytes_fp8, g_opt_mla);
@@ -529,7 +611,7 @@ int dsa_sparse_mla_combine(const float* part_acc, const float* part_m, const flo
   DSA_REQUIRE(part_acc && part_m && part_l && out, "sparse MLA combine: null pointer");
   DSA_REQUIRE(aligned16(part_acc) && aligned16(out), "sparse MLA combine: misaligned pointer");
   DSA_REQUIRE(R > 0 && R <= 65535 && H > 0 && nsplit > 0, "sparse MLA combine: bad geometry");
-  DSA_CUDA(launch_pdl(mla::sparse_mla_combine_kernel, dim3(H, R), dim3(128), 0,
+  DSA_CUDA(launch_pdl(mla::sparse_mla_combine_kernel, dim3(H, R), dim3(mla::kCombineThreads), 0,
                       static_cast<cudaStream_t>(stream), part_acc, part_m, part_l,
                       static_cast<__nv_bfloat16*>(out), H, nsplit));
   return DSA_OK;
@@ -539,6 +621,16 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
                           const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
                           void* out, int R, int rows_per_seq, int H, int topk_k, int nsplit,
                           float sm_scale, int64_t kv_seq_stride, int kv_fp8, void* stream) {
+  DSA_REQUIRE(out && aligned16(out), "sparse MLA: out must be a 16-byte aligned pointer");
+  {
+    // fused form: cluster of up to 16 splits merging through distributed shared memory
+    mla::Params p;
+    int rc0 = mla_prepare(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
+                          nsplit, sm_scale, kv_seq_stride, kv_fp8, false, &p);
+    if (rc0) return rc0;
+    rc0 = launch_mla_cluster(p, out, R, H, nsplit, topk_k, static_cast<cudaStream_t>(stream));
+    if (rc0 <= 0) return rc0;
+  }
   int rc = dsa_sparse_mla_partials(q, kv, indices, seq_lens, part_acc, part_m, part_l, R,
                                    rows_per_seq, H, topk_k, nsplit, sm_scale, kv_seq_stride, kv_fp8,
                                    stream);

@@ -87,8 +87,9 @@ __global__ void __launch_bounds__(kThreads, kStages <= kStagesTwoPerSm ? 2 : 1)
 indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
   constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
+  // 1024-byte alignment for the swizzled tiles, computed on the shared-window
+  // address so the pointer keeps its address space
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* s_tiles = smem;
   uint8_t* s_q = smem + kSmemStages;
   uint32_t* s_hist = reinterpret_cast<uint32_t*>(s_q + kSmemQ);
@@ -301,7 +302,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
       if (g < p.ctx) out_row[g] = logit;
       if (want_hist) {
         const uint32_t bin = ordered_key(logit) >> 20;
-        if (valid) atomicAdd(&s_hist[bin], 1u);
+        if (valid) smem_red_add(&s_hist[bin], 1u);
         bin_lo = min(bin_lo, valid ? bin : uint32_t(kHistBins));
         bin_hi = max(bin_hi, valid ? bin : 0u);
       }
@@ -310,8 +311,8 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
       bin_lo = __reduce_min_sync(0xffffffffu, bin_lo);
       bin_hi = __reduce_max_sync(0xffffffffu, bin_hi);
       if (lane == 0) {
-        atomicMin(&bars->bin_lo, bin_lo);
-        atomicMax(&bars->bin_hi, bin_hi);
+        smem_red_min(&bars->bin_lo, bin_lo);
+        smem_red_max(&bars->bin_hi, bin_hi);
       }
     }
   }

@@ -17,6 +17,8 @@
 // (fp8 -> f32, x group scale, round to bf16; :1181-1196).
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace dsa {
@@ -96,6 +98,153 @@ __device__ __forceinline__ uint2 dequant4(uint32_t w, float s) {
   return r;
 }
 
+// One 64-key tile for the 16 heads of the CTA: S = Q K^T on bf16 tensor cores,
+// base-2 online softmax across the four warps, P rounded to bf16, O += P V.
+// Warp w owns keys [16 w, 16 w + 16) in S and value columns [128 w, 128 w + 128)
+// in O. All 128 threads call it; it contains two block barriers.
+__device__ __forceinline__ void attend_tile(const uint8_t* s_q, const uint8_t* s_k, uint8_t* s_p,
+                                            float* s_red, const int* s_valid, float scale_log2,
+                                            int warp, int lane, float (&m_run)[2], float (&l_run)[2],
+                                            float (&acc)[16][4]) {
+  const int g = lane >> 2, t4 = lane & 3;
+  // ---- S = Q K^T: warp w owns keys [16 w, 16 w + 16) for all 16 heads
+  float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  {
+    const uint32_t a_base = smem_u32(s_q + (lane & 15) * kRowPitch + (lane >> 4) * 16);
+    const uint32_t b_base = smem_u32(s_k + (warp * 16 + (lane & 7) + 8 * (lane >> 4)) * kRowPitch +
+                                     ((lane >> 3) & 1) * 16);
+#pragma unroll 4
+    for (int k0 = 0; k0 < kD; k0 += 16) {
+      uint32_t a[4], b[4];
+      ldsm_x4(a_base + k0 * 2, a);
+      ldsm_x4(b_base + k0 * 2, b);
+      mma_bf16(sc[0], a, b[0], b[1]);
+      mma_bf16(sc[1], a, b[2], b[3]);
+    }
+  }
+  // scale, mask, tile max per head row (rows g and g + 8)
+  float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = warp * 16 + nt * 8 + t4 * 2 + (e & 1);
+      const float v = s_valid[col] ? sc[nt][e] * scale_log2 : -INFINITY;
+      sc[nt][e] = v;
+      tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
+    tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
+  }
+  if (t4 == 0) {
+    s_red[warp * kHB + g] = tmax[0];
+    s_red[warp * kHB + g + 8] = tmax[1];
+  }
+  __syncthreads();
+  float alpha[2], m_new[2], psum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = g + 8 * i;
+    float m = m_run[i];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, s_red[w * kHB + row]);
+    m_new[i] = m;
+    alpha[i] = (m == -INFINITY) ? 1.f : exp2f(m_run[i] - m);
+  }
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    float pr[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float m = m_new[e >> 1];
+      pr[e] = (m == -INFINITY) ? 0.f : exp2f(sc[nt][e] - m);
+    }
+    const __nv_bfloat162 p01 = __floats2bfloat162_rn(pr[0], pr[1]);
+    const __nv_bfloat162 p23 = __floats2bfloat162_rn(pr[2], pr[3]);
+    // the row sum uses the rounded probabilities that P.V will see
+    psum[0] += __bfloat162float(p01.x) + __bfloat162float(p01.y);
+    psum[1] += __bfloat162float(p23.x) + __bfloat162float(p23.y);
+    const int col = warp * 16 + nt * 8 + t4 * 2;
+    *reinterpret_cast<__nv_bfloat162*>(s_p + g * kPPitch + col * 2) = p01;
+    *reinterpret_cast<__nv_bfloat162*>(s_p + (g + 8) * kPPitch + col * 2) = p23;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    psum[i] += __shfl_xor_sync(0xffffffffu, psum[i], 1);
+    psum[i] += __shfl_xor_sync(0xffffffffu, psum[i], 2);
+  }
+  if (t4 == 0) {
+    s_red[4 * kHB + warp * kHB + g] = psum[0];
+    s_red[4 * kHB + warp * kHB + g + 8] = psum[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = g + 8 * i;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) s += s_red[4 * kHB + w * kHB + row];
+    l_run[i] = l_run[i] * alpha[i] + s;
+    m_run[i] = m_new[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    acc[i][0] *= alpha[0];
+    acc[i][1] *= alpha[0];
+    acc[i][2] *= alpha[1];
+    acc[i][3] *= alpha[1];
+  }
+
+  // ---- O += P V: warp w owns value columns [128 w, 128 w + 128)
+  {
+    const uint32_t a_base = smem_u32(s_p + (lane & 15) * kPPitch + (lane >> 4) * 16);
+    const uint32_t b_base = smem_u32(s_k + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kRowPitch +
+                                     (warp * 128 + 8 * (lane >> 4)) * 2);
+#pragma unroll
+    for (int ks = 0; ks < kBN / 16; ++ks) {
+      uint32_t a[4];
+      ldsm_x4(a_base + ks * 32, a);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t b[4];
+        ldsm_x4_t(b_base + ks * 16 * kRowPitch + np * 32, b);
+        mma_bf16(acc[2 * np], a, b[0], b[1]);
+        mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+  }
+}
+
+// Dequantises the valid rows of a staged fp8 tile (656-B rows) into the bf16 K
+// tile: 128 words of 4 e4m3 + 32 words of rope per row.
+// With zero_invalid the masked rows are cleared here (they must be finite:
+// 0 * NaN would poison P.V); otherwise the caller has cleared them already.
+__device__ __forceinline__ void dequant_tile(const uint8_t* s_stage, uint8_t* s_k, const int* s_valid, int tid,
+                                             bool zero_invalid = false) {
+  for (int i = tid; i < kBN * 160; i += kThreads) {
+    const int row = i / 160, wd = i % 160;
+    const uint8_t* src = s_stage + row * kFp8Row;
+    uint8_t* dst = s_k + row * kRowPitch;
+    if (!s_valid[row]) {
+      if (zero_invalid) {
+        if (wd < 128) *reinterpret_cast<uint2*>(dst + wd * 8) = make_uint2(0, 0);
+        else *reinterpret_cast<uint32_t*>(dst + 1024 + (wd - 128) * 4) = 0;
+      }
+      continue;
+    }
+    if (wd < 128) {
+      const float sc = *reinterpret_cast<const float*>(src + 512 + (wd >> 5) * 4);
+      *reinterpret_cast<uint2*>(dst + wd * 8) = dequant4(*reinterpret_cast<const uint32_t*>(src + wd * 4), sc);
+    } else {
+      *reinterpret_cast<uint32_t*>(dst + 1024 + (wd - 128) * 4) =
+          *reinterpret_cast<const uint32_t*>(src + 528 + (wd - 128) * 4);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 sparse_mla_partials_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -173,134 +322,10 @@ sparse_mla_partials_kernel(const Params p) {
     if (tile == 0 && !mbar_wait(bar_q, 0)) timed_out = true;
     if (!mbar_wait(bar_k, tile & 1)) timed_out = true;
     if (timed_out) break;
-    if (p.kv_fp8) {
-      // dequantise 64 staged rows: 128 words of 4 e4m3 + 32 words of rope per row
-      for (int i = tid; i < kBN * 160; i += kThreads) {
-        const int row = i / 160, wd = i % 160;
-        if (!s_valid[row]) continue;
-        const uint8_t* src = s_stage + row * kFp8Row;
-        uint8_t* dst = s_k + row * kRowPitch;
-        if (wd < 128) {
-          const float s = *reinterpret_cast<const float*>(src + 512 + (wd >> 5) * 4);
-          *reinterpret_cast<uint2*>(dst + wd * 8) =
-              dequant4(*reinterpret_cast<const uint32_t*>(src + wd * 4), s);
-        } else {
-          *reinterpret_cast<uint32_t*>(dst + 1024 + (wd - 128) * 4) =
-              *reinterpret_cast<const uint32_t*>(src + 528 + (wd - 128) * 4);
-        }
-      }
-    }
+    if (p.kv_fp8) dequant_tile(s_stage, s_k, s_valid, tid);
     __syncthreads();
 
-    // ---- S = Q K^T: warp w owns keys [16 w, 16 w + 16) for all 16 heads
-    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    {
-      const uint32_t a_base = smem_u32(s_q + (lane & 15) * kRowPitch + (lane >> 4) * 16);
-      const uint32_t b_base = smem_u32(s_k + (warp * 16 + (lane & 7) + 8 * (lane >> 4)) * kRowPitch +
-                                       ((lane >> 3) & 1) * 16);
-#pragma unroll 4
-      for (int k0 = 0; k0 < kD; k0 += 16) {
-        uint32_t a[4], b[4];
-        ldsm_x4(a_base + k0 * 2, a);
-        ldsm_x4(b_base + k0 * 2, b);
-        mma_bf16(sc[0], a, b[0], b[1]);
-        mma_bf16(sc[1], a, b[2], b[3]);
-      }
-    }
-    // scale, mask, tile max per head row (rows g and g + 8)
-    float tmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = warp * 16 + nt * 8 + t4 * 2 + (e & 1);
-        const float v = s_valid[col] ? sc[nt][e] * p.scale_log2 : -INFINITY;
-        sc[nt][e] = v;
-        tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
-      tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
-    }
-    if (t4 == 0) {
-      s_red[warp * kHB + g] = tmax[0];
-      s_red[warp * kHB + g + 8] = tmax[1];
-    }
-    __syncthreads();
-    float alpha[2], m_new[2], psum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int row = g + 8 * i;
-      float m = m_run[i];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) m = fmaxf(m, s_red[w * kHB + row]);
-      m_new[i] = m;
-      alpha[i] = (m == -INFINITY) ? 1.f : exp2f(m_run[i] - m);
-    }
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      float pr[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float m = m_new[e >> 1];
-        pr[e] = (m == -INFINITY) ? 0.f : exp2f(sc[nt][e] - m);
-      }
-      const __nv_bfloat162 p01 = __floats2bfloat162_rn(pr[0], pr[1]);
-      const __nv_bfloat162 p23 = __floats2bfloat162_rn(pr[2], pr[3]);
-      // the row sum uses the rounded probabilities that P.V will see
-      psum[0] += __bfloat162float(p01.x) + __bfloat162float(p01.y);
-      psum[1] += __bfloat162float(p23.x) + __bfloat162float(p23.y);
-      const int col = warp * 16 + nt * 8 + t4 * 2;
-      *reinterpret_cast<__nv_bfloat162*>(s_p + g * kPPitch + col * 2) = p01;
-      *reinterpret_cast<__nv_bfloat162*>(s_p + (g + 8) * kPPitch + col * 2) = p23;
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      psum[i] += __shfl_xor_sync(0xffffffffu, psum[i], 1);
-      psum[i] += __shfl_xor_sync(0xffffffffu, psum[i], 2);
-    }
-    if (t4 == 0) {
-      s_red[4 * kHB + warp * kHB + g] = psum[0];
-      s_red[4 * kHB + warp * kHB + g + 8] = psum[1];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int row = g + 8 * i;
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) s += s_red[4 * kHB + w * kHB + row];
-      l_run[i] = l_run[i] * alpha[i] + s;
-      m_run[i] = m_new[i];
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      acc[i][0] *= alpha[0];
-      acc[i][1] *= alpha[0];
-      acc[i][2] *= alpha[1];
-      acc[i][3] *= alpha[1];
-    }
-
-    // ---- O += P V: warp w owns value columns [128 w, 128 w + 128)
-    {
-      const uint32_t a_base = smem_u32(s_p + (lane & 15) * kPPitch + (lane >> 4) * 16);
-      const uint32_t b_base = smem_u32(s_k + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kRowPitch +
-                                       (warp * 128 + 8 * (lane >> 4)) * 2);
-#pragma unroll
-      for (int ks = 0; ks < kBN / 16; ++ks) {
-        uint32_t a[4];
-        ldsm_x4(a_base + ks * 32, a);
-#pragma unroll
-        for (int np = 0; np < 8; ++np) {
-          uint32_t b[4];
-          ldsm_x4_t(b_base + ks * 16 * kRowPitch + np * 32, b);
-          mma_bf16(acc[2 * np], a, b[0], b[1]);
-          mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
-        }
-      }
-    }
+    attend_tile(s_q, s_k, s_p, s_red, s_valid, p.scale_log2, warp, lane, m_run, l_run, acc);
     __syncthreads();  // the K tile and P are free for the next gather
   }
 
@@ -329,45 +354,283 @@ sparse_mla_partials_kernel(const Params p) {
   DSA_KTIME_END(2);
 }
 
+// ------------------------------------------------------------------------------
+// Fused form: the CL CTAs that split one (row, head block)'s index list form a
+// thread-block cluster and merge their partial results through distributed
+// shared memory, so there are no partials in global memory and no second launch
+// (the reference folds its combine into the main launch too, but with blocks
+// that spin on a global counter: kernels/cuda_fused_sparse_splitk.py:1604-1665).
+// Each CTA streams its share of the list through a two-slot ring of 64-key
+// tiles; after the last tile it publishes (m, l, unnormalised O) in its own
+// shared memory, the cluster meets at a hardware barrier, and CTA c reduces and
+// writes output columns [c 512/CL, (c+1) 512/CL) for the 16 heads.
+struct ClusterSmem {
+  static constexpr int q_off = 0;
+  static constexpr int k0_off = q_off + kHB * kRowPitch;
+  static constexpr int k1_off = k0_off + kBN * kRowPitch;          // second bf16 tile, or fp8 stage 0
+  static constexpr int p_off = k1_off + kBN * kRowPitch;
+  static constexpr int red_off = p_off + kHB * kPPitch;            // float [2][4][16]
+  static constexpr int valid_off = red_off + 2 * 4 * kHB * 4;      // int [2][64]
+  static constexpr int ml_off = valid_off + 2 * kBN * 4;           // float m[16], l[16]
+  static constexpr int bar_off = ml_off + 2 * kHB * 4;             // 3 mbarriers
+  static constexpr int stage1_off = (bar_off + 32 + 15) & ~15;     // fp8 stage 1
+  static constexpr int bytes_bf16 = stage1_off;
+  static constexpr int bytes_fp8 = stage1_off + kBN * kFp8Row;
+  static_assert(kBN * kFp8Row <= kBN * kRowPitch, "fp8 stage 0 must fit the second tile slot");
+  static_assert(kHB * kDV * 4 <= kBN * kRowPitch, "the merge buffer reuses the first tile slot");
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+sparse_mla_cluster_kernel(const Params p, __nv_bfloat16* __restrict__ out) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned CL = cluster.num_blocks();
+  const unsigned crank = cluster.block_rank();
+  uint8_t* s_q = smem + ClusterSmem::q_off;
+  uint8_t* s_k0 = smem + ClusterSmem::k0_off;
+  uint8_t* s_k1 = smem + ClusterSmem::k1_off;
+  uint8_t* s_p = smem + ClusterSmem::p_off;
+  float* s_red = reinterpret_cast<float*>(smem + ClusterSmem::red_off);
+  int* s_valid = reinterpret_cast<int*>(smem + ClusterSmem::valid_off);
+  float* s_ml = reinterpret_cast<float*>(smem + ClusterSmem::ml_off);
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + ClusterSmem::bar_off);
+  uint8_t* s_stage1 = smem + ClusterSmem::stage1_off;
+  float* s_acc = reinterpret_cast<float*>(s_k0);  // after the last tile
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, hg = blockIdx.y, r = blockIdx.z;
+  DSA_KTIME_BEGIN(2);
+  const int stamp_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  DSA_STAMP(stamp_cta, 0);
+  const int seq = r / p.rows_per_seq;
+  const uint32_t bar_q = smem_u32(&s_bar[0]);
+  const bool fp8 = p.kv_fp8 != 0;
+  const int row_bytes = fp8 ? kFp8Row : kRowBytes;
+  const uint8_t* kv_seq = p.kv + int64_t(seq) * p.kv_seq_stride * row_bytes;
+
+  if (tid == 0) {
+    mbar_init(bar_q, kHB);
+    mbar_init(smem_u32(&s_bar[1]), kBN);
+    mbar_init(smem_u32(&s_bar[2]), kBN);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_wait();  // the selection, the queries and the lengths may come from the previous kernel
+  pdl_launch_dependents();
+  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.ctx;
+  len = len < 0 ? 0 : (len > p.ctx ? p.ctx : len);
+
+  if (tid >= kBN && tid < kBN + kHB) {  // queries of this head block: 16 rows of 1152 B
+    const int h = tid - kBN;
+    const __nv_bfloat16* src = p.q + (int64_t(r) * p.H + hg * kHB + h) * kD;
+    mbar_arrive_expect_tx(bar_q, kRowBytes);
+    bulk_g2s(smem_u32(s_q + h * kRowPitch), src, kRowBytes, bar_q);
+  }
+  const int k_begin = split * p.keys_per_split;
+  const int k_end = min(k_begin + p.keys_per_split, p.topk);
+  const int n_tiles = (max(k_end - k_begin, 0) + kBN - 1) / kBN;
+
+  // Tile t is gathered into ring slot t & 1: one bulk copy per visible row.
+  auto gather = [&](int tile) {
+    if (tid >= kBN) return;
+    const int b = tile & 1;
+    const uint32_t bar = smem_u32(&s_bar[1 + b]);
+    const int j = k_begin + tile * kBN + tid;
+    int64_t idx = -1;
+    if (j < k_end) idx = p.indices ? int64_t(p.indices[int64_t(r) * p.topk + j]) : int64_t(j);
+    const bool ok = idx >= 0 && idx < len;
+    s_valid[b * kBN + tid] = ok;
+    uint8_t* krow = (b ? s_k1 : s_k0) + tid * kRowPitch;
+    if (ok) {
+      fence_proxy_async_smem();  // earlier generic accesses of the slot precede the async write
+      mbar_arrive_expect_tx(bar, row_bytes);
+      if (fp8)
+        bulk_g2s(smem_u32((b ? s_stage1 : s_k1) + tid * kFp8Row), kv_seq + idx * kFp8Row, kFp8Row, bar);
+      else
+        bulk_g2s(smem_u32(krow), kv_seq + idx * kRowBytes, kRowBytes, bar);
+    } else {
+      if (!fp8) {  // masked key: its row must be finite (fp8 rows are cleared when dequantised)
+        uint4* z = reinterpret_cast<uint4*>(krow);
+        for (int i = 0; i < kRowBytes / 16; ++i) z[i] = make_uint4(0, 0, 0, 0);
+      }
+      mbar_arrive(bar);
+    }
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float acc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  bool timed_out = false;
+
+  DSA_STAMP(stamp_cta, 1);
+  if (n_tiles > 0) gather(0);
+  if (n_tiles > 1) gather(1);
+  if (!mbar_wait(bar_q, 0)) timed_out = true;
+  for (int tile = 0; tile < n_tiles && !timed_out; ++tile) {
+    const int b = tile & 1;
+    if (!mbar_wait(smem_u32(&s_bar[1 + b]), (tile >> 1) & 1)) {
+      timed_out = true;
+      break;
+    }
+    DSA_STAMP_IF(tid == 0 && tile < 2, stamp_cta, 2 + tile);
+    const uint8_t* s_k = (fp8 || b == 0) ? s_k0 : s_k1;
+    if (fp8) dequant_tile(b ? s_stage1 : s_k1, s_k0, s_valid + b * kBN, tid, true);
+    __syncthreads();
+    attend_tile(s_q, s_k, s_p, s_red, s_valid + b * kBN, p.scale_log2, warp, lane, m_run, l_run, acc);
+    __syncthreads();  // the slot and P are free
+    if (tile + 2 < n_tiles) gather(tile + 2);
+  }
+  if (timed_out) {
+    atomicOr(&g_device_status, kStatusAttnTimeout);
+    m_run[0] = m_run[1] = -INFINITY;
+    l_run[0] = l_run[1] = 0.f;
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let outstanding copies land
+  }
+
+  DSA_STAMP(stamp_cta, 4);
+  // ---- publish this CTA's partial result in its own shared memory
+  __syncthreads();
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int col = warp * 128 + i * 8 + t4 * 2;
+    *reinterpret_cast<float2*>(s_acc + g * kDV + col) = make_float2(acc[i][0], acc[i][1]);
+    *reinterpret_cast<float2*>(s_acc + (g + 8) * kDV + col) = make_float2(acc[i][2], acc[i][3]);
+  }
+  if (warp == 0 && t4 == 0) {
+    s_ml[g] = m_run[0];
+    s_ml[g + 8] = m_run[1];
+    s_ml[kHB + g] = l_run[0];
+    s_ml[kHB + g + 8] = l_run[1];
+  }
+  DSA_STAMP(stamp_cta, 5);
+  cluster.sync();
+  DSA_STAMP(stamp_cta, 6);
+
+  // ---- CTA c reduces output columns [c 512/CL, (c+1) 512/CL) of the 16 heads
+  const int cols_per = kDV / int(CL);
+  const int c4_per = cols_per / 4;
+  for (int it = tid; it < kHB * c4_per; it += kThreads) {
+    const int h = it / c4_per;
+    const int col = int(crank) * cols_per + (it % c4_per) * 4;
+    float mx = -INFINITY;
+    for (unsigned j = 0; j < CL; ++j) mx = fmaxf(mx, cluster.map_shared_rank(s_ml, j)[h]);
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    if (mx != -INFINITY) {
+      for (unsigned j = 0; j < CL; ++j) {  // fixed order: the result does not depend on timing
+        const float* ml = cluster.map_shared_rank(s_ml, j);
+        const float mj = ml[h];
+        const float e = (mj == -INFINITY) ? 0.f : exp2f(mj - mx);
+        const float4 a = *reinterpret_cast<const float4*>(cluster.map_shared_rank(s_acc, j) + h * kDV + col);
+        l = fmaf(ml[kHB + h], e, l);
+        o.x = fmaf(a.x, e, o.x);
+        o.y = fmaf(a.y, e, o.y);
+        o.z = fmaf(a.z, e, o.z);
+        o.w = fmaf(a.w, e, o.w);
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (int64_t(r) * p.H + hg * kHB + h) * kDV + col) = pk;
+  }
+  DSA_STAMP(stamp_cta, 7);
+  cluster.sync();  // nobody leaves while a peer may still read its shared memory
+  DSA_STAMP(stamp_cta, 8);
+  DSA_KTIME_END(2);
+}
+
 // out = sum_s acc_s 2^(m_s - m) / sum_s l_s 2^(m_s - m); splits with m = -inf
-// (no visible key) are skipped, a row with none yields zeros.
-__global__ void __launch_bounds__(128)
+// (no visible key) are skipped, a row with none yields zeros. One CTA per (row,
+// head): four groups of 128 threads each fold a quarter of the splits (group g
+// takes s = g, g + 4, ...) with all loads of a chunk of eight splits in flight
+// at once, then group 0 merges the four group results in a fixed order.
+constexpr int kCombineThreads = 512;
+__global__ void __launch_bounds__(kCombineThreads)
 sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
                           const float* __restrict__ part_l, __nv_bfloat16* __restrict__ out, int H,
                           int nsplit) {
-  const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x;
+  __shared__ float s_m[4], s_l[4];
+  __shared__ __align__(16) float s_o[4][kDV];
+  const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x & 127, grp = threadIdx.x >> 7;
   DSA_KTIME_BEGIN(3);
   pdl_wait();
   pdl_launch_dependents();
   const float* pm = part_m + int64_t(r) * nsplit * H + h;
   const float* pl = part_l + int64_t(r) * nsplit * H + h;
   const float* pa = part_acc + (int64_t(r) * nsplit * H + h) * kDV + tid * 4;
-  // all loads of a loop are independent, so unrolling keeps many of them in flight
-  float m = -INFINITY;
-#pragma unroll 8
-  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, pm[int64_t(s) * H]);
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  float l = 0.f;
-  if (m != -INFINITY) {
-#pragma unroll 8
-    for (int s = 0; s < nsplit; ++s) {
-      const float ms = pm[int64_t(s) * H];
-      const float e = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      const float4 a = *reinterpret_cast<const float4*>(pa + int64_t(s) * H * kDV);
-      l = fmaf(pl[int64_t(s) * H], e, l);
-      o.x = fmaf(a.x, e, o.x);
-      o.y = fmaf(a.y, e, o.y);
-      o.z = fmaf(a.z, e, o.z);
-      o.w = fmaf(a.w, e, o.w);
+  float mg = -INFINITY, lg = 0.f;
+  float4 og = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = grp; s0 < nsplit; s0 += 32) {
+    float ms[8], ls[8];
+    float4 a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int sp = s0 + 4 * u;
+      const bool ok = sp < nsplit;
+      ms[u] = ok ? pm[int64_t(sp) * H] : -INFINITY;
+      ls[u] = ok ? pl[int64_t(sp) * H] : 0.f;
+      a[u] = ok ? *reinterpret_cast<const float4*>(pa + int64_t(sp) * H * kDV) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    float m_new = mg;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) m_new = fmaxf(m_new, ms[u]);
+    if (m_new != -INFINITY) {
+      const float keep = (mg == -INFINITY) ? 0.f : exp2f(mg - m_new);
+      lg *= keep;
+      og.x *= keep;
+      og.y *= keep;
+      og.z *= keep;
+      og.w *= keep;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float e = (ms[u] == -INFINITY) ? 0.f : exp2f(ms[u] - m_new);
+        lg = fmaf(ls[u], e, lg);
+        og.x = fmaf(a[u].x, e, og.x);
+        og.y = fmaf(a[u].y, e, og.y);
+        og.z = fmaf(a[u].z, e, og.z);
+        og.w = fmaf(a[u].w, e, og.w);
+      }
+    }
+    mg = m_new;
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
-  __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
-  uint2 pk;
-  pk.x = *reinterpret_cast<uint32_t*>(&lo);
-  pk.y = *reinterpret_cast<uint32_t*>(&hi);
-  *reinterpret_cast<uint2*>(out + (int64_t(r) * H + h) * kDV + tid * 4) = pk;
+  if (tid == 0) {
+    s_m[grp] = mg;
+    s_l[grp] = lg;
+  }
+  *reinterpret_cast<float4*>(&s_o[grp][tid * 4]) = og;
+  __syncthreads();
+  if (grp == 0) {
+    const float m = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        const float e = (s_m[gi] == -INFINITY) ? 0.f : exp2f(s_m[gi] - m);
+        const float4 a = *reinterpret_cast<const float4*>(&s_o[gi][tid * 4]);
+        l = fmaf(s_l[gi], e, l);
+        o.x = fmaf(a.x, e, o.x);
+        o.y = fmaf(a.y, e, o.y);
+        o.z = fmaf(a.z, e, o.z);
+        o.w = fmaf(a.w, e, o.w);
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (int64_t(r) * H + h) * kDV + tid * 4) = pk;
+  }
   DSA_KTIME_END(3);
 }
 

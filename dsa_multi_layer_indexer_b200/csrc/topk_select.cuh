@@ -144,7 +144,7 @@ topk_hist_kernel(const Params p) {
     const int64_t i = int64_t(blockIdx.x) * kChunk + j * kThreads + tid;
     if (i < len) {
       const uint32_t bin = ordered_key(row[i]) >> kLowBits;
-      atomicAdd(&s_hist[bin], 1u);
+      smem_red_add(&s_hist[bin], 1u);
       lo = min(lo, bin);
       hi = max(hi, bin);
     }
@@ -312,7 +312,7 @@ topk_finish_kernel(const Params p) {
       if (listed) {
         for (uint32_t i = tid; i < C; i += kFinThreads) {
           const uint32_t k = sh.cand_key[i];
-          if ((k & pmask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
+          if ((k & pmask) == prefix) smem_red_add(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
         }
         DSA_STAMP(r, shift == 10 ? 10 : 12);
       } else {
@@ -320,7 +320,7 @@ topk_finish_kernel(const Params p) {
           const uint32_t cn = __ldcg(slot_cnt + s);
           for (uint32_t e = 0; e < cn; ++e) {
             const uint32_t k = __ldcg(slot_cand + size_t(s) * kWarpSpan + e).x;
-            if ((k & pmask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
+            if ((k & pmask) == prefix) smem_red_add(&sh.hist[(k >> shift) & (kRoundBins - 1)], 1u);
           }
         }
       }
@@ -347,7 +347,7 @@ topk_finish_kernel(const Params p) {
         const uint32_t k = sh.cand_key[i];
         bool keep = k > kstar;
         if (k == kstar) keep = tie_rank++ < ties_kept;
-        if (keep) atomicOr(&sh.sel_mask[sh.cand_pos[i] >> 5], 1u << (sh.cand_pos[i] & 31));
+        if (keep) smem_red_or(&sh.sel_mask[sh.cand_pos[i] >> 5], 1u << (sh.cand_pos[i] & 31));
       }
     } else {
       uint32_t ties = 0;
@@ -362,7 +362,7 @@ topk_finish_kernel(const Params p) {
           const uint2 kp = __ldcg(slot_cand + size_t(s) * kWarpSpan + e);
           bool keep = kp.x > kstar;
           if (kp.x == kstar) keep = tie_rank++ < ties_kept;
-          if (keep) atomicOr(&sh.sel_mask[kp.y >> 5], 1u << (kp.y & 31));
+          if (keep) smem_red_or(&sh.sel_mask[kp.y >> 5], 1u << (kp.y & 31));
         }
       }
     }

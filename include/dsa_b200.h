@@ -181,7 +181,10 @@ int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t
  *   part_acc [R, nsplit, H, 512] fp32, part_m / part_l [R, nsplit, H] fp32
  *   out      [R, H, 512] bf16
  * dsa_sparse_mla_decode = partials + combine; the two halves are exported for
- * callers that schedule them separately, as the reference does.
+ * callers that schedule them separately, as the reference does. With the
+ * environment variable DSA_MLA_FUSED=1 the decode call instead launches one
+ * kernel whose splits form a thread-block cluster (up to 16 CTAs) and merge
+ * through distributed shared memory, without touching part_*.
  */
 int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
                             const int32_t* seq_lens, float* part_acc, float* part_m,

@@ -309,3 +309,18 @@ def test_bad_arguments_raise(ops):
                               torch.zeros(10, 576, dtype=torch.bfloat16, device="cuda"), None, 1.0)
     with pytest.raises(DsaError):
         ops.topk_select(torch.zeros(1, (1 << 20) + 1, device="cuda"), 2048)
+
+
+def test_fused_cluster_attention_in_a_fresh_process():
+    """DSA_MLA_FUSED=1 selects the cluster/DSMEM form of dsa_sparse_mla_decode; the
+    switch is read once per process, so the attention tests are re-run in a child."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, DSA_MLA_FUSED="1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    proc = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_kernels_gpu.py"), "-m", "gpu", "-x",
+                           "-q", "-k", "sparse_mla and not fresh_process"], env=env, capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
