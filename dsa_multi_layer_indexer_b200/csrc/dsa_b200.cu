@@ -471,7 +471,8 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
   p.slot_cnt = p.above_mask + int64_t(R) * words;
   p.header = p.slot_cnt + int64_t(R) * slots;
   uint32_t* ws_hist = p.header + int64_t(R) * 4;
-  p.slot_cand = reinterpret_cast<uint2*>(ws_hist + int64_t(R) * topk::kBins);
+  p.hist2 = ws_hist + int64_t(R) * topk::kBins;
+  p.slot_cand = reinterpret_cast<uint2*>(p.hist2 + int64_t(R) * topk::kRoundBins);
   p.hist = hist ? hist : ws_hist;
   p.index_map = index_map;
   p.out_idx = out_idx;
@@ -540,8 +541,8 @@ int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t
   // another (R, n): the histogram of this call's layout has to start at zero.
   const int64_t words = topk::mask_words(n), slots = words / 4;
   uint32_t* hist = static_cast<uint32_t*>(scratch) + int64_t(R) * (words + slots + 4);
-  DSA_CUDA(cudaMemsetAsync(hist, 0, size_t(R) * topk::kBins * sizeof(uint32_t),
-                           static_cast<cudaStream_t>(stream)));
+  DSA_CUDA(cudaMemsetAsync(hist, 0, size_t(R) * (topk::kBins + topk::kRoundBins) * sizeof(uint32_t),
+                           static_cast<cudaStream_t>(stream)));  // both histograms, adjacent in the layout
   return dsa_topk_select(logits, seq_lens, nullptr, nullptr, out_idx, out_val, scratch,
                          DSA_TOPK_STATIC_SCRATCH_BYTES, R, n, slab_stride, topk_k, pad_value,
                          index_offset, stream);

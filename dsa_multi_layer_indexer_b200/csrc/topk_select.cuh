@@ -41,6 +41,7 @@ constexpr int kRoundBins = 1024;                // two 10-bit rounds over the lo
 constexpr int kFinThreads = 1024;               // finish CTA
 constexpr int kFinWarps = kFinThreads / 32;
 constexpr int kCandCap = 8192;                  // candidates held in shared memory (more: re-read from L2)
+constexpr int kTinyCap = 1024;                  // candidates sharing the threshold's top 22 key bits
 constexpr int64_t kMaxN = 1 << 20;              // the selection mask of one row lives in shared memory
 
 struct Params {
@@ -51,6 +52,7 @@ struct Params {
   uint32_t* slot_cnt;    // [R][slots]        candidates in each warp slot
   uint2* slot_cand;      // [R][slots][128]   (key, position), position order
   uint32_t* header;      // [R][4]            T, need
+  uint32_t* hist2;       // [R][1024]         bits 19..10 of the candidates' keys (filled by classify)
   const int32_t* index_map;
   int32_t* out_idx;
   float* out_val;
@@ -64,14 +66,15 @@ struct Params {
 };
 
 // Workspace layout in 32-bit words: [R][words] mask | [R][slots] counts |
-// [R][4] header | [R][4096] histogram | [R][slots][128][2] candidates.
+// [R][4] header | [R][4096] histogram | [R][1024] second-level histogram |
+// [R][slots][128][2] candidates. The two histograms must be zero on entry.
 __host__ __device__ inline int64_t mask_words(int64_t n) {
   const int64_t chunks = (n + kChunk - 1) / kChunk;
   return chunks * (kChunk / 32);
 }
 __host__ __device__ inline int64_t workspace_words(int64_t R, int64_t n) {
   const int64_t words = mask_words(n), slots = words / 4;
-  return R * (words + slots + 4 + kBins + slots * kWarpSpan * 2) + 32;
+  return R * (words + slots + 4 + kBins + kRoundBins + slots * kWarpSpan * 2) + 32;
 }
 
 // Exclusive prefix of v over the block's threads (NW warps); *total = block sum.
@@ -215,6 +218,11 @@ topk_classify_kernel(const Params p) {
     const uint32_t c = __ballot_sync(0xffffffffu, is_cand);
     if (is_cand) cand[cnt + __popc(c & ((1u << lane) - 1u))] = make_uint2(key, uint32_t(i));
     cnt += __popc(c);
+    if (c) {  // lanes with the same digit add once (a row of equal logits stays cheap)
+      const uint32_t digit = is_cand ? ((key >> 10) & (kRoundBins - 1)) : 0xFFFFFFFFu;
+      const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+      if (is_cand && lane == __ffs(peers) - 1) atomicAdd(&p.hist2[size_t(r) * kRoundBins + digit], __popc(peers));
+    }
     if (lane == 0) above_mask[(span0 >> 5) + j] = a;
   }
   if (lane == 0) p.slot_cnt[int64_t(r) * p.slots + slot] = cnt;
@@ -227,6 +235,7 @@ struct FinShared {
   uint32_t hist[kRoundBins];
   uint32_t warp_tot[kFinWarps];
   uint32_t res[2];
+  uint32_t tiny_cnt;
   uint32_t sel_mask[1];          // really p.words entries
 };
 inline size_t fin_smem_bytes(int words) { return sizeof(FinShared) + size_t(words) * 4; }
@@ -270,6 +279,20 @@ topk_finish_kernel(const Params p) {
   uint32_t c_cnt = 0;
   if (!take_all)
     for (int s = s0; s < s1; ++s) c_cnt += __ldcg(slot_cnt + s);
+  // Prefetch into registers, before any block-wide step: this thread's first
+  // kRegCand candidates (its slots are contiguous) and its second-level bin.
+  constexpr int kRegCand = 8;
+  uint2 rc[kRegCand];
+  const bool one_slot = sper == 1 && s0 < s1;  // rows of up to 131072 logits: one slot per thread
+  uint32_t cn0 = 0;
+  const uint32_t h2 = take_all ? 0u : __ldcg(p.hist2 + size_t(r) * kRoundBins + (kRoundBins - 1 - tid));
+  if (!take_all && one_slot) {
+    cn0 = c_cnt;
+    const uint2* src = slot_cand + size_t(s0) * kWarpSpan;
+#pragma unroll
+    for (int u = 0; u < kRegCand; ++u)
+      if (uint32_t(u) < cn0) rc[u] = __ldcg(src + u);
+  }
   uint32_t C = 0;
   const uint32_t c_off = block_exclusive_scan<kFinWarps>(c_cnt, sh.warp_tot, &C);
   // the histogram has served every classify CTA: clear it for the next scan
@@ -280,7 +303,65 @@ topk_finish_kernel(const Params p) {
   DSA_STAMP(r, 1);
 
   uint32_t kstar = 0xFFFFFFFFu;
+  bool resolved = false;
   if (!take_all && C > 0) {
+    // ---- fast path: the classify kernel also histogrammed bits 19..10 of the
+    // candidates, so the threshold's top 22 bits are one scan away; what shares
+    // them (a handful of keys) is ranked by brute force.
+    if (tid == 0) sh.tiny_cnt = 0;
+    const uint32_t c1[1] = {h2};
+    find_threshold_bin<kFinWarps, 1>(c1, kRoundBins, need, sh.warp_tot, sh.res);
+    const uint32_t p22 = (T << 10) | sh.res[0];  // top 22 bits of the k-th largest key
+    const uint32_t need2 = sh.res[1];            // how many keys with exactly these 22 bits are kept
+    p.hist2[size_t(r) * kRoundBins + tid] = 0;   // re-armed (kRoundBins == kFinThreads)
+    auto place = [&](uint2 kp) {
+      const uint32_t k22 = kp.x >> 10;
+      if (k22 > p22) {
+        smem_red_or(&sh.sel_mask[kp.y >> 5], 1u << (kp.y & 31));
+      } else if (k22 == p22) {
+        const uint32_t at = atomicAdd(&sh.tiny_cnt, 1u);
+        if (at < uint32_t(kTinyCap)) {
+          sh.cand_key[at] = kp.x;
+          sh.cand_pos[at] = kp.y;
+        }
+      }
+    };
+    if (one_slot) {
+#pragma unroll
+      for (int u = 0; u < kRegCand; ++u)
+        if (uint32_t(u) < cn0) place(rc[u]);
+      for (uint32_t e = kRegCand; e < cn0; ++e) place(__ldcg(slot_cand + size_t(s0) * kWarpSpan + e));
+    } else {
+      for (int s = s0; s < s1; ++s) {
+        const uint32_t cn = __ldcg(slot_cnt + s);
+        for (uint32_t e = 0; e < cn; ++e) place(__ldcg(slot_cand + size_t(s) * kWarpSpan + e));
+      }
+    }
+    __syncthreads();
+    const uint32_t n3 = sh.tiny_cnt;
+    if (n3 <= uint32_t(kTinyCap)) {
+      if (uint32_t(tid) < n3) {
+        const uint32_t k = sh.cand_key[tid], ps = sh.cand_pos[tid];
+        uint32_t rank = 0;  // keys that precede this one: larger, or equal at a lower position
+        for (uint32_t j = 0; j < n3; ++j) {
+          const uint32_t kj = sh.cand_key[j];
+          rank += (kj > k) || (kj == k && sh.cand_pos[j] < ps);
+        }
+        if (rank < need2) smem_red_or(&sh.sel_mask[ps >> 5], 1u << (ps & 31));
+        if (rank + 1 == need2) sh.res[0] = k;  // the k-th largest key itself
+      }
+      __syncthreads();
+      kstar = sh.res[0];
+      resolved = true;
+    } else {
+      // too many keys share 22 bits (massive ties): clear what the fast path set and
+      // fall through to the general radix path, which handles any multiplicity
+      __syncthreads();
+      for (int w = tid; w < words; w += kFinThreads) sh.sel_mask[w] = __ldcg(above_mask + w);
+      __syncthreads();
+    }
+  }
+  if (!take_all && C > 0 && !resolved) {
     const bool listed = C <= uint32_t(kCandCap);
     if (listed) {
       uint32_t at = c_off;

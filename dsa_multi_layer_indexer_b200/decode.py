@@ -52,19 +52,27 @@ class HotPathState:
         self.rows, self.heads, self.index_heads = rows, heads, index_heads
         self.capacity, self.topk = capacity, topk
         dev = torch.device(device)
-        self.index_q = torch.zeros(rows, index_heads, ops.INDEX_DIM, dtype=torch.uint8, device=dev)
-        self.index_w = torch.zeros(rows, index_heads, dtype=torch.float32, device=dev)
-        self.q = torch.zeros(rows, heads, ops.LATENT_DIM, dtype=torch.bfloat16, device=dev)
+        # The step's inputs live back to back in one allocation, and so do its
+        # outputs, so a host-side caller moves each group with a single copy.
+        nq, nw = rows * index_heads * ops.INDEX_DIM, rows * index_heads * 4
+        nqq = rows * heads * ops.LATENT_DIM * 2
+        self.in_arena = torch.zeros(nq + nw + nqq, dtype=torch.uint8, device=dev)
+        self.index_q = self.in_arena[:nq].view(rows, index_heads, ops.INDEX_DIM)
+        self.index_w = self.in_arena[nq:nq + nw].view(torch.float32).view(rows, index_heads)
+        self.q = self.in_arena[nq + nw:].view(torch.bfloat16).view(rows, heads, ops.LATENT_DIM)
         self.seq_lens = torch.full((rows,), capacity, dtype=torch.int32, device=dev)
         slab = (capacity + 3) // 4 * 4
         self.logits = torch.empty(rows, slab, dtype=torch.float32, device=dev)
         # zero once; the select kernel re-zeroes it after every use
         self.hist = torch.zeros(rows, ops.HIST_BINS, dtype=torch.int32, device=dev) if use_hist else None
-        self.indices = torch.full((rows, topk), -1, dtype=torch.int32, device=dev)
+        no, ni = rows * heads * ops.VALUE_DIM * 2, rows * topk * 4
+        self.out_arena = torch.zeros(no + ni, dtype=torch.uint8, device=dev)
+        self.out = self.out_arena[:no].view(torch.bfloat16).view(rows, heads, ops.VALUE_DIM)
+        self.indices = self.out_arena[no:].view(torch.int32).view(rows, topk)
+        self.indices.fill_(-1)
         self.topk_ws = ops.topk_workspace(rows, capacity, dev)
         self.nsplit = nsplit or ops.default_nsplit(rows, heads, topk)
         self.scratch = ops.MlaScratch(rows, heads, self.nsplit, dev)
-        self.out = torch.empty(rows, heads, ops.VALUE_DIM, dtype=torch.bfloat16, device=dev)
 
     # -- the three launches, on the current stream -----------------------------
     def run_indexer(self, cache: LayerCache, impl: int = 0) -> torch.Tensor:
@@ -109,27 +117,29 @@ class HostDecoder:
         self.state, self.cache = state, cache
         self.graph = state.capture(cache, sm_scale)
         s = state
-        self.h_index_q = torch.zeros(s.index_q.shape, dtype=torch.uint8).pin_memory()
-        self.h_index_w = torch.zeros(s.index_w.shape, dtype=torch.float32).pin_memory()
-        self.h_q = torch.zeros(s.q.shape, dtype=torch.bfloat16).pin_memory()
-        self.h_out = torch.zeros(s.out.shape, dtype=torch.bfloat16).pin_memory()
-        self.h_indices = torch.zeros(s.indices.shape, dtype=torch.int32).pin_memory()
+        # pinned mirrors of the two arenas, with the same views into them
+        self.h_in = torch.zeros(s.in_arena.shape, dtype=torch.uint8).pin_memory()
+        self.h_outbuf = torch.zeros(s.out_arena.shape, dtype=torch.uint8).pin_memory()
+        nq, nw = s.index_q.numel(), s.index_w.numel() * 4
+        no = s.out.numel() * 2
+        self.h_index_q = self.h_in[:nq].view(s.index_q.shape)
+        self.h_index_w = self.h_in[nq:nq + nw].view(torch.float32).view(s.index_w.shape)
+        self.h_q = self.h_in[nq + nw:].view(torch.bfloat16).view(s.q.shape)
+        self.h_out = self.h_outbuf[:no].view(torch.bfloat16).view(s.out.shape)
+        self.h_indices = self.h_outbuf[no:].view(torch.int32).view(s.indices.shape)
 
     @property
     def h2d_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.h_index_q, self.h_index_w, self.h_q))
+        return self.h_in.numel()
 
     @property
     def d2h_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.h_out, self.h_indices))
+        return self.h_outbuf.numel()
 
     def step(self) -> torch.Tensor:
         s = self.state
-        s.index_q.copy_(self.h_index_q, non_blocking=True)
-        s.index_w.copy_(self.h_index_w, non_blocking=True)
-        s.q.copy_(self.h_q, non_blocking=True)
+        s.in_arena.copy_(self.h_in, non_blocking=True)       # one H2D copy: index_q | index_w | q
         self.graph.replay()
-        self.h_out.copy_(s.out, non_blocking=True)
-        self.h_indices.copy_(s.indices, non_blocking=True)
+        self.h_outbuf.copy_(s.out_arena, non_blocking=True)  # one D2H copy: out | indices
         torch.cuda.current_stream().synchronize()
         return self.h_out
