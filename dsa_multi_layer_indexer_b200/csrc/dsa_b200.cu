@@ -9,6 +9,7 @@
 #include <utility>
 
 #include "common.cuh"
+#include "fused_decode.cuh"
 #include "indexer_scan.cuh"
 #include "sparse_mla.cuh"
 #include "topk_select.cuh"
@@ -102,7 +103,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64];
+static bool g_opt_fused[64], g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -636,6 +637,61 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
                                    rows_per_seq, H, topk_k, nsplit, sm_scale, kv_seq_stride, kv_fp8,
                                    stream);
   if (rc) return rc;
+  return dsa_sparse_mla_combine(part_acc, part_m, part_l, out, R, H, nsplit, stream);
+}
+
+// ------------------------------------------------------------------ fused indexer + attention launch
+int dsa_fused_decode(const void* q, const void* kv, const int32_t* attend_indices,
+                     const int32_t* attn_seq_lens, float* part_acc, float* part_m, float* part_l, void* out,
+                     const uint8_t* index_q, const float* index_w, const uint8_t* index_k,
+                     const float* k_scale, const int32_t* index_seq_lens, float* logits, uint32_t* hist,
+                     int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
+                     int64_t kv_seq_stride, int n_index_heads, int64_t ctx, int64_t n_seq,
+                     int64_t k_seq_stride, int64_t scale_seq_stride, int64_t slab_stride, void* stream) {
+  mla::Params pm;
+  int rc = mla_prepare(q, kv, attend_indices, attn_seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H,
+                       topk_k, nsplit, sm_scale, kv_seq_stride, 0, true, &pm);
+  if (rc) return rc;
+  DSA_REQUIRE(out && aligned16(out), "fused decode: out must be a 16-byte aligned pointer");
+  rc = scan_common_checks(index_q, index_w, logits, R, n_index_heads, ctx, slab_stride);
+  if (rc) return rc;
+  DSA_REQUIRE(index_k && k_scale && aligned16(index_k), "fused decode: bad key cache pointers");
+  DSA_REQUIRE(n_seq == R / rows_per_seq, "fused decode: n_seq=%lld but R / rows_per_seq = %d", (long long)n_seq,
+              R / rows_per_seq);
+  DSA_REQUIRE(k_seq_stride >= ctx && scale_seq_stride >= ctx, "fused decode: sequence strides must be >= ctx");
+  DSA_REQUIRE(n_seq * k_seq_stride < (int64_t(1) << 31), "fused decode: key cache too large");
+  scan::Params ps{};
+  ps.q = index_q;
+  ps.w = index_w;
+  ps.keys = index_k;
+  ps.k_scale = k_scale;
+  ps.seq_lens = index_seq_lens;
+  ps.logits = logits;
+  ps.hist = hist;
+  ps.ctx = ctx;
+  ps.k_seq_stride = k_seq_stride;
+  ps.scale_seq_stride = scale_seq_stride;
+  ps.slab_stride = slab_stride;
+  ps.rows_per_seq = rows_per_seq;
+  ps.n_heads = n_index_heads;
+  ps.tiles_per_row = int((ctx + scan::kTileKeys - 1) / scan::kTileKeys);
+  ps.paged = 0;
+  CUtensorMap tmap;
+  const uint64_t rows = uint64_t(n_seq - 1) * uint64_t(k_seq_stride) + uint64_t(ctx);
+  const uint64_t dims[2] = {uint64_t(scan::kKeyBytes), rows};
+  const uint64_t strides[1] = {uint64_t(scan::kKeyBytes)};
+  const uint32_t box[2] = {uint32_t(scan::kKeyBytes), uint32_t(scan::kTileKeys)};
+  rc = encode_tensor_map(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, index_k, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = opt_in_smem(fused::fused_decode_kernel, fused::kSmemBytes, g_opt_fused);
+  if (rc) return rc;
+  const int hgs = H / DSA_HEAD_BLOCK;
+  const int n_attn = nsplit * hgs * R;
+  const int scan_gx = scan_grid_x(R, ps.tiles_per_row, 2);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DSA_CUDA(launch_pdl(fused::fused_decode_kernel, dim3(n_attn + scan_gx * R), dim3(fused::kThreads),
+                      fused::kSmemBytes, st, tmap, ps, pm, n_attn, nsplit, hgs, scan_gx));
   return dsa_sparse_mla_combine(part_acc, part_m, part_l, out, R, H, nsplit, stream);
 }
 

@@ -82,11 +82,15 @@ __device__ __forceinline__ int row_len(const Params& p, int r) {
   return static_cast<int>(len);
 }
 
+// Body of the scan for CTA `bx` of `G` working on row `r` (the kernel below
+// passes its block indices; the fused indexer + attention launch passes indices
+// of its scan partition). `tmap_ptr` must point at a __grid_constant__ kernel
+// parameter; `smem_raw` is the CTA's dynamic shared memory.
 template <int kStages>
-__global__ void __launch_bounds__(kThreads, kStages <= kStagesTwoPerSm ? 2 : 1)
-indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
+__device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const Params& p, const int bx,
+                                             const int G, const int r, uint8_t* smem_raw) {
+  const CUtensorMap& tmap = *tmap_ptr;
   constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
-  extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles, computed on the shared-window
   // address so the pointer keeps its address space
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -99,12 +103,10 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int r = blockIdx.y;
   const int seq = r / p.rows_per_seq;
   int len = 0;  // read after the dependency wait below
-  const int G = gridDim.x;
   const bool want_hist = p.hist != nullptr;
-  const int stamp_cta = blockIdx.y * gridDim.x + blockIdx.x;
+  const int stamp_cta = r * G + bx;
   DSA_STAMP(stamp_cta, 0);
   DSA_KTIME_BEGIN(0);
   if (tid == 0) prefetch_tensor_map(&tmap);
@@ -166,16 +168,17 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     }
   }
   const float wv = tid < p.n_heads ? p.w[size_t(r) * p.n_heads + tid] : 0.f;
-  if (warp == 0) {  // tensor-memory allocation overlaps the latency of those loads
+  if (warp == 1) {  // tensor-memory allocation overlaps the latency of those loads
     __syncwarp();
     tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
     tmem_relinquish();
   }
   DSA_STAMP(stamp_cta, 12);
-  __syncthreads();  // every query load has been issued
+  // Thread 0 starts the key loads right after its own query loads were issued
+  // (the other warps issue theirs within the same few cycles).
   if (tid == 0) {
     int it = 0;
-    for (int t = blockIdx.x; t < p.tiles_per_row && it < kStages; t += G, ++it) {
+    for (int t = bx; t < p.tiles_per_row && it < kStages; t += G, ++it) {
       if (int64_t(t) * kTileKeys >= len) break;
       issue_tile(it, t);
     }
@@ -206,7 +209,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     // (tiles beyond the first kStages: wait for the MMA to release a ring slot)
     if (lane == 0) {
       int it = 0;
-      for (int t = blockIdx.x; t < p.tiles_per_row; t += G, ++it) {
+      for (int t = bx; t < p.tiles_per_row; t += G, ++it) {
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
         if (it < kStages) continue;
         const uint32_t ph = (it / kStages) & 1;
@@ -224,7 +227,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
       constexpr uint32_t idesc = idesc_f8_f32(kTileKeys, kMaxHeads);
       const uint64_t b_desc = smem_desc_k128(smem_u32(s_q));
       int it = 0;
-      for (int t = blockIdx.x; t < p.tiles_per_row; t += G, ++it) {
+      for (int t = bx; t < p.tiles_per_row; t += G, ++it) {
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
@@ -254,7 +257,7 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     int it = 0;
     bool dead = false;
     uint32_t bin_lo = kHistBins, bin_hi = 0;
-    for (int t = blockIdx.x; t < p.tiles_per_row; t += G) {
+    for (int t = bx; t < p.tiles_per_row; t += G) {
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
       if (int64_t(t) * kTileKeys >= len || dead) {  // no visible key in this tile
         if (g < p.ctx) out_row[g] = neg_inf;
@@ -337,10 +340,17 @@ indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   }
   DSA_STAMP(stamp_cta, 10);
   DSA_KTIME_END(0);
-  if (warp == 0) {
+  if (warp == 1) {  // the warp that allocated it
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+template <int kStages>
+__global__ void __launch_bounds__(kThreads, kStages <= kStagesTwoPerSm ? 2 : 1)
+indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
+  extern __shared__ uint8_t scan_smem[];
+  scan_tc_body<kStages>(&tmap, p, blockIdx.x, gridDim.x, blockIdx.y, scan_smem);
 }
 
 // ------------------------------------------------------------------------------

@@ -65,6 +65,11 @@ struct SmemLayout {
   static constexpr int bytes_fp8 = stage_off + kBN * kFp8Row;
 };
 
+// Barrier over the 128 attention threads (named barrier 1). The split-K body also
+// runs inside a 192-thread CTA of the fused launch, whose two spare warps have
+// left, so it must not use the whole-CTA barrier.
+__device__ __forceinline__ void cta128_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -143,7 +148,7 @@ __device__ __forceinline__ void attend_tile(const uint8_t* s_q, const uint8_t* s
     s_red[warp * kHB + g] = tmax[0];
     s_red[warp * kHB + g + 8] = tmax[1];
   }
-  __syncthreads();
+  cta128_sync();
   float alpha[2], m_new[2], psum[2] = {0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -180,7 +185,7 @@ __device__ __forceinline__ void attend_tile(const uint8_t* s_q, const uint8_t* s
     s_red[4 * kHB + warp * kHB + g] = psum[0];
     s_red[4 * kHB + warp * kHB + g + 8] = psum[1];
   }
-  __syncthreads();
+  cta128_sync();
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = g + 8 * i;
@@ -245,9 +250,10 @@ __device__ __forceinline__ void dequant_tile(const uint8_t* s_stage, uint8_t* s_
   }
 }
 
-__global__ void __launch_bounds__(kThreads)
-sparse_mla_partials_kernel(const Params p) {
-  extern __shared__ __align__(16) uint8_t smem[];
+// Body of the split-K partials for CTA (split, hg, r); `smem` is the CTA's
+// dynamic shared memory. Threads 0..127 take part.
+__device__ __forceinline__ void mla_partials_body(const Params& p, const int split, const int hg, const int r,
+                                                  uint8_t* smem) {
   uint8_t* s_q = smem + SmemLayout::q_off;
   uint8_t* s_k = smem + SmemLayout::k_off;
   uint8_t* s_p = smem + SmemLayout::p_off;
@@ -257,7 +263,6 @@ sparse_mla_partials_kernel(const Params p) {
   uint8_t* s_stage = smem + SmemLayout::stage_off;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int split = blockIdx.x, hg = blockIdx.y, r = blockIdx.z;
   DSA_KTIME_BEGIN(2);
   const int seq = r / p.rows_per_seq;
   const uint32_t bar_q = smem_u32(&s_bar[0]);
@@ -270,7 +275,7 @@ sparse_mla_partials_kernel(const Params p) {
     mbar_init(bar_k, kBN);
     mbar_fence_init();
   }
-  __syncthreads();
+  cta128_sync();
   pdl_wait();  // the selection, the queries and the lengths may come from the previous kernel
   pdl_launch_dependents();
   int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.ctx;
@@ -323,10 +328,10 @@ sparse_mla_partials_kernel(const Params p) {
     if (!mbar_wait(bar_k, tile & 1)) timed_out = true;
     if (timed_out) break;
     if (p.kv_fp8) dequant_tile(s_stage, s_k, s_valid, tid);
-    __syncthreads();
+    cta128_sync();
 
     attend_tile(s_q, s_k, s_p, s_red, s_valid, p.scale_log2, warp, lane, m_run, l_run, acc);
-    __syncthreads();  // the K tile and P are free for the next gather
+    cta128_sync();  // the K tile and P are free for the next gather
   }
 
   if (n_tiles == 0 && !mbar_wait(bar_q, 0)) timed_out = true;  // never leave with a copy in flight
@@ -352,6 +357,12 @@ sparse_mla_partials_kernel(const Params p) {
     p.part_l[pbase + g + 8] = l_run[1];
   }
   DSA_KTIME_END(2);
+}
+
+__global__ void __launch_bounds__(kThreads)
+sparse_mla_partials_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t mla_smem[];
+  mla_partials_body(p, blockIdx.x, blockIdx.y, blockIdx.z, mla_smem);
 }
 
 // ------------------------------------------------------------------------------

@@ -89,6 +89,17 @@ class HotPathState:
         return ops.sparse_mla_decode(self.q, cache.kv, attend, sm_scale, self.seq_lens,
                                      scratch=self.scratch, out=self.out)
 
+    def run_lagged_fused(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float) -> torch.Tensor:
+        """Lagged order in ONE role-split launch: attention over ``attend`` (the
+        previous layer's selection) and this layer's indexer scan share the
+        machine; the top-k then fills ``self.indices`` for the next layer."""
+        ops.fused_decode(self.q, cache.kv, attend, sm_scale, self.index_q, self.index_w, cache.index_k,
+                         cache.k_scale, self.seq_lens, scratch=self.scratch, out=self.out,
+                         logits=self.logits, hist=self.hist)
+        ops.topk_select(self.logits[:, :self.capacity], self.topk, self.seq_lens, hist=self.hist,
+                        out_idx=self.indices, workspace=self.topk_ws)
+        return self.out
+
     def run(self, cache: LayerCache, sm_scale: float, impl: int = 0) -> torch.Tensor:
         """Baseline order: the layer attends its own fresh selection."""
         self.run_indexer(cache, impl)

@@ -348,3 +348,67 @@ def sparse_mla_f32(
         _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(out), R, rows_per_seq, H, dqk,
         value_dim, topk, float(sm_scale), ctx, _stream()))
     return out
+
+
+# --------------------------------------------------------------------------- a6
+def fused_decode(
+    q: torch.Tensor,
+    kv: torch.Tensor,
+    attend_indices: torch.Tensor,
+    sm_scale: float,
+    index_q: torch.Tensor,
+    index_w: torch.Tensor,
+    index_k: torch.Tensor,
+    k_scale: torch.Tensor,
+    seq_lens: Optional[torch.Tensor] = None,
+    *,
+    rows_per_seq: int = 1,
+    nsplit: Optional[int] = None,
+    scratch: Optional[MlaScratch] = None,
+    out: Optional[torch.Tensor] = None,
+    logits: Optional[torch.Tensor] = None,
+    hist: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One launch for a layer's sparse MLA over ``attend_indices`` AND its indexer
+    scan (then the LSE merge): returns ``(attention_out [R,H,512] bf16, logits [R,ctx] fp32)``.
+    Same operands as :func:`sparse_mla_decode` (bf16 cache) and :func:`indexer_scan_fp8`."""
+    _cuda_contig(q, "q", (torch.bfloat16,))
+    _need(q.dim() == 3 and q.shape[2] == LATENT_DIM and q.shape[1] % HEAD_BLOCK == 0, "q must be [R, H % 16 == 0, 576]")
+    R, H = q.shape[0], q.shape[1]
+    if kv.dim() == 2:
+        kv = kv.unsqueeze(0)
+    _cuda_contig(kv, "kv", (torch.bfloat16,))
+    _need(kv.dim() == 3 and kv.shape[2] == LATENT_DIM, "kv must be [n_seq, cap, 576] bf16")
+    _cuda_contig(attend_indices, "attend_indices", (torch.int32,))
+    _need(attend_indices.dim() == 2 and attend_indices.shape[0] == R, "attend_indices must be [R, topk]")
+    topk = attend_indices.shape[1]
+    _cuda_contig(index_q, "index_q", (_FP8, torch.uint8))
+    _cuda_contig(index_w, "index_w", (torch.float32,))
+    _cuda_contig(index_k, "index_k", (_FP8, torch.uint8))
+    _cuda_contig(k_scale, "k_scale", (torch.float32,))
+    if index_k.dim() == 2:
+        index_k = index_k.unsqueeze(0)
+        k_scale = k_scale.reshape(1, -1)
+    n_seq, cap = index_k.shape[0], index_k.shape[1]
+    _need(kv.shape[0] == n_seq and R == n_seq * rows_per_seq, "R must equal n_seq * rows_per_seq for both caches")
+    _need(index_q.shape[0] == R and tuple(index_w.shape) == (R, index_q.shape[1]), "index_q / index_w rows differ from q")
+    seq_lens = _lens(seq_lens, R)
+    if nsplit is None:
+        nsplit = scratch.nsplit if scratch is not None else default_nsplit(R, H, topk)
+    if scratch is None:
+        scratch = MlaScratch(R, H, nsplit, q.device)
+    _need(scratch.rows >= R and scratch.heads == H and scratch.nsplit == nsplit, "scratch does not match the launch")
+    if out is None:
+        out = torch.empty(R, H, VALUE_DIM, dtype=torch.bfloat16, device=q.device)
+    if logits is None:
+        logits = torch.empty(R, (cap + 3) // 4 * 4, dtype=torch.float32, device=q.device)
+    _cuda_contig(logits, "logits", (torch.float32,))
+    if hist is not None:
+        _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+        _need(hist.numel() == R * HIST_BINS, "hist must be [R, 4096]")
+    _lib.check(_lib.lib().dsa_fused_decode(
+        _ptr(q), _ptr(kv), _ptr(attend_indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),
+        _ptr(scratch.l), _ptr(out), _ptr(index_q), _ptr(index_w), _ptr(index_k), _ptr(k_scale), _ptr(seq_lens),
+        _ptr(logits), _ptr(hist), R, rows_per_seq, H, topk, nsplit, float(sm_scale), kv.shape[1],
+        index_q.shape[1], cap, n_seq, cap, cap, logits.shape[1], _stream()))
+    return out, logits[:, :cap]

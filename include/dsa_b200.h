@@ -199,6 +199,23 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
                           int nsplit, float sm_scale, int64_t kv_seq_stride, int kv_fp8,
                           void* stream);
 
+/* ---- (a6) fused indexer + attention launch -----------------------------------
+ * One launch whose first CTAs compute the split-K attention partials over
+ * `attend_indices` (under the lagged schedule: the PREVIOUS layer's selection)
+ * and whose remaining CTAs run this layer's indexer scan into `logits` (+ `hist`),
+ * followed by the LSE merge. Same results as dsa_sparse_mla_decode +
+ * dsa_indexer_scan_fp8, bit for bit. Replaces launch_fused_sparse_splitk with
+ * attn_on=1, with_select=1|2 (kernels/cuda_fused_sparse_splitk.py:178-683,
+ * :2634-2655); the top-k stays a separate call. Dense bf16 caches only. */
+int dsa_fused_decode(const void* q, const void* kv, const int32_t* attend_indices,
+                     const int32_t* attn_seq_lens, float* part_acc, float* part_m, float* part_l,
+                     void* out,
+                     const uint8_t* index_q, const float* index_w, const uint8_t* index_k,
+                     const float* k_scale, const int32_t* index_seq_lens, float* logits, uint32_t* hist,
+                     int R, int rows_per_seq, int H, int topk, int nsplit, float sm_scale,
+                     int64_t kv_seq_stride, int n_index_heads, int64_t ctx, int64_t n_seq,
+                     int64_t k_seq_stride, int64_t scale_seq_stride, int64_t slab_stride, void* stream);
+
 /* fp32 form for any head / latent width (src/lagged_indexer_dsa/
  * attention_core.py:94-160): one pass, no split. indices NULL = dense causal. */
 int dsa_sparse_mla_f32(const float* q, const float* kv, const int32_t* indices,

@@ -324,3 +324,32 @@ def test_fused_cluster_attention_in_a_fresh_process():
                            "-q", "-k", "sparse_mla and not fresh_process"], env=env, capture_output=True, text=True,
                           timeout=600)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+
+
+# ----------------------------------------------------------------------------- fused launch
+@pytest.mark.parametrize("B,H,n,topk,nsplit", [(1, 128, 20000, 2048, 32), (3, 32, 5000, 1024, 8), (2, 16, 700, 64, 1)])
+def test_fused_indexer_attention_launch_equals_separate_launches(ops, B, H, n, topk, nsplit):
+    """One role-split launch (attention over a given selection + the indexer scan)
+    returns bit for bit what the two separate launches return."""
+    torch.manual_seed(B * 1000 + H)
+    q = dev(torch.randn(B, H, 576).to(torch.bfloat16))
+    kv = dev(torch.randn(B, n, 576).to(torch.bfloat16))
+    attend = dev(torch.stack([torch.randperm(n)[:topk] for _ in range(B)]).int())
+    iq8, sq = O.quantize_e4m3_rowwise(torch.randn(B, 64, 128))
+    ik8, sk = O.quantize_e4m3_rowwise(torch.randn(B, n, 128))
+    wp = dev(sq * (torch.randn(B, 64) / 8))
+    iq8, ik8, sk = dev(iq8), dev(ik8), dev(sk)
+    lens = dev(torch.randint(max(1, n // 2), n + 1, (B,), dtype=torch.int32))
+    sm = 192 ** -0.5
+    hist_a = torch.zeros(B, 4096, dtype=torch.int32, device="cuda")
+    hist_b = torch.zeros(B, 4096, dtype=torch.int32, device="cuda")
+    out_f, logits_f = ops.fused_decode(q, kv, attend, sm, iq8, wp, ik8, sk, lens, nsplit=nsplit, hist=hist_a)
+    from dsa_multi_layer_indexer_b200 import ops as _o
+    scratch = _o.MlaScratch(B, H, nsplit, "cuda")
+    out_s = ops.sparse_mla_decode(q, kv, attend, sm, lens, nsplit=nsplit, scratch=scratch)
+    logits_s = ops.indexer_scan_fp8(iq8, wp, ik8, sk, lens, hist=hist_b)
+    assert torch.equal(out_f, out_s)
+    assert torch.equal(logits_f, logits_s)
+    assert torch.equal(hist_a, hist_b)
+    sel = ops.topk_select(logits_f, topk, lens, hist=hist_a)
+    assert torch.equal(sel, ops.topk_select(logits_s, topk, lens))
