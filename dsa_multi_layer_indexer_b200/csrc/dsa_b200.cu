@@ -9,6 +9,7 @@
 #include <utility>
 
 #include "common.cuh"
+#include "decode_prep.cuh"
 #include "fused_decode.cuh"
 #include "indexer_scan.cuh"
 #include "sparse_mla.cuh"
@@ -638,6 +639,71 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
                                    stream);
   if (rc) return rc;
   return dsa_sparse_mla_combine(part_acc, part_m, part_l, out, R, H, nsplit, stream);
+}
+
+// ------------------------------------------------------------------ decode-step preparation
+int dsa_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int dim, float eps, int dtype,
+                void* stream) {
+  DSA_REQUIRE(x && weight && out, "rmsnorm: null pointer");
+  DSA_REQUIRE(rows > 0 && rows < (int64_t(1) << 31) && dim > 0, "rmsnorm: bad shape");
+  DSA_REQUIRE(dtype == 0 || dtype == 1, "rmsnorm: dtype must be 0 (fp32) or 1 (bf16)");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) {
+    DSA_CUDA(launch_pdl(prep::rmsnorm_kernel<float>, dim3(unsigned(rows)), dim3(256), 0, st,
+                        static_cast<const float*>(x), static_cast<const float*>(weight), static_cast<float*>(out),
+                        dim, eps));
+  } else {
+    DSA_CUDA(launch_pdl(prep::rmsnorm_kernel<__nv_bfloat16>, dim3(unsigned(rows)), dim3(256), 0, st,
+                        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
+                        static_cast<__nv_bfloat16*>(out), dim, eps));
+  }
+  return DSA_OK;
+}
+
+int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, const void* kv_a,
+                    const void* q_abs, const void* q_pe, int64_t q_pe_stride, const void* kv_norm_w,
+                    const void* mla_cos, const void* mla_sin, const void* idx_cos, const void* idx_sin,
+                    const int64_t* positions, uint8_t* index_q, float* index_w, void* q_full,
+                    uint8_t* cache_index_k, float* cache_k_scale, void* cache_kv, int B, int H,
+                    int n_index_heads, int64_t cap, int interleave, float eps, void* stream) {
+  DSA_REQUIRE(iq_raw && w_raw && ik_raw && kv_a && q_abs && q_pe && kv_norm_w && mla_cos && mla_sin && idx_cos &&
+                  idx_sin && positions && index_q && index_w && q_full && cache_index_k && cache_k_scale && cache_kv,
+              "decode prep: null pointer");
+  DSA_REQUIRE(aligned16(iq_raw) && aligned16(ik_raw) && aligned16(q_abs) && aligned16(q_full) && aligned16(index_q) &&
+                  aligned16(cache_index_k) && aligned16(cache_kv),
+              "decode prep: pointers must be 16-byte aligned");
+  DSA_REQUIRE(B > 0 && B <= 65535 && H > 0 && n_index_heads > 0 && cap > 0, "decode prep: bad shape");
+  DSA_REQUIRE(q_pe_stride >= 64, "decode prep: q_pe_stride must be >= 64 elements");
+  prep::Params p{};
+  p.iq_raw = static_cast<const __nv_bfloat16*>(iq_raw);
+  p.w_raw = static_cast<const __nv_bfloat16*>(w_raw);
+  p.ik_raw = static_cast<const __nv_bfloat16*>(ik_raw);
+  p.kv_a = static_cast<const __nv_bfloat16*>(kv_a);
+  p.q_abs = static_cast<const __nv_bfloat16*>(q_abs);
+  p.q_pe = static_cast<const __nv_bfloat16*>(q_pe);
+  p.q_pe_stride = q_pe_stride;
+  p.kv_norm_w = static_cast<const __nv_bfloat16*>(kv_norm_w);
+  p.mla_cos = static_cast<const __nv_bfloat16*>(mla_cos);
+  p.mla_sin = static_cast<const __nv_bfloat16*>(mla_sin);
+  p.idx_cos = static_cast<const __nv_bfloat16*>(idx_cos);
+  p.idx_sin = static_cast<const __nv_bfloat16*>(idx_sin);
+  p.positions = positions;
+  p.index_q = index_q;
+  p.index_w = index_w;
+  p.q_full = static_cast<__nv_bfloat16*>(q_full);
+  p.cache_index_k = cache_index_k;
+  p.cache_k_scale = cache_k_scale;
+  p.cache_kv = static_cast<__nv_bfloat16*>(cache_kv);
+  p.cap = cap;
+  p.B = B;
+  p.H = H;
+  p.Hidx = n_index_heads;
+  p.interleave = interleave;
+  p.eps = eps;
+  const int items = n_index_heads + 2 + H;
+  DSA_CUDA(launch_pdl(prep::decode_prep_kernel, dim3((items + 3) / 4, B), dim3(128), 0,
+                      static_cast<cudaStream_t>(stream), p));
+  return DSA_OK;
 }
 
 // ------------------------------------------------------------------ fused indexer + attention launch

@@ -46,6 +46,8 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16):
+            return ops.rmsnorm(x, self.weight, self.eps)  # one launch
         xf = x.float()
         inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
         return (xf * inv * self.weight.float()).to(x.dtype)
@@ -264,7 +266,12 @@ class DSALayer(nn.Module):
 
     def decode_project(self, x_norm, rope: RopeCaches, positions, cache: LayerDecodeCache, batch_index):
         """Projections of one new token per sequence, and its keys appended to
-        the caches at ``positions`` [B]. Returns (q [B,H,Dqk], index_q, index_w)."""
+        the caches at ``positions`` [B]. Returns (q [B,H,Dqk], index_q, index_w).
+
+        With FP8 caches and bf16 weights everything after the GEMVs (RoPE, e4m3
+        quantisation with the scale folded into the head weights, both cache
+        appends, assembly of the absorbed query) is ONE launch; index_q then
+        comes back already quantised (uint8) with index_w fp32."""
         c = self.config
         b = x_norm.shape[0]
         h = c.num_attention_heads
@@ -272,18 +279,29 @@ class DSALayer(nn.Module):
         c_q = self.q_latent(x_norm)
         q = self.q_b_proj(c_q).view(b, h, c.qk_nope_head_dim + c.qk_rope_head_dim)
         q_nope, q_rope = q.split([c.qk_nope_head_dim, c.qk_rope_head_dim], dim=-1)
-        q_rope = apply_rotary_at(q_rope, rope.mla_cos, rope.mla_sin, positions)
         kv_a = self.kv_a_proj(x_norm)
+        w_uk, _ = self._w_uk_uv()
+        q_abs = torch.einsum("bhd,hdl->bhl", q_nope, w_uk)
+        iq_raw = self.index_q_proj(c_q).view(b, c.index_n_heads, c.index_head_dim)
+        ik_raw = self.index_k_proj(x_norm)
+        w = self.index_weights_proj(c_q)
+        if cache.k_scale is not None and x_norm.dtype == torch.bfloat16:
+            index_q = torch.empty(b, c.index_n_heads, c.index_head_dim, dtype=torch.uint8, device=x_norm.device)
+            index_w = torch.empty(b, c.index_n_heads, dtype=torch.float32, device=x_norm.device)
+            q_full = torch.empty(b, h, c.qk_head_dim, dtype=torch.bfloat16, device=x_norm.device)
+            ops.decode_prep(iq_raw.contiguous(), w.contiguous(), ik_raw.contiguous(), kv_a.contiguous(),
+                            q_abs.contiguous(), q_rope, self.kv_a_layernorm.weight, rope.mla_cos, rope.mla_sin,
+                            rope.idx_cos, rope.idx_sin, positions, index_q, index_w, q_full, cache.index_k,
+                            cache.k_scale, cache.kv, il, c.rms_norm_eps)
+            return q_full, index_q, index_w
+        q_rope = apply_rotary_at(q_rope, rope.mla_cos, rope.mla_sin, positions)
         c_kv, k_rope = kv_a.split([c.kv_lora_rank, c.qk_rope_head_dim], dim=-1)
         k_rope = apply_rotary_at(k_rope, rope.mla_cos, rope.mla_sin, positions)
-        w_uk, _ = self._w_uk_uv()
-        q_full = torch.cat([torch.einsum("bhd,hdl->bhl", q_nope, w_uk), q_rope], dim=-1)
+        q_full = torch.cat([q_abs, q_rope], dim=-1)
         kv_row = torch.cat([self.kv_a_layernorm(c_kv), k_rope], dim=-1)
         cache.kv[batch_index, positions] = kv_row.to(cache.kv.dtype)
-        iq = apply_rotary_at(self.index_q_proj(c_q).view(b, c.index_n_heads, c.index_head_dim),
-                             rope.idx_cos, rope.idx_sin, positions, interleave=il)
-        ik = apply_rotary_at(self.index_k_proj(x_norm), rope.idx_cos, rope.idx_sin, positions, interleave=il)
-        w = self.index_weights_proj(c_q)
+        iq = apply_rotary_at(iq_raw, rope.idx_cos, rope.idx_sin, positions, interleave=il)
+        ik = apply_rotary_at(ik_raw, rope.idx_cos, rope.idx_sin, positions, interleave=il)
         if cache.k_scale is not None:
             ik8, sk = ops.quantize_e4m3_rowwise(ik.float().contiguous())
             cache.index_k[batch_index, positions] = ik8.view(torch.uint8)
@@ -299,8 +317,11 @@ class DSALayer(nn.Module):
         result live in persistent buffers (nothing is allocated per step)."""
         topk = self.config.index_topk
         if cache.k_scale is not None:
-            iq8, sq = ops.quantize_e4m3_rowwise(iq.float().contiguous())
-            wf = (sq * w.float()).contiguous()
+            if iq.dtype == torch.uint8:  # already quantised by decode_project's fused launch
+                iq8, wf = iq, w
+            else:
+                iq8, sq = ops.quantize_e4m3_rowwise(iq.float().contiguous())
+                wf = (sq * w.float()).contiguous()
             if ws is None:
                 logits = ops.indexer_scan_fp8(iq8, wf, cache.index_k, cache.k_scale, seq_lens)
                 return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value)

@@ -412,3 +412,42 @@ def fused_decode(
         _ptr(logits), _ptr(hist), R, rows_per_seq, H, topk, nsplit, float(sm_scale), kv.shape[1],
         index_q.shape[1], cap, n_seq, cap, cap, logits.shape[1], _stream()))
     return out, logits[:, :cap]
+
+
+# --------------------------------------------------------------------------- decode-step preparation
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the last dimension in one launch (fp32 math, one rounding)."""
+    _need(x.is_cuda and x.dtype in (torch.float32, torch.bfloat16), "x must be CUDA fp32 / bf16")
+    x = x.contiguous()
+    w = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    out = torch.empty_like(x)
+    dim = x.shape[-1]
+    _lib.check(_lib.lib().dsa_rmsnorm(_ptr(x), _ptr(w.contiguous()), _ptr(out), x.numel() // dim, dim, float(eps),
+                                      0 if x.dtype == torch.float32 else 1, _stream()))
+    return out
+
+
+def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, mla_sin, idx_cos, idx_sin,
+                positions, index_q, index_w, q_full, cache_index_k, cache_k_scale, cache_kv,
+                interleave: bool, eps: float) -> None:
+    """One launch for the chain between the projection GEMVs and the hot path
+    (see ``dsa_decode_prep`` in the header). All operands bf16 CUDA tensors;
+    ``q_pe`` may be a strided view ``q[..., nope:]`` of the q_b_proj output."""
+    for t, n in ((iq_raw, "iq_raw"), (w_raw, "w_raw"), (ik_raw, "ik_raw"), (kv_a, "kv_a"), (q_abs, "q_abs"),
+                 (kv_norm_w, "kv_norm_w"), (mla_cos, "mla_cos"), (mla_sin, "mla_sin"), (idx_cos, "idx_cos"),
+                 (idx_sin, "idx_sin")):
+        _cuda_contig(t, n, (torch.bfloat16,))
+    _need(q_pe.dtype == torch.bfloat16 and q_pe.dim() == 3 and q_pe.shape[2] == 64 and q_pe.stride(2) == 1
+          and q_pe.stride(0) == q_pe.shape[1] * q_pe.stride(1), "q_pe must be a [B, H, 64] bf16 view with dense rows")
+    _cuda_contig(positions, "positions", (torch.int64,))
+    B, n_idx = iq_raw.shape[0], iq_raw.shape[1]
+    H = q_abs.shape[1]
+    _need(iq_raw.shape[2] == INDEX_DIM and kv_a.shape[-1] == LATENT_DIM and q_abs.shape[2] == VALUE_DIM,
+          "decode prep needs the production geometry")
+    cap = cache_kv.shape[1]
+    _need(cache_kv.shape[0] == B and cache_index_k.shape[:2] == (B, cap), "caches must be [B, cap, ...]")
+    _lib.check(_lib.lib().dsa_decode_prep(
+        _ptr(iq_raw), _ptr(w_raw), _ptr(ik_raw), _ptr(kv_a), _ptr(q_abs), _ptr(q_pe), q_pe.stride(1), _ptr(kv_norm_w),
+        _ptr(mla_cos), _ptr(mla_sin), _ptr(idx_cos), _ptr(idx_sin), _ptr(positions), _ptr(index_q), _ptr(index_w),
+        _ptr(q_full), _ptr(cache_index_k), _ptr(cache_k_scale), _ptr(cache_kv), B, H, n_idx, cap,
+        1 if interleave else 0, float(eps), _stream()))

@@ -223,6 +223,31 @@ int dsa_sparse_mla_f32(const float* q, const float* kv, const int32_t* indices,
                        int qk_dim, int v_dim, int topk, float sm_scale,
                        int64_t kv_seq_stride, void* stream);
 
+/* ---- decode-step preparation between the projection GEMVs and the hot path ---
+ * dsa_rmsnorm: out = x * rsqrt(mean(x^2) + eps) * weight over rows of `dim`
+ * (src/lagged_indexer_dsa/dsa_layer.py:42-52); dtype 0 = fp32, 1 = bf16.
+ *
+ * dsa_decode_prep: everything the new token needs before scan / attention, in
+ * one launch (the reference's stage_fp8_operands chain,
+ * inference/modeling/transformer.py:1015-1066, :1137-1144, :3268-3276):
+ *   - indexer query heads: RoPE at positions[b], per-head e4m3 quantisation,
+ *     index_w = q_scale * w_raw;
+ *   - the token's index key: RoPE, e4m3 + scale, written at cache row positions[b];
+ *   - the token's latent row: RMSNorm(512) | RoPE(64), written at positions[b];
+ *   - the absorbed query: q_full = [q_abs | RoPE(q_pe)].
+ * All inputs bf16 ([B,Hidx,128], [B,Hidx], [B,128], [B,576], [B,H,512],
+ * [B,H,64] with row stride q_pe_stride elements); rotary tables bf16
+ * [cap,64] / [cap,128]; caches as in dsa_indexer_scan_fp8 / dsa_sparse_mla_*. */
+int dsa_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int dim, float eps,
+                int dtype, void* stream);
+int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, const void* kv_a,
+                    const void* q_abs, const void* q_pe, int64_t q_pe_stride, const void* kv_norm_w,
+                    const void* mla_cos, const void* mla_sin, const void* idx_cos, const void* idx_sin,
+                    const int64_t* positions, uint8_t* index_q, float* index_w, void* q_full,
+                    uint8_t* cache_index_k, float* cache_k_scale, void* cache_kv,
+                    int B, int H, int n_index_heads, int64_t cap, int interleave, float eps,
+                    void* stream);
+
 /* ---- (a7) per-token e4m3 quantisation of index keys / queries --------------
  * scale = max(amax(row), clamp_min) / 448, q = sat(x / scale) -> e4m3 RN
  * (kernels/cuda_fused_sparse_splitk.py:2969-2974). x is fp32 [rows, cols]. */

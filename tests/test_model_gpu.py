@@ -198,3 +198,74 @@ def test_production_geometry_fp8_bf16_path(D):
                     sa, sb = set(ia[r].tolist()) - {-1}, set(ib[r].tolist()) - {-1}
                     overlaps.append(len(sa & sb) / max(1, len(sa | sb)))
     assert min(overlaps) > 0.6 and sum(overlaps) / len(overlaps) > 0.8
+
+
+def test_fused_decode_prep_matches_the_unfused_chain(D):
+    """dsa_decode_prep (one launch) against the same chain written with torch ops in
+    fp32: RoPE, per-head e4m3 quantisation with folded scales, both cache appends
+    and the assembled absorbed query."""
+    from dsa_multi_layer_indexer_b200 import ops
+    from dsa_multi_layer_indexer_b200.rope import apply_rotary_at, build_rope_cache
+    from oracle import dsa_oracle as O
+
+    torch.manual_seed(21)
+    B, H, Hidx, cap = 3, 32, 64, 300
+    dev, bf = "cuda", torch.bfloat16
+    iq_raw = torch.randn(B, Hidx, 128, device=dev).to(bf)
+    w_raw = torch.randn(B, Hidx, device=dev).to(bf)
+    ik_raw = torch.randn(B, 128, device=dev).to(bf)
+    kv_a = torch.randn(B, 576, device=dev).to(bf)
+    q = torch.randn(B, H, 192, device=dev).to(bf)
+    q_abs = torch.randn(B, H, 512, device=dev).to(bf)
+    norm_w = (1 + 0.1 * torch.randn(512, device=dev)).to(bf)
+    pos = torch.tensor([5, 299, 0], device=dev)
+    for interleave in (False, True):
+        mc, ms = build_rope_cache(cap, 64, 10000.0, dev, bf)
+        ic, isn = build_rope_cache(cap, 128, 10000.0, dev, bf, interleave=interleave)
+        index_q = torch.zeros(B, Hidx, 128, dtype=torch.uint8, device=dev)
+        index_w = torch.zeros(B, Hidx, device=dev)
+        q_full = torch.zeros(B, H, 576, dtype=bf, device=dev)
+        c_ik = torch.zeros(B, cap, 128, dtype=torch.uint8, device=dev)
+        c_sk = torch.zeros(B, cap, device=dev)
+        c_kv = torch.zeros(B, cap, 576, dtype=bf, device=dev)
+        ops.decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q[..., 128:], norm_w, mc, ms, ic, isn, pos, index_q,
+                        index_w, q_full, c_ik, c_sk, c_kv, interleave, 1e-6)
+        torch.cuda.synchronize()
+        f = torch.float32
+        # indexer query heads
+        iq = apply_rotary_at(iq_raw.to(f), ic.to(f), isn.to(f), pos, interleave=interleave).cpu()
+        iq8, sq = O.quantize_e4m3_rowwise(iq)
+        got = O.e4m3_to_f32(index_q.cpu()) * (index_w.cpu() / w_raw.float().cpu()).unsqueeze(-1)
+        want = O.e4m3_to_f32(iq8) * sq.unsqueeze(-1)
+        assert rel_err(got, want) < 2e-2  # one e4m3 step at most where a rounding boundary is crossed
+        assert torch.allclose(index_w.cpu(), sq * w_raw.float().cpu(), rtol=1e-5, atol=1e-7)
+        # appended index key
+        ik = apply_rotary_at(ik_raw.to(f), ic.to(f), isn.to(f), pos, interleave=interleave).cpu()
+        ik8, sk = O.quantize_e4m3_rowwise(ik)
+        bi = torch.arange(B)
+        assert torch.allclose(c_sk.cpu()[bi, pos.cpu()], sk, rtol=1e-5)
+        assert rel_err(O.e4m3_to_f32(c_ik.cpu()[bi, pos.cpu()]) * sk[:, None], O.e4m3_to_f32(ik8) * sk[:, None]) < 2e-2
+        assert int(c_ik.sum()) == int(c_ik[bi.to(dev), pos].sum())  # nothing else was written
+        # appended latent row
+        ckv = kv_a[:, :512].to(f)
+        normed = ckv * torch.rsqrt(ckv.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.to(f)
+        krope = apply_rotary_at(kv_a[:, 512:].to(f), mc.to(f), ms.to(f), pos)
+        want_row = torch.cat([normed, krope], -1)
+        assert rel_err(c_kv[bi.to(dev), pos].float().cpu(), want_row.cpu()) < 1e-2
+        # assembled query
+        qr = apply_rotary_at(q[..., 128:].to(f), mc.to(f), ms.to(f), pos)
+        assert torch.equal(q_full[..., :512], q_abs)
+        assert rel_err(q_full[..., 512:].float().cpu(), qr.cpu()) < 1e-2
+
+
+def test_library_rmsnorm_matches_torch(D):
+    from dsa_multi_layer_indexer_b200 import ops
+
+    torch.manual_seed(22)
+    for dt, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+        x = torch.randn(5, 7168, device="cuda").to(dt)
+        w = (1 + 0.1 * torch.randn(7168, device="cuda")).to(dt)
+        xf = x.float()
+        want = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(dt)
+        got = ops.rmsnorm(x, w, 1e-6)
+        assert rel_err(got.float().cpu(), want.float().cpu()) < tol
