@@ -55,6 +55,9 @@ def parse_args():
     ap.add_argument("--seq-shard", action="store_true", help="N>1: shard the scan by KV range + all-gather merge")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scan-impl", type=int, default=0, help="0 tcgen05, 1 legacy mma.sync")
+    ap.add_argument("--tp-emulate", type=int, default=1,
+                    help="mli_stack only: per-GPU shapes of an N-way tensor-parallel layer (heads and MLP width / N) "
+                         "on one GPU, without the all-reduces")
     ap.add_argument("--workload", default="layer_decode", choices=["layer_decode", "batch32_paged", "mli_stack"],
                     help="layer_decode = BASELINE config 2 (the default bench line); the others are extra measurements")
     return ap.parse_args()
@@ -562,7 +565,9 @@ def run_mli_stack(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     n_layers, ctx = 8, args.ctx
-    cfg = D.DSAConfig(num_hidden_layers=n_layers, first_k_dense_replace=0)
+    tp = max(1, args.tp_emulate)
+    cfg = D.DSAConfig(num_hidden_layers=n_layers, first_k_dense_replace=0, num_attention_heads=128 // tp,
+                      intermediate_size=18432 // tp)
     torch.manual_seed(0)
     with torch.device(dev):
         model = D.DSAModel(cfg).to(torch.bfloat16).eval()
@@ -607,7 +612,9 @@ def run_mli_stack(args):
         "metric": "dsa_mli_layer_latency_us_ctx128k", "value": lag, "unit": "us/layer", "n_gpus": 1, "steps": reps,
         "warmup": 3, "ms_per_step": lag * n_layers / 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16 weights/activations, fp8 e4m3 index keys", "data": "synthetic",
-        "config": {"workload": "mli_lagged_8_layer_stack (BASELINE config 3)", "layers": n_layers, "context": ctx,
+        "config": {"workload": "mli_lagged_8_layer_stack (BASELINE config 3)" +
+                               ("" if tp == 1 else " with the per-GPU shapes of TP%d (no all-reduce)" % tp),
+                   "layers": n_layers, "context": ctx,
                    "hidden": cfg.hidden_size, "mla_heads": cfg.num_attention_heads, "intermediate": cfg.intermediate_size,
                    "weights_GB_per_layer": sum(p.numel() for p in model.layers[0].parameters()) * 2 / 1e9,
                    "l2": "1.19 GB of weights + 168 MB of caches per layer: larger than L2"},
