@@ -60,9 +60,8 @@ struct SmemLayout {
   static constexpr int red_off = p_off + kHB * kPPitch;         // float [2][4][16]
   static constexpr int valid_off = red_off + 2 * 4 * kHB * 4;   // int [64]
   static constexpr int bar_off = valid_off + kBN * 4;           // 2 mbarriers
-  static constexpr int stage_off = (bar_off + 16 + 15) & ~15;   // fp8 staging rows
-  static constexpr int bytes_bf16 = stage_off;
-  static constexpr int bytes_fp8 = stage_off + kBN * kFp8Row;
+  static constexpr int bytes_bf16 = (bar_off + 16 + 15) & ~15;
+  static constexpr int bytes_fp8 = bytes_bf16;  // fp8 rows are staged inside their own bf16 slots
 };
 
 // Barrier over the 128 attention threads (named barrier 1). The split-K body also
@@ -223,31 +222,97 @@ __device__ __forceinline__ void attend_tile(const uint8_t* s_q, const uint8_t* s
   }
 }
 
-// Dequantises the valid rows of a staged fp8 tile (656-B rows) into the bf16 K
-// tile: 128 words of 4 e4m3 + 32 words of rope per row.
-// With zero_invalid the masked rows are cleared here (they must be finite:
-// 0 * NaN would poison P.V); otherwise the caller has cleared them already.
+// Dequantises a staged fp8 tile (656-B rows) into the bf16 K tile. Work item =
+// one 16-byte chunk of a row: 32 chunks of 16 e4m3 (-> 32 B of bf16) and 8 chunks
+// of rope that are copied. Items are independent and the loop is unrolled, so
+// each thread keeps several shared-memory loads in flight (the tile is
+// latency-bound with four warps per CTA). With zero_invalid the masked rows are
+// cleared here (they must be finite: 0 * NaN would poison P.V); otherwise the
+// caller has cleared them already.
 __device__ __forceinline__ void dequant_tile(const uint8_t* s_stage, uint8_t* s_k, const int* s_valid, int tid,
                                              bool zero_invalid = false) {
-  for (int i = tid; i < kBN * 160; i += kThreads) {
-    const int row = i / 160, wd = i % 160;
+  constexpr int kChunks = 40;  // per row
+#pragma unroll 4
+  for (int i = tid; i < kBN * kChunks; i += kThreads) {
+    const int row = i / kChunks, c = i - row * kChunks;
     const uint8_t* src = s_stage + row * kFp8Row;
     uint8_t* dst = s_k + row * kRowPitch;
-    if (!s_valid[row]) {
-      if (zero_invalid) {
-        if (wd < 128) *reinterpret_cast<uint2*>(dst + wd * 8) = make_uint2(0, 0);
-        else *reinterpret_cast<uint32_t*>(dst + 1024 + (wd - 128) * 4) = 0;
+    const bool ok = s_valid[row] != 0;
+    if (!ok && !zero_invalid) continue;
+    if (c < 32) {
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+      if (ok) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
+        const float sc = *reinterpret_cast<const float*>(src + 512 + (c >> 3) * 4);
+        const uint2 d0 = dequant4(raw.x, sc), d1 = dequant4(raw.y, sc);
+        const uint2 d2 = dequant4(raw.z, sc), d3 = dequant4(raw.w, sc);
+        lo = make_uint4(d0.x, d0.y, d1.x, d1.y);
+        hi = make_uint4(d2.x, d2.y, d3.x, d3.y);
       }
-      continue;
-    }
-    if (wd < 128) {
-      const float sc = *reinterpret_cast<const float*>(src + 512 + (wd >> 5) * 4);
-      *reinterpret_cast<uint2*>(dst + wd * 8) = dequant4(*reinterpret_cast<const uint32_t*>(src + wd * 4), sc);
+      *reinterpret_cast<uint4*>(dst + c * 32) = lo;
+      *reinterpret_cast<uint4*>(dst + c * 32 + 16) = hi;
     } else {
-      *reinterpret_cast<uint32_t*>(dst + 1024 + (wd - 128) * 4) =
-          *reinterpret_cast<const uint32_t*>(src + 528 + (wd - 128) * 4);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (ok) v = *reinterpret_cast<const uint4*>(src + 528 + (c - 32) * 16);
+      *reinterpret_cast<uint4*>(dst + 1024 + (c - 32) * 16) = v;
     }
   }
+}
+
+// In-place variant for the split-K kernel: the 656 staged bytes of a row sit at
+// the END of that row's 1152-byte bf16 slot (offset 496), so no separate staging
+// buffer is needed and the fp8 path keeps two CTAs per SM. Expanding a chunk
+// overwrites bytes other threads may still have to read, so the tile is done in
+// three passes of "load into registers, barrier, store", ordered so that a pass
+// only overwrites sources of chunks already expanded or loaded:
+//   chunks 0..15  read [496,752)   write [0,512)
+//   chunks 16..23 read [752,880)   write [512,768)
+//   chunks 24..31 + rope read [880,1152) write [768,1152)
+// The four group scales sit at [1008,1024) and are read before the last stores.
+constexpr int kFp8StageOff = kRowBytes - kFp8Row;  // 496
+template <int FIRST, int NDEQ, int NROPE>
+__device__ __forceinline__ void dequant_pass(uint8_t* s_k, const int* s_valid, int tid) {
+  constexpr int kPerRow = NDEQ + NROPE;
+  constexpr int kPer = (kBN * kPerRow) / kThreads;
+  static_assert((kBN * kPerRow) % kThreads == 0, "items must divide evenly");
+  uint4 raw[kPer];
+  float sc[kPer];
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    const int i = tid + u * kThreads, row = i / kPerRow, k = i - row * kPerRow;
+    const uint8_t* src = s_k + row * kRowPitch + kFp8StageOff;
+    raw[u] = make_uint4(0, 0, 0, 0);
+    sc[u] = 0.f;
+    if (s_valid[row]) {
+      if (k < NDEQ) {
+        raw[u] = *reinterpret_cast<const uint4*>(src + (FIRST + k) * 16);
+        sc[u] = *reinterpret_cast<const float*>(src + 512 + ((FIRST + k) >> 3) * 4);
+      } else {
+        raw[u] = *reinterpret_cast<const uint4*>(src + 528 + (k - NDEQ) * 16);
+      }
+    }
+  }
+  cta128_sync();
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    const int i = tid + u * kThreads, row = i / kPerRow, k = i - row * kPerRow;
+    if (!s_valid[row]) continue;  // masked rows were cleared at gather time
+    uint8_t* rowp = s_k + row * kRowPitch;
+    if (k < NDEQ) {
+      const int c = FIRST + k;
+      const uint2 d0 = dequant4(raw[u].x, sc[u]), d1 = dequant4(raw[u].y, sc[u]);
+      const uint2 d2 = dequant4(raw[u].z, sc[u]), d3 = dequant4(raw[u].w, sc[u]);
+      *reinterpret_cast<uint4*>(rowp + c * 32) = make_uint4(d0.x, d0.y, d1.x, d1.y);
+      *reinterpret_cast<uint4*>(rowp + c * 32 + 16) = make_uint4(d2.x, d2.y, d3.x, d3.y);
+    } else {
+      *reinterpret_cast<uint4*>(rowp + 1024 + (k - NDEQ) * 16) = raw[u];
+    }
+  }
+}
+__device__ __forceinline__ void dequant_tile_inplace(uint8_t* s_k, const int* s_valid, int tid) {
+  dequant_pass<0, 16, 0>(s_k, s_valid, tid);
+  dequant_pass<16, 8, 0>(s_k, s_valid, tid);
+  dequant_pass<24, 8, 8>(s_k, s_valid, tid);
 }
 
 // Body of the split-K partials for CTA (split, hg, r); `smem` is the CTA's
@@ -260,7 +325,6 @@ __device__ __forceinline__ void mla_partials_body(const Params& p, const int spl
   float* s_red = reinterpret_cast<float*>(smem + SmemLayout::red_off);
   int* s_valid = reinterpret_cast<int*>(smem + SmemLayout::valid_off);
   uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + SmemLayout::bar_off);
-  uint8_t* s_stage = smem + SmemLayout::stage_off;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   DSA_KTIME_BEGIN(2);
@@ -313,8 +377,8 @@ __device__ __forceinline__ void mla_partials_body(const Params& p, const int spl
       if (ok) {
         fence_proxy_async_smem();  // earlier generic reads of this row precede the async write
         mbar_arrive_expect_tx(bar_k, row_bytes);
-        if (p.kv_fp8)
-          bulk_g2s(smem_u32(s_stage + tid * kFp8Row), kv_seq + idx * kFp8Row, kFp8Row, bar_k);
+        if (p.kv_fp8)  // staged at the end of the row's own slot, expanded in place below
+          bulk_g2s(smem_u32(dst_row + kFp8StageOff), kv_seq + idx * kFp8Row, kFp8Row, bar_k);
         else
           bulk_g2s(smem_u32(dst_row), kv_seq + idx * kRowBytes, kRowBytes, bar_k);
       } else {
@@ -327,7 +391,7 @@ __device__ __forceinline__ void mla_partials_body(const Params& p, const int spl
     if (tile == 0 && !mbar_wait(bar_q, 0)) timed_out = true;
     if (!mbar_wait(bar_k, tile & 1)) timed_out = true;
     if (timed_out) break;
-    if (p.kv_fp8) dequant_tile(s_stage, s_k, s_valid, tid);
+    if (p.kv_fp8) dequant_tile_inplace(s_k, s_valid, tid);
     cta128_sync();
 
     attend_tile(s_q, s_k, s_p, s_red, s_valid, p.scale_log2, warp, lane, m_run, l_run, acc);
