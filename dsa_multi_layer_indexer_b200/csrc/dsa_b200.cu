@@ -287,9 +287,11 @@ static int scan_common_checks(const uint8_t* index_q, const float* index_w, cons
 }
 
 static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
-  // about ctas_per_sm CTAs per SM in total, never more CTAs than tiles in a row
+  // One resident wave for a single row. A batch gets two waves: its rows differ in
+  // length, the grid is sized on the host without reading the lengths, and the
+  // second wave fills the SMs that the short rows' CTAs leave early.
   int per_row = env_int("DSA_SCAN_CTAS_PER_ROW", 0);
-  if (per_row <= 0) per_row = (ctas_per_sm * sm_count() + R - 1) / R;
+  if (per_row <= 0) per_row = ((R > 1 ? 2 : 1) * ctas_per_sm * sm_count() + R - 1) / R;
   if (per_row > tiles_per_row) per_row = tiles_per_row;
   if (per_row < 1) per_row = 1;
   return per_row;

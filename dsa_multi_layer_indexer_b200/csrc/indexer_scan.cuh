@@ -257,6 +257,18 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
     int it = 0;
     bool dead = false;
     uint32_t bin_lo = kHistBins, bin_hi = 0;
+    // Per-key scale of this thread's key in tile t (0 past the row's length). The
+    // scale of the NEXT tile is requested while the current one is processed, so
+    // its latency (two dependent loads in the paged layout) is off the critical path.
+    auto load_scale = [&](int t) -> float {
+      const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
+      if (t >= p.tiles_per_row || g >= len) return 0.f;
+      if (!p.paged) return kscale_row[int64_t(seq) * p.scale_seq_stride + g];
+      const int page = p.page_table[int64_t(r) * p.pt_stride + (g >> 6)];
+      return *reinterpret_cast<const float*>(p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES +
+                                             DSA_PAGE_TOKENS * kKeyBytes + (g & 63) * 4);
+    };
+    float next_scale = load_scale(bx);
     for (int t = bx; t < p.tiles_per_row; t += G) {
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
       if (int64_t(t) * kTileKeys >= len || dead) {  // no visible key in this tile
@@ -264,16 +276,8 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
         continue;
       }
       const bool valid = g < len;
-      float scale = 0.f;
-      if (valid) {
-        if (!p.paged) {
-          scale = kscale_row[int64_t(seq) * p.scale_seq_stride + g];
-        } else {
-          const int page = p.page_table[int64_t(r) * p.pt_stride + (g >> 6)];
-          scale = *reinterpret_cast<const float*>(p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES +
-                                                  DSA_PAGE_TOKENS * kKeyBytes + (g & 63) * 4);
-        }
-      }
+      const float scale = next_scale;
+      next_scale = load_scale(t + G);
       const int b = it & 1;
       const uint32_t bph = (it >> 1) & 1;
       ++it;
