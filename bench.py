@@ -510,7 +510,7 @@ def run_batch32_paged(args):
     hist = torch.zeros(B, ops.HIST_BINS, dtype=torch.int32, device=dev)
     ws = ops.topk_workspace(B, cap, dev)
     idx = torch.empty(B, TOPK, dtype=torch.int32, device=dev)
-    nsplit = 8
+    nsplit = ops.default_nsplit(B, HEADS, TOPK)
     scratch = ops.MlaScratch(B, HEADS, nsplit, dev)
     out = torch.empty(B, HEADS, 512, dtype=torch.bfloat16, device=dev)
 

@@ -17,7 +17,8 @@ CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB = PKG / "libdsa_b200.so"
 SOURCES = ["dsa_b200.cu"]
-HEADERS = ["common.cuh", "indexer_scan.cuh", "topk_select.cuh", "sparse_mla.cuh"]
+HEADERS = ["common.cuh", "indexer_scan.cuh", "topk_select.cuh", "sparse_mla.cuh", "sparse_mla_tc.cuh",
+           "fused_decode.cuh", "decode_prep.cuh"]
 PUBLIC_HEADER = PKG.parent / "include" / "dsa_b200.h"
 
 NVCC_FLAGS = [

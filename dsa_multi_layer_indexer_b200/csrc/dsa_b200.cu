@@ -13,6 +13,7 @@
 #include "fused_decode.cuh"
 #include "indexer_scan.cuh"
 #include "sparse_mla.cuh"
+#include "sparse_mla_tc.cuh"
 #include "topk_select.cuh"
 
 namespace dsa {
@@ -104,7 +105,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64];
+static bool g_opt_fused[64], g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -601,6 +602,20 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   int rc0 = mla_prepare(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
                         nsplit, sm_scale, kv_seq_stride, kv_fp8, true, &p);
   if (rc0) return rc0;
+  // Head counts that fill 64-row blocks go to the tcgen05 kernel once there are enough
+  // 64-head x 64-key tiles to give every SM more than one (a single row of 2048 keys
+  // is faster on the mma.sync kernel's 16-head CTAs); its splits are whole 64-key tiles.
+  const int tc_mode = env_int("DSA_MLA_TC", 1);  // 0 never, 1 by size, 2 whenever the head count allows
+  const int64_t tc_tiles = int64_t(R) * (H / mla_tc::kHG) * ((topk_k + mla_tc::kBN - 1) / mla_tc::kBN);
+  if (H % mla_tc::kHG == 0 && (tc_mode == 2 || (tc_mode == 1 && tc_tiles >= mla_tc::kMinTiles))) {
+    int kps = (topk_k + nsplit - 1) / nsplit;
+    p.keys_per_split = (kps + mla_tc::kBN - 1) / mla_tc::kBN * mla_tc::kBN;
+    int rc = opt_in_smem(mla_tc::sparse_mla_tc_kernel, mla_tc::Smem::bytes, g_opt_mla_tc);
+    if (rc) return rc;
+    DSA_CUDA(launch_pdl(mla_tc::sparse_mla_tc_kernel, dim3(nsplit, H / mla_tc::kHG, R), dim3(mla_tc::kThreads),
+                        mla_tc::Smem::bytes, static_cast<cudaStream_t>(stream), p));
+    return DSA_OK;
+  }
   const size_t smem = kv_fp8 ? mla::SmemLayout::bytes_fp8 : mla::SmemLayout::bytes_bf16;
   {
     int rc = opt_in_smem(mla::sparse_mla_partials_kernel, mla::SmemLayout::bytes_fp8, g_opt_mla);
@@ -616,7 +631,17 @@ int dsa_sparse_mla_combine(const float* part_acc, const float* part_m, const flo
   DSA_REQUIRE(part_acc && part_m && part_l && out, "sparse MLA combine: null pointer");
   DSA_REQUIRE(aligned16(part_acc) && aligned16(out), "sparse MLA combine: misaligned pointer");
   DSA_REQUIRE(R > 0 && R <= 65535 && H > 0 && nsplit > 0, "sparse MLA combine: bad geometry");
-  DSA_CUDA(launch_pdl(mla::sparse_mla_combine_kernel, dim3(H, R), dim3(mla::kCombineThreads), 0,
+  if (nsplit <= mla::kFlatMaxSplit && int64_t(R) * H >= 512) {
+    // many (row, head) pairs, few splits: one thread per four output columns
+    const int64_t n_pairs = int64_t(R) * H;
+    DSA_CUDA(launch_pdl(mla::sparse_mla_combine_flat_kernel, dim3(unsigned((n_pairs * 128 + 255) / 256)), dim3(256),
+                        0, static_cast<cudaStream_t>(stream), part_acc, part_m, part_l,
+                        static_cast<__nv_bfloat16*>(out), H, nsplit, n_pairs));
+    return DSA_OK;
+  }
+  // one load group of 128 threads per split, up to four
+  const int combine_threads = 128 * (nsplit < 4 ? nsplit : 4);
+  DSA_CUDA(launch_pdl(mla::sparse_mla_combine_kernel, dim3(H, R), dim3(combine_threads), 0,
                       static_cast<cudaStream_t>(stream), part_acc, part_m, part_l,
                       static_cast<__nv_bfloat16*>(out), H, nsplit));
   return DSA_OK;

@@ -624,9 +624,9 @@ sparse_mla_cluster_kernel(const Params p, __nv_bfloat16* __restrict__ out) {
 
 // out = sum_s acc_s 2^(m_s - m) / sum_s l_s 2^(m_s - m); splits with m = -inf
 // (no visible key) are skipped, a row with none yields zeros. One CTA per (row,
-// head): four groups of 128 threads each fold a quarter of the splits (group g
-// takes s = g, g + 4, ...) with all loads of a chunk of eight splits in flight
-// at once, then group 0 merges the four group results in a fixed order.
+// head) of 1..4 groups of 128 threads (the launch picks min(nsplit, 4)): group g
+// folds splits g, g + ngrp, ... with all loads of a chunk of eight splits in
+// flight at once, then group 0 merges the group results in a fixed order.
 constexpr int kCombineThreads = 512;
 __global__ void __launch_bounds__(kCombineThreads)
 sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
@@ -635,6 +635,7 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
   __shared__ float s_m[4], s_l[4];
   __shared__ __align__(16) float s_o[4][kDV];
   const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x & 127, grp = threadIdx.x >> 7;
+  const int ngrp = blockDim.x >> 7;  // 1..4 load groups of 128 threads, each taking every ngrp-th split
   DSA_KTIME_BEGIN(3);
   pdl_wait();
   pdl_launch_dependents();
@@ -643,12 +644,12 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
   const float* pa = part_acc + (int64_t(r) * nsplit * H + h) * kDV + tid * 4;
   float mg = -INFINITY, lg = 0.f;
   float4 og = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s0 = grp; s0 < nsplit; s0 += 32) {
+  for (int s0 = grp; s0 < nsplit; s0 += 8 * ngrp) {
     float ms[8], ls[8];
     float4 a[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      const int sp = s0 + 4 * u;
+      const int sp = s0 + ngrp * u;
       const bool ok = sp < nsplit;
       ms[u] = ok ? pm[int64_t(sp) * H] : -INFINITY;
       ls[u] = ok ? pl[int64_t(sp) * H] : 0.f;
@@ -683,12 +684,12 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
   *reinterpret_cast<float4*>(&s_o[grp][tid * 4]) = og;
   __syncthreads();
   if (grp == 0) {
-    const float m = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float m = s_m[0];
+    for (int gi = 1; gi < ngrp; ++gi) m = fmaxf(m, s_m[gi]);
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     float l = 0.f;
     if (m != -INFINITY) {
-#pragma unroll
-      for (int gi = 0; gi < 4; ++gi) {
+      for (int gi = 0; gi < ngrp; ++gi) {
         const float e = (s_m[gi] == -INFINITY) ? 0.f : exp2f(s_m[gi] - m);
         const float4 a = *reinterpret_cast<const float4*>(&s_o[gi][tid * 4]);
         l = fmaf(s_l[gi], e, l);
@@ -705,6 +706,59 @@ sparse_mla_combine_kernel(const float* __restrict__ part_acc, const float* __res
     pk.x = *reinterpret_cast<uint32_t*>(&lo);
     pk.y = *reinterpret_cast<uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(out + (int64_t(r) * H + h) * kDV + tid * 4) = pk;
+  }
+  DSA_KTIME_END(3);
+}
+
+// The same merge for many (row, head) pairs with at most eight splits each (large
+// batches): one thread per four output columns, every load of a thread in flight
+// at once, no shared memory. Splits are folded in ascending order.
+constexpr int kFlatMaxSplit = 8;
+__global__ void __launch_bounds__(256)
+sparse_mla_combine_flat_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
+                               const float* __restrict__ part_l, __nv_bfloat16* __restrict__ out, int H,
+                               int nsplit, int64_t n_pairs) {
+  DSA_KTIME_BEGIN(3);
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t gid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t pair = gid >> 7;  // row * H + head
+  const int c4 = int(gid & 127);
+  if (pair < n_pairs) {
+    const int64_t r = pair / H, h = pair % H;
+    float ms[kFlatMaxSplit], ls[kFlatMaxSplit];
+    float4 a[kFlatMaxSplit];
+#pragma unroll
+    for (int u = 0; u < kFlatMaxSplit; ++u) {
+      const bool ok = u < nsplit;
+      const int64_t row = (r * nsplit + u) * H + h;
+      ms[u] = ok ? part_m[row] : -INFINITY;
+      ls[u] = ok ? part_l[row] : 0.f;
+      a[u] = ok ? *reinterpret_cast<const float4*>(part_acc + row * kDV + c4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float m = ms[0];
+#pragma unroll
+    for (int u = 1; u < kFlatMaxSplit; ++u) m = fmaxf(m, ms[u]);
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int u = 0; u < kFlatMaxSplit; ++u) {
+        const float e = (ms[u] == -INFINITY) ? 0.f : exp2f(ms[u] - m);
+        l = fmaf(ls[u], e, l);
+        o.x = fmaf(a[u].x, e, o.x);
+        o.y = fmaf(a[u].y, e, o.y);
+        o.z = fmaf(a[u].z, e, o.z);
+        o.w = fmaf(a[u].w, e, o.w);
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + pair * kDV + c4 * 4) = pk;
   }
   DSA_KTIME_END(3);
 }
