@@ -288,11 +288,11 @@ static int scan_common_checks(const uint8_t* index_q, const float* index_w, cons
 }
 
 static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
-  // One resident wave for a single row. A batch gets two waves: its rows differ in
-  // length, the grid is sized on the host without reading the lengths, and the
-  // second wave fills the SMs that the short rows' CTAs leave early.
+  // One resident wave for a single row. A batch gets about 1.75 waves: its rows
+  // differ in length, the grid is sized on the host without reading the lengths,
+  // and the later CTAs fill the SMs that the short rows' CTAs leave early.
   int per_row = env_int("DSA_SCAN_CTAS_PER_ROW", 0);
-  if (per_row <= 0) per_row = ((R > 1 ? 2 : 1) * ctas_per_sm * sm_count() + R - 1) / R;
+  if (per_row <= 0) per_row = ((R > 1 ? 7 : 4) * ctas_per_sm * sm_count() / 4 + R - 1) / R;
   if (per_row > tiles_per_row) per_row = tiles_per_row;
   if (per_row < 1) per_row = 1;
   return per_row;
@@ -300,7 +300,10 @@ static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
 
 // Two shapes of the same kernel: two CTAs per SM with a 4-slot ring (default), or
 // one CTA per SM with a 10-slot ring (DSA_SCAN_DEEP=1).
-static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p, int R, cudaStream_t st) {
+static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p_in, int R, cudaStream_t st) {
+  scan::Params p = p_in;
+  // ragged batch: long rows first (DSA_SCAN_BALANCE=0 keeps grid row y on batch row y)
+  p.balance_rows = (R > 1 && R <= 32 && p.seq_lens && env_int("DSA_SCAN_BALANCE", 1) != 0) ? R : 0;
   static const bool deep = env_int("DSA_SCAN_DEEP", 0) != 0;
   if (deep) {
     constexpr size_t smem = scan::smem_bytes<scan::kStagesOnePerSm>();

@@ -54,6 +54,7 @@ struct Params {
   int n_heads;
   int tiles_per_row;
   int paged;
+  int balance_rows;  // > 1: CTAs of grid row y work on the row with the y-th longest sequence (rows <= 32)
 };
 
 template <int kStages>
@@ -82,13 +83,28 @@ __device__ __forceinline__ int row_len(const Params& p, int r) {
   return static_cast<int>(len);
 }
 
+// Row with the y-th longest sequence among rows [0, R), R <= 32 (ties: lower row
+// first). Called by whole warps. A grid is scheduled in block order, so a ragged
+// batch starts its long rows first and the short rows fill the tail.
+__device__ __forceinline__ int row_of_rank(const Params& p, int y, int R) {
+  const int lane = threadIdx.x & 31;
+  const int mine = lane < R ? row_len(p, lane) : -1;
+  int rank = 0;
+  for (int j = 0; j < R; ++j) {
+    const int other = __shfl_sync(0xffffffffu, mine, j);
+    rank += (other > mine || (other == mine && j < lane)) ? 1 : 0;
+  }
+  const uint32_t hit = __ballot_sync(0xffffffffu, lane < R && rank == y);
+  return hit ? __ffs(hit) - 1 : y;
+}
+
 // Body of the scan for CTA `bx` of `G` working on row `r` (the kernel below
 // passes its block indices; the fused indexer + attention launch passes indices
 // of its scan partition). `tmap_ptr` must point at a __grid_constant__ kernel
 // parameter; `smem_raw` is the CTA's dynamic shared memory.
 template <int kStages>
 __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const Params& p, const int bx,
-                                             const int G, const int r, uint8_t* smem_raw) {
+                                             const int G, const int r_grid, uint8_t* smem_raw) {
   const CUtensorMap& tmap = *tmap_ptr;
   constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
   // 1024-byte alignment for the swizzled tiles, computed on the shared-window
@@ -103,10 +119,9 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int seq = r / p.rows_per_seq;
-  int len = 0;  // read after the dependency wait below
+  int r = r_grid, seq = 0, len = 0;  // settled after the dependency wait below
   const bool want_hist = p.hist != nullptr;
-  const int stamp_cta = r * G + bx;
+  const int stamp_cta = r_grid * G + bx;
   DSA_STAMP(stamp_cta, 0);
   DSA_KTIME_BEGIN(0);
   if (tid == 0) prefetch_tensor_map(&tmap);
@@ -153,6 +168,8 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   pdl_wait();  // keys, query, weights and lengths may come from the previous kernel
   pdl_launch_dependents();
   DSA_STAMP(stamp_cta, 13);
+  if (p.balance_rows > 1) r = row_of_rank(p, r_grid, p.balance_rows);
+  seq = r / p.rows_per_seq;
   len = row_len(p, r);
   // q[r] is [n_heads][128 B]. Its loads (and the head weights') are issued before
   // the key tiles' so they are not queued behind 64 KB of TMA traffic per CTA.
