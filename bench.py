@@ -410,7 +410,7 @@ def run_ours(args):
         e2e_dt = (time.perf_counter() - t0) / args.steps
         e2e = {"value": 1.0 / e2e_dt, "unit": UNIT, "ms_per_step": e2e_dt * 1e3,
                "h2d_bytes_per_step": dec[0].h2d_bytes, "d2h_bytes_per_step": dec[0].d2h_bytes,
-               "note": "pinned host operands -> device, graph replay, output + selection -> host, sync every step"}
+               "note": "one graph per step: pinned host operands -> device (q copied beside the scan), kernels, selection -> host on a forked stream, attention output written straight into pinned host memory; sync every step"}
 
     _lib.check_device_status()
     times = torch.tensor([ms_step, scan_ms, topk_ms, attn_ms, e2e["ms_per_step"] if e2e else 0.0],

@@ -180,12 +180,9 @@ sparse_mla_tc_kernel(const mla::Params p) {
     int64_t idx_next[4];
     load_idx(0, idx_next);
     bool q_signalled = false;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int s = t & 1;
-      const uint32_t stage = s_k + uint32_t(s) * kTileBytes;
-      DSA_STAMP_IF(ptid == 0 && t == 4, scta, 0);
-      const uint8_t* src[4];
-      uint32_t vword = 0;
+    // rows of tile t handled by this thread (nullptr: masked key) and the tile's validity bits
+    auto resolve = [&](const uint8_t* (&src)[4], uint32_t& vword) {
+      vword = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const bool ok = idx_next[k] >= 0 && idx_next[k] < len;
@@ -193,9 +190,16 @@ sparse_mla_tc_kernel(const mla::Params p) {
         const uint32_t b = __ballot_sync(0xffffffffu, ok);
         vword |= (((b >> 0) & 1u) | (((b >> 8) & 1u) << 1) | (((b >> 16) & 1u) << 2) | (((b >> 24) & 1u) << 3)) << (4 * k);
       }
-      load_idx(t + 1, idx_next);  // in flight during the waits below
-
-      if (!p.kv_fp8) {
+    };
+    if (!p.kv_fp8) {
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t & 1;
+        const uint32_t stage = s_k + uint32_t(s) * kTileBytes;
+        DSA_STAMP_IF(ptid == 0 && t == 4, scta, 0);
+        const uint8_t* src[4];
+        uint32_t vword;
+        resolve(src, vword);
+        load_idx(t + 1, idx_next);  // in flight during the waits below
         if (t >= 1) {
           // tile t-1 (and the queries) have landed: publish them before waiting for a free slot
           cp_async_wait_all();
@@ -222,51 +226,58 @@ sparse_mla_tc_kernel(const mla::Params p) {
         }
         cp_async_commit();
         DSA_STAMP_IF(ptid == 0 && t == 4, scta, 4);
-      } else {
-        // fp8 rows: 512 e4m3 | 4 fp32 group scales | 64 bf16 rope. Unit u = v8 + 8 g of the
-        // e4m3 part belongs to scale group g and expands to bf16 units 2u, 2u + 1.
-        // Two rows are loaded into registers at a time; the first pair is requested
-        // before the wait for a free slot.
+      }
+    } else {
+      // fp8 rows: 512 e4m3 | 4 fp32 group scales | 64 bf16 rope. Unit u = v8 + 8 g of the
+      // e4m3 part belongs to scale group g and expands to bf16 units 2u, 2u + 1. The raw
+      // bytes of tile t + 1 are requested into registers as soon as tile t is stored, so
+      // they travel while the slot of tile t + 1 is still being read by the tensor core.
+      uint4 raw[4][4], rope[4], sc4[4];
+      uint32_t vword = 0;
+      auto request = [&]() {
+        const uint8_t* src[4];
+        resolve(src, vword);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint4 raw[2][4], rope[2], sc4[2];
+        for (int k = 0; k < 4; ++k) {
+          if (src[k]) {
 #pragma unroll
-          for (int kk = 0; kk < 2; ++kk) {
-            const uint8_t* sp = src[half * 2 + kk];
-            if (sp) {
+            for (int g = 0; g < 4; ++g) raw[k][g] = ld_global_nc_v4(src[k] + (v8 + 8 * g) * 16);
+            sc4[k] = ld_global_nc_v4(src[k] + 512);
+            rope[k] = ld_global_nc_v4(src[k] + 528 + v8 * 16);
+          } else {
 #pragma unroll
-              for (int g = 0; g < 4; ++g) raw[kk][g] = ld_global_nc_v4(sp + (v8 + 8 * g) * 16);
-              sc4[kk] = ld_global_nc_v4(sp + 512);
-              rope[kk] = ld_global_nc_v4(sp + 528 + v8 * 16);
-            } else {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) raw[kk][g] = make_uint4(0, 0, 0, 0);
-              sc4[kk] = make_uint4(0, 0, 0, 0);
-              rope[kk] = make_uint4(0, 0, 0, 0);
-            }
-          }
-          if (half == 0) {
-            if (__any_sync(0xffffffffu, t >= 2 && !mbar_wait(bar(kBarKFree + s), ((t >> 1) - 1) & 1))) failed = true;
-            if (lane == 0) s_validw[s * 4 + (warp - kProducerWarp0)] = vword;
-          }
-          if (failed) break;
-#pragma unroll
-          for (int kk = 0; kk < 2; ++kk) {
-            const int row = rsub + 16 * (half * 2 + kk);
-            const float scs[4] = {__uint_as_float(sc4[kk].x), __uint_as_float(sc4[kk].y),
-                                  __uint_as_float(sc4[kk].z), __uint_as_float(sc4[kk].w)};
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const uint2 d0 = mla::dequant4(raw[kk][g].x, scs[g]), d1 = mla::dequant4(raw[kk][g].y, scs[g]);
-              const uint2 d2 = mla::dequant4(raw[kk][g].z, scs[g]), d3 = mla::dequant4(raw[kk][g].w, scs[g]);
-              const int u = 2 * (v8 + 8 * g);
-              st_shared_v4(stage + swz(row, u), make_uint4(d0.x, d0.y, d1.x, d1.y));
-              st_shared_v4(stage + swz(row, u + 1), make_uint4(d2.x, d2.y, d3.x, d3.y));
-            }
-            st_shared_v4(stage + swz(row, 64 + v8), rope[kk]);
+            for (int g = 0; g < 4; ++g) raw[k][g] = make_uint4(0, 0, 0, 0);
+            sc4[k] = make_uint4(0, 0, 0, 0);
+            rope[k] = make_uint4(0, 0, 0, 0);
           }
         }
-        if (failed) break;
+      };
+      if (n_tiles > 0) {
+        request();
+        load_idx(1, idx_next);
+      }
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t & 1;
+        const uint32_t stage = s_k + uint32_t(s) * kTileBytes;
+        DSA_STAMP_IF(ptid == 0 && t == 4, scta, 0);
+        if (__any_sync(0xffffffffu, t >= 2 && !mbar_wait(bar(kBarKFree + s), ((t >> 1) - 1) & 1))) { failed = true; break; }
+        DSA_STAMP_IF(ptid == 0 && t == 4, scta, 3);
+        if (lane == 0) s_validw[s * 4 + (warp - kProducerWarp0)] = vword;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int row = rsub + 16 * k;
+          const float scs[4] = {__uint_as_float(sc4[k].x), __uint_as_float(sc4[k].y),
+                                __uint_as_float(sc4[k].z), __uint_as_float(sc4[k].w)};
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint2 d0 = mla::dequant4(raw[k][g].x, scs[g]), d1 = mla::dequant4(raw[k][g].y, scs[g]);
+            const uint2 d2 = mla::dequant4(raw[k][g].z, scs[g]), d3 = mla::dequant4(raw[k][g].w, scs[g]);
+            const int u = 2 * (v8 + 8 * g);
+            st_shared_v4(stage + swz(row, u), make_uint4(d0.x, d0.y, d1.x, d1.y));
+            st_shared_v4(stage + swz(row, u + 1), make_uint4(d2.x, d2.y, d3.x, d3.y));
+          }
+          st_shared_v4(stage + swz(row, 64 + v8), rope[k]);
+        }
         if (!q_signalled) {
           cp_async_wait_all();
           q_signalled = true;
@@ -275,6 +286,11 @@ sparse_mla_tc_kernel(const mla::Params p) {
         }
         fence_proxy_async_smem();
         mbar_arrive(bar(kBarKFull + s));
+        DSA_STAMP_IF(ptid == 0 && t == 4, scta, 4);
+        if (t + 1 < n_tiles) {
+          request();
+          load_idx(t + 2, idx_next);
+        }
       }
     }
     cp_async_wait_all();  // never leave with a copy in flight

@@ -126,7 +126,6 @@ class HostDecoder:
 
     def __init__(self, state: HotPathState, cache: LayerCache, sm_scale: float) -> None:
         self.state, self.cache = state, cache
-        self.graph = state.capture(cache, sm_scale)
         s = state
         # pinned mirrors of the two arenas, with the same views into them
         self.h_in = torch.zeros(s.in_arena.shape, dtype=torch.uint8).pin_memory()
@@ -138,6 +137,39 @@ class HostDecoder:
         self.h_q = self.h_in[nq + nw:].view(torch.bfloat16).view(s.q.shape)
         self.h_out = self.h_outbuf[:no].view(torch.bfloat16).view(s.out.shape)
         self.h_indices = self.h_outbuf[no:].view(torch.int32).view(s.indices.shape)
+        # One graph holds the whole step (input copy, kernels, selection copy), so a
+        # step is a single launch on the host.
+        self._side = torch.cuda.Stream()
+        warm = torch.cuda.Stream()
+        warm.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(warm):
+            self._body(sm_scale)
+        torch.cuda.current_stream().wait_stream(warm)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._body(sm_scale)
+
+    def _body(self, sm_scale: float) -> None:
+        s = self.state
+        main, side = torch.cuda.current_stream(), self._side
+        # H2D in two pieces: index_q | index_w (8 KB, needed by the scan at once) on the
+        # main stream, q (needed only by the attention) on a forked stream beside the scan.
+        small = s.index_q.numel() + s.index_w.numel() * 4
+        side.wait_stream(main)
+        s.in_arena[:small].copy_(self.h_in[:small], non_blocking=True)
+        with torch.cuda.stream(side):
+            s.in_arena[small:].copy_(self.h_in[small:], non_blocking=True)
+        s.run_indexer(self.cache)
+        main.wait_stream(side)
+        # The selection goes back on the forked stream while the attention runs, and the
+        # attention's merge kernel writes its output straight into the pinned host
+        # buffer, so no device-to-host copy is left on the step's critical path.
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            self.h_indices.copy_(s.indices, non_blocking=True)
+        ops.sparse_mla_decode(s.q, self.cache.kv, s.indices, sm_scale, s.seq_lens, scratch=s.scratch,
+                              out=self.h_out)
+        main.wait_stream(side)
 
     @property
     def h2d_bytes(self) -> int:
@@ -148,9 +180,8 @@ class HostDecoder:
         return self.h_outbuf.numel()
 
     def step(self) -> torch.Tensor:
-        s = self.state
-        s.in_arena.copy_(self.h_in, non_blocking=True)       # one H2D copy: index_q | index_w | q
+        """Fill ``h_index_q``/``h_index_w``/``h_q`` first; returns ``h_out`` (and
+        ``h_indices`` is valid) once the step has completed."""
         self.graph.replay()
-        self.h_outbuf.copy_(s.out_arena, non_blocking=True)  # one D2H copy: out | indices
         torch.cuda.current_stream().synchronize()
         return self.h_out

@@ -47,6 +47,14 @@ def _cuda_contig(t: torch.Tensor, name: str, dtypes) -> None:
     _need(t.dtype in dtypes, f"{name} has dtype {t.dtype}, expected one of {dtypes}")
 
 
+def _out_contig(t: torch.Tensor, name: str, dtypes) -> None:
+    """An output may also live in pinned host memory (it is mapped into the device's
+    address space): the kernel then writes the result straight to the host."""
+    _need(t.is_cuda or t.is_pinned(), f"{name} must be a CUDA tensor or pinned host memory")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    _need(t.dtype in dtypes, f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+
+
 def _lens(seq_lens: Optional[torch.Tensor], rows: int) -> Optional[torch.Tensor]:
     if seq_lens is not None:
         _cuda_contig(seq_lens, "seq_lens", (torch.int32,))
@@ -309,7 +317,7 @@ def sparse_mla_decode(
     _need(scratch.rows >= R and scratch.heads == H and scratch.nsplit == nsplit, "scratch does not match the launch")
     if out is None:
         out = torch.empty(R, H, VALUE_DIM, dtype=torch.bfloat16, device=q.device)
-    _cuda_contig(out, "out", (torch.bfloat16,))
+    _out_contig(out, "out", (torch.bfloat16,))
     if stage == "both":
         _lib.check(_lib.lib().dsa_sparse_mla_decode(
             _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),

@@ -1,0 +1,71 @@
+"""GPU tests of the decode-time driver: the persistent-buffer step, its CUDA
+graph, and the host-buffer form whose copies are nodes of the same graph and
+whose attention output is written straight into pinned host memory."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import dsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(ctx=8192, heads=32, index_heads=64, topk=2048, seed=5):
+    from dsa_multi_layer_indexer_b200 import ops
+    from dsa_multi_layer_indexer_b200.decode import HotPathState, LayerCache
+
+    g = torch.Generator().manual_seed(seed)
+    iq = torch.randn(1, index_heads, 128, generator=g)
+    ik = torch.randn(ctx, 128, generator=g)
+    w = torch.randn(1, index_heads, generator=g) / 8
+    iq8, ik8, wp, sk = O.make_fp8_indexer_inputs(iq, ik, w)
+    q = torch.randn(1, heads, 576, generator=g).to(torch.bfloat16)
+    kv = torch.randn(1, ctx, 576, generator=g).to(torch.bfloat16)
+    cache = LayerCache(ik8.view(torch.uint8).view(1, ctx, 128).cuda(), sk.view(1, ctx).cuda(), kv.cuda())
+    st = HotPathState(1, heads, index_heads, ctx, topk, "cuda")
+    host = dict(iq8=iq8.view(torch.uint8).view(1, index_heads, 128), w=wp.view(1, index_heads), q=q)
+    st.index_q.copy_(host["iq8"])
+    st.index_w.copy_(host["w"])
+    st.q.copy_(q)
+    st.seq_lens.fill_(ctx - 3)
+    return ops, st, cache, host
+
+
+def test_step_graph_and_host_decoder_agree():
+    from dsa_multi_layer_indexer_b200 import _lib
+    from dsa_multi_layer_indexer_b200.decode import HostDecoder
+
+    ops, st, cache, host = make_case()
+    sm = 192 ** -0.5
+    eager = st.run(cache, sm).clone()
+    idx_eager = st.indices.clone()
+    # the three launches, called one by one through ops, give the same answer
+    logits = ops.indexer_scan_fp8(st.index_q, st.index_w, cache.index_k, cache.k_scale, st.seq_lens, ctx=st.capacity)
+    idx = ops.topk_select(logits, st.topk, st.seq_lens)
+    assert torch.equal(idx, idx_eager)
+    out = ops.sparse_mla_decode(st.q, cache.kv, idx, sm, st.seq_lens, nsplit=st.nsplit)
+    assert torch.equal(out, eager)
+    # captured graph
+    graph = st.capture(cache, sm)
+    st.out.zero_()
+    st.indices.fill_(-7)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(st.out, eager) and torch.equal(st.indices, idx_eager)
+    # host buffers in, host buffers out, twice in a row
+    dec = HostDecoder(st, cache, sm)
+    dec.h_index_q.copy_(host["iq8"])
+    dec.h_index_w.copy_(host["w"])
+    dec.h_q.copy_(host["q"])
+    for _ in range(2):
+        st.in_arena.zero_()  # the step must bring its own inputs
+        dec.h_out.zero_()
+        dec.h_indices.fill_(-7)
+        got = dec.step()
+        assert not got.is_cuda
+        assert torch.equal(got, eager.cpu())
+        assert torch.equal(dec.h_indices, idx_eager.cpu())
+    assert dec.h2d_bytes == st.in_arena.numel() and dec.d2h_bytes == st.out_arena.numel()
+    _lib.check_device_status()
