@@ -138,8 +138,17 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 // Bounded wait on a phase parity. Returns false when the limit ran out: the
 // caller records a status bit and leaves its loop instead of spinning forever.
+// The limit is wall time (a probe may itself suspend the thread for a while, so an
+// iteration count alone would not bound it), checked every 256 probes.
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr unsigned long long kWaitLimitNs = 200ull * 1000 * 1000;
+__device__ __forceinline__ unsigned long long wall_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  unsigned long long t0 = 0;
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     uint32_t done;
     asm volatile(
@@ -150,10 +159,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
+    if ((i & 255u) == 255u) {
+      const unsigned long long now = wall_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) return false;
+    }
   }
   return false;
 }
-
 // Non-blocking probe of a phase parity.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t done;

@@ -15,7 +15,9 @@
 // O^T puts the 512 value dims on the 128 TMEM lanes (4 blocks of 64 columns) and
 // the heads on columns, which is what lets 64 heads x 512 dims fit in 256 of the
 // 512 columns next to two S buffers. S is issued as a 128-row MMA whose rows
-// 64..127 read the bytes after the Q chunk and land in TMEM lanes nobody reads.
+// 64..127 read the bytes after the Q chunk and land in TMEM lanes nobody reads
+// (a 64-row MMA was measured: it takes the same time and spreads the rows over
+// 16 lanes of each lane quadrant, which only costs the softmax half its lanes).
 //
 // Warp roles (384 threads): a warp reaches the TMEM lane quadrant (warp % 4).
 // Warps 0,1 and 4,5 run the softmax on the 64 real S rows (thread = head; warps 0,1
@@ -363,7 +365,8 @@ sparse_mla_tc_kernel(const mla::Params p) {
       const int s = t & 1;
       float x[32];
       if (soft) {
-        if (!mbar_wait(bar(kBarSFull + s), (t >> 1) & 1)) failed = true;
+        // (tcgen05.ld is warp-collective, so the outcome of the wait is made warp-uniform)
+        failed = __any_sync(0xffffffffu, failed || !mbar_wait(bar(kBarSFull + s), (t >> 1) & 1));
         tc_fence_after();
         DSA_STAMP_IF(tid == 0 && t == 4, scta, 9);
         float m_loc = -INFINITY;
@@ -391,7 +394,8 @@ sparse_mla_tc_kernel(const mla::Params p) {
       if (soft) m_tile = fmaxf(s_max[(s * 2) * kHG + head], s_max[(s * 2 + 1) * kHG + head]);
       if (s_flag[s]) {
         // rare: some head's maximum ran away from its reference; scale its O^T column
-        if (t >= 1 && !mbar_wait(bar(kBarKFree + ((t - 1) & 1)), ((t - 1) >> 1) & 1)) failed = true;
+        if (__any_sync(0xffffffffu, t >= 1 && !mbar_wait(bar(kBarKFree + ((t - 1) & 1)), ((t - 1) >> 1) & 1)))
+          failed = true;
         tc_fence_after();
         if (soft) {
           float f = 1.f;
@@ -456,8 +460,8 @@ sparse_mla_tc_kernel(const mla::Params p) {
     if (warp < 4) {
       // ---- partials of this split: O^T (lane = value dim, column = head), reference m, sum l
       const int64_t pbase = (int64_t(r) * p.nsplit + split) * p.H + hg * kHG;
-      bool have = n_tiles > 0 && !failed;
-      if (have && !mbar_wait(bar(kBarOFull), 0)) have = false, failed = true;
+      bool have = n_tiles > 0 && !__any_sync(0xffffffffu, failed);
+      if (__any_sync(0xffffffffu, have && !mbar_wait(bar(kBarOFull), 0))) have = false, failed = true;
       tc_fence_after();
       DSA_STAMP(scta, 7);
 #pragma unroll 1
