@@ -1,0 +1,161 @@
+"""GPU tests of the serving-shaped entry (paged index keys, a slot-addressed latent
+pool, per-row lengths on the device) against the CPU oracle: the reference
+overlay's `_hh_fused_hide_decode_paged` contract (patch :1282-1548)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import corr_diff, rel_err
+from oracle import dsa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ATTN_TOL = 2e-2
+LOGIT_TOL = 1e-2
+
+
+def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=31):
+    g = torch.Generator().manual_seed(seed)
+    lens = [cap, 700, 1300][:B]
+    pages_per = cap // 64
+    num_pages = B * pages_per + 5
+    perm = torch.randperm(num_pages, generator=g)[:B * pages_per].view(B, pages_per).int()
+    pool_pages = torch.zeros(num_pages, 8448, dtype=torch.uint8)
+    iq = torch.randn(B, hidx, 128, generator=g)
+    w = torch.randn(B, hidx, generator=g) / 8
+    iq8 = torch.empty(B, hidx, 128, dtype=torch.uint8)
+    wp = torch.empty(B, hidx)
+    ref_logits = torch.full((B, cap), float("-inf"))
+    # latent rows live in one pool addressed by KV slot = page * 64 + offset
+    lat = torch.randn(num_pages * 64, 576, generator=g)
+    for b in range(B):
+        ik = torch.randn(cap, 128, generator=g)
+        q8, k8, wf, sk = O.make_fp8_indexer_inputs(iq[b:b + 1], ik, w[b:b + 1])
+        lg = O.indexer_logits_fp8(q8, k8, wf, sk)
+        sk_m, _ = O.enforce_topk_margin(lg[0, :lens[b]], sk[:lens[b]], topk)
+        sk = sk.clone()
+        sk[:lens[b]] = sk_m.float()
+        sk_full = sk
+        O.pack_index_pages(k8.view(torch.uint8), sk_full, perm[b].tolist(), num_pages, pool_pages)
+        iq8[b], wp[b] = q8.view(torch.uint8)[0], wf[0]
+        ref_logits[b, :lens[b]] = O.indexer_logits_fp8(q8, k8[:lens[b]], wf, sk[:lens[b]])[0]
+    pos2slot = (perm.long().repeat_interleave(64, dim=1) * 64 + torch.arange(64).repeat(pages_per)).int()
+    kv_pool = O.pack_fp8_latent(lat) if fp8_pool else lat.to(torch.bfloat16)
+    kv_ref = O.unpack_fp8_latent(kv_pool) if fp8_pool else kv_pool
+    q = torch.randn(1, B, heads, 576, generator=g).to(torch.bfloat16)
+    inc = torch.stack([pos2slot[b, torch.randperm(lens[b], generator=g)[:topk].sort().values.long()
+                                  if lens[b] >= topk else
+                                  torch.cat([torch.arange(lens[b]), torch.zeros(topk - lens[b], dtype=torch.long)])]
+                       for b in range(B)]).int()
+    for b in range(B):
+        if lens[b] < topk:
+            inc[b, lens[b]:] = -1
+    inc[:, 5::37] = -1  # padding entries are skipped
+    return dict(B=B, cap=cap, heads=heads, hidx=hidx, topk=topk, lens=lens, q=q, kv_pool=kv_pool, kv_ref=kv_ref,
+                inc=inc, iq8=iq8, wp=wp, pages=pool_pages, pt=perm, pos2slot=pos2slot, ref_logits=ref_logits)
+
+
+def call(case, **kw):
+    from dsa_multi_layer_indexer_b200 import serving
+
+    c = case
+    d = lambda t: t.cuda().contiguous()
+    return serving.fused_hide_decode_paged(
+        d(c["q"]), d(c["kv_pool"]), d(c["inc"]), d(c["iq8"]), d(c["wp"]), d(c["pages"]), d(c["pt"]),
+        d(torch.tensor(c["lens"], dtype=torch.int32)), c["cap"], 192 ** -0.5, kw.pop("pool_map", d(c["pos2slot"])), **kw)
+
+
+def ref_attention(c):
+    out = torch.zeros(c["B"], c["heads"], 512)
+    n = c["kv_ref"].shape[0]
+    for b in range(c["B"]):
+        out[b] = O.sparse_mla_decode(c["q"][0, b:b + 1], c["kv_ref"], c["inc"][b:b + 1], [n], 192 ** -0.5)[0]
+    return out
+
+
+def ref_next(c):
+    want = []
+    for b in range(c["B"]):
+        pos = O.select_topk(c["ref_logits"][b:b + 1], c["topk"], -1)[0]
+        want.append(sorted(int(c["pos2slot"][b, p]) for p in pos.tolist() if p >= 0))
+    return want
+
+
+@pytest.mark.parametrize("fp8_pool", [False, True])
+def test_full_mode_matches_oracle(fp8_pool):
+    from dsa_multi_layer_indexer_b200 import _lib, serving
+
+    serving.clear_scratch()
+    c = build_case(fp8_pool)
+    attn, nxt, logits = call(c, return_logits=True)
+    assert attn.shape == (1, c["B"], c["heads"], 512) and nxt.shape == (c["B"], c["topk"]) and nxt.dtype == torch.int32
+    ref = ref_attention(c)
+    assert rel_err(attn[0].float().cpu(), ref) < ATTN_TOL
+    assert corr_diff(attn[0].float().cpu(), ref) < 1e-3
+    lg = logits.cpu()
+    for b, ln in enumerate(c["lens"]):
+        assert rel_err(lg[b:b + 1, :ln], c["ref_logits"][b:b + 1, :ln]) < LOGIT_TOL
+        assert torch.isinf(lg[b, ln:]).all()
+    got = [sorted(v for v in row if v >= 0) for row in nxt.cpu().tolist()]
+    assert got == ref_next(c)  # bit-exact sets in KV-slot space
+    for b, ln in enumerate(c["lens"]):
+        assert (nxt[b] < 0).sum().item() == max(0, c["topk"] - ln)
+    # the page-table arithmetic gives the same slots as the explicit position -> slot map
+    _, nxt_pt = call(c, pool_map=None)
+    assert torch.equal(nxt_pt, nxt)
+    _lib.check_device_status()
+
+
+def test_modes_and_select_variants():
+    from dsa_multi_layer_indexer_b200 import serving
+
+    serving.clear_scratch()
+    c = build_case(True)
+    attn, nxt = call(c)
+    attn = attn.clone()
+    nxt = nxt.clone()
+    only = call(c, mode="attn_only")
+    assert torch.equal(only, attn)
+    slab = call(c, mode="scan_only")
+    a2, lg = call(c, select=False)
+    assert torch.equal(a2, attn) and torch.equal(lg, slab)
+    a3, n3 = call(c, select="torch")
+    assert n3.dtype == torch.int64
+    for b in range(c["B"]):
+        assert sorted(v for v in n3[b].tolist() if v >= 0) == sorted(v for v in nxt[b].tolist() if v >= 0)
+    with pytest.raises(ValueError):
+        call(c, mode="tap")
+    with pytest.raises(ValueError):
+        call(c, index_topk=c["topk"] // 2)
+
+
+def test_head_padding_and_graph_replay():
+    """20 heads are padded to 32 with zero queries and sliced off again; the call is
+    capturable (no allocation after the first call, no host sync)."""
+    from dsa_multi_layer_indexer_b200 import serving
+
+    serving.clear_scratch()
+    c = build_case(False, heads=20)
+    attn, nxt = call(c)
+    assert attn.shape == (1, c["B"], 20, 512)
+    ref = ref_attention(c)
+    assert rel_err(attn[0].float().cpu(), ref) < ATTN_TOL
+    eager_attn, eager_nxt = attn.clone(), nxt.clone()
+    d = lambda t: t.cuda().contiguous()
+    args = (d(c["q"]), d(c["kv_pool"]), d(c["inc"]), d(c["iq8"]), d(c["wp"]), d(c["pages"]), d(c["pt"]),
+            d(torch.tensor(c["lens"], dtype=torch.int32)), c["cap"], 192 ** -0.5, d(c["pos2slot"]))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        serving.fused_hide_decode_paged(*args)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        g_attn, g_nxt = serving.fused_hide_decode_paged(*args)
+    g_attn.zero_()
+    g_nxt.fill_(-9)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(g_attn, eager_attn) and torch.equal(g_nxt, eager_nxt)
