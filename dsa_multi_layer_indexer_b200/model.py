@@ -19,7 +19,7 @@ the others ("S") reuse the carried selection (overlay :33-51, :4027-4049).
 from __future__ import annotations
 
 import dataclasses
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 from torch import nn
@@ -203,13 +203,21 @@ class DSAModel(nn.Module):
     @torch.no_grad()
     def decode_step(self, state: DecodeState, x: torch.Tensor, mode: ScheduleMode,
                     cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True,
-                    record: Optional[dict] = None) -> torch.Tensor:
+                    record: Optional[dict] = None, lag_depth: int = 1) -> torch.Tensor:
         """One new token per sequence: x [B,hidden] -> final hidden [B,hidden].
 
         Appends the token's keys to every layer's caches at ``state.positions``
         and advances the device-side lengths. In the lagged modes with
-        ``overlap`` the indexers run on ``state.side_stream``. Capturable in a
-        CUDA graph (no host sync, lengths stay on the device)."""
+        ``overlap`` the indexers run on ``state.side_stream``. ``lag_depth`` k >= 2
+        lets an indexer overlap k refresh spans instead of one (see
+        ``_decode_step_depth``). Capturable in a CUDA graph (no host sync, lengths
+        stay on the device)."""
+        if lag_depth < 1:
+            raise ValueError("lag_depth must be >= 1")
+        if lag_depth > 1:
+            if mode is ScheduleMode.BASELINE:
+                raise ValueError("lag_depth > 1 needs a lagged schedule mode")
+            return self._decode_step_depth(state, x, cold_start, overlap, record, lag_depth)
         types = self.config.resolved_attention_types
         n = len(self.layers)
         lagged = mode is not ScheduleMode.BASELINE
@@ -265,8 +273,88 @@ class DSAModel(nn.Module):
             record["used"], record["produced"] = used, produced
         return self.final_norm(x)
 
+    def _decode_step_depth(self, state: DecodeState, x: torch.Tensor, cold_start: ColdStartPolicy,
+                           overlap: bool, record: Optional[dict], depth: int) -> torch.Tensor:
+        """Lag depth k >= 2 (overlay ``_hh_lag_refresh_dispatch_depth``,
+        sglang_overlay/mli-sglang-v0.5.16.patch:3017-3100): a refresh layer (one that
+        keeps its indexer) launches its indexer on the side stream, records an
+        event and queues the fresh set in a FIFO of depth k; once the FIFO is
+        full the layer pops the OLDEST entry, joins on that entry's event only
+        and attends it, so an indexer overlaps k refresh spans. While the FIFO
+        fills, the layer attends the incoming carry. The carry-out of a refresh
+        layer is the set it ATTENDED, which the skip layers after it copy. The
+        first sparse layer bootstraps: EAGER runs its indexer serially and
+        attends it (nothing queued); DENSE attends densely and queues its set."""
+        types = self.config.resolved_attention_types
+        main = torch.cuda.current_stream()
+        side = state.side_stream if overlap else None
+        state.seq_lens.add_(1)  # the new token sees itself
+        carried: Optional[torch.Tensor] = None
+        fifo: List[Tuple[Optional[torch.cuda.Event], torch.Tensor]] = []
+        booted = False
+        forked = False
+        used, produced = [], []
+        for li, layer in enumerate(self.layers):
+            cache = state.caches[li]
+            is_dsa = types[li] is AttentionType.DSA
+            x_norm = layer.attn_norm(x)
+            q, iq, w = layer.decode_project(x_norm, state.rope, state.positions, cache, state.batch_index)
+            made = None
+
+            def dispatch():
+                """This layer's indexer, deferred: (event, fresh set)."""
+                nonlocal forked
+                if side is None:
+                    return None, layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
+                side.wait_stream(main)  # fork: needs iq, w and the appended key
+                with torch.cuda.stream(side):
+                    fresh = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
+                    done = torch.cuda.Event()
+                    done.record(side)
+                forked = True
+                return done, fresh
+
+            if not is_dsa:
+                attend = None
+            elif not booted:
+                booted = True
+                if cold_start is ColdStartPolicy.DENSE:
+                    attend = None
+                    if state.runs_indexer[li]:
+                        ev, made = dispatch()
+                        fifo.append((ev, made))
+                else:
+                    attend = made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
+                carried = attend
+            elif state.runs_indexer[li]:
+                ev, made = dispatch()
+                if len(fifo) >= depth:
+                    old_ev, attend = fifo.pop(0)
+                    if old_ev is not None:
+                        main.wait_event(old_ev)  # join on the oldest entry only
+                else:
+                    attend = carried  # pipeline fill
+                fifo.append((ev, made))
+                carried = attend
+            else:
+                attend = carried
+            attn = layer.decode_attention(q, cache, attend, state.seq_lens)
+            h = x + attn
+            x = h + layer.mlp(layer.ffn_norm(h))
+            if record is not None:
+                used.append(attend)
+                produced.append(made)
+        if forked:  # drain: never leave a fork dangling (a captured graph must end joined)
+            main.wait_stream(side)
+        state.positions.add_(1)
+        state.carried = carried
+        if record is not None:
+            record["used"], record["produced"] = used, produced
+        return self.final_norm(x)
+
     def capture_decode(self, state: DecodeState, mode: ScheduleMode,
-                       cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True):
+                       cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True,
+                       lag_depth: int = 1):
         """Captures one decode step in a CUDA graph. Returns (graph, x_in, x_out):
         copy the token's hidden state into x_in, replay, read x_out. The caches
         and lengths advance on every replay exactly as in eager mode. Warm-up
@@ -280,12 +368,12 @@ class DSAModel(nn.Module):
         warm.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(warm):
             for _ in range(2):
-                self.decode_step(state, x_in, mode, cold_start, overlap)
+                self.decode_step(state, x_in, mode, cold_start, overlap, lag_depth=lag_depth)
                 state.positions.copy_(saved[0])
                 state.seq_lens.copy_(saved[1])
         torch.cuda.current_stream().wait_stream(warm)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            x_out = self.decode_step(state, x_in, mode, cold_start, overlap)
+            x_out = self.decode_step(state, x_in, mode, cold_start, overlap, lag_depth=lag_depth)
         # the capture itself does not execute: lengths are still at their saved values
         return graph, x_in, x_out

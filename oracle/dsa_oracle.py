@@ -278,3 +278,38 @@ def schedule_plan(is_dsa: Sequence[bool], mode: str, cold_start: str) -> List[di
                 attend = "prev"
             plan.append({"attend": attend, "produce": prod[i]})
     return plan
+
+
+def schedule_plan_depth(is_dsa: Sequence[bool], runs_indexer: Sequence[bool], cold_start: str,
+                        depth: int) -> List[dict]:
+    """Lag depth k >= 2 without tensors: per layer, whose fresh set the attention
+    consumes (``("layer", j)``, or ``"dense"``) and whether the layer's indexer
+    runs. Restates the documented semantics of the serving overlay's
+    ``_hh_lag_refresh_dispatch_depth``
+    (sglang_overlay/mli-sglang-v0.5.16.patch:3017-3100): FIFO of depth k of fresh
+    sets; a refresh layer attends the oldest entry once the FIFO is full, else the
+    incoming carry; its carry-out is the set it attended; skip layers copy the
+    carry; the first sparse layer bootstraps (own set under "eager", dense
+    attention with its set queued under "dense")."""
+    plan, fifo, carried, booted = [], [], "dense", False
+    for i, dsa in enumerate(is_dsa):
+        if not dsa:
+            plan.append({"attend": "dense", "produce": False})
+            continue
+        if not booted:
+            booted = True
+            if cold_start == "dense":
+                attend, produce = "dense", bool(runs_indexer[i])
+                if produce:
+                    fifo.append(i)
+            else:
+                attend, produce = ("layer", i), True
+            carried = attend
+        elif runs_indexer[i]:
+            attend = ("layer", fifo.pop(0)) if len(fifo) >= depth else carried
+            fifo.append(i)
+            carried, produce = attend, True
+        else:
+            attend, produce = carried, False
+        plan.append({"attend": attend, "produce": produce})
+    return plan

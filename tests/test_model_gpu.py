@@ -160,6 +160,53 @@ def test_retention_pattern_carries_the_selection(D):
     assert torch.equal(used[4], made[3])
 
 
+@pytest.mark.parametrize("cold,pattern,depth", [("eager", None, 2), ("dense", None, 2), ("eager", "FSFSFS", 2),
+                                                 ("eager", None, 3)])
+def test_lag_depth_k_follows_the_plan_and_overlaps(D, cold, pattern, depth):
+    """Every layer attends exactly the set the depth-k plan names; one stream, the side
+    stream and a captured graph give identical hidden states."""
+    from oracle import dsa_oracle as O
+
+    model = small_model(D, 6)
+    n_layers = len(model.layers)
+    assert n_layers == 6
+    is_dsa = [t is D.AttentionType.DSA for t in model.config.resolved_attention_types]
+    torch.manual_seed(12)
+    B, S0 = 2, 20
+    hid = D.SMALL_CONFIG.hidden_size
+    prompt = torch.randn(B, S0, hid, device="cuda")
+    tok = torch.randn(3, B, hid, device="cuda")
+    mode = D.ScheduleMode.LAGGED_FUSED
+    policy = D.ColdStartPolicy.EAGER if cold == "eager" else D.ColdStartPolicy.DENSE
+
+    def fresh():
+        st = model.init_decode(B, 32, fp8=False, retention=pattern)
+        model.prefill(st, prompt)
+        return st
+
+    st = fresh()
+    rec = {}
+    serial = model.decode_step(st, tok[0], mode, policy, overlap=False, record=rec, lag_depth=depth).clone()
+    plan = O.schedule_plan_depth(is_dsa, st.runs_indexer, cold, depth)
+    for li, p in enumerate(plan):
+        assert (rec["produced"][li] is not None) == p["produce"], li
+        if p["attend"] == "dense":
+            assert rec["used"][li] is None, li
+        else:
+            assert torch.equal(rec["used"][li], rec["produced"][p["attend"][1]]), li
+    st = fresh()
+    overlapped = model.decode_step(st, tok[0], mode, policy, overlap=True, lag_depth=depth)
+    assert torch.equal(serial, overlapped)
+    st = fresh()
+    g, x_in, x_out = model.capture_decode(st, mode, policy, overlap=True, lag_depth=depth)
+    x_in.copy_(tok[0])
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(serial, x_out)
+    with pytest.raises(ValueError):
+        model.decode_step(st, tok[1], D.ScheduleMode.BASELINE, lag_depth=2)
+
+
 def production_config(D, layers=3):
     return D.DSAConfig(hidden_size=256, num_hidden_layers=layers, num_attention_heads=16, q_lora_rank=96,
                        kv_lora_rank=512, qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32,

@@ -125,3 +125,23 @@ def test_schedule_plan():
     assert [p["produce"] for p in plan] == [False, True, True, False]
     plan = O.schedule_plan([True, True], "baseline", "dense")
     assert all(p["attend"] == "own" and p["produce"] for p in plan)
+
+
+def test_schedule_plan_depth_follows_the_overlay_narrative():
+    """The worked example in the overlay's docstring (patch :3017-3100): with depth k
+    the first refresh layer bootstraps, R_1..R_k attend the incoming carry while the
+    FIFO fills, and from then on R_n attends the set of R_(n-k)."""
+    plan = O.schedule_plan_depth([True] * 7, [True] * 7, "eager", 2)
+    assert [p["attend"] for p in plan] == [("layer", 0), ("layer", 0), ("layer", 0), ("layer", 1), ("layer", 2),
+                                           ("layer", 3), ("layer", 4)]
+    assert all(p["produce"] for p in plan)
+    # IndexCache 1/3 retention: skip layers copy the carry, which is the ATTENDED set
+    runs = [c == "F" for c in "FSSFSSFSSFSS"]
+    plan = O.schedule_plan_depth([True] * 12, runs, "eager", 2)
+    att = [p["attend"] for p in plan]
+    assert att[:9] == [("layer", 0)] * 9           # R_0 boots; R_1 (layer 3) and R_2 (layer 6) fill
+    assert att[9:] == [("layer", 3)] * 3           # R_3 (layer 9) pops R_1's set
+    assert [p["produce"] for p in plan] == runs
+    # dense cold start queues the first layer's set; dense layers stay dense
+    plan = O.schedule_plan_depth([False, True, True, True, True], [True] * 5, "dense", 2)
+    assert [p["attend"] for p in plan] == ["dense", "dense", "dense", ("layer", 1), ("layer", 2)]
