@@ -610,7 +610,7 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   // is faster on the mma.sync kernel's 16-head CTAs); its splits are whole 64-key tiles.
   const int tc_mode = env_int("DSA_MLA_TC", 1);  // 0 never, 1 by size, 2 whenever the head count allows
   const int64_t tc_tiles = int64_t(R) * (H / mla_tc::kHG) * ((topk_k + mla_tc::kBN - 1) / mla_tc::kBN);
-  if (H % mla_tc::kHG == 0 && (tc_mode == 2 || (tc_mode == 1 && tc_tiles >= mla_tc::kMinTiles))) {
+  if (H % mla_tc::kHG == 0 && sm_scale > 0.f && (tc_mode == 2 || (tc_mode == 1 && tc_tiles >= mla_tc::kMinTiles))) {
     int kps = (topk_k + nsplit - 1) / nsplit;
     p.keys_per_split = (kps + mla_tc::kBN - 1) / mla_tc::kBN * mla_tc::kBN;
     int rc = opt_in_smem(mla_tc::sparse_mla_tc_kernel, mla_tc::Smem::bytes, g_opt_mla_tc);

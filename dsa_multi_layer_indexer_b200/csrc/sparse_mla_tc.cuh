@@ -377,13 +377,23 @@ sparse_mla_tc_kernel(const mla::Params p) {
           uint32_t vw[4];
 #pragma unroll
           for (int w = 0; w < 4; ++w) vw[w] = s_validw[s * 4 + w] >> (8 * half);
+          // x keeps the raw dot products (-inf for masked keys); the softmax scale (> 0) is
+          // applied to the maximum here and folded into the exponent's multiply-add below
+          if (((vw[0] & vw[1] & vw[2] & vw[3]) & 0xFFu) == 0xFFu) {  // every key of the half-tile visible
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            // key 32 half + i was staged by producer warp (i & 15) >> 2, bit 4 (key >> 4) + (i & 3)
-            const bool ok = (vw[(i & 15) >> 2] >> ((i >> 4) * 4 + (i & 3))) & 1u;
-            x[i] = ok ? __uint_as_float(raw[i]) * p.scale_log2 : -INFINITY;
-            m_loc = fmaxf(m_loc, x[i]);
+            for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(raw[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              // key 32 half + i was staged by producer warp (i & 15) >> 2, bit 4 (key >> 4) + (i & 3)
+              const bool ok = (vw[(i & 15) >> 2] >> ((i >> 4) * 4 + (i & 3))) & 1u;
+              x[i] = ok ? __uint_as_float(raw[i]) : -INFINITY;
+            }
           }
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], x[i]);
+          m_loc = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
           if (m_ref != -INFINITY && m_loc > m_ref + kRescaleLog2) s_flag[s] = 1;
         }
         s_max[(s * 2 + half) * kHG + head] = m_loc;
@@ -431,7 +441,8 @@ sparse_mla_tc_kernel(const mla::Params p) {
         float psum0 = 0.f, psum1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const __nv_bfloat162 b = __floats2bfloat162_rn(ex2_approx(x[2 * i] - mr), ex2_approx(x[2 * i + 1] - mr));
+          const __nv_bfloat162 b = __floats2bfloat162_rn(ex2_approx(fmaf(x[2 * i], p.scale_log2, -mr)),
+                                                         ex2_approx(fmaf(x[2 * i + 1], p.scale_log2, -mr)));
           pk[i] = *reinterpret_cast<const uint32_t*>(&b);
           psum0 += __uint_as_float(pk[i] << 16);
           psum1 += __uint_as_float(pk[i] & 0xFFFF0000u);
