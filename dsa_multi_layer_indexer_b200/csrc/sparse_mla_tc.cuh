@@ -33,6 +33,11 @@
 // it exceeds m by more than 2^kRescaleLog2. Probabilities are floating point, so
 // a stale reference costs no precision; the split's (m, l, O) stay consistent
 // and the merge kernel renormalises them.
+//
+// Tile size: four 32-key ring slots (the same bytes as two 64-key slots, three
+// tiles in flight instead of one) were built and measured 1.5x SLOWER: the
+// per-tile fixed latencies (mbarrier hand-offs, tensor-memory load, proxy
+// fences, the softmax group barrier) do not shrink with the tile.
 #pragma once
 
 #include "sparse_mla.cuh"
