@@ -42,11 +42,13 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_fused_decode": (_i, [_p] * 15 + [_i, _i, _i, _i, _i, _f, _l, _i, _l, _l, _l, _l, _l, _p]),
     "dsa_sparse_mla_f32": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _l, _p]),
     "dsa_rmsnorm": (_i, [_p, _p, _p, _l, _i, _f, _i, _p]),
+    "dsa_add_rmsnorm_bf16": (_i, [_p, _p, _p, _p, _p, _l, _i, _f, _p]),
+    "dsa_silu_mul_bf16": (_i, [_p, _p, _p, _l, _p]),
     "dsa_decode_prep": (_i, [_p, _p, _p, _p, _p, _p, _l] + [_p] * 12 + [_i, _i, _i, _l, _i, _f, _p]),
     "dsa_quantize_e4m3_rowwise": (_i, [_p, _p, _p, _l, _i, _f, _p]),
 }
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 class DsaError(RuntimeError):

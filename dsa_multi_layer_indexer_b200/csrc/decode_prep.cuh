@@ -54,6 +54,116 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ weight, T* __restr
     out[row * dim + i] = from_f32<T>(to_f32<T>(xr[i]) * inv * to_f32<T>(weight[i]));
 }
 
+// bf16 rows of up to 8192 elements (a multiple of 8): each of the 256 threads keeps its
+// 16-byte pieces of the row in registers, so the row is read once. With kAdd the
+// kernel first forms s = x + delta (rounded to bf16 as the separate addition would
+// be, and written to sum_out) and normalises s: the residual addition and the norm
+// that follows it in a decoder layer (src/lagged_indexer_dsa/model.py:137-138,
+// dsa_layer.py:42-52) become one launch.
+constexpr int kNormVecPerThread = 4;
+constexpr int kNormMaxDim = 256 * kNormVecPerThread * 8;
+template <bool kAdd>
+__global__ void __launch_bounds__(256)
+rmsnorm_bf16_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                         const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ sum_out,
+                         __nv_bfloat16* __restrict__ out, int dim, float eps) {
+  __shared__ float s_part[8];
+  const int64_t row = blockIdx.x;
+  const int nvec = dim >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+  const uint4* dr = kAdd ? reinterpret_cast<const uint4*>(delta + row * dim) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(weight);
+  pdl_wait();
+  pdl_launch_dependents();
+  uint4 xv[kNormVecPerThread], wv[kNormVecPerThread], dv[kNormVecPerThread];
+#pragma unroll
+  for (int k = 0; k < kNormVecPerThread; ++k) {
+    const int i = threadIdx.x + 256 * k;
+    xv[k] = wv[k] = dv[k] = make_uint4(0, 0, 0, 0);
+    if (i < nvec) {
+      xv[k] = xr[i];
+      wv[k] = wr[i];
+      if (kAdd) dv[k] = dr[i];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormVecPerThread; ++k) {
+    __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xv[k]);
+    if (kAdd) {
+      const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&dv[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(xp[e]), b = __bfloat1622float2(dp[e]);
+        xp[e] = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+      }
+      const int i = threadIdx.x + 256 * k;
+      if (i < nvec) reinterpret_cast<uint4*>(sum_out + row * dim)[i] = xv[k];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xp[e]);
+      ss = fmaf(a.x, a.x, ss);
+      ss = fmaf(a.y, a.y, ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += s_part[w];
+  const float inv = rsqrtf(tot / float(dim) + eps);
+#pragma unroll
+  for (int k = 0; k < kNormVecPerThread; ++k) {
+    const int i = threadIdx.x + 256 * k;
+    if (i >= nvec) continue;
+    const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv[k]);
+    const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[k]);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xp[e]), w2 = __bfloat1622float2(wp[e]);
+      op[e] = __floats2bfloat162_rn(a.x * inv * w2.x, a.y * inv * w2.y);
+    }
+    reinterpret_cast<uint4*>(out + row * dim)[i] = o;
+  }
+}
+
+// out = silu(gate) * up, elementwise over bf16 (the SwiGLU between the MLP's GEMVs,
+// src/lagged_indexer_dsa/dsa_layer.py:194-196), with the roundings of the two separate
+// operations: silu in fp32 rounded to bf16, then the product rounded to bf16.
+__global__ void __launch_bounds__(256)
+silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                     __nv_bfloat16* __restrict__ out, int64_t n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t i = (int64_t(blockIdx.x) * 256 + threadIdx.x) * 8;
+  if (i + 8 <= n) {
+    const uint4 g = *reinterpret_cast<const uint4*>(gate + i), u = *reinterpret_cast<const uint4*>(up + i);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* upp = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(gp[e]), b = __bfloat1622float2(upp[e]);
+      const __nv_bfloat162 s2 = __floats2bfloat162_rn(a.x / (1.f + __expf(-a.x)), a.y / (1.f + __expf(-a.y)));
+      const float2 sf = __bfloat1622float2(s2);
+      op[e] = __floats2bfloat162_rn(sf.x * b.x, sf.y * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + i) = o;
+  } else {
+    for (int64_t j = i; j < n; ++j) {
+      const float a = __bfloat162float(gate[j]);
+      const float sr = __bfloat162float(__float2bfloat16_rn(a / (1.f + __expf(-a))));
+      out[j] = __float2bfloat16_rn(sr * __bfloat162float(up[j]));
+    }
+  }
+}
+
 // ------------------------------------------------------------------ decode prep
 struct Params {
   // inputs (bf16, outputs of the projection GEMVs), B rows

@@ -682,11 +682,42 @@ int dsa_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int 
     DSA_CUDA(launch_pdl(prep::rmsnorm_kernel<float>, dim3(unsigned(rows)), dim3(256), 0, st,
                         static_cast<const float*>(x), static_cast<const float*>(weight), static_cast<float*>(out),
                         dim, eps));
+  } else if (dim % 8 == 0 && dim <= prep::kNormMaxDim && aligned16(x) && aligned16(weight) && aligned16(out)) {
+    DSA_CUDA(launch_pdl(prep::rmsnorm_bf16_rows_kernel<false>, dim3(unsigned(rows)), dim3(256), 0, st,
+                        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(nullptr),
+                        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(nullptr),
+                        static_cast<__nv_bfloat16*>(out), dim, eps));
   } else {
     DSA_CUDA(launch_pdl(prep::rmsnorm_kernel<__nv_bfloat16>, dim3(unsigned(rows)), dim3(256), 0, st,
                         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
                         static_cast<__nv_bfloat16*>(out), dim, eps));
   }
+  return DSA_OK;
+}
+
+int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, void* sum_out, void* out,
+                         int64_t rows, int dim, float eps, void* stream) {
+  DSA_REQUIRE(x && delta && weight && sum_out && out, "add + rmsnorm: null pointer");
+  DSA_REQUIRE(rows > 0 && rows < (int64_t(1) << 31), "add + rmsnorm: bad row count");
+  DSA_REQUIRE(dim > 0 && dim % 8 == 0 && dim <= prep::kNormMaxDim,
+              "add + rmsnorm: dim=%d must be a multiple of 8 and at most %d", dim, prep::kNormMaxDim);
+  DSA_REQUIRE(aligned16(x) && aligned16(delta) && aligned16(weight) && aligned16(sum_out) && aligned16(out),
+              "add + rmsnorm: pointers must be 16-byte aligned");
+  DSA_CUDA(launch_pdl(prep::rmsnorm_bf16_rows_kernel<true>, dim3(unsigned(rows)), dim3(256), 0,
+                      static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
+                      static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
+                      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(out), dim, eps));
+  return DSA_OK;
+}
+
+int dsa_silu_mul_bf16(const void* gate, const void* up, void* out, int64_t n, void* stream) {
+  DSA_REQUIRE(gate && up && out, "silu * up: null pointer");
+  DSA_REQUIRE(n > 0 && n < (int64_t(1) << 40), "silu * up: bad element count");
+  DSA_REQUIRE(aligned16(gate) && aligned16(up) && aligned16(out), "silu * up: pointers must be 16-byte aligned");
+  const int64_t blocks = (n + 2047) / 2048;
+  DSA_CUDA(launch_pdl(prep::silu_mul_bf16_kernel, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up),
+                      static_cast<__nv_bfloat16*>(out), n));
   return DSA_OK;
 }
 

@@ -227,10 +227,10 @@ class DSAModel(nn.Module):
         carried: Optional[torch.Tensor] = None
         pending = False  # an indexer is in flight on the side stream
         used, produced = [], []
+        x_norm = self.layers[0].attn_norm(x)
         for li, layer in enumerate(self.layers):
             cache = state.caches[li]
             is_dsa = types[li] is AttentionType.DSA
-            x_norm = layer.attn_norm(x)
             q, iq, w = layer.decode_project(x_norm, state.rope, state.positions, cache, state.batch_index)
             made = None
             if not lagged:
@@ -258,8 +258,7 @@ class DSAModel(nn.Module):
                     else:
                         made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
             attn = layer.decode_attention(q, cache, attend, state.seq_lens)
-            h = x + attn
-            x = h + layer.mlp(layer.ffn_norm(h))
+            x, x_norm = self._residual_tail(li, x, attn)
             if lagged and made is not None:
                 carried = made  # becomes visible to layer li+1 after the join
             if record is not None:
@@ -271,7 +270,16 @@ class DSAModel(nn.Module):
         state.carried = carried
         if record is not None:
             record["used"], record["produced"] = used, produced
-        return self.final_norm(x)
+        return x_norm  # the last layer's tail applied the final norm
+
+    def _residual_tail(self, li: int, x: torch.Tensor, attn: torch.Tensor):
+        """``h = x + attn; x' = h + mlp(ffn_norm(h))`` and the norm the next consumer
+        applies to ``x'`` (the next layer's attn_norm, or the final norm after the last
+        layer): each residual addition is fused with the norm that follows it."""
+        layer = self.layers[li]
+        h, h_norm = layer.ffn_norm.add_forward(x, attn)
+        nxt = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
+        return nxt.add_forward(h, layer.mlp(h_norm))
 
     def _decode_step_depth(self, state: DecodeState, x: torch.Tensor, cold_start: ColdStartPolicy,
                            overlap: bool, record: Optional[dict], depth: int) -> torch.Tensor:
@@ -294,10 +302,10 @@ class DSAModel(nn.Module):
         booted = False
         forked = False
         used, produced = [], []
+        x_norm = self.layers[0].attn_norm(x)
         for li, layer in enumerate(self.layers):
             cache = state.caches[li]
             is_dsa = types[li] is AttentionType.DSA
-            x_norm = layer.attn_norm(x)
             q, iq, w = layer.decode_project(x_norm, state.rope, state.positions, cache, state.batch_index)
             made = None
 
@@ -339,8 +347,7 @@ class DSAModel(nn.Module):
             else:
                 attend = carried
             attn = layer.decode_attention(q, cache, attend, state.seq_lens)
-            h = x + attn
-            x = h + layer.mlp(layer.ffn_norm(h))
+            x, x_norm = self._residual_tail(li, x, attn)
             if record is not None:
                 used.append(attend)
                 produced.append(made)
@@ -350,7 +357,7 @@ class DSAModel(nn.Module):
         state.carried = carried
         if record is not None:
             record["used"], record["produced"] = used, produced
-        return self.final_norm(x)
+        return x_norm  # the last layer's tail applied the final norm
 
     def capture_decode(self, state: DecodeState, mode: ScheduleMode,
                        cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True,

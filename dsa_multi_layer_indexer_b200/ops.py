@@ -443,6 +443,32 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float):
+    """``s = x + delta`` and ``rmsnorm(s)`` in one launch (bf16 rows of at most 8192
+    elements, a multiple of 8): returns ``(s, normed)``, both rounded exactly as the
+    separate addition and norm would be."""
+    _need(x.is_cuda and x.dtype == torch.bfloat16 and delta.dtype == torch.bfloat16 and x.shape == delta.shape,
+          "x and delta must be CUDA bf16 tensors of one shape")
+    dim = x.shape[-1]
+    _need(dim % 8 == 0 and dim <= 8192, "the row length must be a multiple of 8 and at most 8192")
+    x, delta = x.contiguous(), delta.contiguous()
+    w = (weight if weight.dtype == x.dtype else weight.to(x.dtype)).contiguous()
+    s, out = torch.empty_like(x), torch.empty_like(x)
+    _lib.check(_lib.lib().dsa_add_rmsnorm_bf16(_ptr(x), _ptr(delta), _ptr(w), _ptr(s), _ptr(out), x.numel() // dim, dim,
+                                               float(eps), _stream()))
+    return s, out
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` over bf16 tensors in one launch, rounded as the two separate operations."""
+    _need(gate.is_cuda and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.shape == up.shape,
+          "gate and up must be CUDA bf16 tensors of one shape")
+    gate, up = gate.contiguous(), up.contiguous()
+    out = torch.empty_like(gate)
+    _lib.check(_lib.lib().dsa_silu_mul_bf16(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _stream()))
+    return out
+
+
 def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, mla_sin, idx_cos, idx_sin,
                 positions, index_q, index_w, q_full, cache_index_k, cache_k_scale, cache_kv,
                 interleave: bool, eps: float) -> None:

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 2
+#define DSA_ABI_VERSION 3
 
 enum dsa_status {
   DSA_OK = 0,
@@ -240,6 +240,14 @@ int dsa_sparse_mla_f32(const float* q, const float* kv, const int32_t* indices,
  * [cap,64] / [cap,128]; caches as in dsa_indexer_scan_fp8 / dsa_sparse_mla_*. */
 int dsa_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int dim, float eps,
                 int dtype, void* stream);
+/* The residual addition and the norm that follows it in a decoder layer
+ * (src/lagged_indexer_dsa/model.py:137-138) in one launch, bf16 rows of dim <= 8192
+ * (a multiple of 8): sum_out = x + delta (rounded to bf16), out = rmsnorm(sum_out). */
+int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, void* sum_out, void* out,
+                         int64_t rows, int dim, float eps, void* stream);
+/* out = silu(gate) * up over n bf16 elements: the SwiGLU between the MLP's GEMVs
+ * (src/lagged_indexer_dsa/dsa_layer.py:194-196), rounded as the two separate operations. */
+int dsa_silu_mul_bf16(const void* gate, const void* up, void* out, int64_t n, void* stream);
 int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, const void* kv_a,
                     const void* q_abs, const void* q_pe, int64_t q_pe_stride, const void* kv_norm_w,
                     const void* mla_cos, const void* mla_sin, const void* idx_cos, const void* idx_sin,

