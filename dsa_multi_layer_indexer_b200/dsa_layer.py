@@ -150,6 +150,33 @@ class DSALayer(nn.Module):
         w = self.kv_b_proj.weight.view(c.num_attention_heads, c.qk_nope_head_dim + c.v_head_dim, c.kv_lora_rank)
         return w[:, : c.qk_nope_head_dim, :], w[:, c.qk_nope_head_dim:, :]
 
+    # ------------------------------------------------------------------ stacked decode projections
+    def fuse_decode_weights(self) -> None:
+        """Stacks the weights of the three projections that read x_norm (q_a, kv_a,
+        index_k) and of the three that read c_q (q_b, index_q, index_weights), so a
+        decode step needs two GEMVs instead of six small launches. The parameters
+        become views of the stacked tensors: no extra memory, ``state_dict`` and
+        ``load_state_dict`` keep working, and moving or casting the module afterwards
+        simply drops the stacking (``decode_project`` notices and uses the six)."""
+        with torch.no_grad():
+            for name, mods in (("_wx", (self.q_a_proj, self.kv_a_proj, self.index_k_proj)),
+                               ("_wc", (self.q_b_proj, self.index_q_proj, self.index_weights_proj))):
+                stacked = torch.cat([m.weight for m in mods], dim=0)
+                row = 0
+                for m in mods:
+                    n = m.weight.shape[0]
+                    m.weight.data = stacked[row:row + n]
+                    row += n
+                setattr(self, name, stacked)
+
+    def _stacked(self) -> bool:
+        wx, wc = getattr(self, "_wx", None), getattr(self, "_wc", None)
+        return (wx is not None and wc is not None and self.q_a_proj.weight.data_ptr() == wx.data_ptr()
+                and self.q_b_proj.weight.data_ptr() == wc.data_ptr()
+                and self.index_k_proj.weight.data_ptr() == wx[wx.shape[0] - self.index_k_proj.weight.shape[0]:].data_ptr()
+                and self.index_weights_proj.weight.data_ptr()
+                == wc[wc.shape[0] - self.index_weights_proj.weight.shape[0]:].data_ptr())
+
     # ------------------------------------------------------------------ projections (torch)
     def q_latent(self, x_norm: torch.Tensor) -> torch.Tensor:
         """c_q = q_a_layernorm(q_a_proj(x_norm)), shared by attention and indexer."""
@@ -288,15 +315,26 @@ class DSALayer(nn.Module):
         b = x_norm.shape[0]
         h = c.num_attention_heads
         il = c.indexer_rope_interleave
-        c_q = self.q_latent(x_norm)
-        q = self.q_b_proj(c_q).view(b, h, c.qk_nope_head_dim + c.qk_rope_head_dim)
+        if self._stacked():  # two GEMVs: everything that reads x_norm, then everything that reads c_q
+            qa, kv_a, ik_raw = torch.nn.functional.linear(x_norm, self._wx).split(
+                [c.q_lora_rank, c.kv_lora_rank + c.qk_rope_head_dim, c.index_head_dim], dim=-1)
+            c_q = self.q_a_layernorm(qa)
+            q, iq_raw, w = torch.nn.functional.linear(c_q, self._wc).split(
+                [h * (c.qk_nope_head_dim + c.qk_rope_head_dim), c.index_n_heads * c.index_head_dim, c.index_n_heads],
+                dim=-1)
+            # (rows of a batch must be dense for the fused prep launch; one row already is)
+            q = (q if b == 1 else q.contiguous()).reshape(b, h, c.qk_nope_head_dim + c.qk_rope_head_dim)
+            iq_raw = iq_raw.reshape(b, c.index_n_heads, c.index_head_dim)
+        else:
+            c_q = self.q_latent(x_norm)
+            q = self.q_b_proj(c_q).view(b, h, c.qk_nope_head_dim + c.qk_rope_head_dim)
+            kv_a = self.kv_a_proj(x_norm)
+            iq_raw = self.index_q_proj(c_q).view(b, c.index_n_heads, c.index_head_dim)
+            ik_raw = self.index_k_proj(x_norm)
+            w = self.index_weights_proj(c_q)
         q_nope, q_rope = q.split([c.qk_nope_head_dim, c.qk_rope_head_dim], dim=-1)
-        kv_a = self.kv_a_proj(x_norm)
         w_uk, _ = self._w_uk_uv()
         q_abs = torch.einsum("bhd,hdl->bhl", q_nope, w_uk)
-        iq_raw = self.index_q_proj(c_q).view(b, c.index_n_heads, c.index_head_dim)
-        ik_raw = self.index_k_proj(x_norm)
-        w = self.index_weights_proj(c_q)
         if cache.k_scale is not None and x_norm.dtype == torch.bfloat16:
             index_q = torch.empty(b, c.index_n_heads, c.index_head_dim, dtype=torch.uint8, device=x_norm.device)
             index_w = torch.empty(b, c.index_n_heads, dtype=torch.float32, device=x_norm.device)

@@ -161,6 +161,10 @@ class DSAModel(nn.Module):
         if fp8 and not self.config.is_production_geometry:
             raise ValueError("fp8 caches need the production geometry (576-wide latent, 128-wide index keys)")
         dev = p.device
+        if fp8 and p.dtype == torch.bfloat16:
+            for layer in self.layers:  # two stacked GEMVs per layer instead of six small ones
+                if not layer._stacked():
+                    layer.fuse_decode_weights()
         caches = [layer.new_cache(batch, capacity, dev, fp8) for layer in self.layers]
         return DecodeState(
             caches=caches, rope=self._build_rope(capacity, dev, p.dtype),

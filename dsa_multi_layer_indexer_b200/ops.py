@@ -480,7 +480,8 @@ def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, ml
                  (idx_sin, "idx_sin")):
         _cuda_contig(t, n, (torch.bfloat16,))
     _need(q_pe.dtype == torch.bfloat16 and q_pe.dim() == 3 and q_pe.shape[2] == 64 and q_pe.stride(2) == 1
-          and q_pe.stride(0) == q_pe.shape[1] * q_pe.stride(1), "q_pe must be a [B, H, 64] bf16 view with dense rows")
+          and (q_pe.shape[0] == 1 or q_pe.stride(0) == q_pe.shape[1] * q_pe.stride(1)),
+          "q_pe must be a [B, H, 64] bf16 view with dense rows")
     _cuda_contig(positions, "positions", (torch.int64,))
     B, n_idx = iq_raw.shape[0], iq_raw.shape[1]
     H = q_abs.shape[1]

@@ -343,3 +343,42 @@ def test_fused_add_rmsnorm_and_silu_mul_match_torch_bitwise(D, rows, dim):
     odd = ops.silu_mul(g.flatten()[:dim - 3].clone(), u.flatten()[:dim - 3].clone()) if dim % 8 == 0 else None
     if odd is not None:  # a length that is not a multiple of 8 takes the scalar tail
         assert torch.equal(odd, got.flatten()[:dim - 3])
+
+
+def test_stacked_decode_projections_share_storage_and_agree(D):
+    """init_decode stacks the six small projections into two GEMVs: the parameters are
+    views of the stacked weights (same state_dict, no copy), a state_dict load lands in
+    the stacked storage, and the decode step agrees with the six separate GEMVs."""
+    cfg = production_config(D, layers=2)
+    torch.manual_seed(3)
+    model = D.DSAModel(cfg).to(torch.bfloat16).eval().cuda()
+    before = {k: v.clone() for k, v in model.state_dict().items()}
+    hid = cfg.hidden_size
+    prompt = torch.randn(1, 40, hid, device="cuda").to(torch.bfloat16)
+    tok = torch.randn(1, hid, device="cuda").to(torch.bfloat16)
+
+    def step(m):
+        st = m.init_decode(1, 64, fp8=True)
+        m.prefill(st, prompt)
+        return m.decode_step(st, tok, D.ScheduleMode.BASELINE).float()
+
+    layer = model.layers[0]
+    assert not layer._stacked()
+    out = step(model)  # init_decode stacks
+    assert layer._stacked()
+    assert layer.kv_a_proj.weight.data_ptr() == layer._wx[cfg.q_lora_rank:].data_ptr()
+    after = model.state_dict()
+    assert all(torch.equal(before[k], after[k]) for k in before)
+    # loading weights writes through the views into the stacked tensors
+    other = D.DSAModel(cfg).to(torch.bfloat16).eval().cuda()
+    model.load_state_dict(other.state_dict())
+    assert layer._stacked() and torch.equal(layer._wc[:layer.q_b_proj.weight.shape[0]], other.layers[0].q_b_proj.weight)
+    model.load_state_dict(before)
+    # moving / casting the module drops the stacking and the six-GEMV path gives the same answer
+    plain = D.DSAModel(cfg).to(torch.bfloat16).eval().cuda()
+    plain.load_state_dict(before)
+    for l in plain.layers:
+        l.fuse_decode_weights = lambda: None  # keep this copy unstacked
+    ref = step(plain)
+    assert not plain.layers[0]._stacked()
+    assert rel_err(out.cpu(), ref.cpu()) < 2e-2
