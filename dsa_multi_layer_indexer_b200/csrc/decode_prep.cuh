@@ -164,6 +164,83 @@ silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16
   }
 }
 
+// ------------------------------------------------------------------ skinny GEMV
+// y[b, n] = sum_k W[n, k] x[b, k] for 1..4 rows of x (decode batch): bf16 operands,
+// fp32 accumulation, one rounding. The weight matrix is streamed once with 16-byte
+// loads, eight per lane in flight, x staged in shared memory. This is the
+// projection GEMV of a decode step (src/lagged_indexer_dsa/dsa_layer.py:87-125) for
+// the shapes where the library GEMV is latency-bound (a few thousand output rows).
+constexpr int kGemvThreads = 256;
+constexpr int kGemvLoads = 8;  // independent 16-byte weight loads per lane per step
+// R rows per warp, kGemvLoads / R consecutive 512-byte column blocks per step: the
+// launch picks R so that there are enough warps to fill the machine.
+template <int B, int R>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_bf16_kernel(const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ x,
+                 __nv_bfloat16* __restrict__ y, int n, int k, int64_t x_stride, int64_t y_stride) {
+  constexpr int UK = kGemvLoads / R;
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  uint4* s_x = reinterpret_cast<uint4*>(gemv_smem);  // [B][k / 8]
+  const int kv = k >> 3;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < B * kv; i += kGemvThreads) {
+    const int b = i / kv, c = i - b * kv;
+    s_x[i] = *reinterpret_cast<const uint4*>(x + b * x_stride + c * 8);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp_global = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5;
+  const int n_warps = (gridDim.x * kGemvThreads) >> 5;
+  for (int row0 = warp_global * R; row0 < n; row0 += n_warps * R) {
+    float acc[R][B];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+    for (int c0 = lane; c0 < kv; c0 += 32 * UK) {
+      uint4 wv[R][UK];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(w + int64_t(min(row0 + r, n - 1)) * k);
+#pragma unroll
+        for (int u = 0; u < UK; ++u) {
+          const int c = c0 + 32 * u;
+          wv[r][u] = c < kv ? __ldcs(wrow + c) : make_uint4(0, 0, 0, 0);  // streamed once
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UK; ++u) {
+        const int c = min(c0 + 32 * u, kv - 1);
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const uint4 xv = s_x[b * kv + c];
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[r][u]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 a = __bfloat1622float2(wp[e]), v = __bfloat1622float2(xp[e]);
+              acc[r][b] = fmaf(a.x, v.x, acc[r][b]);
+              acc[r][b] = fmaf(a.y, v.y, acc[r][b]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        float v = acc[r][b];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && row0 + r < n) y[b * y_stride + row0 + r] = __float2bfloat16_rn(v);
+      }
+  }
+}
+
 // ------------------------------------------------------------------ decode prep
 struct Params {
   // inputs (bf16, outputs of the projection GEMVs), B rows

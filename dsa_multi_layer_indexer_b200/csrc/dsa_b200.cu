@@ -105,7 +105,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64];
+static bool g_opt_fused[64], g_opt_scan[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_gemv[4][3][64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -707,6 +707,51 @@ int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, v
                       static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x),
                       static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
                       static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(out), dim, eps));
+  return DSA_OK;
+}
+
+int dsa_gemv_bf16(const void* w, const void* x, void* y, int batch, int n, int k, int64_t x_stride,
+                  int64_t y_stride, void* stream) {
+  DSA_REQUIRE(w && x && y, "gemv: null pointer");
+  DSA_REQUIRE(batch >= 1 && batch <= 4, "gemv: batch=%d must be 1..4", batch);
+  DSA_REQUIRE(n > 0 && k > 0 && k % 8 == 0, "gemv: k=%d must be a positive multiple of 8", k);
+  DSA_REQUIRE(int64_t(batch) * k * 2 <= 96 * 1024, "gemv: batch * k too large for the shared-memory copy of x");
+  DSA_REQUIRE(x_stride >= k && x_stride % 8 == 0 && y_stride >= n, "gemv: bad row strides");
+  DSA_REQUIRE(aligned16(w) && aligned16(x), "gemv: w and x must be 16-byte aligned");
+  const size_t smem = size_t(batch) * k * 2;
+  // rows per warp: 4 when that still leaves two waves of warps, else 2, else 1
+  const int wave = 8 * sm_count();  // warps of one resident wave of 256-thread CTAs (8 per SM is plenty here)
+  const int rows_per_warp = n / 4 >= 2 * wave ? 4 : (n / 2 >= 2 * wave ? 2 : 1);
+  const int warps_needed = (n + rows_per_warp - 1) / rows_per_warp;
+  int blocks = (warps_needed * 32 + prep::kGemvThreads - 1) / prep::kGemvThreads;
+  if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+#define DSA_GEMV_LAUNCH(BV, RV)                                                                              \
+  {                                                                                                          \
+    if (smem > 48 * 1024) {                                                                                  \
+      int rc = opt_in_smem(prep::gemv_bf16_kernel<BV, RV>, 96 * 1024, g_opt_gemv[BV - 1][RV >> 1]);          \
+      if (rc) return rc;                                                                                     \
+    }                                                                                                        \
+    DSA_CUDA(launch_pdl(prep::gemv_bf16_kernel<BV, RV>, dim3(blocks), dim3(prep::kGemvThreads), smem, st, wp, xp, yp, \
+                        n, k, x_stride, y_stride));                                                          \
+  }
+#define DSA_GEMV_CASE(BV)                                 \
+  case BV:                                                \
+    if (rows_per_warp == 4) DSA_GEMV_LAUNCH(BV, 4)        \
+    else if (rows_per_warp == 2) DSA_GEMV_LAUNCH(BV, 2)   \
+    else DSA_GEMV_LAUNCH(BV, 1)                           \
+    break;
+  switch (batch) {
+    DSA_GEMV_CASE(1)
+    DSA_GEMV_CASE(2)
+    DSA_GEMV_CASE(3)
+    DSA_GEMV_CASE(4)
+  }
+#undef DSA_GEMV_LAUNCH
+#undef DSA_GEMV_CASE
   return DSA_OK;
 }
 

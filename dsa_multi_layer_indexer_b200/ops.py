@@ -469,6 +469,23 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gemv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``x @ weight.T`` for a decode batch of 1..4 rows (bf16, fp32 accumulation): the weight
+    matrix ``[n, k]`` is streamed once. For the projection shapes where the library GEMV is
+    latency-bound."""
+    _need(x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2,
+          "x must be a CUDA bf16 [B, k] tensor and weight bf16")
+    b, k = x.shape
+    n = weight.shape[0]
+    _need(weight.dim() == 2 and weight.shape[1] == k and weight.is_contiguous(), "weight must be contiguous [n, k]")
+    _need(1 <= b <= 4 and k % 8 == 0 and b * k * 2 <= 96 * 1024, "batch 1..4, k a multiple of 8, batch * k <= 48K")
+    x = x if x.stride(1) == 1 and x.stride(0) % 8 == 0 else x.contiguous()
+    y = torch.empty(b, n, dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.lib().dsa_gemv_bf16(_ptr(weight), _ptr(x), _ptr(y), b, n, k, x.stride(0) if b > 1 else k, n,
+                                        _stream()))
+    return y
+
+
 def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, mla_sin, idx_cos, idx_sin,
                 positions, index_q, index_w, q_full, cache_index_k, cache_k_scale, cache_kv,
                 interleave: bool, eps: float) -> None:

@@ -245,6 +245,12 @@ int dsa_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int 
  * (a multiple of 8): sum_out = x + delta (rounded to bf16), out = rmsnorm(sum_out). */
 int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, void* sum_out, void* out,
                          int64_t rows, int dim, float eps, void* stream);
+/* y[b, n] = sum_k w[n, k] x[b, k] for a decode batch of 1..4 rows: bf16 operands, fp32
+ * accumulation, w [n, k] row-major streamed once (the projection GEMVs of
+ * src/lagged_indexer_dsa/dsa_layer.py:87-125 at decode). k a multiple of 8,
+ * batch * k * 2 <= 96 KB; row strides of x and y in elements. */
+int dsa_gemv_bf16(const void* w, const void* x, void* y, int batch, int n, int k, int64_t x_stride,
+                  int64_t y_stride, void* stream);
 /* out = silu(gate) * up over n bf16 elements: the SwiGLU between the MLP's GEMVs
  * (src/lagged_indexer_dsa/dsa_layer.py:194-196), rounded as the two separate operations. */
 int dsa_silu_mul_bf16(const void* gate, const void* up, void* out, int64_t n, void* stream);

@@ -382,3 +382,21 @@ def test_stacked_decode_projections_share_storage_and_agree(D):
     ref = step(plain)
     assert not plain.layers[0]._stacked()
     assert rel_err(out.cpu(), ref.cpu()) < 2e-2
+
+
+@pytest.mark.parametrize("b,n,k", [(1, 2240, 7168), (2, 515, 1536), (4, 64, 264), (3, 7, 8), (1, 4099, 4096)])
+def test_skinny_gemv_matches_fp32_reference(D, b, n, k):
+    from dsa_multi_layer_indexer_b200 import ops
+
+    torch.manual_seed(n + k)
+    x = torch.randn(b, k, device="cuda").to(torch.bfloat16)
+    w = torch.randn(n, k, device="cuda").to(torch.bfloat16)
+    got = ops.gemv(x, w)
+    assert got.shape == (b, n) and got.dtype == torch.bfloat16
+    ref = x.float() @ w.float().T
+    assert (got.float() - ref).abs().max() <= 2 ** -7 * ref.abs().max() + 1e-3
+    # a strided x (rows of a wider matrix) is accepted
+    wide = torch.randn(b, k + 64, device="cuda").to(torch.bfloat16)
+    assert torch.equal(ops.gemv(wide[:, :k], w), ops.gemv(wide[:, :k].contiguous(), w))
+    with pytest.raises(ValueError):
+        ops.gemv(torch.zeros(5, k, device="cuda", dtype=torch.bfloat16), w)
