@@ -40,6 +40,7 @@ INDEX_HEADS = 64
 TOPK = 2048
 SM_SCALE = 192 ** -0.5
 SCAN_BYTES_PER_KEY = 132          # 128 B e4m3 key + 4 B fp32 scale
+SCAN_TRAFFIC_CTX128K = 17368832   # bytes: ncu dram read + write of one scan launch over 131072 keys
 METRIC = "dsa_decode_layer_tokens_per_s_ctx128k"
 UNIT = "tok/s"
 
@@ -442,7 +443,11 @@ def run_ours(args):
                          "frac": achieved / peak, "peak_source": peak_src,
                          "frac_of_nominal_8TBs": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": scan_bytes,
-                         "traffic": None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+                         # summarised in profiles/indexer_scan_tc_kernel_ctx128k.md (131072 keys, 64 heads);
+                         # other shapes were not captured
+                         "traffic": SCAN_TRAFFIC_CTX128K if (args.ctx == 131072 and args.scan_impl == 0
+                                                              and not seq_shard) else None},
             "lagged_pair": lag,
             "gpu_launches": args.steps * (8 if seq_shard else 5),
             "clocks": clocks,
