@@ -443,9 +443,8 @@ def run_ours(args):
                          "frac": achieved / peak, "peak_source": peak_src,
                          "frac_of_nominal_8TBs": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": scan_bytes,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
-                         # summarised in profiles/indexer_scan_tc_kernel_ctx128k.md (131072 keys, 64 heads);
-                         # other shapes were not captured
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from an ncu capture of
+                         # this kernel at 131072 keys x 64 heads; other shapes were not captured
                          "traffic": SCAN_TRAFFIC_CTX128K if (args.ctx == 131072 and args.scan_impl == 0
                                                               and not seq_shard) else None},
             "lagged_pair": lag,

@@ -35,7 +35,7 @@ def _bits(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference repository")
     args = ap.parse_args()
     ref = Path(args.reference)
     sys.path.insert(0, str(ref / "src"))
