@@ -53,7 +53,7 @@ def key_range(rank: int, world: int, n_keys: int, align: int = SCAN_TILE) -> Tup
 def interleave_gathered(gathered: torch.Tensor, world: int, rows: int, topk: int) -> torch.Tensor:
     """[world, rows, topk] (all-gather order) -> [rows, world * topk] with each
     row's candidates in rank order, i.e. ascending position order."""
-    return gathered.view(world, rows, topk).permute(1, 0, 2).reshape(rows, world * topk).contiguous()
+    return gathered.reshape(world, rows, topk).permute(1, 0, 2).reshape(rows, world * topk).contiguous()
 
 
 def all_reduce_hidden(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
@@ -84,10 +84,11 @@ class SeqShardedIndexer:
         self.logits = torch.empty(rows, slab, dtype=torch.float32, device=dev)
         self.hist = torch.zeros(rows, ops.HIST_BINS, dtype=torch.int32, device=dev)
         self.local_ws = ops.topk_workspace(rows, max(local_ctx, 1), dev)
-        self.cand_idx = torch.empty(rows, topk, dtype=torch.int32, device=dev)
-        self.cand_val = torch.empty(rows, topk, dtype=torch.float32, device=dev)
-        self.gath_idx = torch.empty(self.world, rows, topk, dtype=torch.int32, device=dev)
-        self.gath_val = torch.empty(self.world, rows, topk, dtype=torch.float32, device=dev)
+        # (index, logit) candidates travel as ONE buffer: [2, rows, topk] 32-bit words per rank
+        self.cand = torch.empty(2, rows, topk, dtype=torch.int32, device=dev)
+        self.cand_idx = self.cand[0]
+        self.cand_val = self.cand[1].view(torch.float32)
+        self.gath = torch.empty(self.world, 2, rows, topk, dtype=torch.int32, device=dev)
         self.merge_ws = ops.topk_workspace(rows, self.world * topk, dev)
         self.indices = torch.empty(rows, topk, dtype=torch.int32, device=dev)
 
@@ -107,9 +108,8 @@ class SeqShardedIndexer:
         if self.world == 1:
             self.indices.copy_(self.cand_idx)
             return self.indices
-        dist.all_gather_into_tensor(self.gath_idx.view(-1), self.cand_idx.view(-1), group=self.group)
-        dist.all_gather_into_tensor(self.gath_val.view(-1), self.cand_val.view(-1), group=self.group)
-        vals = interleave_gathered(self.gath_val, self.world, self.rows, self.topk)
-        idxs = interleave_gathered(self.gath_idx, self.world, self.rows, self.topk)
+        dist.all_gather_into_tensor(self.gath.view(-1), self.cand.view(-1), group=self.group)  # the one exchange step
+        idxs = interleave_gathered(self.gath[:, 0], self.world, self.rows, self.topk)
+        vals = interleave_gathered(self.gath[:, 1], self.world, self.rows, self.topk).view(torch.float32)
         ops.topk_select(vals, self.topk, None, index_map=idxs, out_idx=self.indices, workspace=self.merge_ws)
         return self.indices
