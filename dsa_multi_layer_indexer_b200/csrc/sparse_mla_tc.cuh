@@ -60,7 +60,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;                  // two S buffers of 64 columns
 constexpr uint32_t kColO = 128;                // four O^T blocks of 64 columns
 constexpr uint32_t kSpinLimit = 1u << 24;
-constexpr int kMinTiles = 192;                 // fewer 64x64 tiles than this: the mma.sync kernel is faster
+constexpr int kMinTiles = 128;                 // fewer 64x64 tiles than this: the mma.sync kernel is faster
 
 struct Smem {
   static constexpr int q_off = 0;

@@ -258,16 +258,20 @@ class MlaScratch:
 def default_nsplit(rows: int, heads: int, topk: int, sm_count: int = 148) -> int:
     """Splits of the index list, each a whole number of 64-key tiles. Head counts
     that are a multiple of 64 run on the tcgen05 kernel (one CTA per SM, 64 heads
-    per CTA): about one CTA per SM in total. Other head counts run on the
-    mma.sync kernel (16 heads per CTA, two CTAs per SM)."""
+    per CTA) once the launch has 128 tiles of 64 heads x 64 keys: about one CTA per
+    SM in total, and a split count that divides the tiles so no split is empty.
+    Smaller launches and other head counts run on the mma.sync kernel (16 heads
+    per CTA, two CTAs per SM)."""
     tiles = max(1, math.ceil(topk / 64))
     mode = os.environ.get("DSA_MLA_TC", "1")
-    if heads % 64 == 0 and (mode == "2" or (mode == "1" and rows * (heads // 64) * tiles >= 192)):
+    if heads % 64 == 0 and (mode == "2" or (mode == "1" and rows * (heads // 64) * tiles >= 128)):
         blocks = max(1, rows * (heads // 64))
-        want = max(1, sm_count // blocks)
-    else:
-        blocks = max(1, rows * (heads // HEAD_BLOCK))
-        want = max(1, (2 * sm_count) // blocks)
+        want = max(1, min(sm_count // blocks, tiles))
+        while tiles % want:
+            want -= 1
+        return want
+    blocks = max(1, rows * (heads // HEAD_BLOCK))
+    want = max(1, (2 * sm_count) // blocks)
     return max(1, min(want, tiles))
 
 
