@@ -613,6 +613,9 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   if (H % mla_tc::kHG == 0 && sm_scale > 0.f && (tc_mode == 2 || (tc_mode == 1 && tc_tiles >= mla_tc::kMinTiles))) {
     int kps = (topk_k + nsplit - 1) / nsplit;
     p.keys_per_split = (kps + mla_tc::kBN - 1) / mla_tc::kBN * mla_tc::kBN;
+    if (env_int("DSA_VERBOSE", 0))
+      fprintf(stderr, "[dsa] sparse_mla: tcgen05 kernel, R=%d H=%d topk=%d nsplit=%d (%lld tiles)\n", R, H, topk_k, nsplit,
+              (long long)tc_tiles);
     int rc = opt_in_smem(mla_tc::sparse_mla_tc_kernel, mla_tc::Smem::bytes, g_opt_mla_tc);
     if (rc) return rc;
     DSA_CUDA(launch_pdl(mla_tc::sparse_mla_tc_kernel, dim3(nsplit, H / mla_tc::kHG, R), dim3(mla_tc::kThreads),
