@@ -76,3 +76,24 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     finally:
         monkeypatch.delenv("DSA_B200_LIB")
         importlib.reload(_lib)
+
+
+def test_default_nsplit_heuristic(monkeypatch):
+    """Host-side split heuristic: large launches of 64-head blocks get about one CTA
+    per SM with a split count that divides the 64-key tiles (no empty split); small
+    ones and other head counts get two 16-head CTAs per SM."""
+    from dsa_multi_layer_indexer_b200 import ops
+
+    monkeypatch.delenv("DSA_MLA_TC", raising=False)
+    assert ops.default_nsplit(1, 128, 2048) == 32          # 64 tiles: mma.sync kernel, 8 head blocks
+    assert ops.default_nsplit(1, 16, 2048) == 32           # TP8 shape
+    assert ops.default_nsplit(32, 128, 2048) == 2          # 2048 tiles: tcgen05 kernel, 64 blocks
+    assert ops.default_nsplit(3, 128, 2048) == 16          # 148 // 6 = 24 -> 16 divides the 32 tiles
+    for rows, heads, topk in [(2, 128, 2048), (5, 64, 1000), (8, 192, 2048), (64, 128, 512), (4, 128, 1024)]:
+        n = ops.default_nsplit(rows, heads, topk)
+        tiles = -(-topk // 64)
+        assert 1 <= n <= tiles
+        if rows * (heads // 64) * tiles >= 128:
+            assert tiles % n == 0 and rows * (heads // 64) * n <= max(148, rows * (heads // 64))
+    monkeypatch.setenv("DSA_MLA_TC", "0")
+    assert ops.default_nsplit(32, 128, 2048) == 1          # 256 head blocks of 16: one split each
