@@ -328,9 +328,11 @@ def test_fused_cluster_attention_in_a_fresh_process():
 
 # ----------------------------------------------------------------------------- fused launch
 @pytest.mark.parametrize("B,H,n,topk,nsplit", [(1, 128, 20000, 2048, 32), (3, 32, 5000, 1024, 8), (2, 16, 700, 64, 1)])
-def test_fused_indexer_attention_launch_equals_separate_launches(ops, B, H, n, topk, nsplit):
+def test_fused_indexer_attention_launch_equals_separate_launches(ops, monkeypatch, B, H, n, topk, nsplit):
     """One role-split launch (attention over a given selection + the indexer scan)
-    returns bit for bit what the two separate launches return."""
+    returns bit for bit what the two separate launches return (the role-split launch
+    contains the mma.sync attention body, so the separate launch is pinned to it)."""
+    monkeypatch.setenv("DSA_MLA_TC", "0")
     torch.manual_seed(B * 1000 + H)
     q = dev(torch.randn(B, H, 576).to(torch.bfloat16))
     kv = dev(torch.randn(B, n, 576).to(torch.bfloat16))
