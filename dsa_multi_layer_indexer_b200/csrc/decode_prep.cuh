@@ -164,6 +164,17 @@ silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16
   }
 }
 
+// ------------------------------------------------------------------ small copies
+// dst[0, n) = src[0, n) in 16-byte pieces. Either side may be pinned host memory (it is
+// mapped into the device's address space): a kernel node starts sooner than a copy-engine
+// node inside a CUDA graph, which matters for the few KB a decode step brings from the host.
+__global__ void __launch_bounds__(256)
+copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n16) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n16; i += int64_t(gridDim.x) * 256) dst[i] = src[i];
+}
+
 // ------------------------------------------------------------------ skinny GEMV
 // y[b, n] = sum_k W[n, k] x[b, k] for 1..4 rows of x (decode batch): bf16 operands,
 // fp32 accumulation, one rounding. The weight matrix is streamed once with 16-byte

@@ -713,6 +713,18 @@ int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, v
   return DSA_OK;
 }
 
+int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream) {
+  DSA_REQUIRE(dst && src, "copy: null pointer");
+  DSA_REQUIRE(bytes > 0 && bytes % 16 == 0 && aligned16(dst) && aligned16(src),
+              "copy: size and both pointers must be multiples of 16 bytes");
+  const int64_t n16 = bytes / 16;
+  int64_t blocks = (n16 + 255) / 256;
+  if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+  DSA_CUDA(launch_pdl(prep::copy16_kernel, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<uint4*>(dst), static_cast<const uint4*>(src), n16));
+  return DSA_OK;
+}
+
 int dsa_gemv_bf16(const void* w, const void* x, void* y, int batch, int n, int k, int64_t x_stride,
                   int64_t y_stride, void* stream) {
   DSA_REQUIRE(w && x && y, "gemv: null pointer");

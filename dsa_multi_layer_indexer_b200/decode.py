@@ -124,8 +124,9 @@ class HostDecoder:
     output (and the selection) back. This is the call a host-side integrator
     makes when its tensors are not already on the device."""
 
-    def __init__(self, state: HotPathState, cache: LayerCache, sm_scale: float) -> None:
+    def __init__(self, state: HotPathState, cache: LayerCache, sm_scale: float, kernel_copies: bool = True) -> None:
         self.state, self.cache = state, cache
+        self.kernel_copies = kernel_copies
         s = state
         # pinned mirrors of the two arenas, with the same views into them
         self.h_in = torch.zeros(s.in_arena.shape, dtype=torch.uint8).pin_memory()
@@ -156,9 +157,12 @@ class HostDecoder:
         # main stream, q (needed only by the attention) on a forked stream beside the scan.
         small = s.index_q.numel() + s.index_w.numel() * 4
         side.wait_stream(main)
-        s.in_arena[:small].copy_(self.h_in[:small], non_blocking=True)
+        if self.kernel_copies and small % 16 == 0:
+            ops.copy_bytes(s.in_arena[:small], self.h_in[:small])  # a kernel node: starts sooner than a copy node
+        else:
+            s.in_arena[:small].copy_(self.h_in[:small], non_blocking=True)
         with torch.cuda.stream(side):
-            s.in_arena[small:].copy_(self.h_in[small:], non_blocking=True)
+            s.in_arena[small:].copy_(self.h_in[small:], non_blocking=True)  # copy engine (a kernel copy measured no better)
         s.run_indexer(self.cache)
         main.wait_stream(side)
         # The selection goes back on the forked stream while the attention runs, and the
@@ -166,7 +170,10 @@ class HostDecoder:
         # buffer, so no device-to-host copy is left on the step's critical path.
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            self.h_indices.copy_(s.indices, non_blocking=True)
+            if self.kernel_copies:
+                ops.copy_bytes(self.h_indices, s.indices)
+            else:
+                self.h_indices.copy_(s.indices, non_blocking=True)
         ops.sparse_mla_decode(s.q, self.cache.kv, s.indices, sm_scale, s.seq_lens, scratch=s.scratch,
                               out=self.h_out)
         main.wait_stream(side)

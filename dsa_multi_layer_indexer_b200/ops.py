@@ -473,6 +473,16 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def copy_bytes(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """``dst <- src`` (same byte count, a multiple of 16) by a kernel on the current stream.
+    Each side is a contiguous CUDA tensor or pinned host memory."""
+    for t, name in ((dst, "dst"), (src, "src")):
+        _need((t.is_cuda or t.is_pinned()) and t.is_contiguous(), f"{name} must be contiguous CUDA or pinned memory")
+    nbytes = dst.numel() * dst.element_size()
+    _need(nbytes == src.numel() * src.element_size() and nbytes % 16 == 0, "byte counts must match and be a multiple of 16")
+    _lib.check(_lib.lib().dsa_copy_bytes(_ptr(dst), _ptr(src), nbytes, _stream()))
+
+
 def gemv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``x @ weight.T`` for a decode batch of 1..4 rows (bf16, fp32 accumulation): the weight
     matrix ``[n, k]`` is streamed once. For the projection shapes where the library GEMV is

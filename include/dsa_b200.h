@@ -253,6 +253,12 @@ int dsa_rmsnorm(const void* x, const void* weight, void* out, int64_t rows, int 
  * (a multiple of 8): sum_out = x + delta (rounded to bf16), out = rmsnorm(sum_out). */
 int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, void* sum_out, void* out,
                          int64_t rows, int dim, float eps, void* stream);
+/* dst[0, bytes) = src[0, bytes) by a kernel (16-byte pieces; bytes and both pointers
+ * multiples of 16). Either side may be pinned host memory: inside a CUDA graph a kernel
+ * node starts sooner than a copy-engine node, which matters for the few KB a decode step
+ * brings from the host. No counterpart in the reference. */
+int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream);
+
 /* y[b, n] = sum_k w[n, k] x[b, k] for a decode batch of 1..4 rows: bf16 operands, fp32
  * accumulation, w [n, k] row-major streamed once (the projection GEMVs of
  * src/lagged_indexer_dsa/dsa_layer.py:87-125 at decode). k a multiple of 8,

@@ -69,3 +69,19 @@ def test_step_graph_and_host_decoder_agree():
         assert torch.equal(dec.h_indices, idx_eager.cpu())
     assert dec.h2d_bytes == st.in_arena.numel() and dec.d2h_bytes == st.out_arena.numel()
     _lib.check_device_status()
+
+
+def test_copy_bytes_between_pinned_host_and_device():
+    from dsa_multi_layer_indexer_b200 import ops
+
+    src = torch.arange(4096, dtype=torch.int32).pin_memory()
+    dst = torch.zeros(4096, dtype=torch.int32, device="cuda")
+    ops.copy_bytes(dst, src)
+    back = torch.zeros(4096, dtype=torch.int32).pin_memory()
+    ops.copy_bytes(back, dst)
+    torch.cuda.synchronize()
+    assert torch.equal(dst.cpu(), src) and torch.equal(back, src)
+    with pytest.raises(ValueError):
+        ops.copy_bytes(dst[:3], src[:3])  # 12 bytes: not a multiple of 16
+    with pytest.raises(ValueError):
+        ops.copy_bytes(dst, torch.zeros(4096, dtype=torch.int32))  # pageable host memory
