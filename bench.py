@@ -421,7 +421,8 @@ def run_ours(args):
     # ---- end to end with host buffers (rank-local operands in pinned memory)
     e2e = None
     if not seq_shard:
-        dec = [HostDecoder(states[l], caches[l], SM_SCALE, kernel_copies=os.environ.get("DSA_E2E_KERNEL_COPIES", "1") != "0")
+        dec = [HostDecoder(states[l], caches[l], SM_SCALE, kernel_copies=os.environ.get("DSA_E2E_KERNEL_COPIES", "1") != "0",
+                            poll=os.environ.get("DSA_E2E_POLL", "1") != "0")
                for l in range(min(L, 4))]
         for d in dec:
             d.h_index_q.copy_(h_iq8)
@@ -437,7 +438,7 @@ def run_ours(args):
         e2e_dt = (time.perf_counter() - t0) / args.steps
         e2e = {"value": 1.0 / e2e_dt, "unit": UNIT, "ms_per_step": e2e_dt * 1e3,
                "h2d_bytes_per_step": dec[0].h2d_bytes, "d2h_bytes_per_step": dec[0].d2h_bytes,
-               "note": "one graph per step: index_q / index_w pinned host -> device by a kernel node, q by the copy engine beside the scan, kernels, selection -> pinned host by a kernel node on a forked stream, attention output written straight into pinned host memory; sync every step"}
+               "note": "one graph per step: index_q / index_w pinned host -> device by a kernel node, q by the copy engine beside the scan, kernels, selection -> pinned host by a kernel node on a forked stream, attention output written straight into pinned host memory; the host polls the epoch word the graph's last node posts, every step"}
 
     _lib.check_device_status()
     times = torch.tensor([ms_step, scan_ms, topk_ms, attn_ms, e2e["ms_per_step"] if e2e else 0.0],

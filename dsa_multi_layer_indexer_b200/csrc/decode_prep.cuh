@@ -175,6 +175,18 @@ copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n1
   for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n16; i += int64_t(gridDim.x) * 256) dst[i] = src[i];
 }
 
+// Completion signal for a host that polls instead of synchronising: bumps a device-side
+// epoch counter and posts the new value to a word of pinned host memory, after a
+// system-wide fence so that everything the stream wrote to host memory before this
+// launch is visible first.
+__global__ void post_epoch_kernel(uint32_t* __restrict__ counter, volatile uint32_t* __restrict__ host_flag) {
+  pdl_wait();
+  const uint32_t e = *counter + 1;
+  *counter = e;
+  __threadfence_system();
+  *host_flag = e;
+}
+
 // ------------------------------------------------------------------ skinny GEMV
 // y[b, n] = sum_k W[n, k] x[b, k] for 1..4 rows of x (decode batch): bf16 operands,
 // fp32 accumulation, one rounding. The weight matrix is streamed once with 16-byte

@@ -725,6 +725,14 @@ int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream) {
   return DSA_OK;
 }
 
+int dsa_post_epoch(uint32_t* counter, uint32_t* host_flag, void* stream) {
+  DSA_REQUIRE(counter && host_flag, "post epoch: null pointer");
+  // an ordinary launch (no programmatic overlap): it must start after everything before it has completed
+  prep::post_epoch_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter, host_flag);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
 int dsa_gemv_bf16(const void* w, const void* x, void* y, int batch, int n, int k, int64_t x_stride,
                   int64_t y_stride, void* stream) {
   DSA_REQUIRE(w && x && y, "gemv: null pointer");

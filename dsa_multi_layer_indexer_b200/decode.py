@@ -11,7 +11,9 @@ are read on the device, and a step makes no allocation and no host sync.
 
 from __future__ import annotations
 
+import ctypes
 import dataclasses
+import time
 from typing import Optional
 
 import torch
@@ -124,10 +126,17 @@ class HostDecoder:
     output (and the selection) back. This is the call a host-side integrator
     makes when its tensors are not already on the device."""
 
-    def __init__(self, state: HotPathState, cache: LayerCache, sm_scale: float, kernel_copies: bool = True) -> None:
+    def __init__(self, state: HotPathState, cache: LayerCache, sm_scale: float, kernel_copies: bool = True,
+                 poll: bool = True) -> None:
         self.state, self.cache = state, cache
         self.kernel_copies = kernel_copies
+        self.poll = poll
         s = state
+        # completion by polling: the graph's last node posts an epoch to pinned host memory
+        self._epoch_dev = torch.zeros(1, dtype=torch.int32, device=s.in_arena.device)
+        self._flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._flag_word = ctypes.c_uint32.from_address(self._flag.data_ptr())
+        self._expected = 0
         # pinned mirrors of the two arenas, with the same views into them
         self.h_in = torch.zeros(s.in_arena.shape, dtype=torch.uint8).pin_memory()
         self.h_outbuf = torch.zeros(s.out_arena.shape, dtype=torch.uint8).pin_memory()
@@ -149,6 +158,8 @@ class HostDecoder:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._body(sm_scale)
+        torch.cuda.synchronize()
+        self._expected = int(self._flag.item())  # the warm-up launch above already posted once
 
     def _body(self, sm_scale: float) -> None:
         s = self.state
@@ -177,6 +188,8 @@ class HostDecoder:
         ops.sparse_mla_decode(s.q, self.cache.kv, s.indices, sm_scale, s.seq_lens, scratch=s.scratch,
                               out=self.h_out)
         main.wait_stream(side)
+        if self.poll:
+            ops.post_epoch(self._epoch_dev, self._flag)  # after the join: every output is in host memory
 
     @property
     def h2d_bytes(self) -> int:
@@ -188,7 +201,25 @@ class HostDecoder:
 
     def step(self) -> torch.Tensor:
         """Fill ``h_index_q``/``h_index_w``/``h_q`` first; returns ``h_out`` (and
-        ``h_indices`` is valid) once the step has completed."""
+        ``h_indices`` is valid) once the step has completed. With ``poll`` the host
+        waits on the epoch word the graph's last node posts to pinned memory (falling
+        back to a stream synchronise after 2 s) instead of a stream synchronise."""
         self.graph.replay()
-        torch.cuda.current_stream().synchronize()
+        if self.poll:
+            self._expected = (self._expected + 1) & 0xFFFFFFFF
+            word, want = self._flag_word, self._expected
+            deadline = None
+            spins = 0
+            while word.value != want:
+                spins += 1
+                if spins & 0xFFFF == 0:
+                    now = time.monotonic()
+                    if deadline is None:
+                        deadline = now + 2.0
+                    elif now > deadline:
+                        break
+            if word.value != want:
+                torch.cuda.current_stream().synchronize()
+        else:
+            torch.cuda.current_stream().synchronize()
         return self.h_out

@@ -483,6 +483,16 @@ def copy_bytes(dst: torch.Tensor, src: torch.Tensor) -> None:
     _lib.check(_lib.lib().dsa_copy_bytes(_ptr(dst), _ptr(src), nbytes, _stream()))
 
 
+def post_epoch(counter: torch.Tensor, host_flag: torch.Tensor) -> None:
+    """Enqueues the completion signal: ``counter`` (one int32 on the device) is bumped and
+    its value posted to ``host_flag`` (one int32 of pinned host memory) after everything
+    enqueued so far on the current stream."""
+    _need(counter.is_cuda and counter.dtype == torch.int32 and counter.numel() == 1, "counter: one CUDA int32")
+    _need(host_flag.is_pinned() and host_flag.dtype == torch.int32 and host_flag.numel() == 1,
+          "host_flag: one pinned int32")
+    _lib.check(_lib.lib().dsa_post_epoch(_ptr(counter), _ptr(host_flag), _stream()))
+
+
 def gemv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``x @ weight.T`` for a decode batch of 1..4 rows (bf16, fp32 accumulation): the weight
     matrix ``[n, k]`` is streamed once. For the projection shapes where the library GEMV is

@@ -259,6 +259,12 @@ int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, v
  * brings from the host. No counterpart in the reference. */
 int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream);
 
+/* Completion signal for a host that polls instead of calling a stream synchronise:
+ * *counter (device) is incremented and its new value posted to *host_flag (pinned
+ * host memory) once everything enqueued before it on the stream has completed and its
+ * writes to host memory are visible. No counterpart in the reference. */
+int dsa_post_epoch(uint32_t* counter, uint32_t* host_flag, void* stream);
+
 /* y[b, n] = sum_k w[n, k] x[b, k] for a decode batch of 1..4 rows: bf16 operands, fp32
  * accumulation, w [n, k] row-major streamed once (the projection GEMVs of
  * src/lagged_indexer_dsa/dsa_layer.py:87-125 at decode). k a multiple of 8,

@@ -85,3 +85,22 @@ def test_copy_bytes_between_pinned_host_and_device():
         ops.copy_bytes(dst[:3], src[:3])  # 12 bytes: not a multiple of 16
     with pytest.raises(ValueError):
         ops.copy_bytes(dst, torch.zeros(4096, dtype=torch.int32))  # pageable host memory
+
+
+def test_host_decoder_stream_sync_mode_agrees_with_polling():
+    from dsa_multi_layer_indexer_b200.decode import HostDecoder
+
+    ops, st, cache, host = make_case(ctx=4096, heads=16, topk=512, seed=6)
+    sm = 192 ** -0.5
+    outs = []
+    for kw in (dict(poll=True, kernel_copies=True), dict(poll=False, kernel_copies=False)):
+        dec = HostDecoder(st, cache, sm, **kw)
+        dec.h_index_q.copy_(host["iq8"])
+        dec.h_index_w.copy_(host["w"])
+        dec.h_q.copy_(host["q"])
+        for _ in range(3):
+            dec.h_out.zero_()
+            got = dec.step().clone()
+        outs.append((got, dec.h_indices.clone()))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert float(outs[0][0].float().abs().max()) > 0
