@@ -82,7 +82,7 @@ def workload_config(args, world):
                    if args.graph_per_layer or args.layers <= 1 else
                    "one CUDA graph over %d consecutive layer steps, as a model's decode step is captured "
                    "(5 kernels per step: scan, classify, finish, attention partials, combine); "
-                   "steps beyond a multiple of %d use one graph per step" % (args.layers, args.layers)),
+                   "steps beyond a multiple of %d share one more graph" % (args.layers, args.layers)),
     }
 
 
@@ -317,25 +317,38 @@ def run_ours(args):
     # A decode step of a real model is ONE graph over all its layers, so the timed loop
     # replays a graph that holds the hot paths of L consecutive layers (L steps per
     # replay, distinct caches); --graph-per-layer launches one graph per step instead.
-    big = None
+    big = tail = None
+    n_big, rem = 0, args.steps
     if not seq_shard and not args.graph_per_layer and L > 1:
-        big = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(big):
-            for l in range(L):
-                hot_path(states[l], caches[l])
-        torch.cuda.synchronize()
-    n_big, rem = divmod(args.steps, L) if big is not None else (0, args.steps)
+        n_big, rem = divmod(args.steps, L)
+
+        def capture_steps(count):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for l in range(count):
+                    hot_path(states[l], caches[l])
+            torch.cuda.synchronize()
+            return g
+
+        if n_big:
+            big = capture_steps(L)
+        if rem > 1:  # the steps beyond a multiple of L share a graph too
+            tail = capture_steps(rem)
 
     def run_steps():
         for _ in range(n_big):
             big.replay()
-        for i in range(rem):
-            graphs[i % L].replay()
+        if tail is not None:
+            tail.replay()
+        else:
+            for i in range(rem):
+                graphs[i % L].replay()
 
     for i in range(max(args.warmup, 3)):
         graphs[i % L].replay()
-    if big is not None:
-        big.replay()
+    for g in (big, tail):
+        if g is not None:
+            g.replay()
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
