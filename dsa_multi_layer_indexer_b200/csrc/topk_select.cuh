@@ -293,8 +293,7 @@ topk_finish_kernel(const Params p) {
     for (int u = 0; u < kRegCand; ++u)
       if (uint32_t(u) < cn0) rc[u] = __ldcg(src + u);
   }
-  uint32_t C = 0;
-  const uint32_t c_off = block_exclusive_scan<kFinWarps>(c_cnt, sh.warp_tot, &C);
+  // (!take_all implies the threshold bin holds at least one candidate: need >= 1)
   // the histogram has served every classify CTA: clear it for the next scan
   {
     uint4* gh4 = reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins);
@@ -304,7 +303,7 @@ topk_finish_kernel(const Params p) {
 
   uint32_t kstar = 0xFFFFFFFFu;
   bool resolved = false;
-  if (!take_all && C > 0) {
+  if (!take_all) {
     // ---- fast path: the classify kernel also histogrammed bits 19..10 of the
     // candidates, so the threshold's top 22 bits are one scan away; what shares
     // them (a handful of keys) is ranked by brute force.
@@ -361,7 +360,10 @@ topk_finish_kernel(const Params p) {
       __syncthreads();
     }
   }
-  if (!take_all && C > 0 && !resolved) {
+  if (!take_all && !resolved) {
+    // the general path needs every thread's offset into the candidate list and the total
+    uint32_t C = 0;
+    const uint32_t c_off = block_exclusive_scan<kFinWarps>(c_cnt, sh.warp_tot, &C);
     const bool listed = C <= uint32_t(kCandCap);
     if (listed) {
       uint32_t at = c_off;
