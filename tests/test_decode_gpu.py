@@ -104,3 +104,41 @@ def test_host_decoder_stream_sync_mode_agrees_with_polling():
         outs.append((got, dec.h_indices.clone()))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     assert float(outs[0][0].float().abs().max()) > 0
+
+
+def test_hot_path_at_config2_size_matches_oracle():
+    """BASELINE config 2 at full size (batch 1, context 131072, 64 x 128 FP8 indexer,
+    top-2048, 128 MLA heads bf16) through the persistent-buffer step: logits within
+    1e-2, the selected set bit-exact on margin-enforced inputs, attention within 2e-2."""
+    from conftest import corr_diff, rel_err
+    from dsa_multi_layer_indexer_b200 import _lib
+    from dsa_multi_layer_indexer_b200.decode import HotPathState, LayerCache
+
+    ctx, heads, topk = 131072, 128, 2048
+    g = torch.Generator().manual_seed(0)
+    iq = torch.randn(1, 64, 128, generator=g)
+    ik = torch.randn(ctx, 128, generator=g)
+    w = torch.randn(1, 64, generator=g) / 8
+    iq8, ik8, wp, sk = O.make_fp8_indexer_inputs(iq, ik, w)
+    ref_logits = O.indexer_logits_fp8(iq8, ik8, wp, sk)
+    sk, ref_row = O.enforce_topk_margin(ref_logits[0], sk, topk)
+    sk = sk.float()
+    q = torch.randn(1, heads, 576, generator=g).to(torch.bfloat16)
+    kv = torch.randn(ctx, 576, generator=g).to(torch.bfloat16)
+    cache = LayerCache(ik8.view(torch.uint8).view(1, ctx, 128).cuda(), sk.view(1, ctx).cuda(), kv.unsqueeze(0).cuda())
+    st = HotPathState(1, heads, 64, ctx, topk, "cuda")
+    st.index_q.copy_(iq8.view(torch.uint8).view(1, 64, 128))
+    st.index_w.copy_(wp.view(1, 64))
+    st.q.copy_(q)
+    sm = 192 ** -0.5
+    out = st.run(cache, sm).float().cpu()
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    logits = st.logits[:, :ctx].cpu()
+    assert rel_err(logits, ref_row.float().unsqueeze(0)) < 1e-2
+    ref_idx = O.select_topk(ref_row.float().unsqueeze(0), topk, pad_value=-1)
+    assert torch.equal(st.indices.cpu().long(), ref_idx)
+    ref_out = O.sparse_mla_decode(q, kv, ref_idx, [ctx], sm)
+    assert rel_err(out, ref_out) < 2e-2
+    assert corr_diff(out, ref_out) < 1e-3
+    assert int(st.hist.abs().sum()) == 0  # the histogram is re-armed for the next step
