@@ -16,9 +16,10 @@ ATTN_TOL = 2e-2
 LOGIT_TOL = 1e-2
 
 
-def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=31):
+def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=31, lens=None):
     g = torch.Generator().manual_seed(seed)
-    lens = [cap, 700, 1300][:B]
+    lens = [cap, 700, 1300][:B] if lens is None else list(lens)
+    B = len(lens)
     pages_per = cap // 64
     num_pages = B * pages_per + 5
     perm = torch.randperm(num_pages, generator=g)[:B * pages_per].view(B, pages_per).int()
@@ -159,3 +160,21 @@ def test_head_padding_and_graph_replay():
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(g_attn, eager_attn) and torch.equal(g_nxt, eager_nxt)
+
+
+def test_ragged_batch_at_serving_size():
+    """A batch shaped like BASELINE config 4 at reduced batch (6 rows, lengths from 16384 to
+    65536, page-64 index keys, fp8-packed latent pool, 128 heads, top-2048): the batch is large
+    enough for the tcgen05 attention kernel; sets bit-exact, attention within 2e-2."""
+    from dsa_multi_layer_indexer_b200 import _lib, serving
+
+    serving.clear_scratch()
+    lens = [65536, 16384, 40000, 23456, 65000, 32768]
+    c = build_case(True, cap=65536, heads=128, topk=2048, seed=41, lens=lens)
+    attn, nxt = call(c)
+    ref = ref_attention(c)
+    assert rel_err(attn[0].float().cpu(), ref) < ATTN_TOL
+    assert corr_diff(attn[0].float().cpu(), ref) < 1e-3
+    got = [sorted(v for v in row if v >= 0) for row in nxt.cpu().tolist()]
+    assert got == ref_next(c)
+    _lib.check_device_status()
