@@ -31,7 +31,8 @@ constexpr int kTileBytes = kTileKeys * kKeyBytes;
 constexpr int kStagesTwoPerSm = 4;   // 92 KB of shared memory: two CTAs per SM
 constexpr int kStagesOnePerSm = 10;  // 190 KB: one CTA per SM with every tile of a 128K row in flight
 constexpr int kMaxHeads = DSA_INDEX_MAX_HEADS;
-constexpr int kThreads = 192;    // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kThreads = 192;    // one epilogue group: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kThreads2 = 320;   // two epilogue groups: warps 2..5 take the even tiles, warps 6..9 the odd ones
 constexpr int kTmemCols = 128;   // two 64-column fp32 accumulators
 constexpr int kHistBins = DSA_TOPK_HIST_BINS;
 
@@ -102,10 +103,11 @@ __device__ __forceinline__ int row_of_rank(const Params& p, int y, int R) {
 // passes its block indices; the fused indexer + attention launch passes indices
 // of its scan partition). `tmap_ptr` must point at a __grid_constant__ kernel
 // parameter; `smem_raw` is the CTA's dynamic shared memory.
-template <int kStages>
+template <int kStages, int kEpiGroups = 1>
 __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const Params& p, const int bx,
                                              const int G, const int r_grid, uint8_t* smem_raw) {
   const CUtensorMap& tmap = *tmap_ptr;
+  constexpr int kBodyThreads = 64 + 128 * kEpiGroups;  // threads that take part (the caller's CTA may not be larger)
   constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
   // 1024-byte alignment for the swizzled tiles, computed on the shared-window
   // address so the pointer keeps its address space
@@ -163,7 +165,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   }
   DSA_STAMP(stamp_cta, 11);
   if (want_hist)
-    for (int i = tid; i < kHistBins / 4; i += kThreads)
+    for (int i = tid; i < kHistBins / 4; i += kBodyThreads)
       reinterpret_cast<uint4*>(s_hist)[i] = make_uint4(0, 0, 0, 0);
   pdl_wait();  // keys, query, weights and lengths may come from the previous kernel
   pdl_launch_dependents();
@@ -173,13 +175,13 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   len = row_len(p, r);
   // q[r] is [n_heads][128 B]. Its loads (and the head weights') are issued before
   // the key tiles' so they are not queued behind 64 KB of TMA traffic per CTA.
-  constexpr int kQChunks = (kMaxHeads * 8 + kThreads - 1) / kThreads;
+  constexpr int kQChunks = (kMaxHeads * 8 + kBodyThreads - 1) / kBodyThreads;
   uint4 qv[kQChunks];
   {
     const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + size_t(r) * p.n_heads * kKeyBytes);
 #pragma unroll
     for (int k = 0; k < kQChunks; ++k) {
-      const int i = tid + k * kThreads;
+      const int i = tid + k * kBodyThreads;
       qv[k] = make_uint4(0, 0, 0, 0);
       if (i < kMaxHeads * 8 && (i >> 3) < p.n_heads) qv[k] = qsrc[i];
     }
@@ -205,7 +207,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   // lands in chunk c ^ (h & 7)); rows past n_heads are zero -> relu(0) * 0.
 #pragma unroll
   for (int k = 0; k < kQChunks; ++k) {
-    const int i = tid + k * kThreads;
+    const int i = tid + k * kBodyThreads;
     if (i < kMaxHeads * 8) {
       const int h = i >> 3, c = i & 7;
       *reinterpret_cast<uint4*>(s_q + h * kKeyBytes + ((c ^ (h & 7)) << 4)) = qv[k];
@@ -268,6 +270,9 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // tcgen05.ld: warp w may touch lanes 32 (w % 4) ..
+    // With two epilogue groups, warps 2..5 take the even live tiles (accumulator 0) and warps
+    // 6..9 the odd ones (accumulator 1), so two tiles are in their epilogue at once.
+    const int grp = kEpiGroups > 1 ? (warp - 2) >> 2 : 0;
     const float* kscale_row = p.k_scale;
     float* out_row = p.logits + int64_t(r) * p.slab_stride;
     const float neg_inf = __int_as_float(0xff800000);
@@ -285,8 +290,9 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       return *reinterpret_cast<const float*>(p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES +
                                              DSA_PAGE_TOKENS * kKeyBytes + (g & 63) * 4);
     };
-    float next_scale = load_scale(bx);
-    for (int t = bx; t < p.tiles_per_row; t += G) {
+    float next_scale = load_scale(bx + grp * G);
+    for (int t = bx, j = 0; t < p.tiles_per_row; t += G, ++j) {
+      if ((j % kEpiGroups) != grp) continue;  // the other group's tile
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
       if (int64_t(t) * kTileKeys >= len || dead) {  // no visible key in this tile
         if (g < p.ctx) out_row[g] = neg_inf;
@@ -294,7 +300,8 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       }
       const bool valid = g < len;
       const float scale = next_scale;
-      next_scale = load_scale(t + G);
+      next_scale = load_scale(t + kEpiGroups * G);
+      it = j;  // live tiles come first, so the j-th tile of the CTA is its j-th live tile
       const int b = it & 1;
       const uint32_t bph = (it >> 1) & 1;
       ++it;
@@ -354,7 +361,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
     // only the bins this CTA touched (a narrow band around the logits' magnitude)
     uint32_t* gh = p.hist + size_t(r) * kHistBins;
     const int hi = int(bars->bin_hi);
-    for (int i = int(bars->bin_lo) + tid; i <= hi; i += kThreads) {
+    for (int i = int(bars->bin_lo) + tid; i <= hi; i += kBodyThreads) {
       const uint32_t c = s_hist[i];
       if (c) atomicAdd(&gh[i], c);
     }
@@ -367,11 +374,11 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   }
 }
 
-template <int kStages>
-__global__ void __launch_bounds__(kThreads, kStages <= kStagesTwoPerSm ? 2 : 1)
+template <int kStages, int kEpiGroups = 1>
+__global__ void __launch_bounds__(64 + 128 * kEpiGroups, kStages <= kStagesTwoPerSm ? 2 : 1)
 indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
   extern __shared__ uint8_t scan_smem[];
-  scan_tc_body<kStages>(&tmap, p, blockIdx.x, gridDim.x, blockIdx.y, scan_smem);
+  scan_tc_body<kStages, kEpiGroups>(&tmap, p, blockIdx.x, gridDim.x, blockIdx.y, scan_smem);
 }
 
 // ------------------------------------------------------------------------------
