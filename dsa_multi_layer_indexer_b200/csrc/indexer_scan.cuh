@@ -33,7 +33,8 @@ constexpr int kStagesOnePerSm = 10;  // 190 KB: one CTA per SM with every tile o
 constexpr int kMaxHeads = DSA_INDEX_MAX_HEADS;
 constexpr int kThreads = 192;    // one epilogue group: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int kThreads2 = 320;   // two epilogue groups: warps 2..5 take the even tiles, warps 6..9 the odd ones
-constexpr int kTmemCols = 128;   // two 64-column fp32 accumulators
+constexpr int kMaxAcc = 4;       // accumulators (64 fp32 columns each): one per epilogue group, at least two
+__host__ __device__ constexpr int tmem_cols(int n_acc) { return n_acc <= 2 ? 128 : 256; }  // allocations are powers of two
 constexpr int kHistBins = DSA_TOPK_HIST_BINS;
 
 struct Params {
@@ -62,8 +63,8 @@ template <int kStages>
 struct __align__(8) Barriers {
   uint64_t full[kStages];
   uint64_t empty[kStages];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t acc_full[kMaxAcc];
+  uint64_t acc_empty[kMaxAcc];
   uint32_t tmem_base;
   uint32_t abort;
   uint32_t bin_lo;  // range of histogram bins this CTA touched
@@ -108,6 +109,9 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
                                              const int G, const int r_grid, uint8_t* smem_raw) {
   const CUtensorMap& tmap = *tmap_ptr;
   constexpr int kBodyThreads = 64 + 128 * kEpiGroups;  // threads that take part (the caller's CTA may not be larger)
+  constexpr int kAcc = kEpiGroups < 2 ? 2 : kEpiGroups;  // tile `it` accumulates in buffer it % kAcc
+  constexpr int kTmemCols = tmem_cols(kAcc);
+  static_assert(kAcc <= kMaxAcc, "at most four epilogue groups");
   constexpr size_t kSmemStages = size_t(kStages) * kTileBytes;
   // 1024-byte alignment for the swizzled tiles, computed on the shared-window
   // address so the pointer keeps its address space
@@ -154,7 +158,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       mbar_init(smem_u32(&bars->full[s]), 1);
       mbar_init(smem_u32(&bars->empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAcc; ++b) {
       mbar_init(smem_u32(&bars->acc_full[b]), 1);
       mbar_init(smem_u32(&bars->acc_empty[b]), 4);
     }
@@ -250,8 +254,8 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
         const int s = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
-        const int b = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
+        const int b = it % kAcc;
+        const uint32_t bph = (it / kAcc) & 1;
         if (!mbar_wait(smem_u32(&bars->acc_empty[b]), bph ^ 1) ||
             !mbar_wait(smem_u32(&bars->full[s]), ph)) {
           atomicOr(&g_device_status, kStatusScanTimeout);
@@ -270,8 +274,8 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;  // tcgen05.ld: warp w may touch lanes 32 (w % 4) ..
-    // With two epilogue groups, warps 2..5 take the even live tiles (accumulator 0) and warps
-    // 6..9 the odd ones (accumulator 1), so two tiles are in their epilogue at once.
+    // With several epilogue groups, group g (warps 2 + 4 g .. 5 + 4 g) takes the live tiles
+    // it = g (mod groups) and their accumulator, so that many tiles are in their epilogue at once.
     const int grp = kEpiGroups > 1 ? (warp - 2) >> 2 : 0;
     const float* kscale_row = p.k_scale;
     float* out_row = p.logits + int64_t(r) * p.slab_stride;
@@ -302,8 +306,8 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       const float scale = next_scale;
       next_scale = load_scale(t + kEpiGroups * G);
       it = j;  // live tiles come first, so the j-th tile of the CTA is its j-th live tile
-      const int b = it & 1;
-      const uint32_t bph = (it >> 1) & 1;
+      const int b = it % kAcc;
+      const uint32_t bph = (it / kAcc) & 1;
       ++it;
       if (!mbar_wait(smem_u32(&bars->acc_full[b]), bph)) {
         atomicOr(&g_device_status, kStatusScanTimeout);
