@@ -417,5 +417,170 @@ decode_prep_kernel(const Params p) {
   }
 }
 
+// ------------------------------------------------------------------ serving-form indexer staging
+// Everything the serving model's indexer does to the new token between its
+// projection GEMVs and the scan (inference/modeling/transformer.py:1015-1066):
+//   q = wq_b(qr) [B, heads, 128], k = wk(x) [B, 128], w = weights_proj(x.float())
+//   k <- LayerNorm(k) in fp32, rounded to bf16                      (:418-433, :1052)
+//   rotary embedding of the first 64 dims in fp32, rounded to bf16  (:525-547),
+//     pairs (2i, 2i+1) when interleaved, (i, i+32) otherwise
+//   128-point Walsh-Hadamard butterfly in fp32, times 128^-0.5, rounded to bf16
+//     (:550-568, :571-592)
+//   act_quant over the 128 dims: amax = max(|x|, 1e-4), scale = amax / 448 or, with a
+//     scale format, 2^ceil(log2(amax / 448)); e4m3(x / scale)       (kernels.py:19-117)
+//   q bytes -> index_q, head weight = w * heads^-0.5 * q_scale * softmax_scale (:1063-1065)
+//   k bytes and scale -> the key cache at the token's position (:1062-1063), dense
+//     [B, cap, 128] + [B, cap] or 64-token pages of 8448 bytes.
+// One warp per 128-wide row (lane l holds dims 4l .. 4l+3); every product and sum is
+// rounded on its own (no fused multiply-add) so the arithmetic matches the reference's
+// elementwise torch ops.
+struct StageParams {
+  const __nv_bfloat16* q_raw;
+  const __nv_bfloat16* k_raw;
+  const float* w_raw;
+  const float* norm_w;
+  const float* norm_b;
+  const float* rope_cos;  // [cap, 32] real part of the rotary table
+  const float* rope_sin;  // [cap, 32] imaginary part
+  const int64_t* positions;
+  uint8_t* index_q;
+  float* index_w;
+  uint8_t* cache_index_k;
+  float* cache_k_scale;
+  uint8_t* pages;
+  const int32_t* page_table;
+  int64_t pt_stride;
+  int64_t cap;
+  int B, n_heads, interleave, round_scale;
+  float eps, head_scale, softmax_scale, hadamard_scale;
+};
+
+constexpr int kStageWarps = 8;
+
+__global__ void __launch_bounds__(kStageWarps * 32)
+indexer_stage_kernel(const StageParams p) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kStageWarps + (threadIdx.x >> 5);
+  const int rows_per_b = p.n_heads + 1;
+  const int b = row / rows_per_b, item = row % rows_per_b;
+  if (b >= p.B) return;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t pos = p.positions[b];
+  if (pos < 0 || pos >= p.cap) return;
+  const bool is_key = item == p.n_heads;
+  const __nv_bfloat16* src = is_key ? p.k_raw + int64_t(b) * 128 : p.q_raw + (int64_t(b) * p.n_heads + item) * 128;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * lane);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  float v[4] = {__bfloat162float(lo.x), __bfloat162float(lo.y), __bfloat162float(hi.x), __bfloat162float(hi.y)};
+  auto round_bf16 = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
+
+  if (is_key) {  // LayerNorm over the 128 dims: biased variance, weight and bias in fp32
+    float s = __fadd_rn(__fadd_rn(v[0], v[1]), __fadd_rn(v[2], v[3]));
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
+    const float mean = __fdiv_rn(s, 128.f);
+    float d[4], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      d[j] = __fsub_rn(v[j], mean);
+      ss = __fadd_rn(ss, __fmul_rn(d[j], d[j]));
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    const float rstd = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), p.eps)));
+    const float4 w4 = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
+    const float4 b4 = *reinterpret_cast<const float4*>(p.norm_b + 4 * lane);
+    const float w[4] = {w4.x, w4.y, w4.z, w4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = round_bf16(__fadd_rn(__fmul_rn(__fmul_rn(d[j], rstd), w[j]), bb[j]));
+  }
+
+  {  // rotary embedding of dims 0..63 (lanes 0..15); complex product (a + bi)(c + si)
+    const float* cr = p.rope_cos + pos * 32;
+    const float* sr = p.rope_sin + pos * 32;
+    float partner[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) partner[j] = __shfl_xor_sync(0xffffffffu, v[j], 8);
+    if (lane < 16) {
+      if (p.interleave) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float c = cr[2 * lane + u], s = sr[2 * lane + u];
+          const float a = v[2 * u], bi = v[2 * u + 1];
+          v[2 * u] = round_bf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(bi, s)));
+          v[2 * u + 1] = round_bf16(__fadd_rn(__fmul_rn(a, s), __fmul_rn(bi, c)));
+        }
+      } else {
+        const bool first = lane < 8;  // dims 0..31 are the real parts, 32..63 the imaginary parts
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = 4 * (lane & 7) + j;
+          const float c = cr[i], s = sr[i];
+          const float a = first ? v[j] : partner[j], bi = first ? partner[j] : v[j];
+          v[j] = first ? round_bf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(bi, s)))
+                       : round_bf16(__fadd_rn(__fmul_rn(a, s), __fmul_rn(bi, c)));
+        }
+      }
+    }
+  }
+
+  {  // Walsh-Hadamard butterfly: strides 1, 2 inside the lane, 4 .. 64 across lanes
+    float t0 = __fadd_rn(v[0], v[1]), t1 = __fsub_rn(v[0], v[1]);
+    float t2 = __fadd_rn(v[2], v[3]), t3 = __fsub_rn(v[2], v[3]);
+    v[0] = __fadd_rn(t0, t2);
+    v[2] = __fsub_rn(t0, t2);
+    v[1] = __fadd_rn(t1, t3);
+    v[3] = __fsub_rn(t1, t3);
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+      const bool upper = (lane & m) != 0;  // this lane holds the element with the stride bit set
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], m);
+        v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = round_bf16(__fmul_rn(v[j], p.hadamard_scale));
+  }
+
+  // act_quant over the row
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  amax = fmaxf(amax, 1e-4f);
+  float scale = __fmul_rn(amax, 1.0f / 448.0f);
+  if (p.round_scale) {  // next power of two at or above amax / 448
+    const uint32_t bits = __float_as_uint(scale);
+    const int e = int((bits >> 23) & 0xFFu) - 127 + ((bits & 0x7FFFFFu) != 0u ? 1 : 0);
+    scale = __uint_as_float(uint32_t(e + 127) << 23);
+  }
+  uint32_t packed = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float q = fminf(fmaxf(__fdiv_rn(v[j], scale), -448.f), 448.f);
+    packed |= uint32_t(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+  }
+  if (!is_key) {
+    *reinterpret_cast<uint32_t*>(p.index_q + (int64_t(b) * p.n_heads + item) * 128 + 4 * lane) = packed;
+    if (lane == 0) {
+      const float w = p.w_raw[int64_t(b) * p.n_heads + item];
+      p.index_w[int64_t(b) * p.n_heads + item] =
+          __fmul_rn(__fmul_rn(__fmul_rn(w, p.head_scale), scale), p.softmax_scale);
+    }
+  } else if (p.pages) {
+    const int32_t page = p.page_table[int64_t(b) * p.pt_stride + (pos >> 6)];
+    uint8_t* pg = p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES;
+    const int slot = int(pos & 63);
+    *reinterpret_cast<uint32_t*>(pg + slot * 128 + 4 * lane) = packed;
+    if (lane == 0) *reinterpret_cast<float*>(pg + DSA_PAGE_TOKENS * 128 + slot * 4) = scale;
+  } else {
+    *reinterpret_cast<uint32_t*>(p.cache_index_k + (int64_t(b) * p.cap + pos) * 128 + 4 * lane) = packed;
+    if (lane == 0) p.cache_k_scale[int64_t(b) * p.cap + pos] = scale;
+  }
+}
+
 }  // namespace prep
 }  // namespace dsa

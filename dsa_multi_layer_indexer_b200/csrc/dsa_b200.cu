@@ -807,6 +807,54 @@ int dsa_silu_mul_bf16(const void* gate, const void* up, void* out, int64_t n, vo
   return DSA_OK;
 }
 
+int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_raw,
+                          const float* k_norm_weight, const float* k_norm_bias, float k_norm_eps,
+                          const float* rope_cos, const float* rope_sin, const int64_t* positions,
+                          uint8_t* index_q, float* index_w, uint8_t* cache_index_k,
+                          float* cache_k_scale, uint8_t* pages, const int32_t* page_table,
+                          int64_t pt_stride, int B, int n_heads, int64_t cap, int rope_interleave,
+                          int round_scale, float head_scale, float softmax_scale, void* stream) {
+  DSA_REQUIRE(q_raw && k_raw && w_raw && k_norm_weight && k_norm_bias && rope_cos && rope_sin && positions &&
+                  index_q && index_w,
+              "indexer stage: null pointer");
+  DSA_REQUIRE((pages && page_table && pt_stride > 0) || (!pages && cache_index_k && cache_k_scale),
+              "indexer stage: give either the dense key cache or pages + page table");
+  DSA_REQUIRE(aligned16(q_raw) && aligned16(index_q) && aligned16(k_norm_weight) && aligned16(k_norm_bias) &&
+                  (pages ? aligned16(pages) : aligned16(cache_index_k)) && (uintptr_t(k_raw) & 7) == 0,
+              "indexer stage: pointers must be 16-byte aligned (k_raw: 8)");
+  DSA_REQUIRE(B > 0 && n_heads > 0 && cap > 0 && int64_t(B) * (n_heads + 1) < (int64_t(1) << 30),
+              "indexer stage: bad shape");
+  prep::StageParams p{};
+  p.q_raw = static_cast<const __nv_bfloat16*>(q_raw);
+  p.k_raw = static_cast<const __nv_bfloat16*>(k_raw);
+  p.w_raw = w_raw;
+  p.norm_w = k_norm_weight;
+  p.norm_b = k_norm_bias;
+  p.rope_cos = rope_cos;
+  p.rope_sin = rope_sin;
+  p.positions = positions;
+  p.index_q = index_q;
+  p.index_w = index_w;
+  p.cache_index_k = cache_index_k;
+  p.cache_k_scale = cache_k_scale;
+  p.pages = pages;
+  p.page_table = page_table;
+  p.pt_stride = pt_stride;
+  p.cap = cap;
+  p.B = B;
+  p.n_heads = n_heads;
+  p.interleave = rope_interleave;
+  p.round_scale = round_scale;
+  p.eps = k_norm_eps;
+  p.head_scale = head_scale;
+  p.softmax_scale = softmax_scale;
+  p.hadamard_scale = 0.08838834764831845f;  // 128^-0.5
+  const int rows = B * (n_heads + 1);
+  DSA_CUDA(launch_pdl(prep::indexer_stage_kernel, dim3((rows + prep::kStageWarps - 1) / prep::kStageWarps),
+                      dim3(prep::kStageWarps * 32), 0, static_cast<cudaStream_t>(stream), p));
+  return DSA_OK;
+}
+
 int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, const void* kv_a,
                     const void* q_abs, const void* q_pe, int64_t q_pe_stride, const void* kv_norm_w,
                     const void* mla_cos, const void* mla_sin, const void* idx_cos, const void* idx_sin,

@@ -510,6 +510,56 @@ def gemv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def indexer_stage_fp8(q_raw, k_raw, w_raw, k_norm_weight, k_norm_bias, k_norm_eps: float, rope_cos, rope_sin,
+                      positions, index_q, index_w, cache_index_k=None, cache_k_scale=None, pages=None,
+                      page_table=None, rope_interleave: bool = False, scale_fmt: Optional[str] = None,
+                      softmax_scale: Optional[float] = None) -> None:
+    """Serving-form indexer staging in one launch: the reference's
+    ``Indexer.stage_fp8_operands`` after its three projections
+    (inference/modeling/transformer.py:1015-1066) -- LayerNorm of the key, rotary
+    embedding, Hadamard rotation, ``act_quant`` (``scale_fmt`` not None = power-of-two
+    scales), folded head weights, and the append of the key to the dense cache
+    (``cache_index_k`` [B, cap, 128] u8 + ``cache_k_scale`` [B, cap]) or to 64-token
+    ``pages`` through ``page_table``. ``q_raw`` [B, heads, 128] / ``k_raw`` [B, 128] bf16,
+    ``w_raw`` [B, heads] fp32, ``rope_cos`` / ``rope_sin`` [cap, 32] fp32."""
+    _cuda_contig(q_raw, "q_raw", (torch.bfloat16,))
+    _cuda_contig(k_raw, "k_raw", (torch.bfloat16,))
+    for t, n in ((w_raw, "w_raw"), (k_norm_weight, "k_norm_weight"), (k_norm_bias, "k_norm_bias"),
+                 (rope_cos, "rope_cos"), (rope_sin, "rope_sin"), (index_w, "index_w")):
+        _cuda_contig(t, n, (torch.float32,))
+    _cuda_contig(positions, "positions", (torch.int64,))
+    _cuda_contig(index_q, "index_q", (torch.uint8, torch.float8_e4m3fn))
+    _need(q_raw.dim() == 3 and q_raw.shape[2] == INDEX_DIM, "q_raw must be [B, heads, 128]")
+    B, n_heads = q_raw.shape[0], q_raw.shape[1]
+    _need(k_raw.shape == (B, INDEX_DIM) and w_raw.shape == (B, n_heads) and index_w.shape == (B, n_heads)
+          and index_q.shape == q_raw.shape and positions.shape == (B,), "operand shapes disagree")
+    _need(k_norm_weight.numel() == INDEX_DIM and k_norm_bias.numel() == INDEX_DIM, "LayerNorm parameters must be [128]")
+    cap = rope_cos.shape[0]
+    _need(rope_cos.shape == (cap, 32) and rope_sin.shape == (cap, 32), "rotary tables must be [cap, 32]")
+    paged = pages is not None
+    if paged:
+        _cuda_contig(pages, "pages", (torch.uint8,))
+        _cuda_contig(page_table, "page_table", (torch.int32,))
+        _need(page_table.dim() == 2 and page_table.shape[0] == B, "page_table must be [B, pages per sequence]")
+        _need(pages.numel() % INDEX_PAGE_BYTES == 0, "page pool must be whole pages")
+        cap = min(cap, page_table.shape[1] * PAGE_TOKENS)
+    else:
+        _cuda_contig(cache_index_k, "cache_index_k", (torch.uint8, torch.float8_e4m3fn))
+        _cuda_contig(cache_k_scale, "cache_k_scale", (torch.float32,))
+        _need(cache_index_k.dim() == 3 and cache_index_k.shape[0] == B and cache_index_k.shape[2] == INDEX_DIM
+              and cache_k_scale.shape == cache_index_k.shape[:2], "caches must be [B, cap, 128] and [B, cap]")
+        cap = min(cap, cache_index_k.shape[1])
+    if softmax_scale is None:
+        softmax_scale = INDEX_DIM ** -0.5
+    _lib.check(_lib.lib().dsa_indexer_stage_fp8(
+        _ptr(q_raw), _ptr(k_raw), _ptr(w_raw), _ptr(k_norm_weight), _ptr(k_norm_bias), float(k_norm_eps),
+        _ptr(rope_cos), _ptr(rope_sin), _ptr(positions), _ptr(index_q), _ptr(index_w),
+        _ptr(cache_index_k) if not paged else None, _ptr(cache_k_scale) if not paged else None,
+        _ptr(pages) if paged else None, _ptr(page_table) if paged else None,
+        page_table.shape[1] if paged else 0, B, n_heads, cap, 1 if rope_interleave else 0,
+        0 if scale_fmt is None else 1, float(n_heads ** -0.5), float(softmax_scale), _stream()))
+
+
 def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, mla_sin, idx_cos, idx_sin,
                 positions, index_q, index_w, q_full, cache_index_k, cache_k_scale, cache_kv,
                 interleave: bool, eps: float) -> None:

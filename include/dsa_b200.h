@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 3
+#define DSA_ABI_VERSION 4
 
 enum dsa_status {
   DSA_OK = 0,
@@ -281,6 +281,30 @@ int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, c
                     uint8_t* cache_index_k, float* cache_k_scale, void* cache_kv,
                     int B, int H, int n_index_heads, int64_t cap, int interleave, float eps,
                     void* stream);
+
+/* Serving-form indexer staging: what the serving model's indexer does to the new
+ * token between its projection GEMVs and the scan
+ * (src/lagged_indexer_dsa/inference/modeling/transformer.py:1015-1066
+ * Indexer.stage_fp8_operands), one launch:
+ *   k = LayerNorm(k_raw) (fp32, weight + bias, :418-433); rotary embedding of dims 0..63 of
+ *   every query head and of k (:525-547; rope_interleave 1: pairs (2i, 2i+1), 0: pairs
+ *   (i, i+32)); 128-point Hadamard rotation times 128^-0.5 (:550-592); act_quant over the 128
+ *   dims (inference/modeling/kernels.py:19-117: scale = max(amax, 1e-4) / 448, or its next
+ *   power of two when round_scale != 0); index_q <- query bytes, index_w <- w_raw * head_scale *
+ *   q_scale * softmax_scale (:1063-1065, head_scale = heads^-0.5); the key's bytes and scale
+ *   are appended at positions[b] (:1061-1062) in the dense cache (pages NULL) or in 64-token
+ *   pages of DSA_INDEX_PAGE_BYTES addressed through page_table [B, pt_stride].
+ * q_raw bf16 [B, n_heads, 128]; k_raw bf16 [B, 128]; w_raw fp32 [B, n_heads]; k_norm_weight /
+ * k_norm_bias fp32 [128]; rope_cos / rope_sin fp32 [cap, 32] (real / imaginary part of the
+ * reference's freqs_cis); positions int64 [B]. Rounding follows the reference's op sequence
+ * (bf16 after LayerNorm, after the rotary embedding and after the rotation). */
+int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_raw,
+                          const float* k_norm_weight, const float* k_norm_bias, float k_norm_eps,
+                          const float* rope_cos, const float* rope_sin, const int64_t* positions,
+                          uint8_t* index_q, float* index_w, uint8_t* cache_index_k,
+                          float* cache_k_scale, uint8_t* pages, const int32_t* page_table,
+                          int64_t pt_stride, int B, int n_heads, int64_t cap, int rope_interleave,
+                          int round_scale, float head_scale, float softmax_scale, void* stream);
 
 /* ---- (a7) per-token e4m3 quantisation of index keys / queries --------------
  * scale = max(amax(row), clamp_min) / 448, q = sat(x / scale) -> e4m3 RN

@@ -313,3 +313,90 @@ def schedule_plan_depth(is_dsa: Sequence[bool], runs_indexer: Sequence[bool], co
             attend, produce = carried, False
         plan.append({"attend": attend, "produce": produce})
     return plan
+
+
+# ------------------------------------------------- serving-form indexer staging
+def layer_norm_128(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    """LayerNorm in fp32 with weight and bias, result in x's dtype
+    (inference/modeling/transformer.py:418-433)."""
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), weight, bias, eps).type_as(x)
+
+
+def rotary_embed(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """Rotary embedding as a complex product in fp32, result in x's dtype
+    (inference/modeling/transformer.py:525-547). x [..., 2n]; cos / sin broadcast
+    to [..., n] (real / imaginary part of freqs_cis). interleaved: the complex
+    pair i is (x[2i], x[2i+1]); otherwise (x[i], x[i+n]) and the output keeps the
+    real parts in the first half."""
+    xf = x.float()
+    n = x.shape[-1] // 2
+    if interleaved:
+        a, b = xf[..., 0::2], xf[..., 1::2]
+    else:
+        a, b = xf[..., :n], xf[..., n:]
+    re = a * cos - b * sin
+    im = a * sin + b * cos
+    if interleaved:
+        y = torch.stack([re, im], dim=-1).flatten(-2)
+    else:
+        y = torch.cat([re, im], dim=-1)
+    return y.to(x.dtype)
+
+
+def hadamard_rotate(x: torch.Tensor) -> torch.Tensor:
+    """rotate_activation on its pure-torch path: bf16 input, Walsh-Hadamard
+    butterfly in fp32 (strides 1, 2, ..., n/2; the element with the stride bit
+    clear gets the sum, the other the difference), times n^-0.5, back to bf16
+    (inference/modeling/transformer.py:550-568, :571-592)."""
+    dtype = x.dtype
+    n = x.shape[-1]
+    v = x.to(torch.bfloat16).float().reshape(-1, n).clone()
+    h = 1
+    while h < n:
+        w = v.view(-1, n // (2 * h), 2, h)
+        even, odd = w[:, :, 0, :].clone(), w[:, :, 1, :].clone()
+        w[:, :, 0, :] = even + odd
+        w[:, :, 1, :] = even - odd
+        h *= 2
+    y = (v * (n ** -0.5)).view(x.shape).to(torch.bfloat16)
+    return y.to(dtype)
+
+
+def act_quant_128(x: torch.Tensor, round_scale: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """act_quant over blocks of 128 (inference/modeling/kernels.py:19-117), for a
+    last dimension of exactly 128: amax = max(|x|, 1e-4) in fp32, scale =
+    amax * (1/448) or, with a scale format, 2^ceil(log2(amax * (1/448))) by the
+    reference's bit arithmetic (exponent + 1 when the mantissa is non-zero);
+    y = e4m3(clamp(x / scale, -448, 448)). Returns (uint8 bytes, fp32 scale [..., 1])."""
+    xf = x.float()
+    amax = xf.abs().amax(dim=-1, keepdim=True).clamp_min(1e-4)
+    scale = amax * torch.tensor(1.0 / 448.0, dtype=torch.float32)
+    if round_scale:
+        bits = scale.view(torch.int32)
+        e = ((bits >> 23) & 0xFF) - 127 + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+        scale = ((e + 127) << 23).to(torch.int32).view(torch.float32)
+    y = (xf / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
+    return y, scale
+
+
+def indexer_stage_fp8(q_raw: torch.Tensor, k_raw: torch.Tensor, w_raw: torch.Tensor, norm_w: torch.Tensor,
+                      norm_b: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor,
+                      positions: Sequence[int], interleaved: bool, round_scale: bool,
+                      softmax_scale: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Indexer.stage_fp8_operands after its three projections
+    (inference/modeling/transformer.py:1044-1066): q_raw bf16 [B, H, 128],
+    k_raw bf16 [B, 128], w_raw fp32 [B, H], cos / sin fp32 [cap, 32]. Returns
+    (q bytes [B, H, 128], folded head weights [B, H], key bytes [B, 128], key
+    scale [B])."""
+    B, H, _ = q_raw.shape
+    pos = torch.as_tensor(list(positions), dtype=torch.long)
+    c, s = cos[pos], sin[pos]                                    # [B, 32]
+    q = torch.cat([rotary_embed(q_raw[..., :64], c[:, None, :], s[:, None, :], interleaved), q_raw[..., 64:]], dim=-1)
+    k = layer_norm_128(k_raw, norm_w, norm_b, eps)
+    k = torch.cat([rotary_embed(k[..., :64], c, s, interleaved), k[..., 64:]], dim=-1)
+    q, k = hadamard_rotate(q), hadamard_rotate(k)
+    q8, q_scale = act_quant_128(q, round_scale)
+    k8, k_scale = act_quant_128(k, round_scale)
+    weights = w_raw.float() * (H ** -0.5)
+    weights = (weights.unsqueeze(-1) * q_scale * softmax_scale).squeeze(-1)
+    return q8, weights, k8, k_scale.squeeze(-1)

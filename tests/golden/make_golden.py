@@ -122,6 +122,38 @@ def main() -> None:
                         rec[f"produced_{key}_{li}"] = p.numpy().astype(np.int32)
     np.savez_compressed(HERE / "model_small.npz", **rec)
 
+    # ---- serving-form indexer staging (Indexer.stage_fp8_operands after its projections,
+    # inference/modeling/transformer.py:1044-1066): the reference's own LayerNorm,
+    # apply_rotary_emb and rotate_activation, chained in its order. Its act_quant is a
+    # TileLang GPU kernel (inference/modeling/kernels.py:35-117) that cannot run here, so the
+    # fixture stops at the rotated bf16 operands; the quantiser is pinned by its definition.
+    import lagged_indexer_dsa.inference.modeling.transformer as T  # noqa: E402
+
+    torch.manual_seed(11)
+    B, Hq = 3, 64
+    sq = torch.randn(B, 1, Hq, 128).to(torch.bfloat16)
+    sk = (torch.randn(B, 1, 128) * 2 + 0.3).to(torch.bfloat16)
+    ang = torch.rand(B, 32) * 6.2831853
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    ln = T.LayerNorm(128)
+    ln.weight.data = 1 + 0.1 * torch.randn(128)
+    ln.bias.data = 0.05 * torch.randn(128)
+    rec = dict(q_raw=_bits(sq.squeeze(1)), k_raw=_bits(sk.squeeze(1)), cos=cos.numpy(), sin=sin.numpy(),
+               norm_w=ln.weight.data.numpy(), norm_b=ln.bias.data.numpy(), eps=np.float32(ln.eps))
+    for inter in (False, True):
+        q_rot, k_rot = [], []
+        for b in range(B):  # one position per sequence: freqs_cis is [seqlen = 1, 32]
+            fc = torch.complex(cos[b:b + 1], sin[b:b + 1])
+            q = sq[b:b + 1]
+            q = torch.cat([T.apply_rotary_emb(q[..., :64], fc, inter), q[..., 64:]], dim=-1)
+            k = ln(sk[b:b + 1])
+            k = torch.cat([T.apply_rotary_emb(k[..., :64].unsqueeze(2), fc, inter).squeeze(2), k[..., 64:]], dim=-1)
+            q_rot.append(T.rotate_activation(q))
+            k_rot.append(T.rotate_activation(k))
+        rec[f"q_rot_{int(inter)}"] = _bits(torch.cat(q_rot).squeeze(1))
+        rec[f"k_rot_{int(inter)}"] = _bits(torch.cat(k_rot).squeeze(1))
+    np.savez_compressed(HERE / "indexer_stage.npz", **rec)
+
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 

@@ -145,3 +145,61 @@ def test_schedule_plan_depth_follows_the_overlay_narrative():
     # dense cold start queues the first layer's set; dense layers stay dense
     plan = O.schedule_plan_depth([False, True, True, True, True], [True] * 5, "dense", 2)
     assert [p["attend"] for p in plan] == ["dense", "dense", "dense", ("layer", 1), ("layer", 2)]
+
+
+def _stage_chain(g, inter: bool):
+    """The oracle's staging chain up to the rotated bf16 operands."""
+    q_raw, k_raw = bf16_from_bits(g["q_raw"]), bf16_from_bits(g["k_raw"])
+    cos, sin = torch.from_numpy(g["cos"]), torch.from_numpy(g["sin"])
+    q = torch.cat([O.rotary_embed(q_raw[..., :64], cos[:, None, :], sin[:, None, :], inter), q_raw[..., 64:]], dim=-1)
+    k = O.layer_norm_128(k_raw, torch.from_numpy(g["norm_w"]), torch.from_numpy(g["norm_b"]), float(g["eps"]))
+    k = torch.cat([O.rotary_embed(k[..., :64], cos, sin, inter), k[..., 64:]], dim=-1)
+    return O.hadamard_rotate(q), O.hadamard_rotate(k)
+
+
+def test_indexer_staging_chain_matches_reference_bitwise():
+    """LayerNorm -> rotary -> Hadamard rotation, both rotary layouts, against the
+    reference's own functions chained in stage_fp8_operands' order."""
+    g = load_golden("indexer_stage.npz")
+    for inter in (False, True):
+        q, k = _stage_chain(g, inter)
+        assert torch.equal(q.view(torch.int16), bf16_from_bits(g[f"q_rot_{int(inter)}"]).view(torch.int16))
+        assert torch.equal(k.view(torch.int16), bf16_from_bits(g[f"k_rot_{int(inter)}"]).view(torch.int16))
+
+
+def test_act_quant_definition():
+    """Known answers of the block quantiser (inference/modeling/kernels.py:19-117)."""
+    x = torch.zeros(4, 128, dtype=torch.bfloat16)
+    x[0, 5] = 448.0          # amax 448 -> scale 1 (up to the rounding of 1/448)
+    x[1, 7] = -3.0           # amax 3
+    x[3, :] = 1.0            # row 2 stays all zero: amax clamps at 1e-4
+    y, s = O.act_quant_128(x, round_scale=False)
+    inv = torch.tensor(1.0 / 448.0, dtype=torch.float32)
+    assert torch.equal(s[:, 0], torch.tensor([448.0, 3.0, 1e-4, 1.0]) * inv)
+    assert y[0, 5] == 0x7E and y[1, 7] == 0xFE and y[2].eq(0).all() and y[3].eq(0x7E).all()
+    y2, s2 = O.act_quant_128(x, round_scale=True)
+    # power-of-two scales at or above amax / 448
+    assert torch.equal(torch.log2(s2).round(), torch.log2(s2)) and (s2 >= s).all() and (s2 < 2 * s).all()
+    assert s2[1, 0] == 2.0 ** -7 and s2[3, 0] == 2.0 ** -8
+    deq = O.e4m3_to_f32(y2) * s2
+    assert torch.allclose(deq, x.float(), rtol=2 ** -4, atol=0)
+
+
+def test_indexer_stage_fp8_folds_the_query_scale():
+    g = load_golden("indexer_stage.npz")
+    q_raw, k_raw = bf16_from_bits(g["q_raw"]), bf16_from_bits(g["k_raw"])
+    B, H, _ = q_raw.shape
+    torch.manual_seed(3)
+    w_raw = torch.randn(B, H)
+    cos, sin = torch.from_numpy(g["cos"]), torch.from_numpy(g["sin"])
+    for inter in (False, True):
+        q8, w, k8, ks = O.indexer_stage_fp8(q_raw, k_raw, w_raw, torch.from_numpy(g["norm_w"]),
+                                            torch.from_numpy(g["norm_b"]), float(g["eps"]), cos, sin,
+                                            range(B), inter, False, 128 ** -0.5)
+        q_rot = bf16_from_bits(g[f"q_rot_{int(inter)}"]).float()
+        k_rot = bf16_from_bits(g[f"k_rot_{int(inter)}"]).float()
+        q_scale = w / (w_raw * H ** -0.5 * 128 ** -0.5)
+        # e4m3: 3 mantissa bits (half a step = 2^-4 relative), subnormal step 2^-9 of the scale
+        for deq, ref, sc in ((O.e4m3_to_f32(q8) * q_scale.unsqueeze(-1), q_rot, q_scale.unsqueeze(-1)),
+                             (O.e4m3_to_f32(k8) * ks.unsqueeze(-1), k_rot, ks.unsqueeze(-1))):
+            assert ((deq - ref).abs() <= ref.abs() * 2 ** -4 + sc.abs() * 2 ** -10 * 1.001).all()
