@@ -194,4 +194,57 @@ def fused_hide_decode_paged(
     return attn_out, next_idx
 
 
+def forward_hide_operands(
+    q_proj: torch.Tensor,
+    k_proj: torch.Tensor,
+    head_gates: torch.Tensor,
+    k_norm_weight: torch.Tensor,
+    k_norm_bias: torch.Tensor,
+    k_norm_eps: float,
+    rope_cos: torch.Tensor,
+    rope_sin: torch.Tensor,
+    positions: torch.Tensor,
+    index_k_paged: torch.Tensor,
+    page_table_64: torch.Tensor,
+    seq_lens: torch.Tensor,
+    rope_interleave: bool = False,
+    scale_fmt: Optional[str] = None,
+    softmax_scale: Optional[float] = None,
+):
+    """This layer's indexer PREPARE + STORE without a top-k, for a batch of decode
+    rows: the operands ``fused_hide_decode_paged`` scans with. Counterpart of the
+    overlay's ``Indexer.forward_hide_operands`` after its projections
+    (sglang_overlay/mli-sglang-v0.5.16.patch:252-363, non-fusion branch :322-342):
+    ``q_proj`` = wq_b(q_lora) ``[B, Hidx, 128]`` bf16, ``k_proj`` = wk(x) ``[B, 128]``
+    bf16, ``head_gates`` = weights_proj(x) ``[B, Hidx]`` fp32 (not yet scaled). One
+    launch rotates, quantises, folds ``n_heads^-0.5 * q_scale * softmax_scale`` into
+    the gates and stores each row's key at ``positions[b]`` in its page.
+
+    Returns the reference's tuple ``(q_fp8 [B,Hidx,128] uint8 bytes, weights [B,Hidx]
+    fp32, index_k_paged, page_table_64 int32, seq_lens int32, skv_cap)``; the first
+    two are views of persistent scratch keyed by the static shape (graph-capturable:
+    no host integer is read from the device). Raises where the reference refuses to
+    engage (:279-312): page size other than 64, missing table or lengths."""
+    if page_table_64 is None or seq_lens is None:
+        raise RuntimeError("[HIDE VOID] page-64 table / int32 seqlens unavailable")
+    if index_k_paged.dim() != 2 or index_k_paged.shape[1] != ops.INDEX_PAGE_BYTES:
+        raise RuntimeError(f"[HIDE VOID] index-K pages must be [num_pages, {ops.INDEX_PAGE_BYTES}] "
+                           "(64-token pages)")
+    if page_table_64.dtype != torch.int32:
+        page_table_64 = page_table_64.to(torch.int32)
+    if seq_lens.dtype != torch.int32:
+        seq_lens = seq_lens.to(torch.int32)
+    B, n_heads = q_proj.shape[0], q_proj.shape[1]
+    device = q_proj.device
+    q_fp8 = _hide_scratch(("hide_q", B, n_heads, device),
+                          lambda: torch.empty(B, n_heads, ops.INDEX_DIM, dtype=torch.uint8, device=device))
+    weights = _hide_scratch(("hide_w", B, n_heads, device),
+                            lambda: torch.empty(B, n_heads, dtype=torch.float32, device=device))
+    ops.indexer_stage_fp8(q_proj, k_proj, head_gates, k_norm_weight, k_norm_bias, k_norm_eps, rope_cos, rope_sin,
+                          positions, q_fp8, weights, pages=index_k_paged.view(-1), page_table=page_table_64,
+                          rope_interleave=rope_interleave, scale_fmt=scale_fmt, softmax_scale=softmax_scale)
+    skv_cap = int(page_table_64.shape[1]) * ops.PAGE_TOKENS
+    return q_fp8, weights, index_k_paged, page_table_64, seq_lens, skv_cap
+
+
 _hh_fused_hide_decode_paged = fused_hide_decode_paged  # the reference's name for it

@@ -178,3 +178,56 @@ def test_ragged_batch_at_serving_size():
     got = [sorted(v for v in row if v >= 0) for row in nxt.cpu().tolist()]
     assert got == ref_next(c)
     _lib.check_device_status()
+
+
+def test_forward_hide_operands_stages_and_feeds_the_paged_scan():
+    """A few decode steps through the overlay-shaped operand hook (prepare + store,
+    no top-k), then the paged scan over what it stored, against the oracle's staging
+    and logits (patch :252-363 + :1282-1548 in the reference)."""
+    from dsa_multi_layer_indexer_b200 import serving
+
+    dev = "cuda"
+    B, H, pages_per, T = 3, 64, 3, 150
+    cap = pages_per * 64
+    g = torch.Generator().manual_seed(5)
+    num_pages = B * pages_per + 2
+    perm = torch.randperm(num_pages, generator=g)[: B * pages_per].view(B, pages_per).to(torch.int32)
+    pages = torch.zeros(num_pages, 8448, dtype=torch.uint8, device=dev)
+    ang = torch.rand(cap, 32, generator=g) * 6.2831853
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    norm_w, norm_b = 1 + 0.1 * torch.randn(128, generator=g), 0.05 * torch.randn(128, generator=g)
+    o_k = torch.zeros(B, cap, 128, dtype=torch.uint8)
+    o_s = torch.zeros(B, cap)
+    lens = torch.zeros(B, dtype=torch.int32, device=dev)
+    ptrs = set()
+    for t in range(T):
+        q_proj = torch.randn(B, H, 128, generator=g).to(torch.bfloat16)
+        k_proj = torch.randn(B, 128, generator=g).to(torch.bfloat16)
+        gates = torch.randn(B, H, generator=g)
+        positions = torch.full((B,), t, dtype=torch.int64)
+        lens.fill_(t + 1)
+        ret = serving.forward_hide_operands(q_proj.to(dev), k_proj.to(dev), gates.to(dev), norm_w.to(dev),
+                                            norm_b.to(dev), 1e-6, cos.to(dev), sin.to(dev), positions.to(dev),
+                                            pages, perm.to(dev), lens)
+        q_fp8, weights, pg, pt, sl, skv_cap = ret
+        ptrs.add((q_fp8.data_ptr(), weights.data_ptr()))
+        q8, w, k8, ks = O.indexer_stage_fp8(q_proj, k_proj, gates, norm_w, norm_b, 1e-6, cos, sin, [t] * B,
+                                            False, False, 128 ** -0.5)
+        o_k[:, t], o_s[:, t] = k8, ks
+    assert len(ptrs) == 1 and skv_cap == cap and pt.dtype == torch.int32 and sl.dtype == torch.int32
+    assert q_fp8.shape == (B, H, 128) and weights.shape == (B, H) and pg.data_ptr() == pages.data_ptr()
+    assert torch.equal(q_fp8.cpu(), q8) and torch.equal(weights.cpu(), w)
+    logits = serving.fused_hide_decode_paged(
+        torch.zeros(1, B, 128, 576, dtype=torch.bfloat16, device=dev), torch.zeros(64, 576, dtype=torch.bfloat16, device=dev),
+        torch.full((B, 2048), -1, dtype=torch.int32, device=dev), q_fp8, weights, pages, pt, sl, skv_cap,
+        192 ** -0.5, None, index_topk=2048, mode="scan_only")
+    torch.cuda.synchronize()
+    for b in range(B):
+        ref = O.indexer_logits_fp8(q8[b:b + 1], o_k[b, :T], w[b:b + 1], o_s[b, :T])[0]
+        got = logits[b, :T].cpu()
+        assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
+        assert torch.isinf(logits[b, T:].cpu()).all()
+    with pytest.raises(RuntimeError, match="HIDE VOID"):
+        serving.forward_hide_operands(q_proj.to(dev), k_proj.to(dev), gates.to(dev), norm_w.to(dev), norm_b.to(dev),
+                                      1e-6, cos.to(dev), sin.to(dev), positions.to(dev),
+                                      torch.zeros(4, 4224, dtype=torch.uint8, device=dev), perm.to(dev), lens)
