@@ -582,5 +582,136 @@ indexer_stage_kernel(const StageParams p) {
   }
 }
 
+// ------------------------------------------------------------------ serving-form latent append
+// The new token's latent row between wkv_a and the cache
+// (inference/modeling/transformer.py:3264-3276): RMSNorm of the 512 latent dims
+// (fp32 weight, :380-410), rotary embedding of the 64 rope dims (:525-547), then one of
+//   format 0: the bf16 row [512 | 64] as it is,
+//   format 1: the same row with the latent dims passed through act_quant and back
+//             (e4m3 with one scale per 128 dims, dequantised and rounded to bf16: the
+//             reference's bf16 cache holds these values, :3268-3274),
+//   format 2: the serving pool's 656-byte row: 512 e4m3 | 4 fp32 scales | 64 bf16
+//             (kernels/cuda_fused_sparse_splitk.py:1098-1104),
+// written at slots[b] of the pool. One warp per token; lane l holds dims 4l..4l+3 of
+// each 128-dim group, so a group's amax is one warp reduction.
+struct LatentParams {
+  const __nv_bfloat16* kv_a;  // [B, 576]
+  const float* norm_w;        // [512]
+  const float* rope_cos;      // [cap, 32]
+  const float* rope_sin;
+  const int64_t* positions;
+  const int64_t* slots;
+  uint8_t* pool;
+  int64_t cap, n_slots;
+  int B, interleave, format, round_scale;
+  float eps;
+};
+
+__global__ void __launch_bounds__(kStageWarps * 32)
+latent_append_kernel(const LatentParams p) {
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x * kStageWarps + (threadIdx.x >> 5);
+  if (b >= p.B) return;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int64_t pos = p.positions[b], slot = p.slots[b];
+  if (pos < 0 || pos >= p.cap || slot < 0 || slot >= p.n_slots) return;
+  auto round_bf16 = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
+  const __nv_bfloat16* src = p.kv_a + int64_t(b) * 576;
+  float v[4][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + 128 * g + 4 * lane);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    v[g][0] = __bfloat162float(lo.x);
+    v[g][1] = __bfloat162float(lo.y);
+    v[g][2] = __bfloat162float(hi.x);
+    v[g][3] = __bfloat162float(hi.y);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss = __fadd_rn(ss, __fmul_rn(v[g][j], v[g][j]));
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+  const float rstd = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 512.f), p.eps)));
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const float4 w4 = *reinterpret_cast<const float4*>(p.norm_w + 128 * g + 4 * lane);
+    const float w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[g][j] = round_bf16(__fmul_rn(w[j], __fmul_rn(v[g][j], rstd)));
+  }
+  // rope dims: 2 per lane; pair layout as in indexer_stage_kernel
+  float r0 = __bfloat162float(src[512 + 2 * lane]), r1 = __bfloat162float(src[512 + 2 * lane + 1]);
+  {
+    const float* cr = p.rope_cos + pos * 32;
+    const float* sr = p.rope_sin + pos * 32;
+    const float q0 = __shfl_xor_sync(0xffffffffu, r0, 16), q1 = __shfl_xor_sync(0xffffffffu, r1, 16);
+    if (p.interleave) {
+      const float c = cr[lane], s = sr[lane];
+      const float a = r0, bi = r1;
+      r0 = round_bf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(bi, s)));
+      r1 = round_bf16(__fadd_rn(__fmul_rn(a, s), __fmul_rn(bi, c)));
+    } else {
+      const bool first = lane < 16;  // dims 0..31 real parts, 32..63 imaginary parts
+      const int i = 2 * (lane & 15);
+      const float a0 = first ? r0 : q0, b0 = first ? q0 : r0, a1 = first ? r1 : q1, b1 = first ? q1 : r1;
+      r0 = first ? round_bf16(__fsub_rn(__fmul_rn(a0, cr[i]), __fmul_rn(b0, sr[i])))
+                 : round_bf16(__fadd_rn(__fmul_rn(a0, sr[i]), __fmul_rn(b0, cr[i])));
+      r1 = first ? round_bf16(__fsub_rn(__fmul_rn(a1, cr[i + 1]), __fmul_rn(b1, sr[i + 1])))
+                 : round_bf16(__fadd_rn(__fmul_rn(a1, sr[i + 1]), __fmul_rn(b1, cr[i + 1])));
+    }
+  }
+  const __nv_bfloat162 rope2 = __halves2bfloat162(__float2bfloat16_rn(r0), __float2bfloat16_rn(r1));
+  uint32_t packed[4];
+  float scale[4];
+  if (p.format != 0) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float amax = fmaxf(fmaxf(fabsf(v[g][0]), fabsf(v[g][1])), fmaxf(fabsf(v[g][2]), fabsf(v[g][3])));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      float sc = __fmul_rn(fmaxf(amax, 1e-4f), 1.0f / 448.0f);
+      if (p.round_scale) {
+        const uint32_t bits = __float_as_uint(sc);
+        const int e = int((bits >> 23) & 0xFFu) - 127 + ((bits & 0x7FFFFFu) != 0u ? 1 : 0);
+        sc = __uint_as_float(uint32_t(e + 127) << 23);
+      }
+      scale[g] = sc;
+      packed[g] = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float q = fminf(fmaxf(__fdiv_rn(v[g][j], sc), -448.f), 448.f);
+        const uint32_t byte = __nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
+        packed[g] |= byte << (8 * j);
+        if (p.format == 1) {
+          const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+          v[g][j] = round_bf16(__fmul_rn(__half2float(__half(hr)), sc));
+        }
+      }
+    }
+  }
+  if (p.format == 2) {
+    uint8_t* row = p.pool + slot * int64_t(DSA_FP8_LATENT_ROW);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) *reinterpret_cast<uint32_t*>(row + 128 * g + 4 * lane) = packed[g];
+    if (lane < 4) *reinterpret_cast<float*>(row + 512 + 4 * lane) = scale[lane];
+    *reinterpret_cast<__nv_bfloat162*>(row + 528 + 4 * lane) = rope2;
+  } else {
+    __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(p.pool) + slot * 576;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      __nv_bfloat162 a = __halves2bfloat162(__float2bfloat16_rn(v[g][0]), __float2bfloat16_rn(v[g][1]));
+      __nv_bfloat162 c = __halves2bfloat162(__float2bfloat16_rn(v[g][2]), __float2bfloat16_rn(v[g][3]));
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&a);
+      o.y = *reinterpret_cast<uint32_t*>(&c);
+      *reinterpret_cast<uint2*>(row + 128 * g + 4 * lane) = o;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(row + 512 + 2 * lane) = rope2;
+  }
+}
+
 }  // namespace prep
 }  // namespace dsa

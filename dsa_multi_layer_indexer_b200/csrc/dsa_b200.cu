@@ -855,6 +855,36 @@ int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_r
   return DSA_OK;
 }
 
+int dsa_latent_append(const void* kv_a, const float* kv_norm_weight, float eps, const float* rope_cos,
+                      const float* rope_sin, const int64_t* positions, const int64_t* slots, void* pool,
+                      int B, int64_t cap, int64_t n_slots, int rope_interleave, int format,
+                      int round_scale, void* stream) {
+  DSA_REQUIRE(kv_a && kv_norm_weight && rope_cos && rope_sin && positions && slots && pool,
+              "latent append: null pointer");
+  DSA_REQUIRE(aligned16(kv_a) && aligned16(kv_norm_weight) && aligned16(pool),
+              "latent append: pointers must be 16-byte aligned");
+  DSA_REQUIRE(B > 0 && cap > 0 && n_slots > 0, "latent append: bad shape");
+  DSA_REQUIRE(format >= 0 && format <= 2, "latent append: format must be 0 (bf16), 1 (bf16, quantised values) or 2 (fp8-packed)");
+  prep::LatentParams p{};
+  p.kv_a = static_cast<const __nv_bfloat16*>(kv_a);
+  p.norm_w = kv_norm_weight;
+  p.rope_cos = rope_cos;
+  p.rope_sin = rope_sin;
+  p.positions = positions;
+  p.slots = slots;
+  p.pool = static_cast<uint8_t*>(pool);
+  p.cap = cap;
+  p.n_slots = n_slots;
+  p.B = B;
+  p.interleave = rope_interleave;
+  p.format = format;
+  p.round_scale = round_scale;
+  p.eps = eps;
+  DSA_CUDA(launch_pdl(prep::latent_append_kernel, dim3((B + prep::kStageWarps - 1) / prep::kStageWarps),
+                      dim3(prep::kStageWarps * 32), 0, static_cast<cudaStream_t>(stream), p));
+  return DSA_OK;
+}
+
 int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, const void* kv_a,
                     const void* q_abs, const void* q_pe, int64_t q_pe_stride, const void* kv_norm_w,
                     const void* mla_cos, const void* mla_sin, const void* idx_cos, const void* idx_sin,

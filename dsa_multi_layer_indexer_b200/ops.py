@@ -560,6 +560,38 @@ def indexer_stage_fp8(q_raw, k_raw, w_raw, k_norm_weight, k_norm_bias, k_norm_ep
         0 if scale_fmt is None else 1, float(n_heads ** -0.5), float(softmax_scale), _stream()))
 
 
+def latent_append(kv_a, kv_norm_weight, eps: float, rope_cos, rope_sin, positions, slots, pool,
+                  rope_interleave: bool = True, fmt: str = "fp8", scale_fmt: Optional[str] = None) -> None:
+    """Serving-form latent append in one launch (inference/modeling/transformer.py:3264-3276
+    in the reference): RMSNorm of the 512 latent dims of ``kv_a`` [B, 576] bf16, rotary
+    embedding of its 64 rope dims, row written at ``slots[b]`` of ``pool``: ``fmt="bf16"``
+    [n_slots, 576] bf16 as it is, ``"bf16_quant"`` the same with the latent dims passed
+    through act_quant and back, ``"fp8"`` the 656-byte packed rows [n_slots, 656] uint8."""
+    _cuda_contig(kv_a, "kv_a", (torch.bfloat16,))
+    for t, n in ((kv_norm_weight, "kv_norm_weight"), (rope_cos, "rope_cos"), (rope_sin, "rope_sin")):
+        _cuda_contig(t, n, (torch.float32,))
+    _cuda_contig(positions, "positions", (torch.int64,))
+    _cuda_contig(slots, "slots", (torch.int64,))
+    _need(kv_a.dim() == 2 and kv_a.shape[1] == LATENT_DIM, "kv_a must be [B, 576]")
+    B = kv_a.shape[0]
+    _need(positions.shape == (B,) and slots.shape == (B,), "positions and slots must be [B]")
+    _need(kv_norm_weight.numel() == VALUE_DIM, "kv_norm_weight must be [512]")
+    cap = rope_cos.shape[0]
+    _need(rope_cos.shape == (cap, 32) and rope_sin.shape == (cap, 32), "rotary tables must be [cap, 32]")
+    formats = {"bf16": 0, "bf16_quant": 1, "fp8": 2}
+    _need(fmt in formats, f"fmt must be one of {sorted(formats)}")
+    if fmt == "fp8":
+        _cuda_contig(pool, "pool", (torch.uint8,))
+        _need(pool.dim() == 2 and pool.shape[1] == FP8_LATENT_ROW, "an fp8 pool is [n_slots, 656] uint8")
+    else:
+        _cuda_contig(pool, "pool", (torch.bfloat16,))
+        _need(pool.dim() == 2 and pool.shape[1] == LATENT_DIM, "a bf16 pool is [n_slots, 576]")
+    _lib.check(_lib.lib().dsa_latent_append(
+        _ptr(kv_a), _ptr(kv_norm_weight), float(eps), _ptr(rope_cos), _ptr(rope_sin), _ptr(positions), _ptr(slots),
+        _ptr(pool), B, cap, pool.shape[0], 1 if rope_interleave else 0, formats[fmt],
+        0 if scale_fmt is None else 1, _stream()))
+
+
 def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, mla_sin, idx_cos, idx_sin,
                 positions, index_q, index_w, q_full, cache_index_k, cache_k_scale, cache_kv,
                 interleave: bool, eps: float) -> None:

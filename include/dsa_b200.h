@@ -306,6 +306,25 @@ int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_r
                           int64_t pt_stride, int B, int n_heads, int64_t cap, int rope_interleave,
                           int round_scale, float head_scale, float softmax_scale, void* stream);
 
+/* Serving-form latent append: the new token's latent row between wkv_a and the cache
+ * (src/lagged_indexer_dsa/inference/modeling/transformer.py:3264-3276): RMSNorm of the 512
+ * latent dims (fp32 weight, :380-410), rotary embedding of the 64 rope dims (:525-547),
+ * written at row slots[b] of `pool` as
+ *   format 0: bf16 [512 | 64];
+ *   format 1: bf16 [512 | 64] whose latent dims went through act_quant and back (one e4m3
+ *             scale per 128 dims, dequantised, rounded to bf16: what the reference's bf16
+ *             cache holds, :3268-3274);
+ *   format 2: the serving pool's DSA_FP8_LATENT_ROW bytes: 512 e4m3 | 4 fp32 scales | 64 bf16
+ *             (kernels/cuda_fused_sparse_splitk.py:1098-1104), the rows
+ *             dsa_sparse_mla_* reads with kv_fp8 = 1.
+ * kv_a bf16 [B, 576]; kv_norm_weight fp32 [512]; rope tables fp32 [cap, 32]; positions and
+ * slots int64 [B] (slot < 0 or >= n_slots: the row is skipped); round_scale as in
+ * dsa_indexer_stage_fp8. */
+int dsa_latent_append(const void* kv_a, const float* kv_norm_weight, float eps, const float* rope_cos,
+                      const float* rope_sin, const int64_t* positions, const int64_t* slots, void* pool,
+                      int B, int64_t cap, int64_t n_slots, int rope_interleave, int format,
+                      int round_scale, void* stream);
+
 /* ---- (a7) per-token e4m3 quantisation of index keys / queries --------------
  * scale = max(amax(row), clamp_min) / 448, q = sat(x / scale) -> e4m3 RN
  * (kernels/cuda_fused_sparse_splitk.py:2969-2974). x is fp32 [rows, cols]. */

@@ -400,3 +400,35 @@ def indexer_stage_fp8(q_raw: torch.Tensor, k_raw: torch.Tensor, w_raw: torch.Ten
     weights = w_raw.float() * (H ** -0.5)
     weights = (weights.unsqueeze(-1) * q_scale * softmax_scale).squeeze(-1)
     return q8, weights, k8, k_scale.squeeze(-1)
+
+
+# --------------------------------------------------- serving-form latent append
+def rms_norm_f32w(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm of the serving model: fp32 math, fp32 weight, result in x's dtype
+    (inference/modeling/transformer.py:380-410)."""
+    xf = x.float()
+    var = xf.pow(2).mean(-1, keepdim=True)
+    return (weight * (xf * torch.rsqrt(var + eps))).to(x.dtype)
+
+
+def latent_append_rows(kv_a: torch.Tensor, norm_w: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor,
+                       positions: Sequence[int], interleaved: bool, fmt: str, round_scale: bool) -> torch.Tensor:
+    """The new token's latent row as the cache receives it
+    (inference/modeling/transformer.py:3264-3276): kv_a bf16 [B, 576] = wkv_a(x);
+    RMSNorm of dims 0..511, rotary embedding of dims 512..575. fmt "bf16": the row as
+    it is; "bf16_quant": latent dims through act_quant and back (:3268-3274);
+    "fp8": the 656-byte packed row (kernels/cuda_fused_sparse_splitk.py:1098-1104),
+    uint8 [B, 656]."""
+    pos = torch.as_tensor(list(positions), dtype=torch.long)
+    kv = rms_norm_f32w(kv_a[:, :512], norm_w, eps)
+    pe = rotary_embed(kv_a[:, 512:], cos[pos], sin[pos], interleaved)
+    if fmt == "bf16":
+        return torch.cat([kv, pe], dim=-1)
+    B = kv.shape[0]
+    y, scale = act_quant_128(kv.reshape(B, 4, 128), round_scale)
+    if fmt == "bf16_quant":
+        deq = (e4m3_to_f32(y) * scale).to(kv.dtype).reshape(B, 512)
+        return torch.cat([deq, pe], dim=-1)
+    rope = pe.to(torch.bfloat16).contiguous().view(torch.uint8).reshape(B, 128)
+    sc = scale.reshape(B, 4).contiguous().view(torch.uint8).reshape(B, 16)
+    return torch.cat([y.reshape(B, 512), sc, rope], dim=1).contiguous()

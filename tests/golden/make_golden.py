@@ -154,6 +154,22 @@ def main() -> None:
         rec[f"k_rot_{int(inter)}"] = _bits(torch.cat(k_rot).squeeze(1))
     np.savez_compressed(HERE / "indexer_stage.npz", **rec)
 
+    # ---- serving-form latent append (MLA decode branch, transformer.py:3264-3267): the
+    # reference's RMSNorm and apply_rotary_emb (interleaved, its default for MLA)
+    torch.manual_seed(12)
+    B = 5
+    kv_a = (torch.randn(B, 1, 576) * 1.5).to(torch.bfloat16)
+    ang = torch.rand(B, 32) * 6.2831853
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    rn = T.RMSNorm(512)
+    rn.weight.data = 1 + 0.1 * torch.randn(512)
+    kv_n = rn(kv_a[..., :512])
+    pe = torch.cat([T.apply_rotary_emb(kv_a[b:b + 1, :, 512:].unsqueeze(2), torch.complex(cos[b:b + 1], sin[b:b + 1]))
+                    .squeeze(2) for b in range(B)])
+    np.savez_compressed(HERE / "latent_append.npz", kv_a=_bits(kv_a.squeeze(1)), cos=cos.numpy(), sin=sin.numpy(),
+                        norm_w=rn.weight.data.numpy(), eps=np.float32(rn.eps), kv_norm=_bits(kv_n.squeeze(1)),
+                        k_pe=_bits(pe.squeeze(1)))
+
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")
 

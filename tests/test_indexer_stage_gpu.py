@@ -153,3 +153,90 @@ def test_staged_operands_feed_the_scan(D):
     got = logits.cpu()[0, :T]
     assert (got - ref).abs().max() <= 1e-2 * ref.abs().max()
     assert torch.isinf(logits.cpu()[0, T:]).all()
+
+
+# ------------------------------------------------------------------ latent append
+def _latent_inputs(B, cap, n_slots, seed):
+    g = torch.Generator().manual_seed(seed)
+    kv_a = (torch.randn(B, 576, generator=g) * 1.5).to(torch.bfloat16)
+    norm_w = 1 + 0.1 * torch.randn(512, generator=g)
+    ang = torch.rand(cap, 32, generator=g) * 6.2831853
+    positions = torch.randint(0, cap, (B,), generator=g)
+    slots = torch.randperm(n_slots, generator=g)[:B]
+    return kv_a, norm_w, torch.cos(ang), torch.sin(ang), positions, slots
+
+
+@pytest.mark.parametrize("inter", [True, False])
+@pytest.mark.parametrize("fmt,scale_fmt", [("bf16", None), ("bf16_quant", None), ("fp8", None), ("fp8", "ue8m0")])
+def test_latent_append_matches_oracle(D, inter, fmt, scale_fmt):
+    dev = "cuda"
+    B, cap, n_slots = 9, 300, 64
+    kv_a, norm_w, cos, sin, positions, slots = _latent_inputs(B, cap, n_slots, seed=17)
+    slots[3] = -1  # a skipped row
+    if fmt == "fp8":
+        pool = torch.full((n_slots, 656), 0x55, dtype=torch.uint8, device=dev)
+    else:
+        pool = torch.full((n_slots, 576), 7.0, dtype=torch.bfloat16, device=dev)
+    before = pool.clone()
+    D.latent_append(kv_a.to(dev), norm_w.to(dev), 1e-6, cos.to(dev), sin.to(dev), positions.to(dev), slots.to(dev),
+                    pool, rope_interleave=inter, fmt=fmt, scale_fmt=scale_fmt)
+    torch.cuda.synchronize()
+    want = O.latent_append_rows(kv_a, norm_w, 1e-6, cos, sin, positions.tolist(), inter, fmt, scale_fmt is not None)
+    live = [b for b in range(B) if slots[b] >= 0]
+    got = pool.cpu()[slots[live]]
+    want = want[live]
+    if fmt == "fp8":
+        assert torch.equal(got[:, 528:], want[:, 528:])  # rope dims: the same rounded operations
+        gs, ws = got[:, 512:528].contiguous().view(torch.float32), want[:, 512:528].contiguous().view(torch.float32)
+        assert torch.allclose(gs, ws, rtol=2 ** -7, atol=0)
+        g_lat, w_lat = O.unpack_fp8_latent(got)[:, :512].float(), O.unpack_fp8_latent(want)[:, :512].float()
+        step = w_lat.abs() * 2 ** -3 + ws.repeat_interleave(128, dim=1) * 2 ** -9
+        assert ((g_lat - w_lat).abs() <= step * 1.01).all()
+        assert (got[:, :512] == want[:, :512]).float().mean() > 0.97
+    else:
+        assert torch.equal(got[:, 512:].view(torch.int16), want[:, 512:].view(torch.int16))
+        g_lat, w_lat = got[:, :512].float(), want[:, :512].float()
+        # RMSNorm's fp32 summation order differs from torch's: a bf16 may round the other way
+        tol = 2 ** -7 if fmt == "bf16" else 2 ** -3
+        assert ((g_lat - w_lat).abs() <= w_lat.abs() * tol + 1e-6).all()
+        assert (got[:, :512].view(torch.int16) == want[:, :512].view(torch.int16)).float().mean() > 0.97
+    untouched = torch.ones(n_slots, dtype=torch.bool)
+    untouched[slots[live]] = False
+    assert torch.equal(pool.cpu()[untouched].view(torch.uint8), before.cpu()[untouched].view(torch.uint8))
+
+
+def test_latent_append_against_reference_fixture_and_attention(D):
+    """Rows appended in the packed format are what the attention kernel reads: decode over
+    them equals the oracle's decode over the reference-made rows, packed by the oracle."""
+    dev = "cuda"
+    g = load_golden("latent_append.npz")
+    kv_a = bf16_from_bits(g["kv_a"])
+    B = kv_a.shape[0]
+    cos, sin = torch.from_numpy(g["cos"]), torch.from_numpy(g["sin"])
+    pool = torch.zeros(B, 576, dtype=torch.bfloat16, device=dev)
+    ar = torch.arange(B)
+    D.latent_append(kv_a.to(dev), torch.from_numpy(g["norm_w"]).to(dev), float(g["eps"]), cos.to(dev), sin.to(dev),
+                    ar.to(dev), ar.to(dev), pool, rope_interleave=True, fmt="bf16")
+    torch.cuda.synchronize()
+    ref_row = torch.cat([bf16_from_bits(g["kv_norm"]), bf16_from_bits(g["k_pe"])], dim=-1)
+    assert torch.equal(pool.cpu()[:, 512:].view(torch.int16), ref_row[:, 512:].view(torch.int16))
+    assert ((pool.cpu()[:, :512].float() - ref_row[:, :512].float()).abs() <= ref_row[:, :512].float().abs() * 2 ** -7).all()
+
+    # many tokens into an fp8 pool, then sparse decode over the pool
+    N, H, topk = 256, 16, 128
+    gen = torch.Generator().manual_seed(4)
+    kv_many = (torch.randn(N, 576, generator=gen)).to(torch.bfloat16)
+    ang = torch.rand(N, 32, generator=gen) * 6.2831853
+    cosN, sinN = torch.cos(ang), torch.sin(ang)
+    norm_w = torch.ones(512)
+    pool8 = torch.zeros(1, N, 656, dtype=torch.uint8, device=dev)
+    pos = torch.arange(N)
+    D.latent_append(kv_many.to(dev), norm_w.to(dev), 1e-6, cosN.to(dev), sinN.to(dev), pos.to(dev), pos.to(dev),
+                    pool8.view(N, 656), fmt="fp8")
+    q = torch.randn(1, H, 576, generator=gen).to(torch.bfloat16)
+    idx = torch.randperm(N, generator=gen)[:topk].sort().values.int().view(1, topk)
+    out = D.sparse_mla_decode(q.to(dev), pool8, idx.to(dev), 192 ** -0.5)
+    torch.cuda.synchronize()
+    rows = O.unpack_fp8_latent(O.latent_append_rows(kv_many, norm_w, 1e-6, cosN, sinN, range(N), True, "fp8", False))
+    ref = O.sparse_mla_decode(q, rows, idx, [N], 192 ** -0.5)
+    assert (out.cpu().float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()

@@ -203,3 +203,28 @@ def test_indexer_stage_fp8_folds_the_query_scale():
         for deq, ref, sc in ((O.e4m3_to_f32(q8) * q_scale.unsqueeze(-1), q_rot, q_scale.unsqueeze(-1)),
                              (O.e4m3_to_f32(k8) * ks.unsqueeze(-1), k_rot, ks.unsqueeze(-1))):
             assert ((deq - ref).abs() <= ref.abs() * 2 ** -4 + sc.abs() * 2 ** -10 * 1.001).all()
+
+
+def test_latent_append_matches_reference_and_packing():
+    """RMSNorm + rotary of the new latent row against the reference's own modules; the
+    packed and fake-quantised forms against each other and pack_fp8_latent."""
+    g = load_golden("latent_append.npz")
+    kv_a = bf16_from_bits(g["kv_a"])
+    B = kv_a.shape[0]
+    args = (kv_a, torch.from_numpy(g["norm_w"]), float(g["eps"]), torch.from_numpy(g["cos"]),
+            torch.from_numpy(g["sin"]), range(B), True)
+    row = O.latent_append_rows(*args, "bf16", False)
+    assert torch.equal(row[:, :512].view(torch.int16), bf16_from_bits(g["kv_norm"]).view(torch.int16))
+    assert torch.equal(row[:, 512:].view(torch.int16), bf16_from_bits(g["k_pe"]).view(torch.int16))
+    packed = O.latent_append_rows(*args, "fp8", False)
+    # pack_fp8_latent divides by 448 where act_quant multiplies by 1/448: scales agree to an ulp
+    other = O.pack_fp8_latent(row)
+    assert packed.shape == (B, 656) and torch.equal(packed[:, 528:], other[:, 528:])
+    s_a, s_b = packed[:, 512:528].contiguous().view(torch.float32), other[:, 512:528].contiguous().view(torch.float32)
+    assert torch.allclose(s_a, s_b, rtol=2 ** -22, atol=0)
+    assert (packed[:, :512] == other[:, :512]).float().mean() > 0.99
+    fake = O.latent_append_rows(*args, "bf16_quant", False)
+    assert torch.equal(fake.view(torch.int16), O.unpack_fp8_latent(packed).view(torch.int16))
+    p2 = O.latent_append_rows(*args, "fp8", True)
+    sc = p2[:, 512:528].contiguous().view(torch.float32)
+    assert torch.equal(torch.log2(sc).round(), torch.log2(sc))
