@@ -19,11 +19,12 @@
 // (a 64-row MMA was measured: it takes the same time and spreads the rows over
 // 16 lanes of each lane quadrant, which only costs the softmax half its lanes).
 //
-// Warp roles (384 threads): a warp reaches the TMEM lane quadrant (warp % 4).
+// Warp roles (512 threads): a warp reaches the TMEM lane quadrant (warp % 4).
 // Warps 0,1 and 4,5 run the softmax on the 64 real S rows (thread = head; warps 0,1
 // take key columns 0..31, warps 4,5 columns 32..63); warps 0-3 rescale and write
-// O^T; warp 6 allocates TMEM and issues every MMA from one lane; warps 8-11 gather
-// rows: 16-byte asynchronous copies straight into the swizzled image (bf16 rows)
+// O^T; warp 6 allocates TMEM and issues every MMA from one lane; warps 8-15 gather
+// rows (eight threads per row; with four gather warps the fp8 conversion paced the
+// kernel: 63 us against 56 us at batch 32, bf16 rows unchanged): 16-byte asynchronous copies straight into the swizzled image (bf16 rows)
 // or load / dequantise / store (fp8 rows, fp8 -> f32, x group scale, round to
 // bf16; :1181-1196).
 //
@@ -42,6 +43,10 @@
 
 #include "sparse_mla.cuh"
 
+#ifndef DSA_MLA_TC_PROD_WARPS
+#define DSA_MLA_TC_PROD_WARPS 8
+#endif
+
 namespace dsa {
 namespace mla_tc {
 
@@ -50,11 +55,14 @@ constexpr int kBN = 64;                        // keys per tile
 constexpr int kChunks = mla::kD / 64;          // 9 chunks of 64 dims (128 B of bf16)
 constexpr int kChunkBytes = 64 * 128;          // [64 rows][128 B]
 constexpr int kTileBytes = kChunks * kChunkBytes;  // 73,728
-constexpr int kThreads = 384;
+constexpr int kProdWarps = DSA_MLA_TC_PROD_WARPS;  // gather warps: 4 or 8
+constexpr int kThreads = 256 + 32 * kProdWarps;
 constexpr int kSoftThreads = 192;              // warps 0-5: softmax / rescale group
 constexpr int kMmaWarp = 6;
 constexpr int kProducerWarp0 = 8;
-constexpr int kProducers = 128;
+constexpr int kProducers = 32 * kProdWarps;
+constexpr int kRowsPerPass = 4 * kProdWarps;    // 8 threads per row
+constexpr int kPasses = kBN / kRowsPerPass;     // rows of a tile per gather thread
 constexpr float kRescaleLog2 = 40.f;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;                  // two S buffers of 64 columns
@@ -70,7 +78,7 @@ struct Smem {
   static constexpr int bar_off = misc_off;             // 9 mbarriers
   static constexpr int tmem_off = misc_off + 96;
   static constexpr int flag_off = misc_off + 104;      // int [2]
-  static constexpr int valid_off = misc_off + 112;     // uint32 [2 stages][4 producer warps]
+  static constexpr int valid_off = misc_off + 112;     // uint32 [2 stages][producer warps]
   static constexpr int factor_off = misc_off + 256;    // float [64]
   static constexpr int max_off = misc_off + 512;       // float [2 parities][2 halves][64]
   static constexpr int bytes = misc_off + 1536 + 1024;  // + slack for the 1024-byte alignment
@@ -160,13 +168,13 @@ sparse_mla_tc_kernel(const mla::Params p) {
   if (warp >= kProducerWarp0) {
     // ===================================================================== gather
     const int ptid = tid - kProducerWarp0 * 32;
-    const int v8 = ptid & 7, rsub = ptid >> 3;  // 8 threads per row, 16 rows per pass
+    const int v8 = ptid & 7, rsub = ptid >> 3;  // 8 threads per row, kRowsPerPass rows per pass
     {
       // queries of this head block: [64 heads][1152 B] -> swizzled chunks
       const uint8_t* qsrc = reinterpret_cast<const uint8_t*>(p.q + (int64_t(r) * p.H + hg * kHG) * mla::kD);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int row = rsub + 16 * k;
+      for (int k = 0; k < kPasses; ++k) {
+        const int row = rsub + kRowsPerPass * k;
 #pragma unroll
         for (int c = 0; c < kChunks; ++c)
           cp_async16(s_q + swz(row, c * 8 + v8), qsrc + row * mla::kRowBytes + c * 128 + v8 * 16);
@@ -176,22 +184,22 @@ sparse_mla_tc_kernel(const mla::Params p) {
     const int row_bytes = p.kv_fp8 ? mla::kFp8Row : mla::kRowBytes;
     const uint8_t* kv_seq = p.kv + int64_t(seq) * p.kv_seq_stride * row_bytes;
     // selection entries of this thread's four rows of tile t (-1 past the split)
-    auto load_idx = [&](int t, int64_t (&idx)[4]) {
+    auto load_idx = [&](int t, int64_t (&idx)[kPasses]) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int j = k_begin + t * kBN + rsub + 16 * k;
+      for (int k = 0; k < kPasses; ++k) {
+        const int j = k_begin + t * kBN + rsub + kRowsPerPass * k;
         idx[k] = -1;
         if (t < n_tiles && j < k_end) idx[k] = p.indices ? int64_t(p.indices[int64_t(r) * p.topk + j]) : int64_t(j);
       }
     };
-    int64_t idx_next[4];
+    int64_t idx_next[kPasses];
     load_idx(0, idx_next);
     bool q_signalled = false;
     // rows of tile t handled by this thread (nullptr: masked key) and the tile's validity bits
-    auto resolve = [&](const uint8_t* (&src)[4], uint32_t& vword) {
+    auto resolve = [&](const uint8_t* (&src)[kPasses], uint32_t& vword) {
       vword = 0;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < kPasses; ++k) {
         const bool ok = idx_next[k] >= 0 && idx_next[k] < len;
         src[k] = ok ? kv_seq + idx_next[k] * row_bytes : nullptr;
         const uint32_t b = __ballot_sync(0xffffffffu, ok);
@@ -203,7 +211,7 @@ sparse_mla_tc_kernel(const mla::Params p) {
         const int s = t & 1;
         const uint32_t stage = s_k + uint32_t(s) * kTileBytes;
         DSA_STAMP_IF(ptid == 0 && t == 4, scta, 0);
-        const uint8_t* src[4];
+        const uint8_t* src[kPasses];
         uint32_t vword;
         resolve(src, vword);
         load_idx(t + 1, idx_next);  // in flight during the waits below
@@ -218,10 +226,10 @@ sparse_mla_tc_kernel(const mla::Params p) {
         // (the outcome of a wait is made warp-uniform: the loop contains warp votes)
         if (__any_sync(0xffffffffu, t >= 2 && !mbar_wait(bar(kBarKFree + s), ((t >> 1) - 1) & 1))) { failed = true; break; }
         DSA_STAMP_IF(ptid == 0 && t == 4, scta, 3);
-        if (lane == 0) s_validw[s * 4 + (warp - kProducerWarp0)] = vword;
+        if (lane == 0) s_validw[s * kProdWarps + (warp - kProducerWarp0)] = vword;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int row = rsub + 16 * k;
+        for (int k = 0; k < kPasses; ++k) {
+          const int row = rsub + kRowsPerPass * k;
           if (src[k]) {
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) cp_async16(stage + swz(row, c * 8 + v8), src[k] + c * 128 + v8 * 16);
@@ -239,13 +247,13 @@ sparse_mla_tc_kernel(const mla::Params p) {
       // e4m3 part belongs to scale group g and expands to bf16 units 2u, 2u + 1. The raw
       // bytes of tile t + 1 are requested into registers as soon as tile t is stored, so
       // they travel while the slot of tile t + 1 is still being read by the tensor core.
-      uint4 raw[4][4], rope[4], sc4[4];
+      uint4 raw[kPasses][4], rope[kPasses], sc4[kPasses];
       uint32_t vword = 0;
       auto request = [&]() {
-        const uint8_t* src[4];
+        const uint8_t* src[kPasses];
         resolve(src, vword);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < kPasses; ++k) {
           if (src[k]) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) raw[k][g] = ld_global_nc_v4(src[k] + (v8 + 8 * g) * 16);
@@ -269,10 +277,10 @@ sparse_mla_tc_kernel(const mla::Params p) {
         DSA_STAMP_IF(ptid == 0 && t == 4, scta, 0);
         if (__any_sync(0xffffffffu, t >= 2 && !mbar_wait(bar(kBarKFree + s), ((t >> 1) - 1) & 1))) { failed = true; break; }
         DSA_STAMP_IF(ptid == 0 && t == 4, scta, 3);
-        if (lane == 0) s_validw[s * 4 + (warp - kProducerWarp0)] = vword;
+        if (lane == 0) s_validw[s * kProdWarps + (warp - kProducerWarp0)] = vword;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int row = rsub + 16 * k;
+        for (int k = 0; k < kPasses; ++k) {
+          const int row = rsub + kRowsPerPass * k;
           const float scs[4] = {__uint_as_float(sc4[k].x), __uint_as_float(sc4[k].y),
                                 __uint_as_float(sc4[k].z), __uint_as_float(sc4[k].w)};
 #pragma unroll
@@ -379,19 +387,24 @@ sparse_mla_tc_kernel(const mla::Params p) {
           uint32_t raw[32];
           tmem_ld_32x32(tq + kColS + 64u * s + 32u * half, raw);
           tmem_ld_wait();
-          uint32_t vw[4];
+          // key j of the tile was staged by producer warp (j % kRowsPerPass) >> 2 in its pass
+          // j / kRowsPerPass: bit 4 pass + (j & 3) of that warp's word
+          constexpr int kHalfPasses = kPasses / 2;  // passes that make up 32 keys
+          uint32_t vw[kProdWarps], vall = 0xFFFFFFFFu;
 #pragma unroll
-          for (int w = 0; w < 4; ++w) vw[w] = s_validw[s * 4 + w] >> (8 * half);
+          for (int w = 0; w < kProdWarps; ++w) {
+            vw[w] = s_validw[s * kProdWarps + w] >> (4 * kHalfPasses * half);
+            vall &= vw[w];
+          }
           // x keeps the raw dot products (-inf for masked keys); the softmax scale (> 0) is
           // applied to the maximum here and folded into the exponent's multiply-add below
-          if (((vw[0] & vw[1] & vw[2] & vw[3]) & 0xFFu) == 0xFFu) {  // every key of the half-tile visible
+          if ((vall & ((1u << (4 * kHalfPasses)) - 1u)) == (1u << (4 * kHalfPasses)) - 1u) {  // every key of the half-tile visible
 #pragma unroll
             for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(raw[i]);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              // key 32 half + i was staged by producer warp (i & 15) >> 2, bit 4 (key >> 4) + (i & 3)
-              const bool ok = (vw[(i & 15) >> 2] >> ((i >> 4) * 4 + (i & 3))) & 1u;
+              const bool ok = (vw[(i % kRowsPerPass) >> 2] >> ((i / kRowsPerPass) * 4 + (i & 3))) & 1u;
               x[i] = ok ? __uint_as_float(raw[i]) : -INFINITY;
             }
           }
