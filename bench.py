@@ -219,6 +219,7 @@ def run_ours(args):
 
     from dsa_multi_layer_indexer_b200 import _lib, ops
     from dsa_multi_layer_indexer_b200.decode import HostDecoder, HotPathState, LayerCache
+    from dsa_multi_layer_indexer_b200.parallel import SeqShardedIndexer
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -256,26 +257,14 @@ def run_ours(args):
     h_q = q_all[:, rank * heads_local:(rank + 1) * heads_local].contiguous()
 
     states, graphs = [], []
-    cand_idx = cand_val = gath_idx = gath_val = merge_ws = None
-    if seq_shard:
-        cand_idx = torch.empty(1, TOPK, dtype=torch.int32, device=dev)
-        cand_val = torch.empty(1, TOPK, dtype=torch.float32, device=dev)
-        gath_idx = torch.empty(1, world * TOPK, dtype=torch.int32, device=dev)
-        gath_val = torch.empty(1, world * TOPK, dtype=torch.float32, device=dev)
-        merge_ws = ops.topk_workspace(1, world * TOPK, dev)
+    shard_indexers = []
 
-    def hot_path(state, cache):
+    def hot_path(state, cache, l=None):
         if not seq_shard:
             state.run(cache, SM_SCALE, impl=args.scan_impl)
             return
-        logits = ops.indexer_scan_fp8(state.index_q, state.index_w, cache.index_k, cache.k_scale, None,
-                                      ctx=ctx_local, out=state.logits, hist=state.hist, impl=args.scan_impl)
-        ops.topk_select(logits, TOPK, None, hist=state.hist, out_idx=cand_idx, out_val=cand_val,
-                        index_offset=key_lo, workspace=state.topk_ws)
-        dist.all_gather_into_tensor(gath_idx.view(-1), cand_idx.view(-1))
-        dist.all_gather_into_tensor(gath_val.view(-1), cand_val.view(-1))
-        ops.topk_select(gath_val, TOPK, None, index_map=gath_idx, out_idx=state.indices, workspace=merge_ws)
-        state.run_attention(cache, state.indices, SM_SCALE)
+        idx = shard_indexers[l].select(state.index_q, state.index_w, cache.index_k, cache.k_scale)
+        state.run_attention(cache, idx, SM_SCALE)
 
     for l in range(L):
         st = HotPathState(1, heads_local, INDEX_HEADS, ctx_local, TOPK, dev)
@@ -284,24 +273,29 @@ def run_ours(args):
         st.q.copy_(h_q)
         if seq_shard:
             st.seq_lens.fill_(ctx)  # attention sees the whole (replicated) latent cache
+            shard_indexers.append(SeqShardedIndexer(1, TOPK, ctx_local, key_lo, dev))
         states.append(st)
     torch.cuda.synchronize()
     # eager warm-up (also the NCCL communicator), then one graph per layer
     for l in range(L):
-        hot_path(states[l], caches[l])
+        hot_path(states[l], caches[l], l)
     torch.cuda.synchronize()
-    class _Eager:  # same interface as a captured graph
-        def __init__(self, l):
-            self.l = l
+    class _TwoGraphs:  # same interface as a captured graph
+        def __init__(self, step):
+            self.step = step
 
         def replay(self):
-            hot_path(states[self.l], caches[self.l])
+            self.step()
 
     for l in range(L):
         if seq_shard:
-            # The NCCL all-gathers stay outside CUDA graphs: a capture that contained
-            # them did not finish on this software stack, so this mode launches eagerly.
-            graphs.append(_Eager(l))
+            # The NCCL all-gather stays outside CUDA graphs (a capture that contained it did
+            # not finish on this software stack): local scan + top-k are one graph, merge +
+            # attention another, and the all-gather is enqueued between the two replays.
+            st, cache = states[l], caches[l]
+            graphs.append(_TwoGraphs(shard_indexers[l].capture(
+                st.index_q, st.index_w, cache.index_k, cache.k_scale,
+                after=lambda idx, st=st, cache=cache: st.run_attention(cache, idx, SM_SCALE))))
             continue
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):

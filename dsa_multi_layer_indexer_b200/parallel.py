@@ -25,7 +25,7 @@ through NCCL before the merge kernel runs.
 
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Callable, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -68,8 +68,8 @@ class SeqShardedIndexer:
 
     Each rank holds only its slice of the index keys (``local_ctx`` keys starting
     at global position ``key_lo``). ``select`` returns the global top-k
-    positions, identical on every rank. Buffers are persistent, so the call can
-    be captured in a CUDA graph together with the NCCL all-gathers."""
+    positions, identical on every rank. Buffers are persistent: ``capture`` turns the
+    call into two CUDA graphs with the one NCCL all-gather enqueued between them."""
 
     def __init__(self, rows: int, topk: int, local_ctx: int, key_lo: int, device,
                  group: Optional[dist.ProcessGroup] = None) -> None:
@@ -96,6 +96,61 @@ class SeqShardedIndexer:
                k_scale: torch.Tensor, local_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """index_k / k_scale: this rank's slice ``[n_seq, local_ctx(, 128)]``;
         local_lens: visible keys inside the slice per row (None = all)."""
+        self._local(index_q, index_w, index_k, k_scale, local_lens)
+        if self.world == 1:
+            self.indices.copy_(self.cand_idx)
+            return self.indices
+        self._exchange()
+        self._merge()
+        return self.indices
+
+    def capture(self, index_q: torch.Tensor, index_w: torch.Tensor, index_k: torch.Tensor,
+                k_scale: torch.Tensor, local_lens: Optional[torch.Tensor] = None,
+                after: Optional[Callable[[torch.Tensor], None]] = None) -> Callable[[], torch.Tensor]:
+        """``select`` on fixed buffers as two CUDA graphs around the one NCCL call: the
+        local scan + top-k before it, the merge (and ``after(indices)``, e.g. this rank's
+        attention over the merged set) behind it. The all-gather itself is enqueued
+        between the two replays, outside any graph. Returns the step function."""
+        self._local(index_q, index_w, index_k, k_scale, local_lens)  # warm-up, also of lazy state
+        if self.world > 1:
+            self._exchange()
+            self._merge()
+        else:
+            self.indices.copy_(self.cand_idx)
+        if after is not None:
+            after(self.indices)
+        torch.cuda.synchronize()
+        g_local, g_merge = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_local):
+            self._local(index_q, index_w, index_k, k_scale, local_lens)
+        with torch.cuda.graph(g_merge):
+            if self.world > 1:
+                self._merge()
+            else:
+                self.indices.copy_(self.cand_idx)
+            if after is not None:
+                after(self.indices)
+
+        def step() -> torch.Tensor:
+            g_local.replay()
+            if self.world > 1:
+                self._exchange()
+            g_merge.replay()
+            return self.indices
+
+        self._graphs = (g_local, g_merge)  # keep them alive with the indexer
+        return step
+
+    def _exchange(self) -> None:
+        dist.all_gather_into_tensor(self.gath.view(-1), self.cand.view(-1), group=self.group)  # the one exchange step
+
+    def _merge(self) -> None:
+        idxs = interleave_gathered(self.gath[:, 0], self.world, self.rows, self.topk)
+        vals = interleave_gathered(self.gath[:, 1], self.world, self.rows, self.topk).view(torch.float32)
+        self.ops.topk_select(vals, self.topk, None, index_map=idxs, out_idx=self.indices, workspace=self.merge_ws)
+
+    def _local(self, index_q: torch.Tensor, index_w: torch.Tensor, index_k: torch.Tensor,
+               k_scale: torch.Tensor, local_lens: Optional[torch.Tensor]) -> None:
         ops = self.ops
         if self.local_ctx > 0:
             logits = ops.indexer_scan_fp8(index_q, index_w, index_k, k_scale, local_lens,
@@ -105,11 +160,3 @@ class SeqShardedIndexer:
         else:  # an empty shard contributes only padding
             self.cand_idx.fill_(-1)
             self.cand_val.fill_(float("-inf"))
-        if self.world == 1:
-            self.indices.copy_(self.cand_idx)
-            return self.indices
-        dist.all_gather_into_tensor(self.gath.view(-1), self.cand.view(-1), group=self.group)  # the one exchange step
-        idxs = interleave_gathered(self.gath[:, 0], self.world, self.rows, self.topk)
-        vals = interleave_gathered(self.gath[:, 1], self.world, self.rows, self.topk).view(torch.float32)
-        ops.topk_select(vals, self.topk, None, index_map=idxs, out_idx=self.indices, workspace=self.merge_ws)
-        return self.indices

@@ -117,6 +117,14 @@ def _nccl_worker(rank: int, world: int, port: int, n: int, topk: int, out_path: 
         keys = ik8[lo:hi].unsqueeze(0).expand(2, -1, -1).contiguous()
         scales = sk[lo:hi].unsqueeze(0).expand(2, -1).contiguous()
         sel = idxr.select(iq8, wp, keys, scales).clone()
+        # the same step as two graphs around the all-gather, with a consumer behind the merge
+        seen = torch.zeros_like(sel)
+        step = idxr.capture(iq8, wp, keys, scales, after=lambda idx: seen.copy_(idx))
+        seen.zero_()
+        idxr.indices.fill_(-7)
+        sel_g = step().clone()
+        torch.cuda.synchronize()
+        assert torch.equal(sel_g, sel) and torch.equal(seen, sel)
         h0, h1 = head_range(rank, world, 32)
         kv2 = kv.unsqueeze(0).expand(2, -1, -1).contiguous()
         part = ops.sparse_mla_decode(q[:, h0:h1].contiguous(), kv2, sel, 0.07, nsplit=8)
