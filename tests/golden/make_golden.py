@@ -7,7 +7,9 @@ tests):
 
 It imports the reference's pure-PyTorch package (src/lagged_indexer_dsa) and the
 host-side helpers of its kernel file (kernels/cuda_fused_sparse_splitk.py:
-quantize_e4m3_rowwise, ref_indexer_logits_fp8, ref_sparse_mla, make_indices),
+quantize_e4m3_rowwise, ref_indexer_logits_fp8, ref_sparse_mla, make_indices) and,
+from its serving model (inference/modeling/transformer.py), LayerNorm, RMSNorm,
+apply_rotary_emb and rotate_activation,
 feeds them seeded inputs and stores inputs + outputs as small .npz files. The
 reference code is only called, never copied. bf16 / fp8 tensors are stored as
 their raw uint16 / uint8 bit patterns.
