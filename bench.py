@@ -40,7 +40,7 @@ INDEX_HEADS = 64
 TOPK = 2048
 SM_SCALE = 192 ** -0.5
 SCAN_BYTES_PER_KEY = 132          # 128 B e4m3 key + 4 B fp32 scale
-SCAN_TRAFFIC_CTX128K = 17368832   # bytes: ncu dram read + write of one scan launch over 131072 keys
+SCAN_TRAFFIC_CTX128K = 17368576   # bytes: ncu dram read + write of one scan launch over 131072 keys
 METRIC = "dsa_decode_layer_tokens_per_s_ctx128k"
 UNIT = "tok/s"
 
