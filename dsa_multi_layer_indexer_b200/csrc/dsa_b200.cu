@@ -760,9 +760,11 @@ int dsa_gemv_bf16(const void* w, const void* x, void* y, int batch, int n, int k
   DSA_REQUIRE(x_stride >= k && x_stride % 8 == 0 && y_stride >= n, "gemv: bad row strides");
   DSA_REQUIRE(aligned16(w) && aligned16(x), "gemv: w and x must be 16-byte aligned");
   const size_t smem = size_t(batch) * k * 2;
-  // rows per warp: 4 when that still leaves two waves of warps, else 2, else 1
-  const int wave = 8 * sm_count();  // warps of one resident wave of 256-thread CTAs (8 per SM is plenty here)
-  const int rows_per_warp = n / 4 >= 2 * wave ? 4 : (n / 2 >= 2 * wave ? 2 : 1);
+  // One row per warp with eight 16-byte loads per lane in flight measured best at every
+  // shape tried ([32832, 1536]: 18.5 us against 20.9 / 25.6 us with 2 / 4 rows per warp and
+  // fewer loads per row; [36864, 7168]: 79 / 84 / 107 us). DSA_GEMV_ROWS=2|4 selects the others.
+  static const int force_rows = env_int("DSA_GEMV_ROWS", 0);
+  const int rows_per_warp = (force_rows == 2 || force_rows == 4) ? force_rows : 1;
   const int warps_needed = (n + rows_per_warp - 1) / rows_per_warp;
   int blocks = (warps_needed * 32 + prep::kGemvThreads - 1) / prep::kGemvThreads;
   if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
