@@ -48,8 +48,8 @@ UNIT = "tok/s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
-    ap.add_argument("--warmup", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=4096)
+    ap.add_argument("--warmup", type=int, default=64)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=CTX)
     ap.add_argument("--layers", type=int, default=16, help="distinct per-layer caches cycled through")
@@ -98,7 +98,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -338,14 +338,16 @@ def run_ours(args):
             for i in range(rem):
                 graphs[i % L].replay()
 
+    # the clock sampler starts before the warm-up (nvidia-smi needs ~0.1 s to deliver its first
+    # sample), so that its samples cover the timed region and the per-kernel legs behind it
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(max(args.warmup, 3)):
         graphs[i % L].replay()
     for g in (big, tail):
         if g is not None:
             g.replay()
-    sampler = ClockSampler(local)
     barrier()
-    sampler.start()
     st_ev, en_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     st_ev.record()
     run_steps()
