@@ -61,6 +61,33 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert rc == -1 and b"multiple of 16" in h.dsa_last_error()
     rc = h.dsa_topk_select(addr, None, None, None, addr, None, addr, 16, 1, 1 << 21, 1 << 21, 2048, -1, 0, None)
     assert rc == -2
+    # the staging entry points: a missing operand, both cache forms missing, an unknown row format
+    rc = h.dsa_indexer_stage_fp8(addr, None, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, addr, addr, None, None,
+                                 0, 1, 64, 128, 0, 0, 0.125, 0.088, None)
+    assert rc == -1 and b"null pointer" in h.dsa_last_error()
+    rc = h.dsa_indexer_stage_fp8(addr, addr, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, None, None, None, None,
+                                 0, 1, 64, 128, 0, 0, 0.125, 0.088, None)
+    assert rc == -1 and b"dense key cache or pages" in h.dsa_last_error()
+    rc = h.dsa_latent_append(addr, addr, 1e-6, addr, addr, addr, addr, addr, 1, 128, 16, 1, 3, 0, None)
+    assert rc == -1 and b"format" in h.dsa_last_error()
+
+
+def test_staging_wrappers_reject_host_tensors():
+    """The Python wrappers of the staging kernels check their operands before any launch."""
+    import torch
+
+    from dsa_multi_layer_indexer_b200 import ops
+
+    q = torch.zeros(1, 64, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.indexer_stage_fp8(q, q[0, 0:1], torch.zeros(1, 64), torch.ones(128), torch.zeros(128), 1e-6,
+                              torch.zeros(8, 32), torch.zeros(8, 32), torch.zeros(1, dtype=torch.int64),
+                              torch.zeros(1, 64, 128, dtype=torch.uint8), torch.zeros(1, 64),
+                              torch.zeros(1, 8, 128, dtype=torch.uint8), torch.zeros(1, 8))
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.latent_append(torch.zeros(1, 576, dtype=torch.bfloat16), torch.ones(512), 1e-6, torch.zeros(8, 32),
+                          torch.zeros(8, 32), torch.zeros(1, dtype=torch.int64), torch.zeros(1, dtype=torch.int64),
+                          torch.zeros(4, 656, dtype=torch.uint8))
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
