@@ -47,14 +47,14 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_gemv_bf16": (_i, [_p, _p, _p, _i, _i, _i, _l, _l, _p]),
     "dsa_copy_bytes": (_i, [_p, _p, _l, _p]),
     "dsa_post_epoch": (_i, [_p, _p, _p]),
-    "dsa_indexer_stage_fp8": (_i, [_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _p, _p, _l,
+    "dsa_indexer_stage_fp8": (_i, [_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _p, _l, _p, _l,
                                    _i, _i, _l, _i, _i, _f, _f, _p]),
     "dsa_latent_append": (_i, [_p, _p, _f, _p, _p, _p, _p, _p, _i, _l, _l, _i, _i, _i, _p]),
     "dsa_decode_prep": (_i, [_p, _p, _p, _p, _p, _p, _l] + [_p] * 12 + [_i, _i, _i, _l, _i, _f, _p]),
     "dsa_quantize_e4m3_rowwise": (_i, [_p, _p, _p, _l, _i, _f, _p]),
 }
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 class DsaError(RuntimeError):

@@ -47,9 +47,11 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, con
 // Bit set by a kernel whose bounded wait ran out; read by dsa_check_device_status.
 // (This library is one translation unit, so the word is simply defined here.)
 __device__ unsigned int g_device_status = 0;
-constexpr unsigned int kStatusScanTimeout = 1u;
-constexpr unsigned int kStatusAttnTimeout = 2u;
-constexpr unsigned int kStatusSelectOverflow = 4u;
+constexpr unsigned int kStatusScanTimeout = DSA_STATUS_SCAN_TIMEOUT;
+constexpr unsigned int kStatusAttnTimeout = DSA_STATUS_ATTN_TIMEOUT;
+constexpr unsigned int kStatusSelectOverflow = DSA_STATUS_SELECT_OVERFLOW;
+constexpr unsigned int kStatusBadPage = DSA_STATUS_BAD_PAGE;  // a page-table entry outside [0, num_pages): the access was skipped
+constexpr unsigned int kStatusExchangeTimeout = DSA_STATUS_EXCHANGE_TIMEOUT;  // a peer's candidates did not arrive in time
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------- device: phase stamps
@@ -122,6 +124,42 @@ __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- device: thread-block clusters
+// Distributed shared memory is only ever WRITTEN remotely in this library (stores and
+// reductions pushed into a peer CTA's window before a cluster barrier both sides
+// take part in), so no CTA reads memory of a CTA that may already have exited.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_num_ctas() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `smem_addr` in CTA `cta` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ void cluster_red_add(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("red.relaxed.cluster.shared::cluster.add.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_st(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Hardware barrier over every thread of the cluster (the CTAs of a cluster are
+// co-scheduled, so this is not a wait on another launch). Split in two so that work
+// can sit between the arrival and the wait.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- device: mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -166,6 +204,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
   }
   return false;
+}
+// After a bounded wait ran out: about two milliseconds for copies that may still be in
+// flight to land before the CTA's shared memory is reused. (Kept as a rolled loop: unrolled it is
+// 32 KB of machine code in the middle of a kernel.)
+__device__ __forceinline__ void drain_after_timeout() {
+#pragma unroll 1
+  for (int i = 0; i < 2000; ++i) __nanosleep(1000);
 }
 // Non-blocking probe of a phase parity.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {

@@ -450,6 +450,7 @@ struct StageParams {
   uint8_t* pages;
   const int32_t* page_table;
   int64_t pt_stride;
+  int64_t num_pages;
   int64_t cap;
   int B, n_heads, interleave, round_scale;
   float eps, head_scale, softmax_scale, hadamard_scale;
@@ -571,7 +572,12 @@ indexer_stage_kernel(const StageParams p) {
           __fmul_rn(__fmul_rn(__fmul_rn(w, p.head_scale), scale), p.softmax_scale);
     }
   } else if (p.pages) {
-    const int32_t page = p.page_table[int64_t(b) * p.pt_stride + (pos >> 6)];
+    // a stale or negative page-table entry must not become a wild write: skip the token and say so
+    const int32_t page = (pos >> 6) < p.pt_stride ? p.page_table[int64_t(b) * p.pt_stride + (pos >> 6)] : -1;
+    if (page < 0 || int64_t(page) >= p.num_pages) {
+      if (lane == 0) atomicOr(&g_device_status, kStatusBadPage);
+      return;
+    }
     uint8_t* pg = p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES;
     const int slot = int(pos & 63);
     *reinterpret_cast<uint32_t*>(pg + slot * 128 + 4 * lane) = packed;

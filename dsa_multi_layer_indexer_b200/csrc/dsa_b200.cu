@@ -105,16 +105,15 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_scan[64], g_opt_scan2[64], g_opt_scan3[64], g_opt_scan_deep[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_mla_cluster[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_gemv[4][3][64];
+static bool g_opt_fused[64], g_opt_scan2[64], g_opt_scan3[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_topk_cluster[64], g_opt_gemv[4][64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
 // griddepcontrol.wait (pdl_wait) before it touches anything the predecessor
-// wrote. DSA_PDL=0 turns the attribute off.
+// wrote.
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t st, Args&&... args) {
-  static const bool enabled = env_int("DSA_PDL", 1) != 0;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -124,76 +123,8 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = enabled ? 1 : 0;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
-}
-
-// Fused sparse MLA: the splits of one (row, head block) form a thread-block
-// cluster and merge through distributed shared memory. Returns DSA_OK after the
-// launch, or 1 when the fused form is not selected (it is opt-in: DSA_MLA_FUSED=1).
-static int launch_mla_cluster(mla::Params p, void* out, int R, int H, int nsplit, int topk_k,
-                              cudaStream_t st) {
-  static const bool fused = env_int("DSA_MLA_FUSED", 0) != 0;
-  if (!fused) return 1;
-  static int cl16_ok[64];  // 0 unknown, 1 yes, -1 no: a 16-CTA cluster needs an opt-in and room in a GPC
-  int dev = 0;
-  DSA_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return 1;
-  const size_t smem = p.kv_fp8 ? mla::ClusterSmem::bytes_fp8 : mla::ClusterSmem::bytes_bf16;
-  int rc = opt_in_smem(mla::sparse_mla_cluster_kernel, mla::ClusterSmem::bytes_fp8, g_opt_mla_cluster);
-  if (rc) return rc;
-  static const int cl_max = env_int("DSA_MLA_CLUSTER_MAX", 16);
-  int cl = 1;
-  while (cl * 2 <= nsplit && cl * 2 <= 16 && cl * 2 <= cl_max) cl *= 2;
-  cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[2];
-  auto fill = [&](int c) {
-    cfg.gridDim = dim3(c, H / DSA_HEAD_BLOCK, R);
-    cfg.blockDim = dim3(mla::kThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = c;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = env_int("DSA_PDL", 1) != 0 ? 2 : 1;
-  };
-  if (cl == 16) {
-    if (cl16_ok[dev] == 0) {
-      cl16_ok[dev] = -1;
-      if (cudaFuncSetAttribute(mla::sparse_mla_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed,
-                               1) == cudaSuccess) {
-        fill(16);
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, mla::sparse_mla_cluster_kernel, &cfg) == cudaSuccess && n >= 1)
-          cl16_ok[dev] = 1;
-      }
-      (void)cudaGetLastError();
-    }
-    if (cl16_ok[dev] != 1) cl = 8;
-  }
-  int kps = (topk_k + cl - 1) / cl;
-  p.keys_per_split = (kps + 15) / 16 * 16;
-  p.nsplit = cl;
-  fill(cl);
-  if (env_int("DSA_VERBOSE", 0)) {
-    for (int c = 1; c <= 16; c *= 2) {
-      fill(c);
-      cfg.numAttrs = 1;
-      int n = -1;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, mla::sparse_mla_cluster_kernel, &cfg);
-      fprintf(stderr, "[dsa] sparse_mla_cluster: cluster size %d, smem %zu: max active clusters %d (%s)\n", c,
-              smem, n, cudaGetErrorString(e));
-    }
-    (void)cudaGetLastError();
-    fill(cl);
-  }
-  DSA_CUDA(cudaLaunchKernelEx(&cfg, mla::sparse_mla_cluster_kernel, p, static_cast<__nv_bfloat16*>(out)));
-  return DSA_OK;
 }
 
 }  // namespace dsa
@@ -245,7 +176,11 @@ int dsa_check_device_status(uint32_t* detail) {
   DSA_CUDA(cudaMemcpyFromSymbol(&word, g_device_status, sizeof(word)));
   if (word) DSA_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
   if (detail) *detail = word;
-  if (word) return fail(DSA_ERR_DEVICE_TIMEOUT, "device status word 0x%x", word);
+  if (word & ~kStatusBadPage)
+    return fail(DSA_ERR_DEVICE_TIMEOUT, "device status word 0x%x: a bounded device-side wait ran out", word);
+  if (word)
+    return fail(DSA_ERR_INVALID_ARGUMENT,
+                "device status word 0x%x: a page-table entry outside [0, num_pages) was not followed", word);
   return DSA_OK;
 }
 
@@ -291,51 +226,30 @@ static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
   // One resident wave for a single row. A batch gets about 1.75 waves: its rows
   // differ in length, the grid is sized on the host without reading the lengths,
   // and the later CTAs fill the SMs that the short rows' CTAs leave early.
-  int per_row = env_int("DSA_SCAN_CTAS_PER_ROW", 0);
-  if (per_row <= 0) per_row = ((R > 1 ? 7 : 4) * ctas_per_sm * sm_count() / 4 + R - 1) / R;
+  int per_row = ((R > 1 ? 7 : 4) * ctas_per_sm * sm_count() / 4 + R - 1) / R;
   if (per_row > tiles_per_row) per_row = tiles_per_row;
   if (per_row < 1) per_row = 1;
   return per_row;
 }
 
-// Two shapes of the same kernel: two CTAs per SM with a 4-slot ring (default), or
-// one CTA per SM with a 10-slot ring (DSA_SCAN_DEEP=1).
+// Two CTAs per SM with a 4-slot ring. Tiles in their epilogue at once per CTA: three for a
+// batch (measured 1.5-2 % faster than two on 32 rows), two for one row (three is 0.15 us
+// slower there). A ragged batch works on its long rows first.
 static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p_in, int R, cudaStream_t st) {
   scan::Params p = p_in;
-  // ragged batch: long rows first (DSA_SCAN_BALANCE=0 keeps grid row y on batch row y)
-  p.balance_rows = (R > 1 && R <= 32 && p.seq_lens && env_int("DSA_SCAN_BALANCE", 1) != 0) ? R : 0;
-  static const bool deep = env_int("DSA_SCAN_DEEP", 0) != 0;
-  if (deep) {
-    constexpr size_t smem = scan::smem_bytes<scan::kStagesOnePerSm>();
-    int rc = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesOnePerSm>, smem, g_opt_scan_deep);
-    if (rc) return rc;
-    DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesOnePerSm>,
-                        dim3(scan_grid_x(R, p.tiles_per_row, 1), R), dim3(scan::kThreads), smem, st, tmap, p));
-    return DSA_OK;
-  }
+  p.balance_rows = (R > 1 && R <= 32 && p.seq_lens) ? R : 0;
   constexpr size_t smem = scan::smem_bytes<scan::kStagesTwoPerSm>();
-  // Tiles in their epilogue at once per CTA.  Unset: three for a batch (measured 1.5-2 %
-  // faster than two on 32 rows), two for one row (three is 0.15 us slower there).
-  static const int epi_env = env_int("DSA_SCAN_EPI_GROUPS", 0);
-  const int epi_groups = epi_env > 0 ? epi_env : (R > 1 ? 3 : 2);
-  if (epi_groups == 3) {
+  if (R > 1) {
     int rc3 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>, smem, g_opt_scan3);
     if (rc3) return rc3;
     DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>,
                         dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(64 + 128 * 3), smem, st, tmap, p));
     return DSA_OK;
   }
-  if (epi_groups == 2) {
-    int rc2 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>, smem, g_opt_scan2);
-    if (rc2) return rc2;
-    DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>,
-                        dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(scan::kThreads2), smem, st, tmap, p));
-    return DSA_OK;
-  }
-  int rc = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm>, smem, g_opt_scan);
-  if (rc) return rc;
-  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm>,
-                      dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(scan::kThreads), smem, st, tmap, p));
+  int rc2 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>, smem, g_opt_scan2);
+  if (rc2) return rc2;
+  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>,
+                      dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(scan::kThreads2), smem, st, tmap, p));
   return DSA_OK;
 }
 
@@ -421,6 +335,7 @@ int dsa_indexer_scan_fp8_paged(const uint8_t* index_q, const float* index_w,
   p.pages = index_k_pages;
   p.page_table = page_table;
   p.pt_stride = pt_stride;
+  p.num_pages = num_pages;
   p.ctx = ctx;
   p.slab_stride = slab_stride;
   p.rows_per_seq = 1;
@@ -470,7 +385,63 @@ int dsa_indexer_scan_f32(const float* index_q, const float* index_w, const float
 // ------------------------------------------------------------------ top-k
 int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
   if (R <= 0 || n <= 0) return 0;
+  if (n <= topk::kClMaxN) return 16;  // the cluster kernel keeps everything in shared memory
   return topk::workspace_words(R, n) * 4;
+}
+
+// Rows of up to kClMaxN logits: one cluster of 1..16 CTAs per row, no scratch. A cluster of
+// 16 needs an opt-in and a GPC with 16 free SMs; where the device cannot hold one, 8 is used.
+static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStream_t st) {
+  int rc = opt_in_smem(topk::topk_cluster_kernel, topk::cl_smem_bytes(topk::kClMaxGroups), g_opt_topk_cluster);
+  if (rc) return rc;
+  static int cl16_ok[64];  // 0 unknown, 1 yes, -1 no
+  int dev = 0;
+  DSA_CUDA(cudaGetDevice(&dev));
+  int max_ctas = 8;
+  if (dev >= 0 && dev < 64) {
+    if (cl16_ok[dev] == 0) {
+      cl16_ok[dev] = -1;
+      if (cudaFuncSetAttribute(topk::topk_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
+          cudaSuccess) {
+        cudaLaunchConfig_t q{};
+        cudaLaunchAttribute qa[1];
+        q.gridDim = dim3(16, 1);
+        q.blockDim = dim3(topk::kClThreads);
+        q.dynamicSmemBytes = topk::cl_smem_bytes(4);
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 16;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        q.attrs = qa;
+        q.numAttrs = 1;
+        int n_cl = 0;
+        if (cudaOccupancyMaxActiveClusters(&n_cl, topk::topk_cluster_kernel, &q) == cudaSuccess && n_cl >= 4)
+          cl16_ok[dev] = 1;
+      }
+      (void)cudaGetLastError();
+    }
+    if (cl16_ok[dev] == 1 && env_int("DSA_TOPK_CLUSTER16", 1) != 0) max_ctas = 16;
+  }
+  int ctas = 1;
+  while (ctas < max_ctas && int64_t(ctas) * topk::kClThreads * 4 < n) ctas *= 2;
+  const int64_t per_group = int64_t(ctas) * topk::kClThreads * 4;
+  const int groups = int((n + per_group - 1) / per_group);
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[2];
+  cfg.gridDim = dim3(ctas, R);
+  cfg.blockDim = dim3(topk::kClThreads);
+  cfg.dynamicSmemBytes = topk::cl_smem_bytes(groups);
+  cfg.stream = st;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ctas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel, p, groups));
+  return DSA_OK;
 }
 
 int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist,
@@ -488,6 +459,21 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
   DSA_REQUIRE(workspace_bytes >= dsa_topk_workspace_bytes(R, n),
               "topk: workspace of %lld bytes is smaller than dsa_topk_workspace_bytes = %lld",
               (long long)workspace_bytes, (long long)dsa_topk_workspace_bytes(R, n));
+  if (n <= topk::kClMaxN) {
+    topk::Params p{};
+    p.logits = logits;
+    p.seq_lens = seq_lens;
+    p.hist = hist;
+    p.index_map = index_map;
+    p.out_idx = out_idx;
+    p.out_val = out_val;
+    p.n = n;
+    p.slab_stride = slab_stride;
+    p.topk = topk_k;
+    p.pad = pad_value;
+    p.index_offset = index_offset;
+    return launch_topk_cluster(p, R, n, static_cast<cudaStream_t>(stream));
+  }
   const int64_t words = topk::mask_words(n), slots = words / 4;
   uint32_t* ws = static_cast<uint32_t*>(workspace);
   topk::Params p{};
@@ -533,12 +519,15 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
 // only a stand-in, so the device address is looked up once per device below.
 static __device__ __align__(256) unsigned char g_topk_static_scratch[DSA_TOPK_STATIC_SCRATCH_BYTES];
 
-// Device address of the array on the current device (looked up on first use).
+// Device address of the array on the current device (looked up on first use;
+// host threads making that first call together are serialised by a mutex).
 static int topk_static_scratch(void** out) {
   static void* ptr[64];
+  static std::mutex mu;
   int dev = 0;
   DSA_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(DSA_ERR_UNSUPPORTED, "topk (static scratch): device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
   if (ptr[dev] == nullptr) {
     void* p = nullptr;
     DSA_CUDA(cudaGetSymbolAddress(&p, g_topk_static_scratch));
@@ -553,7 +542,12 @@ extern "C" {
 int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t* out_idx,
                            float* out_val, int R, int64_t n, int64_t slab_stride, int topk_k,
                            int32_t pad_value, int32_t index_offset, void* stream) {
-  DSA_REQUIRE(R > 0 && n > 0, "topk (static scratch): need R > 0 and n > 0");
+  // every argument is checked before anything is enqueued: a rejected call puts nothing on the stream
+  DSA_REQUIRE(logits && out_idx, "topk (static scratch): null pointer");
+  DSA_REQUIRE(aligned16(logits), "topk (static scratch): logits must be 16-byte aligned");
+  DSA_REQUIRE(R > 0 && R <= 65535, "topk (static scratch): R=%d out of range", R);
+  DSA_REQUIRE(n > 0 && slab_stride >= n, "topk (static scratch): need 0 < n <= slab_stride");
+  DSA_REQUIRE(topk_k > 0 && topk_k <= 65536, "topk (static scratch): k=%d out of range [1, 65536]", topk_k);
   const int64_t need = dsa_topk_workspace_bytes(R, n);
   if (n > topk::kMaxN || need > int64_t(DSA_TOPK_STATIC_SCRATCH_BYTES))
     return fail(DSA_ERR_UNSUPPORTED,
@@ -563,12 +557,14 @@ int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t
   void* scratch = nullptr;
   int rc = topk_static_scratch(&scratch);
   if (rc) return rc;
-  // The array still holds whatever the previous call left, possibly laid out for
-  // another (R, n): the histogram of this call's layout has to start at zero.
-  const int64_t words = topk::mask_words(n), slots = words / 4;
-  uint32_t* hist = static_cast<uint32_t*>(scratch) + int64_t(R) * (words + slots + 4);
-  DSA_CUDA(cudaMemsetAsync(hist, 0, size_t(R) * (topk::kBins + topk::kRoundBins) * sizeof(uint32_t),
-                           static_cast<cudaStream_t>(stream)));  // both histograms, adjacent in the layout
+  if (n > topk::kClMaxN) {
+    // The array still holds whatever the previous call left, possibly laid out for
+    // another (R, n): the histograms of this call's layout have to start at zero.
+    const int64_t words = topk::mask_words(n), slots = words / 4;
+    uint32_t* hist = static_cast<uint32_t*>(scratch) + int64_t(R) * (words + slots + 4);
+    DSA_CUDA(cudaMemsetAsync(hist, 0, size_t(R) * (topk::kBins + topk::kRoundBins) * sizeof(uint32_t),
+                             static_cast<cudaStream_t>(stream)));  // both histograms, adjacent in the layout
+  }
   return dsa_topk_select(logits, seq_lens, nullptr, nullptr, out_idx, out_val, scratch,
                          DSA_TOPK_STATIC_SCRATCH_BYTES, R, n, slab_stride, topk_k, pad_value,
                          index_offset, stream);
@@ -626,14 +622,10 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   // Head counts that fill 64-row blocks go to the tcgen05 kernel once there are enough
   // 64-head x 64-key tiles to give every SM more than one (a single row of 2048 keys
   // is faster on the mma.sync kernel's 16-head CTAs); its splits are whole 64-key tiles.
-  const int tc_mode = env_int("DSA_MLA_TC", 1);  // 0 never, 1 by size, 2 whenever the head count allows
   const int64_t tc_tiles = int64_t(R) * (H / mla_tc::kHG) * ((topk_k + mla_tc::kBN - 1) / mla_tc::kBN);
-  if (H % mla_tc::kHG == 0 && sm_scale > 0.f && (tc_mode == 2 || (tc_mode == 1 && tc_tiles >= mla_tc::kMinTiles))) {
+  if (H % mla_tc::kHG == 0 && sm_scale > 0.f && tc_tiles >= mla_tc::kMinTiles) {
     int kps = (topk_k + nsplit - 1) / nsplit;
     p.keys_per_split = (kps + mla_tc::kBN - 1) / mla_tc::kBN * mla_tc::kBN;
-    if (env_int("DSA_VERBOSE", 0))
-      fprintf(stderr, "[dsa] sparse_mla: tcgen05 kernel, R=%d H=%d topk=%d nsplit=%d (%lld tiles)\n", R, H, topk_k, nsplit,
-              (long long)tc_tiles);
     int rc = opt_in_smem(mla_tc::sparse_mla_tc_kernel, mla_tc::Smem::bytes, g_opt_mla_tc);
     if (rc) return rc;
     DSA_CUDA(launch_pdl(mla_tc::sparse_mla_tc_kernel, dim3(nsplit, H / mla_tc::kHG, R), dim3(mla_tc::kThreads),
@@ -676,15 +668,6 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
                           void* out, int R, int rows_per_seq, int H, int topk_k, int nsplit,
                           float sm_scale, int64_t kv_seq_stride, int kv_fp8, void* stream) {
   DSA_REQUIRE(out && aligned16(out), "sparse MLA: out must be a 16-byte aligned pointer");
-  {
-    // fused form: cluster of up to 16 splits merging through distributed shared memory
-    mla::Params p;
-    int rc0 = mla_prepare(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
-                          nsplit, sm_scale, kv_seq_stride, kv_fp8, false, &p);
-    if (rc0) return rc0;
-    rc0 = launch_mla_cluster(p, out, R, H, nsplit, topk_k, static_cast<cudaStream_t>(stream));
-    if (rc0 <= 0) return rc0;
-  }
   int rc = dsa_sparse_mla_partials(q, kv, indices, seq_lens, part_acc, part_m, part_l, R,
                                    rows_per_seq, H, topk_k, nsplit, sm_scale, kv_seq_stride, kv_fp8,
                                    stream);
@@ -760,40 +743,29 @@ int dsa_gemv_bf16(const void* w, const void* x, void* y, int batch, int n, int k
   DSA_REQUIRE(x_stride >= k && x_stride % 8 == 0 && y_stride >= n, "gemv: bad row strides");
   DSA_REQUIRE(aligned16(w) && aligned16(x), "gemv: w and x must be 16-byte aligned");
   const size_t smem = size_t(batch) * k * 2;
-  // One row per warp with eight 16-byte loads per lane in flight measured best at every
-  // shape tried ([32832, 1536]: 18.5 us against 20.9 / 25.6 us with 2 / 4 rows per warp and
-  // fewer loads per row; [36864, 7168]: 79 / 84 / 107 us). DSA_GEMV_ROWS=2|4 selects the others.
-  static const int force_rows = env_int("DSA_GEMV_ROWS", 0);
-  const int rows_per_warp = (force_rows == 2 || force_rows == 4) ? force_rows : 1;
-  const int warps_needed = (n + rows_per_warp - 1) / rows_per_warp;
-  int blocks = (warps_needed * 32 + prep::kGemvThreads - 1) / prep::kGemvThreads;
+  // One row per warp with eight 16-byte loads per lane in flight ([32832, 1536]: 18.5 us against
+  // 20.9 / 25.6 us with 2 / 4 rows per warp and fewer loads per row; [36864, 7168]: 79 / 84 / 107 us).
+  int blocks = (n * 32 + prep::kGemvThreads - 1) / prep::kGemvThreads;
   if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
-#define DSA_GEMV_LAUNCH(BV, RV)                                                                              \
-  {                                                                                                          \
-    if (smem > 48 * 1024) {                                                                                  \
-      int rc = opt_in_smem(prep::gemv_bf16_kernel<BV, RV>, 96 * 1024, g_opt_gemv[BV - 1][RV >> 1]);          \
-      if (rc) return rc;                                                                                     \
-    }                                                                                                        \
-    DSA_CUDA(launch_pdl(prep::gemv_bf16_kernel<BV, RV>, dim3(blocks), dim3(prep::kGemvThreads), smem, st, wp, xp, yp, \
-                        n, k, x_stride, y_stride));                                                          \
-  }
-#define DSA_GEMV_CASE(BV)                                 \
-  case BV:                                                \
-    if (rows_per_warp == 4) DSA_GEMV_LAUNCH(BV, 4)        \
-    else if (rows_per_warp == 2) DSA_GEMV_LAUNCH(BV, 2)   \
-    else DSA_GEMV_LAUNCH(BV, 1)                           \
-    break;
+#define DSA_GEMV_CASE(BV)                                                                                     \
+  case BV: {                                                                                                  \
+    if (smem > 48 * 1024) {                                                                                   \
+      int rc = opt_in_smem(prep::gemv_bf16_kernel<BV, 1>, 96 * 1024, g_opt_gemv[BV - 1]);                     \
+      if (rc) return rc;                                                                                      \
+    }                                                                                                         \
+    DSA_CUDA(launch_pdl(prep::gemv_bf16_kernel<BV, 1>, dim3(blocks), dim3(prep::kGemvThreads), smem, st, wp,  \
+                        xp, yp, n, k, x_stride, y_stride));                                                   \
+  } break;
   switch (batch) {
     DSA_GEMV_CASE(1)
     DSA_GEMV_CASE(2)
     DSA_GEMV_CASE(3)
     DSA_GEMV_CASE(4)
   }
-#undef DSA_GEMV_LAUNCH
 #undef DSA_GEMV_CASE
   return DSA_OK;
 }
@@ -813,9 +785,10 @@ int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_r
                           const float* k_norm_weight, const float* k_norm_bias, float k_norm_eps,
                           const float* rope_cos, const float* rope_sin, const int64_t* positions,
                           uint8_t* index_q, float* index_w, uint8_t* cache_index_k,
-                          float* cache_k_scale, uint8_t* pages, const int32_t* page_table,
-                          int64_t pt_stride, int B, int n_heads, int64_t cap, int rope_interleave,
-                          int round_scale, float head_scale, float softmax_scale, void* stream) {
+                          float* cache_k_scale, uint8_t* pages, int64_t num_pages,
+                          const int32_t* page_table, int64_t pt_stride, int B, int n_heads, int64_t cap,
+                          int rope_interleave, int round_scale, float head_scale, float softmax_scale,
+                          void* stream) {
   DSA_REQUIRE(q_raw && k_raw && w_raw && k_norm_weight && k_norm_bias && rope_cos && rope_sin && positions &&
                   index_q && index_w,
               "indexer stage: null pointer");
@@ -826,6 +799,10 @@ int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_r
               "indexer stage: pointers must be 16-byte aligned (k_raw: 8)");
   DSA_REQUIRE(B > 0 && n_heads > 0 && cap > 0 && int64_t(B) * (n_heads + 1) < (int64_t(1) << 30),
               "indexer stage: bad shape");
+  DSA_REQUIRE(!pages || (num_pages > 0 && num_pages < (int64_t(1) << 31)), "indexer stage: bad num_pages");
+  DSA_REQUIRE(!pages || pt_stride * DSA_PAGE_TOKENS >= cap,
+              "indexer stage: pt_stride=%lld pages cannot cover cap=%lld positions", (long long)pt_stride,
+              (long long)cap);
   prep::StageParams p{};
   p.q_raw = static_cast<const __nv_bfloat16*>(q_raw);
   p.k_raw = static_cast<const __nv_bfloat16*>(k_raw);
@@ -842,6 +819,7 @@ int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_r
   p.pages = pages;
   p.page_table = page_table;
   p.pt_stride = pt_stride;
+  p.num_pages = num_pages;
   p.cap = cap;
   p.B = B;
   p.n_heads = n_heads;

@@ -29,7 +29,6 @@ constexpr int kTileKeys = 128;
 constexpr int kKeyBytes = DSA_INDEX_DIM;  // 128 e4m3 per key
 constexpr int kTileBytes = kTileKeys * kKeyBytes;
 constexpr int kStagesTwoPerSm = 4;   // 92 KB of shared memory: two CTAs per SM
-constexpr int kStagesOnePerSm = 10;  // 190 KB: one CTA per SM with every tile of a 128K row in flight
 constexpr int kMaxHeads = DSA_INDEX_MAX_HEADS;
 constexpr int kThreads = 192;    // one epilogue group: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int kThreads2 = 320;   // two epilogue groups: warps 2..5 take the even tiles, warps 6..9 the odd ones
@@ -48,6 +47,7 @@ struct Params {
   const uint8_t* pages;        // paged only
   const int32_t* page_table;   // paged only
   int64_t pt_stride;
+  int64_t num_pages;           // paged only: entries of the page table outside [0, num_pages) are not followed
   int64_t ctx;
   int64_t k_seq_stride;
   int64_t scale_seq_stride;
@@ -201,6 +201,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   // (the other warps issue theirs within the same few cycles).
   if (tid == 0) {
     int it = 0;
+#pragma unroll 1
     for (int t = bx; t < p.tiles_per_row && it < kStages; t += G, ++it) {
       if (int64_t(t) * kTileKeys >= len) break;
       issue_tile(it, t);
@@ -232,6 +233,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
     // (tiles beyond the first kStages: wait for the MMA to release a ring slot)
     if (lane == 0) {
       int it = 0;
+#pragma unroll 1
       for (int t = bx; t < p.tiles_per_row; t += G, ++it) {
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
         if (it < kStages) continue;
@@ -250,6 +252,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       constexpr uint32_t idesc = idesc_f8_f32(kTileKeys, kMaxHeads);
       const uint64_t b_desc = smem_desc_k128(smem_u32(s_q));
       int it = 0;
+#pragma unroll 1
       for (int t = bx; t < p.tiles_per_row; t += G, ++it) {
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
         const int s = it % kStages;
@@ -290,11 +293,18 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
       if (t >= p.tiles_per_row || g >= len) return 0.f;
       if (!p.paged) return kscale_row[int64_t(seq) * p.scale_seq_stride + g];
+      // The tensor-map load of a page outside the pool is zero-filled; this plain load would
+      // not be, so a bad entry is not followed: the key's logit becomes -inf (NaN scale marks it).
       const int page = p.page_table[int64_t(r) * p.pt_stride + (g >> 6)];
+      if (page < 0 || int64_t(page) >= p.num_pages) {
+        atomicOr(&g_device_status, kStatusBadPage);
+        return __int_as_float(0x7fc00000);
+      }
       return *reinterpret_cast<const float*>(p.pages + int64_t(page) * DSA_INDEX_PAGE_BYTES +
                                              DSA_PAGE_TOKENS * kKeyBytes + (g & 63) * 4);
     };
     float next_scale = load_scale(bx + grp * G);
+#pragma unroll 1
     for (int t = bx, j = 0; t < p.tiles_per_row; t += G, ++j) {
       if ((j % kEpiGroups) != grp) continue;  // the other group's tile
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
@@ -333,11 +343,11 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
 #pragma unroll
       for (int h = 0; h < 32; ++h)
         sum = fmaf(s_w[32 + h], fmaxf(__uint_as_float(v[h]), 0.f), sum);
-      const float logit = valid ? sum * scale : neg_inf;
+      const float logit = (valid && scale == scale) ? sum * scale : neg_inf;  // scale != scale: bad page
       if (g < p.ctx) out_row[g] = logit;
       if (want_hist) {
         const uint32_t bin = ordered_key(logit) >> 20;
-        if (valid) smem_red_add(&s_hist[bin], 1u);
+        if (valid) smem_red_add(&s_hist[bin], 1u);  // (a bad page's -inf is counted too: the row keeps len entries)
         bin_lo = min(bin_lo, valid ? bin : uint32_t(kHistBins));
         bin_hi = max(bin_hi, valid ? bin : 0u);
       }
@@ -359,7 +369,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   DSA_STAMP(stamp_cta, 9);
   if (*abort_flag) {
     // let copies that may still be in flight land before the CTA's shared memory is reused
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    drain_after_timeout();
   }
   if (want_hist) {
     // only the bins this CTA touched (a narrow band around the logits' magnitude)

@@ -17,7 +17,6 @@
 // (fp8 -> f32, x group scale, round to bf16; :1181-1196).
 #pragma once
 
-#include <cooperative_groups.h>
 
 #include "common.cuh"
 
@@ -68,6 +67,16 @@ struct SmemLayout {
 // runs inside a 192-thread CTA of the fused launch, whose two spare warps have
 // left, so it must not use the whole-CTA barrier.
 __device__ __forceinline__ void cta128_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Barrier of the same 128 threads that also ORs a flag over them: every thread gets the same answer.
+__device__ __forceinline__ bool cta128_any(bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(uint32_t(flag))
+      : "memory");
+  return r != 0;
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -390,20 +399,25 @@ __device__ __forceinline__ void mla_partials_body(const Params& p, const int spl
     }
     if (tile == 0 && !mbar_wait(bar_q, 0)) timed_out = true;
     if (!mbar_wait(bar_k, tile & 1)) timed_out = true;
+    // Each thread ran its own clock: the 128 threads agree on leaving here, so nobody is left
+    // alone at the barriers below.
+    timed_out = cta128_any(timed_out);
     if (timed_out) break;
-    if (p.kv_fp8) dequant_tile_inplace(s_k, s_valid, tid);
-    cta128_sync();
+    if (p.kv_fp8) {
+      dequant_tile_inplace(s_k, s_valid, tid);
+      cta128_sync();
+    }
 
     attend_tile(s_q, s_k, s_p, s_red, s_valid, p.scale_log2, warp, lane, m_run, l_run, acc);
     cta128_sync();  // the K tile and P are free for the next gather
   }
 
-  if (n_tiles == 0 && !mbar_wait(bar_q, 0)) timed_out = true;  // never leave with a copy in flight
+  if (n_tiles == 0) timed_out = cta128_any(!mbar_wait(bar_q, 0));  // never leave with a copy in flight
   if (timed_out) {
     atomicOr(&g_device_status, kStatusAttnTimeout);
     m_run[0] = m_run[1] = -INFINITY;
     l_run[0] = l_run[1] = 0.f;
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let outstanding copies land
+    drain_after_timeout();  // let outstanding copies land
   }
 
   // ---- partials of this split: unnormalised accumulator, running max (base 2), sum
@@ -430,198 +444,6 @@ sparse_mla_partials_kernel(const Params p) {
 }
 
 // ------------------------------------------------------------------------------
-// Fused form: the CL CTAs that split one (row, head block)'s index list form a
-// thread-block cluster and merge their partial results through distributed
-// shared memory, so there are no partials in global memory and no second launch
-// (the reference folds its combine into the main launch too, but with blocks
-// that spin on a global counter: kernels/cuda_fused_sparse_splitk.py:1604-1665).
-// Each CTA streams its share of the list through a two-slot ring of 64-key
-// tiles; after the last tile it publishes (m, l, unnormalised O) in its own
-// shared memory, the cluster meets at a hardware barrier, and CTA c reduces and
-// writes output columns [c 512/CL, (c+1) 512/CL) for the 16 heads.
-struct ClusterSmem {
-  static constexpr int q_off = 0;
-  static constexpr int k0_off = q_off + kHB * kRowPitch;
-  static constexpr int k1_off = k0_off + kBN * kRowPitch;          // second bf16 tile, or fp8 stage 0
-  static constexpr int p_off = k1_off + kBN * kRowPitch;
-  static constexpr int red_off = p_off + kHB * kPPitch;            // float [2][4][16]
-  static constexpr int valid_off = red_off + 2 * 4 * kHB * 4;      // int [2][64]
-  static constexpr int ml_off = valid_off + 2 * kBN * 4;           // float m[16], l[16]
-  static constexpr int bar_off = ml_off + 2 * kHB * 4;             // 3 mbarriers
-  static constexpr int stage1_off = (bar_off + 32 + 15) & ~15;     // fp8 stage 1
-  static constexpr int bytes_bf16 = stage1_off;
-  static constexpr int bytes_fp8 = stage1_off + kBN * kFp8Row;
-  static_assert(kBN * kFp8Row <= kBN * kRowPitch, "fp8 stage 0 must fit the second tile slot");
-  static_assert(kHB * kDV * 4 <= kBN * kRowPitch, "the merge buffer reuses the first tile slot");
-};
-
-__global__ void __launch_bounds__(kThreads, 1)
-sparse_mla_cluster_kernel(const Params p, __nv_bfloat16* __restrict__ out) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  namespace cg = cooperative_groups;
-  cg::cluster_group cluster = cg::this_cluster();
-  const unsigned CL = cluster.num_blocks();
-  const unsigned crank = cluster.block_rank();
-  uint8_t* s_q = smem + ClusterSmem::q_off;
-  uint8_t* s_k0 = smem + ClusterSmem::k0_off;
-  uint8_t* s_k1 = smem + ClusterSmem::k1_off;
-  uint8_t* s_p = smem + ClusterSmem::p_off;
-  float* s_red = reinterpret_cast<float*>(smem + ClusterSmem::red_off);
-  int* s_valid = reinterpret_cast<int*>(smem + ClusterSmem::valid_off);
-  float* s_ml = reinterpret_cast<float*>(smem + ClusterSmem::ml_off);
-  uint64_t* s_bar = reinterpret_cast<uint64_t*>(smem + ClusterSmem::bar_off);
-  uint8_t* s_stage1 = smem + ClusterSmem::stage1_off;
-  float* s_acc = reinterpret_cast<float*>(s_k0);  // after the last tile
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int split = blockIdx.x, hg = blockIdx.y, r = blockIdx.z;
-  DSA_KTIME_BEGIN(2);
-  const int stamp_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-  DSA_STAMP(stamp_cta, 0);
-  const int seq = r / p.rows_per_seq;
-  const uint32_t bar_q = smem_u32(&s_bar[0]);
-  const bool fp8 = p.kv_fp8 != 0;
-  const int row_bytes = fp8 ? kFp8Row : kRowBytes;
-  const uint8_t* kv_seq = p.kv + int64_t(seq) * p.kv_seq_stride * row_bytes;
-
-  if (tid == 0) {
-    mbar_init(bar_q, kHB);
-    mbar_init(smem_u32(&s_bar[1]), kBN);
-    mbar_init(smem_u32(&s_bar[2]), kBN);
-    mbar_fence_init();
-  }
-  __syncthreads();
-  pdl_wait();  // the selection, the queries and the lengths may come from the previous kernel
-  pdl_launch_dependents();
-  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.ctx;
-  len = len < 0 ? 0 : (len > p.ctx ? p.ctx : len);
-
-  if (tid >= kBN && tid < kBN + kHB) {  // queries of this head block: 16 rows of 1152 B
-    const int h = tid - kBN;
-    const __nv_bfloat16* src = p.q + (int64_t(r) * p.H + hg * kHB + h) * kD;
-    mbar_arrive_expect_tx(bar_q, kRowBytes);
-    bulk_g2s(smem_u32(s_q + h * kRowPitch), src, kRowBytes, bar_q);
-  }
-  const int k_begin = split * p.keys_per_split;
-  const int k_end = min(k_begin + p.keys_per_split, p.topk);
-  const int n_tiles = (max(k_end - k_begin, 0) + kBN - 1) / kBN;
-
-  // Tile t is gathered into ring slot t & 1: one bulk copy per visible row.
-  auto gather = [&](int tile) {
-    if (tid >= kBN) return;
-    const int b = tile & 1;
-    const uint32_t bar = smem_u32(&s_bar[1 + b]);
-    const int j = k_begin + tile * kBN + tid;
-    int64_t idx = -1;
-    if (j < k_end) idx = p.indices ? int64_t(p.indices[int64_t(r) * p.topk + j]) : int64_t(j);
-    const bool ok = idx >= 0 && idx < len;
-    s_valid[b * kBN + tid] = ok;
-    uint8_t* krow = (b ? s_k1 : s_k0) + tid * kRowPitch;
-    if (ok) {
-      fence_proxy_async_smem();  // earlier generic accesses of the slot precede the async write
-      mbar_arrive_expect_tx(bar, row_bytes);
-      if (fp8)
-        bulk_g2s(smem_u32((b ? s_stage1 : s_k1) + tid * kFp8Row), kv_seq + idx * kFp8Row, kFp8Row, bar);
-      else
-        bulk_g2s(smem_u32(krow), kv_seq + idx * kRowBytes, kRowBytes, bar);
-    } else {
-      if (!fp8) {  // masked key: its row must be finite (fp8 rows are cleared when dequantised)
-        uint4* z = reinterpret_cast<uint4*>(krow);
-        for (int i = 0; i < kRowBytes / 16; ++i) z[i] = make_uint4(0, 0, 0, 0);
-      }
-      mbar_arrive(bar);
-    }
-  };
-
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.f, 0.f};
-  float acc[16][4];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  bool timed_out = false;
-
-  DSA_STAMP(stamp_cta, 1);
-  if (n_tiles > 0) gather(0);
-  if (n_tiles > 1) gather(1);
-  if (!mbar_wait(bar_q, 0)) timed_out = true;
-  for (int tile = 0; tile < n_tiles && !timed_out; ++tile) {
-    const int b = tile & 1;
-    if (!mbar_wait(smem_u32(&s_bar[1 + b]), (tile >> 1) & 1)) {
-      timed_out = true;
-      break;
-    }
-    DSA_STAMP_IF(tid == 0 && tile < 2, stamp_cta, 2 + tile);
-    const uint8_t* s_k = (fp8 || b == 0) ? s_k0 : s_k1;
-    if (fp8) dequant_tile(b ? s_stage1 : s_k1, s_k0, s_valid + b * kBN, tid, true);
-    __syncthreads();
-    attend_tile(s_q, s_k, s_p, s_red, s_valid + b * kBN, p.scale_log2, warp, lane, m_run, l_run, acc);
-    __syncthreads();  // the slot and P are free
-    if (tile + 2 < n_tiles) gather(tile + 2);
-  }
-  if (timed_out) {
-    atomicOr(&g_device_status, kStatusAttnTimeout);
-    m_run[0] = m_run[1] = -INFINITY;
-    l_run[0] = l_run[1] = 0.f;
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let outstanding copies land
-  }
-
-  DSA_STAMP(stamp_cta, 4);
-  // ---- publish this CTA's partial result in its own shared memory
-  __syncthreads();
-  const int g = lane >> 2, t4 = lane & 3;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int col = warp * 128 + i * 8 + t4 * 2;
-    *reinterpret_cast<float2*>(s_acc + g * kDV + col) = make_float2(acc[i][0], acc[i][1]);
-    *reinterpret_cast<float2*>(s_acc + (g + 8) * kDV + col) = make_float2(acc[i][2], acc[i][3]);
-  }
-  if (warp == 0 && t4 == 0) {
-    s_ml[g] = m_run[0];
-    s_ml[g + 8] = m_run[1];
-    s_ml[kHB + g] = l_run[0];
-    s_ml[kHB + g + 8] = l_run[1];
-  }
-  DSA_STAMP(stamp_cta, 5);
-  cluster.sync();
-  DSA_STAMP(stamp_cta, 6);
-
-  // ---- CTA c reduces output columns [c 512/CL, (c+1) 512/CL) of the 16 heads
-  const int cols_per = kDV / int(CL);
-  const int c4_per = cols_per / 4;
-  for (int it = tid; it < kHB * c4_per; it += kThreads) {
-    const int h = it / c4_per;
-    const int col = int(crank) * cols_per + (it % c4_per) * 4;
-    float mx = -INFINITY;
-    for (unsigned j = 0; j < CL; ++j) mx = fmaxf(mx, cluster.map_shared_rank(s_ml, j)[h]);
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    float l = 0.f;
-    if (mx != -INFINITY) {
-      for (unsigned j = 0; j < CL; ++j) {  // fixed order: the result does not depend on timing
-        const float* ml = cluster.map_shared_rank(s_ml, j);
-        const float mj = ml[h];
-        const float e = (mj == -INFINITY) ? 0.f : exp2f(mj - mx);
-        const float4 a = *reinterpret_cast<const float4*>(cluster.map_shared_rank(s_acc, j) + h * kDV + col);
-        l = fmaf(ml[kHB + h], e, l);
-        o.x = fmaf(a.x, e, o.x);
-        o.y = fmaf(a.y, e, o.y);
-        o.z = fmaf(a.z, e, o.z);
-        o.w = fmaf(a.w, e, o.w);
-      }
-    }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
-    uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-    pk.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(out + (int64_t(r) * p.H + hg * kHB + h) * kDV + col) = pk;
-  }
-  DSA_STAMP(stamp_cta, 7);
-  cluster.sync();  // nobody leaves while a peer may still read its shared memory
-  DSA_STAMP(stamp_cta, 8);
-  DSA_KTIME_END(2);
-}
-
 // out = sum_s acc_s 2^(m_s - m) / sum_s l_s 2^(m_s - m); splits with m = -inf
 // (no visible key) are skipped, a row with none yields zeros. One CTA per (row,
 // head) of 1..4 groups of 128 threads (the launch picks min(nsplit, 4)): group g

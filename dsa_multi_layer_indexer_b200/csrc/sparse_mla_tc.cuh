@@ -517,7 +517,7 @@ sparse_mla_tc_kernel(const mla::Params p) {
 
   if (failed) {
     atomicOr(&g_device_status, kStatusAttnTimeout);
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let outstanding copies and MMAs drain
+    drain_after_timeout();  // let outstanding copies and MMAs drain
   }
   tc_fence_before();
   __syncthreads();

@@ -507,5 +507,379 @@ topk_finish_kernel(const Params p) {
   DSA_KTIME_END(4);
 }
 
+// ------------------------------------------------------------------------------
+// One launch for rows of up to kClMaxN logits: a thread-block cluster per row.
+//
+// Every CTA of the cluster keeps its contiguous slice of the row in shared
+// memory as order-preserving keys (loaded once, 16-byte coalesced). The k-th
+// largest key is found exactly by three radix levels (12 + 10 + 10 bits): a
+// level's histogram is built in each CTA's shared memory, its non-zero bins are
+// PUSHED into every CTA's copy (distributed-shared-memory reductions), and one
+// cluster barrier later each CTA holds the whole row's histogram and finds the
+// threshold bin by itself. With the key k* and the number of elements equal to
+// k* that are kept, one prefix sum over the pair (larger than k*, equal to k*)
+// in position order gives each kept element its slot in the ascending output:
+//   slot(x) = larger_before(x) + min(equal_before(x), ties_kept)
+// so ties go to the lower positions, and no candidate list, no scratch in
+// global memory and no capacity limit is involved. The first level's histogram
+// comes from the indexer scan when the caller passes it.
+//
+// The kernel runs once through its code on a handful of SMs, so its time is
+// set by the barriers it crosses and by how much machine code it has to fetch:
+// every loop over the keys is a rolled loop with a small body.
+constexpr int kClThreads = 1024;
+constexpr int kClWarps = kClThreads / 32;
+constexpr int kClMaxGroups = 8;                               // 16-byte groups of keys per thread
+constexpr int kClMaxCtas = 16;                                // 8 is the portable cluster size, 16 needs an opt-in
+constexpr int64_t kClMaxN = int64_t(8) * kClThreads * 4 * kClMaxGroups;  // 262144 (with the portable cluster size)
+
+struct ClShared {
+  uint32_t hist1[kBins];        // whole row, complete after the level's cluster barrier
+  uint32_t local1[kBins];       // this CTA's part
+  uint32_t hist2[kRoundBins];
+  uint32_t local2[kRoundBins];
+  uint32_t hist3[kRoundBins];
+  uint32_t local3[kRoundBins];
+  uint32_t warp_tot[kClWarps];
+  uint32_t cta_tot[kClMaxCtas];  // (equal << 16 | larger) of every CTA of the cluster
+  uint32_t pad_[16];
+  uint4 keys[1];                 // really groups * kClThreads entries: this CTA's slice in position order
+};
+inline size_t cl_smem_bytes(int groups) { return offsetof(ClShared, keys) + size_t(groups) * kClThreads * 16; }
+
+// Adds 1 to h[digit] for the lanes with `pred`. The lanes that share the first such
+// lane's digit add once, so a row of equal logits does not serialise on one address.
+__device__ __forceinline__ void hist_add_warp(uint32_t* h, bool pred, uint32_t digit) {
+  const uint32_t m = __ballot_sync(0xffffffffu, pred);
+  if (m == 0) return;
+  const int leader = __ffs(m) - 1;
+  const uint32_t first = __shfl_sync(0xffffffffu, digit, leader);
+  const uint32_t same = __ballot_sync(0xffffffffu, pred && digit == first);
+  if (pred) {
+    if (digit != first) smem_red_add(&h[digit], 1u);
+    else if (int(threadIdx.x & 31) == leader) smem_red_add(&h[digit], __popc(same));
+  }
+}
+
+// Pushes this CTA's non-zero bins of `local` (one per thread, or four when kWide)
+// into `whole` of every CTA of the cluster.
+template <bool kWide>
+__device__ __forceinline__ void push_bins(const uint32_t* local, uint32_t* whole, uint32_t n_ctas) {
+  const int tid = threadIdx.x;
+  if (kWide) {
+    const uint4 x = reinterpret_cast<const uint4*>(local)[tid];
+    if (x.x | x.y | x.z | x.w) {
+      const uint32_t a = smem_u32(whole + 4 * tid);
+#pragma unroll 1
+      for (uint32_t cc = 0; cc < n_ctas; ++cc) {
+        const uint32_t ra = cluster_map(a, cc);
+        if (x.x) cluster_red_add(ra, x.x);
+        if (x.y) cluster_red_add(ra + 4, x.y);
+        if (x.z) cluster_red_add(ra + 8, x.z);
+        if (x.w) cluster_red_add(ra + 12, x.w);
+      }
+    }
+  } else {
+    const uint32_t x = local[tid];
+    if (x) {
+      const uint32_t a = smem_u32(whole + tid);
+#pragma unroll 1
+      for (uint32_t cc = 0; cc < n_ctas; ++cc) cluster_red_add(cluster_map(a, cc), x);
+    }
+  }
+}
+
+// Bin holding the k-th largest element of a histogram of NB bins in shared memory
+// (searched from the top bin down), and the element's rank inside that bin; the
+// result is returned to every thread. `own` are the counts of this thread's
+// NB / 1024 bins, highest first: thread t owns the bins just below NB - t * NB / 1024.
+// One block barrier: each warp sums its 32 threads' bins, every warp scans the 32
+// warp sums, then reads the target warp's bins itself.
+template <int NB>
+__device__ __forceinline__ void find_kth_bin(const uint32_t* h, const uint32_t (&own)[NB / kClThreads], uint32_t k,
+                                             uint32_t* warp_tot, uint32_t& bin, uint32_t& rank) {
+  constexpr int PER = NB / kClThreads;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t s = 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) s += own[i];
+  const uint32_t wsum = __reduce_add_sync(0xffffffffu, s);
+  if (lane == 0) warp_tot[warp] = wsum;
+  __syncthreads();
+  const uint32_t wt = warp_tot[lane];
+  uint32_t inc = wt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += up;
+  }
+  const uint32_t hit = __ballot_sync(0xffffffffu, inc >= k);
+  const int W = hit ? __ffs(hit) - 1 : 31;
+  const uint32_t k2 = k - __shfl_sync(0xffffffffu, inc - wt, W);
+  const int top = NB - 1 - (W * 32 + lane) * PER;  // highest bin of this lane inside warp W's range
+  uint32_t c[PER];
+  uint32_t s2 = 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    c[i] = h[top - i];
+    s2 += c[i];
+  }
+  uint32_t inc2 = s2;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t up = __shfl_up_sync(0xffffffffu, inc2, o);
+    if (lane >= o) inc2 += up;
+  }
+  const uint32_t hit2 = __ballot_sync(0xffffffffu, inc2 >= k2);
+  const int L = hit2 ? __ffs(hit2) - 1 : 31;
+  uint32_t running = inc2 - s2, b = uint32_t(top), rk = 1;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    if (running < k2 && k2 <= running + c[i]) {
+      b = uint32_t(top - i);
+      rk = k2 - running;
+    }
+    running += c[i];
+  }
+  bin = __shfl_sync(0xffffffffu, b, L);
+  rank = __shfl_sync(0xffffffffu, rk, L);
+}
+
+__global__ void __launch_bounds__(kClThreads, 1)
+topk_cluster_kernel(const Params p, const int groups) {
+  extern __shared__ __align__(16) uint8_t topk_smem[];
+  ClShared& sh = *reinterpret_cast<ClShared*>(topk_smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = blockIdx.y;
+  const uint32_t c = cluster_cta_rank(), C = cluster_num_ctas();
+  const int stamp_cta = 512 + r * int(C) + int(c);
+  DSA_KTIME_BEGIN(1);
+  DSA_STAMP(stamp_cta, 0);
+  // ---- input-free set-up: clear the histograms, then tell the cluster they are clear
+  {
+    uint4* z = reinterpret_cast<uint4*>(&sh);
+    constexpr int kZero16 = int(offsetof(ClShared, keys) / 16);
+    for (int i = tid; i < kZero16; i += kClThreads) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  cluster_arrive();
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* row = p.logits + int64_t(r) * p.slab_stride;
+  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
+  len = len < 0 ? 0 : (len > p.n ? p.n : len);
+  const bool take_all = len <= p.topk;
+  const bool have_hist = p.hist != nullptr;
+
+  // ---- this CTA's slice as order-preserving keys (0 = not a visible position); thread
+  // (warp, lane) owns the 16-byte groups j * 32 + lane of its warp's run of `groups` * 128 positions
+  const int64_t base = int64_t(c) * (kClThreads * 4 * groups) + int64_t(warp) * (128 * groups) + lane * 4;
+  uint4* my_keys = sh.keys + warp * groups * 32 + lane;
+  {
+    // every load of the slice is issued before the first key is stored
+    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+    float4 v[kClMaxGroups];
+#pragma unroll
+    for (int j = 0; j < kClMaxGroups; ++j) {
+      const int64_t p0 = base + j * 128;
+      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < groups && p0 < len) {
+        if (vec && p0 + 4 <= p.n) {
+          v[j] = *reinterpret_cast<const float4*>(row + p0);
+        } else {
+          v[j].x = row[p0];
+          if (p0 + 1 < len) v[j].y = row[p0 + 1];
+          if (p0 + 2 < len) v[j].z = row[p0 + 2];
+          if (p0 + 3 < len) v[j].w = row[p0 + 3];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kClMaxGroups; ++j) {
+      if (j < groups) {
+        const int64_t p0 = base + j * 128;
+        uint4 k;
+        k.x = p0 + 0 < len ? ordered_key(v[j].x) : 0u;
+        k.y = p0 + 1 < len ? ordered_key(v[j].y) : 0u;
+        k.z = p0 + 2 < len ? ordered_key(v[j].z) : 0u;
+        k.w = p0 + 3 < len ? ordered_key(v[j].w) : 0u;
+        my_keys[j * 32] = k;
+      }
+    }
+  }
+  DSA_STAMP(stamp_cta, 1);
+
+  uint32_t kstar = 0, ties_kept = 0;  // short rows keep every visible position: all keys exceed 0
+  if (!take_all) {
+    // ---- level 1: top 12 key bits
+    uint32_t own1[4];
+    if (have_hist) {  // from the scan: every CTA reads all of it (this thread's bins, highest first)
+      const uint4 h1 = __ldcg(reinterpret_cast<const uint4*>(p.hist + size_t(r) * kBins) + (kClThreads - 1 - tid));
+      reinterpret_cast<uint4*>(sh.hist1)[kClThreads - 1 - tid] = h1;
+      own1[0] = h1.w, own1[1] = h1.z, own1[2] = h1.y, own1[3] = h1.x;
+    } else {
+#pragma unroll 1
+      for (int j = 0; j < groups; ++j) {
+        const uint4 k = my_keys[j * 32];
+        hist_add_warp(sh.local1, k.x != 0u, k.x >> kLowBits);
+        hist_add_warp(sh.local1, k.y != 0u, k.y >> kLowBits);
+        hist_add_warp(sh.local1, k.z != 0u, k.z >> kLowBits);
+        hist_add_warp(sh.local1, k.w != 0u, k.w >> kLowBits);
+      }
+      __syncthreads();
+      cluster_wait();  // every CTA of the cluster has cleared its histograms: remote adds may start
+      push_bins<true>(sh.local1, sh.hist1, C);
+      cluster_arrive();
+      cluster_wait();
+      const uint4 h1 = reinterpret_cast<const uint4*>(sh.hist1)[kClThreads - 1 - tid];
+      own1[0] = h1.w, own1[1] = h1.z, own1[2] = h1.y, own1[3] = h1.x;
+    }
+    uint32_t T, need;
+    find_kth_bin<kBins>(sh.hist1, own1, uint32_t(p.topk), sh.warp_tot, T, need);
+    DSA_STAMP(stamp_cta, 2);
+    // ---- level 2: bits 19..10 of the keys in bin T
+#pragma unroll 1
+    for (int j = 0; j < groups; ++j) {
+      const uint4 k = my_keys[j * 32];
+      hist_add_warp(sh.local2, (k.x >> kLowBits) == T && k.x != 0u, (k.x >> 10) & (kRoundBins - 1));
+      hist_add_warp(sh.local2, (k.y >> kLowBits) == T && k.y != 0u, (k.y >> 10) & (kRoundBins - 1));
+      hist_add_warp(sh.local2, (k.z >> kLowBits) == T && k.z != 0u, (k.z >> 10) & (kRoundBins - 1));
+      hist_add_warp(sh.local2, (k.w >> kLowBits) == T && k.w != 0u, (k.w >> 10) & (kRoundBins - 1));
+    }
+    __syncthreads();
+    if (have_hist) cluster_wait();  // (see above; without the scan's histogram it was taken at level 1)
+    push_bins<false>(sh.local2, sh.hist2, C);
+    cluster_arrive();
+    cluster_wait();
+    // every CTA has read the scan's histogram by now: re-arm it for the next scan
+    if (have_hist && c == 0)
+      reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins)[tid] = make_uint4(0, 0, 0, 0);
+    uint32_t d2, need2;
+    {
+      const uint32_t own2[1] = {sh.hist2[kRoundBins - 1 - tid]};
+      find_kth_bin<kRoundBins>(sh.hist2, own2, need, sh.warp_tot, d2, need2);
+    }
+    const uint32_t p22 = (T << 10) | d2;
+    DSA_STAMP(stamp_cta, 3);
+    // ---- level 3: the low 10 bits of the keys that share those 22 bits
+#pragma unroll 1
+    for (int j = 0; j < groups; ++j) {
+      const uint4 k = my_keys[j * 32];
+      hist_add_warp(sh.local3, (k.x >> 10) == p22, k.x & (kRoundBins - 1));
+      hist_add_warp(sh.local3, (k.y >> 10) == p22, k.y & (kRoundBins - 1));
+      hist_add_warp(sh.local3, (k.z >> 10) == p22, k.z & (kRoundBins - 1));
+      hist_add_warp(sh.local3, (k.w >> 10) == p22, k.w & (kRoundBins - 1));
+    }
+    __syncthreads();
+    push_bins<false>(sh.local3, sh.hist3, C);
+    cluster_arrive();
+    cluster_wait();
+    uint32_t d3;
+    {
+      const uint32_t own3[1] = {sh.hist3[kRoundBins - 1 - tid]};
+      find_kth_bin<kRoundBins>(sh.hist3, own3, need2, sh.warp_tot, d3, ties_kept);
+    }
+    kstar = (p22 << 10) | d3;  // the k-th largest key of the row; ties_kept of its copies are kept
+    DSA_STAMP(stamp_cta, 4);
+  } else {
+    cluster_wait();
+    if (have_hist && c == 0)
+      reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins)[tid] = make_uint4(0, 0, 0, 0);
+  }
+
+  // ---- (larger, equal) counts, packed equal << 16 | larger: this warp's, then the warps and CTAs before it
+  auto count4 = [&](const uint4& k) -> uint32_t {
+    return (k.x > kstar ? 1u : 0u) + (k.y > kstar ? 1u : 0u) + (k.z > kstar ? 1u : 0u) + (k.w > kstar ? 1u : 0u) +
+           (((k.x == kstar ? 1u : 0u) + (k.y == kstar ? 1u : 0u) + (k.z == kstar ? 1u : 0u) + (k.w == kstar ? 1u : 0u)) << 16);
+  };
+  {
+    uint32_t tot = 0;
+#pragma unroll 1
+    for (int j = 0; j < groups; ++j) tot += count4(my_keys[j * 32]);
+    if (take_all) tot &= 0xFFFFu;  // key 0 marks the invisible positions, they are not ties
+    const uint32_t wsum = __reduce_add_sync(0xffffffffu, tot);  // at most 1024 of each kind per warp
+    __syncthreads();  // earlier readers of warp_tot are done
+    if (lane == 0) sh.warp_tot[warp] = wsum;
+  }
+  __syncthreads();
+  uint32_t before_warp, cta_sum;
+  {
+    const uint32_t w = sh.warp_tot[lane];
+    uint32_t inc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += up;
+    }
+    before_warp = __shfl_sync(0xffffffffu, inc - w, warp);
+    cta_sum = __shfl_sync(0xffffffffu, inc, 31);  // at most 32768 of each kind per CTA
+  }
+  if (tid < int(C)) cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(tid)), cta_sum);
+  cluster_arrive();
+  cluster_wait();
+  uint32_t gt_before = before_warp & 0xFFFFu, eq_before = before_warp >> 16, gt_total = 0, eq_total = 0;
+#pragma unroll 1
+  for (uint32_t cc = 0; cc < C; ++cc) {
+    const uint32_t t = sh.cta_tot[cc];
+    if (cc < c) {
+      gt_before += t & 0xFFFFu;
+      eq_before += t >> 16;
+    }
+    gt_total += t & 0xFFFFu;
+    eq_total += t >> 16;
+  }
+  DSA_STAMP(stamp_cta, 5);
+
+  // ---- emit: ascending positions, ties to the lower position
+  int32_t* out_idx = p.out_idx + int64_t(r) * p.topk;
+  float* out_val = p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
+  const int32_t* imap = p.index_map ? p.index_map + int64_t(r) * p.n : nullptr;
+  const uint32_t kNegInfKey = 0x007FFFFFu;  // ordered_key(-inf)
+  const uint32_t topk_u = uint32_t(p.topk);
+#pragma unroll 1
+  for (int j = 0; j < groups; ++j) {
+    const uint4 k4 = my_keys[j * 32];
+    uint32_t cnt = count4(k4);
+    if (take_all) cnt &= 0xFFFFu;
+    if (__ballot_sync(0xffffffffu, cnt != 0u) == 0u) continue;  // nothing of this group is near the cutoff
+    uint32_t inc = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += up;
+    }
+    uint32_t g = gt_before + ((inc - cnt) & 0xFFFFu);
+    uint32_t q = eq_before + ((inc - cnt) >> 16);
+    const uint32_t ks[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t k = ks[e];
+      const bool gt = k > kstar;
+      const bool eq = !take_all && k == kstar;
+      if (gt || (eq && q < ties_kept)) {
+        const uint32_t slot = g + min(q, ties_kept);
+        if (slot < topk_u) {
+          const int64_t pos = base + j * 128 + e;
+          const int32_t id = imap ? imap[pos] : int32_t(pos) + p.index_offset;
+          out_idx[slot] = (k == kNegInfKey) ? p.pad : id;
+          if (out_val) out_val[slot] = __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+        }
+      }
+      g += gt ? 1u : 0u;
+      q += eq ? 1u : 0u;
+    }
+    const uint32_t wj = __shfl_sync(0xffffffffu, inc, 31);  // this group's total over the warp
+    gt_before += wj & 0xFFFFu;
+    eq_before += wj >> 16;
+  }
+  const uint32_t total = gt_total + min(eq_total, ties_kept);
+  const float neg_inf = __int_as_float(0xff800000);
+  for (uint32_t i = total + c * kClThreads + tid; i < topk_u; i += C * kClThreads) {
+    out_idx[i] = p.pad;
+    if (out_val) out_val[i] = neg_inf;
+  }
+  DSA_STAMP(stamp_cta, 6);
+  DSA_KTIME_END(1);
+}
+
 }  // namespace topk
 }  // namespace dsa

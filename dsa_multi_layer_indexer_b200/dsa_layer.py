@@ -21,7 +21,6 @@ from __future__ import annotations
 import dataclasses
 from typing import Optional, Tuple
 
-import os
 
 import torch
 from torch import nn
@@ -275,7 +274,7 @@ class DSALayer(nn.Module):
 
     def mlp(self, h_norm: torch.Tensor) -> torch.Tensor:
         if (h_norm.is_cuda and h_norm.dtype == torch.bfloat16 and h_norm.dim() == 2 and h_norm.shape[0] <= 2
-                and not torch.is_grad_enabled() and os.environ.get("DSA_GEMV_WIDE", "1") == "1"):
+                and not torch.is_grad_enabled()):
             gate, up = ops.gemv(h_norm, self.gate_proj.weight), ops.gemv(h_norm, self.up_proj.weight)
             return self.down_proj(ops.silu_mul(gate, up))
         gate, up = self.gate_proj(h_norm), self.up_proj(h_norm)
@@ -330,8 +329,8 @@ class DSALayer(nn.Module):
                 [c.q_lora_rank, c.kv_lora_rank + c.qk_rope_head_dim, c.index_head_dim], dim=-1)
             c_q = self.q_a_layernorm(qa)
             # the c_q-side projection and the MLP's gate / up take the same kernel at one or two
-            # tokens (252 against 255 us per layer of the 8-layer stack; DSA_GEMV_WIDE=0: library GEMV)
-            wide = b <= 2 and c_q.dtype == torch.bfloat16 and os.environ.get("DSA_GEMV_WIDE", "1") == "1"
+            # tokens (252 against 255 us per layer of the 8-layer stack)
+            wide = b <= 2 and c_q.dtype == torch.bfloat16
             q, iq_raw, w = (ops.gemv(c_q, self._wc) if wide else torch.nn.functional.linear(c_q, self._wc)).split(
                 [h * (c.qk_nope_head_dim + c.qk_rope_head_dim), c.index_n_heads * c.index_head_dim, c.index_n_heads],
                 dim=-1)

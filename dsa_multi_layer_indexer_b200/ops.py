@@ -9,7 +9,6 @@ at the first call (``_lib.lib()``).
 from __future__ import annotations
 
 import math
-import os
 from typing import Optional, Tuple
 
 import torch
@@ -152,6 +151,9 @@ def indexer_scan_fp8_paged(
     if out is None:
         out = torch.empty(R, (ctx + 3) // 4 * 4, dtype=torch.float32, device=index_q.device)
     _cuda_contig(out, "out", (torch.float32,))
+    _need(out.dim() == 2 and out.shape[0] == R and out.shape[1] >= ctx, "out must be [R, >= ctx]")
+    _need(tuple(index_w.shape) == (R, n_heads), "index_w must be [R, Hidx]")
+    _need(page_table.shape[1] * PAGE_TOKENS >= ctx, "page_table rows cannot cover ctx positions")
     if hist is not None:
         _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
         _need(hist.numel() == R * HIST_BINS, "hist must be [R, 4096]")
@@ -226,14 +228,20 @@ def topk_select(
     if out_idx is None:
         out_idx = torch.empty(R, topk, dtype=torch.int32, device=logits.device)
     _cuda_contig(out_idx, "out_idx", (torch.int32,))
+    _need(tuple(out_idx.shape) == (R, topk), f"out_idx must be [R, topk] = [{R}, {topk}]")
     if out_val is None and return_values:
         out_val = torch.empty(R, topk, dtype=torch.float32, device=logits.device)
+    if out_val is not None:
+        _cuda_contig(out_val, "out_val", (torch.float32,))
+        _need(tuple(out_val.shape) == (R, topk), f"out_val must be [R, topk] = [{R}, {topk}]")
     if hist is not None:
         _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+        _need(hist.numel() == R * HIST_BINS, "hist must be [R, 4096]")
     if workspace is None:
         # a fresh zeroed scratch per call is always safe; steady-state callers pass their own
         workspace = topk_workspace(R, n, logits.device)
     _cuda_contig(workspace, "workspace", (torch.uint8,))
+    _need(0 < int(topk) <= 65536, "topk must be in [1, 65536]")
     _lib.check(_lib.lib().dsa_topk_select(
         _ptr(logits), _ptr(seq_lens), _ptr(hist), _ptr(index_map), _ptr(out_idx), _ptr(out_val),
         _ptr(workspace), workspace.numel(), R, n, slab_stride, int(topk), int(pad_value),
@@ -263,8 +271,7 @@ def default_nsplit(rows: int, heads: int, topk: int, sm_count: int = 148) -> int
     Smaller launches and other head counts run on the mma.sync kernel (16 heads
     per CTA, two CTAs per SM)."""
     tiles = max(1, math.ceil(topk / 64))
-    mode = os.environ.get("DSA_MLA_TC", "1")
-    if heads % 64 == 0 and (mode == "2" or (mode == "1" and rows * (heads // 64) * tiles >= 128)):
+    if heads % 64 == 0 and rows * (heads // 64) * tiles >= 128:
         blocks = max(1, rows * (heads // 64))
         want = max(1, min(sm_count // blocks, tiles))
         while tiles % want:
@@ -555,8 +562,8 @@ def indexer_stage_fp8(q_raw, k_raw, w_raw, k_norm_weight, k_norm_bias, k_norm_ep
         _ptr(q_raw), _ptr(k_raw), _ptr(w_raw), _ptr(k_norm_weight), _ptr(k_norm_bias), float(k_norm_eps),
         _ptr(rope_cos), _ptr(rope_sin), _ptr(positions), _ptr(index_q), _ptr(index_w),
         _ptr(cache_index_k) if not paged else None, _ptr(cache_k_scale) if not paged else None,
-        _ptr(pages) if paged else None, _ptr(page_table) if paged else None,
-        page_table.shape[1] if paged else 0, B, n_heads, cap, 1 if rope_interleave else 0,
+        _ptr(pages) if paged else None, pages.numel() // INDEX_PAGE_BYTES if paged else 0,
+        _ptr(page_table) if paged else None, page_table.shape[1] if paged else 0, B, n_heads, cap, 1 if rope_interleave else 0,
         0 if scale_fmt is None else 1, float(n_heads ** -0.5), float(softmax_scale), _stream()))
 
 

@@ -17,7 +17,7 @@ import os
 import sys
 from pathlib import Path
 
-KERNELS = {0: "indexer_scan", 1: "topk_classify", 4: "topk_finish", 2: "sparse_mla_partials", 3: "sparse_mla_combine"}
+KERNELS = {0: "indexer_scan", 1: "topk_cluster", 2: "sparse_mla_partials", 3: "sparse_mla_combine"}
 
 
 def main() -> None:

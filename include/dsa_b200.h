@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 4
+#define DSA_ABI_VERSION 5
 
 enum dsa_status {
   DSA_OK = 0,
@@ -57,9 +57,16 @@ int dsa_abi_version(void);
 const char* dsa_last_error(void);
 const char* dsa_status_string(int status);
 
-/* Reads and clears the per-device status word that kernels set when one of
- * their bounded waits ran out. Synchronises the device. Returns DSA_OK or
- * DSA_ERR_DEVICE_TIMEOUT; *detail (optional) receives the raw word. */
+/* Reads and clears the per-device status word. Kernels set a bit in it when one of
+ * their bounded waits ran out (DSA_STATUS_*_TIMEOUT) or when they declined to follow a
+ * page-table entry outside the pool (DSA_STATUS_BAD_PAGE). Synchronises the device.
+ * Returns DSA_OK, DSA_ERR_DEVICE_TIMEOUT when a wait ran out, else
+ * DSA_ERR_INVALID_ARGUMENT for a bad page; *detail (optional) receives the raw word. */
+#define DSA_STATUS_SCAN_TIMEOUT 1u
+#define DSA_STATUS_ATTN_TIMEOUT 2u
+#define DSA_STATUS_SELECT_OVERFLOW 4u
+#define DSA_STATUS_BAD_PAGE 8u
+#define DSA_STATUS_EXCHANGE_TIMEOUT 16u
 int dsa_check_device_status(uint32_t* detail);
 
 /* Tracing builds only (compiled with -DDSA_STAMPS): copies the per-CTA phase
@@ -142,22 +149,24 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
  * This entry point has no counterpart in the reference. It is dsa_topk_select
  * (no histogram input, no index map) for hosts that have no way to obtain device
  * memory for scratch: a runtime whose memory pool is closed once serving starts,
- * a plugin that is handed only its input and output buffers, or code running
- * where cudaMalloc is forbidden (for example while a stream is being captured).
- * The scratch is a fixed DSA_TOPK_STATIC_SCRATCH_BYTES array inside the library's
+ * a plugin that is handed only its input and output buffers, or code running at
+ * a point where cudaMalloc is forbidden. Rows of up to 131072 logits need no
+ * scratch at all (one cluster kernel, shared memory only); for longer rows the
+ * scratch is a fixed DSA_TOPK_STATIC_SCRATCH_BYTES array inside the library's
  * device image, so each GPU that loads the library gives up that much memory
  * until the process exits; the call itself performs no cudaMalloc / cudaFree
  * and calls no allocating routine.
  *   - Limit: dsa_topk_workspace_bytes(R, n) <= DSA_TOPK_STATIC_SCRATCH_BYTES
- *     (one row of up to ~480k logits, or 4 rows of 114k); larger requests return
- *     DSA_ERR_UNSUPPORTED with a message naming both sizes.
+ *     (for rows longer than 131072: one row of up to ~480k logits, or two of
+ *     ~240k); larger requests return DSA_ERR_UNSUPPORTED with a message naming
+ *     both sizes. Every argument is checked before anything is enqueued.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call before starting any stream
- *     capture.
+ *     capture. Host threads may make it concurrently (the look-up is locked).
  *   - All calls on a device share the one array and it keeps the previous call's
  *     contents; the part that must start at zero is cleared on `stream` by every
- *     call. Two calls that overlap on the GPU (different streams, or graphs
- *     replayed concurrently) race on it: serialise them.
+ *     call that uses the array. Two such calls that overlap on the GPU
+ *     (different streams, or work replayed concurrently) race on it: serialise them.
  */
 #define DSA_TOPK_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
 int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t* out_idx,
@@ -293,7 +302,11 @@ int dsa_decode_prep(const void* iq_raw, const void* w_raw, const void* ik_raw, c
  *   power of two when round_scale != 0); index_q <- query bytes, index_w <- w_raw * head_scale *
  *   q_scale * softmax_scale (:1063-1065, head_scale = heads^-0.5); the key's bytes and scale
  *   are appended at positions[b] (:1061-1062) in the dense cache (pages NULL) or in 64-token
- *   pages of DSA_INDEX_PAGE_BYTES addressed through page_table [B, pt_stride].
+ *   pages of DSA_INDEX_PAGE_BYTES addressed through page_table [B, pt_stride]; the pool holds
+ *   num_pages pages and pt_stride * 64 >= cap is required. A page-table entry outside
+ *   [0, num_pages) is not followed: that token is skipped and a bit is set in the device status
+ *   word (dsa_check_device_status). The paged scan treats such an entry the same way (the keys
+ *   behind it get logit -inf).
  * q_raw bf16 [B, n_heads, 128]; k_raw bf16 [B, 128]; w_raw fp32 [B, n_heads]; k_norm_weight /
  * k_norm_bias fp32 [128]; rope_cos / rope_sin fp32 [cap, 32] (real / imaginary part of the
  * reference's freqs_cis); positions int64 [B]. Rounding follows the reference's op sequence
@@ -302,9 +315,10 @@ int dsa_indexer_stage_fp8(const void* q_raw, const void* k_raw, const float* w_r
                           const float* k_norm_weight, const float* k_norm_bias, float k_norm_eps,
                           const float* rope_cos, const float* rope_sin, const int64_t* positions,
                           uint8_t* index_q, float* index_w, uint8_t* cache_index_k,
-                          float* cache_k_scale, uint8_t* pages, const int32_t* page_table,
-                          int64_t pt_stride, int B, int n_heads, int64_t cap, int rope_interleave,
-                          int round_scale, float head_scale, float softmax_scale, void* stream);
+                          float* cache_k_scale, uint8_t* pages, int64_t num_pages,
+                          const int32_t* page_table, int64_t pt_stride, int B, int n_heads, int64_t cap,
+                          int rope_interleave, int round_scale, float head_scale, float softmax_scale,
+                          void* stream);
 
 /* Serving-form latent append: the new token's latent row between wkv_a and the cache
  * (src/lagged_indexer_dsa/inference/modeling/transformer.py:3264-3276): RMSNorm of the 512

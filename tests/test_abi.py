@@ -62,12 +62,19 @@ def test_bad_arguments_are_rejected_before_any_launch():
     rc = h.dsa_topk_select(addr, None, None, None, addr, None, addr, 16, 1, 1 << 21, 1 << 21, 2048, -1, 0, None)
     assert rc == -2
     # the staging entry points: a missing operand, both cache forms missing, an unknown row format
-    rc = h.dsa_indexer_stage_fp8(addr, None, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, addr, addr, None, None,
+    rc = h.dsa_indexer_stage_fp8(addr, None, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, addr, addr, None, 0, None,
                                  0, 1, 64, 128, 0, 0, 0.125, 0.088, None)
     assert rc == -1 and b"null pointer" in h.dsa_last_error()
-    rc = h.dsa_indexer_stage_fp8(addr, addr, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, None, None, None, None,
+    rc = h.dsa_indexer_stage_fp8(addr, addr, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, None, None, None, 0, None,
                                  0, 1, 64, 128, 0, 0, 0.125, 0.088, None)
     assert rc == -1 and b"dense key cache or pages" in h.dsa_last_error()
+    # paged form: the page table must be able to cover every position below cap, and num_pages must be given
+    rc = h.dsa_indexer_stage_fp8(addr, addr, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, None, None, addr, 4, addr,
+                                 1, 1, 64, 128, 0, 0, 0.125, 0.088, None)
+    assert rc == -1 and b"cannot cover" in h.dsa_last_error()
+    rc = h.dsa_indexer_stage_fp8(addr, addr, addr, addr, addr, 1e-6, addr, addr, addr, addr, addr, None, None, addr, 0, addr,
+                                 2, 1, 64, 128, 0, 0, 0.125, 0.088, None)
+    assert rc == -1 and b"num_pages" in h.dsa_last_error()
     rc = h.dsa_latent_append(addr, addr, 1e-6, addr, addr, addr, addr, addr, 1, 128, 16, 1, 3, 0, None)
     assert rc == -1 and b"format" in h.dsa_last_error()
 
@@ -105,13 +112,12 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         importlib.reload(_lib)
 
 
-def test_default_nsplit_heuristic(monkeypatch):
+def test_default_nsplit_heuristic():
     """Host-side split heuristic: large launches of 64-head blocks get about one CTA
     per SM with a split count that divides the 64-key tiles (no empty split); small
     ones and other head counts get two 16-head CTAs per SM."""
     from dsa_multi_layer_indexer_b200 import ops
 
-    monkeypatch.delenv("DSA_MLA_TC", raising=False)
     assert ops.default_nsplit(1, 128, 2048) == 32          # 64 tiles: mma.sync kernel, 8 head blocks
     assert ops.default_nsplit(1, 16, 2048) == 32           # TP8 shape
     assert ops.default_nsplit(32, 128, 2048) == 2          # 2048 tiles: tcgen05 kernel, 64 blocks
@@ -122,5 +128,3 @@ def test_default_nsplit_heuristic(monkeypatch):
         assert 1 <= n <= tiles
         if rows * (heads // 64) * tiles >= 128:
             assert tiles % n == 0 and rows * (heads // 64) * n <= max(148, rows * (heads // 64))
-    monkeypatch.setenv("DSA_MLA_TC", "0")
-    assert ops.default_nsplit(32, 128, 2048) == 1          # 256 head blocks of 16: one split each

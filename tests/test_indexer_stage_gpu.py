@@ -126,6 +126,59 @@ def test_stage_paged_append_equals_dense(D):
     assert int((pg != 0x55).sum()) <= touched
 
 
+def test_stage_and_scan_do_not_follow_a_bad_page_table_entry(D):
+    """A page-table entry of -1 (or one beyond the pool) must not become a wild access: the
+    staging kernel skips that token and leaves every pool byte as it was, the paged scan gives
+    the keys behind such an entry logit -inf, and both report through the device status word."""
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    dev = "cuda"
+    B, H, cap = 3, 64, 256
+    q_raw, k_raw, w_raw, cos, sin, norm_w, norm_b, positions = _inputs(B, H, cap, seed=21)
+    pages_per_seq = cap // 64
+    n_pages = B * pages_per_seq
+    perm = torch.randperm(n_pages).to(torch.int32).view(B, pages_per_seq)
+    bad = perm.clone()
+    bad[1, int(positions[1]) // 64] = -1          # the page sequence 1 would append to
+    bad[2, int(positions[2]) // 64] = n_pages + 5  # beyond the pool
+    pages = torch.full((n_pages * 8448,), 0x55, dtype=torch.uint8, device=dev)
+    index_q = torch.zeros(B, H, 128, dtype=torch.uint8, device=dev)
+    index_w = torch.zeros(B, H, device=dev)
+    _lib.check_device_status()
+    D.indexer_stage_fp8(q_raw.to(dev), k_raw.to(dev), w_raw.to(dev), norm_w.to(dev), norm_b.to(dev), 1e-6,
+                        cos.to(dev), sin.to(dev), positions.to(dev), index_q, index_w, pages=pages,
+                        page_table=bad.to(dev))
+    with pytest.raises(_lib.DsaError) as err:
+        _lib.check_device_status()
+    assert err.value.status == -1 and "page-table" in str(err.value)
+    _lib.check_device_status()  # the word was cleared by the read
+    pg = pages.cpu().view(n_pages, 8448)
+    assert int((pg != 0x55).sum()) <= 132  # only sequence 0's token was written
+    pos0 = int(positions[0])
+    assert bool((pg[int(perm[0, pos0 // 64])][(pos0 % 64) * 128:(pos0 % 64 + 1) * 128] != 0x55).any())
+    # the paged scan: keys behind a bad entry get -inf, every other logit is what the good table gives
+    g = torch.Generator().manual_seed(5)
+    ik8, sk = O.quantize_e4m3_rowwise(torch.randn(B, cap, 128, generator=g))
+    iq8, sq = O.quantize_e4m3_rowwise(torch.randn(B, H, 128, generator=g))
+    wp = sq * (torch.randn(B, H, generator=g) / 8)
+    pool = torch.zeros(n_pages, 8448, dtype=torch.uint8)
+    for b in range(B):
+        O.pack_index_pages(ik8[b], sk[b], perm[b].tolist(), n_pages, pool)
+    lens = torch.full((B,), cap, dtype=torch.int32, device=dev)
+    good = D.indexer_scan_fp8_paged(iq8.to(dev), wp.to(dev), pool.to(dev), perm.to(dev), lens, cap).cpu()
+    _lib.check_device_status()
+    got = D.indexer_scan_fp8_paged(iq8.to(dev), wp.to(dev), pool.to(dev), bad.to(dev), lens, cap).cpu()
+    with pytest.raises(_lib.DsaError):
+        _lib.check_device_status()
+    for b in range(B):
+        for pidx in range(pages_per_seq):
+            span = slice(pidx * 64, pidx * 64 + 64)
+            if int(bad[b, pidx]) != int(perm[b, pidx]):
+                assert torch.isinf(got[b, span]).all() and (got[b, span] < 0).all()
+            else:
+                assert torch.equal(got[b, span], good[b, span])
+
+
 def test_staged_operands_feed_the_scan(D):
     """Staging a run of tokens one by one, then scanning: logits equal the oracle's
     on its own staged operands (same bytes in, so only the fp32 summation order differs)."""

@@ -200,6 +200,31 @@ def test_topk_with_scan_histogram_equals_plain(ops):
         assert int(hist.abs().sum()) == 0  # re-armed for the next launch
 
 
+def test_topk_and_paged_scan_wrappers_reject_buffers_of_the_wrong_extent(ops):
+    """The wrappers hand raw pointers to the kernels, so every caller-owned output is checked
+    for device, dtype and extent first: a short or host buffer is a ValueError, not a wild write."""
+    logits = torch.randn(2, 5000, device="cuda")
+    with pytest.raises(ValueError, match="out_idx"):
+        ops.topk_select(logits, 64, out_idx=torch.empty(2, 32, dtype=torch.int32, device="cuda"))
+    with pytest.raises(ValueError, match="out_val"):
+        ops.topk_select(logits, 64, out_val=torch.empty(2, 64))  # host memory
+    with pytest.raises(ValueError, match="out_val"):
+        ops.topk_select(logits, 64, out_val=torch.empty(2, 63, device="cuda"))
+    with pytest.raises(ValueError, match="hist"):
+        ops.topk_select(logits, 64, hist=torch.zeros(1, 4096, dtype=torch.int32, device="cuda"))
+    iq = torch.zeros(2, 64, 128, dtype=torch.uint8, device="cuda")
+    w = torch.zeros(2, 64, device="cuda")
+    pool = torch.zeros(8, 8448, dtype=torch.uint8, device="cuda")
+    pt = torch.zeros(2, 4, dtype=torch.int32, device="cuda")
+    lens = torch.full((2,), 256, dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError, match="out must be"):
+        ops.indexer_scan_fp8_paged(iq, w, pool, pt, lens, 256, out=torch.empty(2, 128, device="cuda"))
+    with pytest.raises(ValueError, match="out must be"):
+        ops.indexer_scan_fp8_paged(iq, w, pool, pt, lens, 256, out=torch.empty(1, 256, device="cuda"))
+    with pytest.raises(ValueError, match="cannot cover"):
+        ops.indexer_scan_fp8_paged(iq, w, pool, pt, lens, 512)
+
+
 # ----------------------------------------------------------------------------- sparse MLA
 def test_sparse_mla_golden(ops):
     g = load_golden("sparse_mla.npz")
