@@ -393,10 +393,16 @@ __host__ __device__ constexpr uint32_t idesc_bf16_f32(int m, int n, bool a_mn_ma
 }
 
 // ---------------------------------------------------------------- device: numerics
-// Monotone map fp32 -> u32: a > b  <=>  key(a) > key(b) (NaN sorts above +inf).
+// Monotone map fp32 -> u32: a > b  <=>  key(a) > key(b), and a == b <=> key(a) == key(b) for
+// every pair of numbers: -0.0 is first folded onto +0.0, so ordering by key is exactly the
+// ordering of floating-point comparisons (NaNs aside: a positive NaN sorts above +inf).
 __device__ __forceinline__ uint32_t ordered_key(float x) {
-  uint32_t u = __float_as_uint(x);
+  uint32_t u = __float_as_uint(x + 0.0f);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+// The number whose key is `key` (inverse of the map above).
+__device__ __forceinline__ float key_to_float(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 #endif  // __CUDACC__
 

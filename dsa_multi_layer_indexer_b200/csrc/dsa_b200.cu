@@ -389,48 +389,19 @@ int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
   return topk::workspace_words(R, n) * 4;
 }
 
-// Rows of up to kClMaxN logits: one cluster of 1..16 CTAs per row, no scratch. A cluster of
-// 16 needs an opt-in and a GPC with 16 free SMs; where the device cannot hold one, 8 is used.
+// Rows of up to kClMaxN logits: one cluster of 1..8 CTAs per row, no scratch.
 static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStream_t st) {
-  int rc = opt_in_smem(topk::topk_cluster_kernel, topk::cl_smem_bytes(topk::kClMaxGroups), g_opt_topk_cluster);
+  int rc = opt_in_smem(topk::topk_cluster_kernel, sizeof(topk::ClShared), g_opt_topk_cluster);
   if (rc) return rc;
-  static int cl16_ok[64];  // 0 unknown, 1 yes, -1 no
-  int dev = 0;
-  DSA_CUDA(cudaGetDevice(&dev));
-  int max_ctas = 8;
-  if (dev >= 0 && dev < 64) {
-    if (cl16_ok[dev] == 0) {
-      cl16_ok[dev] = -1;
-      if (cudaFuncSetAttribute(topk::topk_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
-          cudaSuccess) {
-        cudaLaunchConfig_t q{};
-        cudaLaunchAttribute qa[1];
-        q.gridDim = dim3(16, 1);
-        q.blockDim = dim3(topk::kClThreads);
-        q.dynamicSmemBytes = topk::cl_smem_bytes(4);
-        qa[0].id = cudaLaunchAttributeClusterDimension;
-        qa[0].val.clusterDim.x = 16;
-        qa[0].val.clusterDim.y = 1;
-        qa[0].val.clusterDim.z = 1;
-        q.attrs = qa;
-        q.numAttrs = 1;
-        int n_cl = 0;
-        if (cudaOccupancyMaxActiveClusters(&n_cl, topk::topk_cluster_kernel, &q) == cudaSuccess && n_cl >= 4)
-          cl16_ok[dev] = 1;
-      }
-      (void)cudaGetLastError();
-    }
-    if (cl16_ok[dev] == 1 && env_int("DSA_TOPK_CLUSTER16", 1) != 0) max_ctas = 16;
-  }
-  int ctas = 1;
-  while (ctas < max_ctas && int64_t(ctas) * topk::kClThreads * 4 < n) ctas *= 2;
-  const int64_t per_group = int64_t(ctas) * topk::kClThreads * 4;
-  const int groups = int((n + per_group - 1) / per_group);
+  int ctas = 1;  // at least 4 logits per thread before another CTA is added
+  while (ctas < topk::kClMaxCtas && int64_t(ctas) * topk::kClThreads * 4 < n) ctas *= 2;
+  const int64_t per_key = int64_t(ctas) * topk::kClThreads;
+  const int nk = int((n + per_key - 1) / per_key);
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
   cfg.gridDim = dim3(ctas, R);
   cfg.blockDim = dim3(topk::kClThreads);
-  cfg.dynamicSmemBytes = topk::cl_smem_bytes(groups);
+  cfg.dynamicSmemBytes = sizeof(topk::ClShared);
   cfg.stream = st;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = ctas;
@@ -440,7 +411,7 @@ static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStre
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel, p, groups));
+  DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel, p, nk));
   return DSA_OK;
 }
 

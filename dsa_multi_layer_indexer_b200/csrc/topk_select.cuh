@@ -510,45 +510,56 @@ topk_finish_kernel(const Params p) {
 // ------------------------------------------------------------------------------
 // One launch for rows of up to kClMaxN logits: a thread-block cluster per row.
 //
-// Every CTA of the cluster keeps its contiguous slice of the row in shared
-// memory as order-preserving keys (loaded once, 16-byte coalesced). The k-th
-// largest key is found exactly by three radix levels (12 + 10 + 10 bits): a
-// level's histogram is built in each CTA's shared memory, its non-zero bins are
-// PUSHED into every CTA's copy (distributed-shared-memory reductions), and one
-// cluster barrier later each CTA holds the whole row's histogram and finds the
-// threshold bin by itself. With the key k* and the number of elements equal to
-// k* that are kept, one prefix sum over the pair (larger than k*, equal to k*)
-// in position order gives each kept element its slot in the ascending output:
-//   slot(x) = larger_before(x) + min(equal_before(x), ties_kept)
-// so ties go to the lower positions, and no candidate list, no scratch in
-// global memory and no capacity limit is involved. The first level's histogram
-// comes from the indexer scan when the caller passes it.
+// Each CTA of the cluster owns a contiguous slice of the row and looks at every
+// logit of it exactly once. With the threshold bin T of the 12-bit histogram
+// (the indexer scan's, when the caller passes it) one sweep over the slice
+// leaves, per warp, a bit mask of the positions that are certainly kept (bin
+// above T) and a compact list of the few candidates in bin T. Everything after
+// that touches only mask words and candidates:
+//   * two more radix levels (7 + 13 bits) over the candidates find the k-th
+//     largest key k* exactly. A level's counts are PUSHED into every CTA's
+//     histogram (distributed-shared-memory reductions), and one cluster barrier
+//     later each CTA finds the threshold bin by itself;
+//   * candidates above k* join the kept mask, those equal to k* a tie mask;
+//   * one prefix sum over the pair (kept, tie) in position order gives each
+//     element its slot in the ascending output:
+//       slot(x) = kept_before(x) + min(ties_before(x), ties_kept)
+//     so ties go to the lower positions.
+// No scratch in global memory, no capacity limit (a warp's candidate list holds
+// the warp's whole share), no wait on another launch.
 //
-// The kernel runs once through its code on a handful of SMs, so its time is
-// set by the barriers it crosses and by how much machine code it has to fetch:
-// every loop over the keys is a rolled loop with a small body.
-constexpr int kClThreads = 1024;
+// Cost model that shaped it: a CTA's warps share four issue ports, so every
+// instruction a thread executes costs (warps per port) cycles of wall time.
+// Hence 512 threads, one heavy sweep, sections that only one warp needs to run
+// are run by one warp while the others wait at a barrier, and loops are rolled.
+constexpr int kClThreads = 512;
 constexpr int kClWarps = kClThreads / 32;
-constexpr int kClMaxGroups = 8;                               // 16-byte groups of keys per thread
-constexpr int kClMaxCtas = 16;                                // 8 is the portable cluster size, 16 needs an opt-in
-constexpr int64_t kClMaxN = int64_t(8) * kClThreads * 4 * kClMaxGroups;  // 262144 (with the portable cluster size)
+constexpr int kClMaxKeys = 32;                                // logits per thread (= mask words per warp)
+constexpr int kClMaxCtas = 8;                                 // portable cluster size
+constexpr int64_t kClMaxN = int64_t(kClMaxCtas) * kClThreads * kClMaxKeys;  // 131072
+constexpr int kL2Bits = 7, kL2Bins = 1 << kL2Bits;            // key bits 19..13
+constexpr int kL3Bits = 13, kL3Bins = 1 << kL3Bits;           // key bits 12..0
+constexpr int kWarpKeys = 32 * kClMaxKeys;                    // 1024: a warp's share of the slice
 
 struct ClShared {
-  uint32_t hist1[kBins];        // whole row, complete after the level's cluster barrier
-  uint32_t local1[kBins];       // this CTA's part
-  uint32_t hist2[kRoundBins];
-  uint32_t local2[kRoundBins];
-  uint32_t hist3[kRoundBins];
-  uint32_t local3[kRoundBins];
+  uint32_t hist1[kBins];         // level 1: whole row (copy of the scan's, or pushed by the CTAs)
+  uint32_t hist3[kL3Bins];       // level 3: whole row, pushed; stored as swizzled_bin<kL3Bins> says
+  uint32_t hist2[kL2Bins];       // level 2: whole row, pushed
+  uint32_t local2[kL2Bins];      // level 2: this CTA's part
+  uint32_t kept[kClWarps][kClMaxKeys];   // bit (w, i, l): position w * 32 * nk + i * 32 + l of the slice is kept
+  uint32_t ties[kClWarps][kClMaxKeys];   // same, for the elements equal to k*
   uint32_t warp_tot[kClWarps];
-  uint32_t cta_tot[kClMaxCtas];  // (equal << 16 | larger) of every CTA of the cluster
-  uint32_t pad_[16];
-  uint4 keys[1];                 // really groups * kClThreads entries: this CTA's slice in position order
+  uint32_t warp_base[kClWarps];
+  uint32_t cta_tot[kClMaxCtas];  // (ties << 16 | kept) of every CTA of the cluster
+  uint32_t res[4];
+  uint64_t load_bar;                       // mbarrier of the slice's bulk copy
+  alignas(128) uint32_t bits[kClWarps][kWarpKeys];  // (a bulk copy's destination must be 16-byte aligned)      // the slice's raw logits: word (w, i * 32 + l) is thread (w, l)'s i-th
 };
-inline size_t cl_smem_bytes(int groups) { return offsetof(ClShared, keys) + size_t(groups) * kClThreads * 16; }
+static_assert(kL3Bins >= kBins, "hist3 doubles as the local level-1 histogram");
+static_assert(offsetof(ClShared, bits) % 128 == 0 && offsetof(ClShared, load_bar) % 8 == 0, "alignment of the copy target and its barrier");
 
-// Adds 1 to h[digit] for the lanes with `pred`. The lanes that share the first such
-// lane's digit add once, so a row of equal logits does not serialise on one address.
+// Adds `amount` of 1s to h[digit] for the lanes with `pred`. The lanes that share the first
+// such lane's digit add once, so a row of equal logits does not serialise on one address.
 __device__ __forceinline__ void hist_add_warp(uint32_t* h, bool pred, uint32_t digit) {
   const uint32_t m = __ballot_sync(0xffffffffu, pred);
   if (m == 0) return;
@@ -560,324 +571,384 @@ __device__ __forceinline__ void hist_add_warp(uint32_t* h, bool pred, uint32_t d
     else if (int(threadIdx.x & 31) == leader) smem_red_add(&h[digit], __popc(same));
   }
 }
-
-// Pushes this CTA's non-zero bins of `local` (one per thread, or four when kWide)
-// into `whole` of every CTA of the cluster.
-template <bool kWide>
-__device__ __forceinline__ void push_bins(const uint32_t* local, uint32_t* whole, uint32_t n_ctas) {
-  const int tid = threadIdx.x;
-  if (kWide) {
-    const uint4 x = reinterpret_cast<const uint4*>(local)[tid];
-    if (x.x | x.y | x.z | x.w) {
-      const uint32_t a = smem_u32(whole + 4 * tid);
+// The same into `whole` of every CTA of the cluster.
+__device__ __forceinline__ void hist_push_warp(uint32_t* whole, bool pred, uint32_t digit, uint32_t n_ctas) {
+  const uint32_t m = __ballot_sync(0xffffffffu, pred);
+  if (m == 0) return;
+  const int leader = __ffs(m) - 1;
+  const uint32_t first = __shfl_sync(0xffffffffu, digit, leader);
+  const uint32_t same = __ballot_sync(0xffffffffu, pred && digit == first);
+  uint32_t add = 0;
+  if (pred) add = digit != first ? 1u : (int(threadIdx.x & 31) == leader ? uint32_t(__popc(same)) : 0u);
+  if (add) {
+    const uint32_t a = smem_u32(whole + digit);
 #pragma unroll 1
-      for (uint32_t cc = 0; cc < n_ctas; ++cc) {
-        const uint32_t ra = cluster_map(a, cc);
-        if (x.x) cluster_red_add(ra, x.x);
-        if (x.y) cluster_red_add(ra + 4, x.y);
-        if (x.z) cluster_red_add(ra + 8, x.z);
-        if (x.w) cluster_red_add(ra + 12, x.w);
-      }
-    }
-  } else {
-    const uint32_t x = local[tid];
-    if (x) {
-      const uint32_t a = smem_u32(whole + tid);
-#pragma unroll 1
-      for (uint32_t cc = 0; cc < n_ctas; ++cc) cluster_red_add(cluster_map(a, cc), x);
-    }
+    for (uint32_t cc = 0; cc < n_ctas; ++cc) cluster_red_add(cluster_map(a, cc), add);
   }
 }
 
-// Bin holding the k-th largest element of a histogram of NB bins in shared memory
-// (searched from the top bin down), and the element's rank inside that bin; the
-// result is returned to every thread. `own` are the counts of this thread's
-// NB / 1024 bins, highest first: thread t owns the bins just below NB - t * NB / 1024.
-// One block barrier: each warp sums its 32 threads' bins, every warp scans the 32
-// warp sums, then reads the target warp's bins itself.
+// Inclusive prefix sum over the lanes of a warp.
+__device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t up = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += up;
+  }
+  return v;
+}
+
+// Bin holding the k-th largest element of the NB-bin histogram h (shared memory, searched
+// from the top bin down) and the element's rank inside that bin, left in res[0], res[1] for
+// every thread. Thread t owns the PER = NB / kClThreads bins just below NB - PER t (for
+// NB < kClThreads: one bin for the first NB threads). All warps prefix-sum their threads' bin
+// sums at once; after a barrier every warp prefix-sums the 16 warp totals, the warp that holds
+// the k-th element picks its thread by ballot and that thread walks its own bins (registers);
+// a second barrier publishes the result. The dependent chain is two warp scans long.
+// Where bin b of an NB-bin histogram lives when it is stored for conflict-free reads by
+// find_kth_bin<NB, true>: bins are numbered from the top (rb = NB - 1 - b), thread t owns
+// rb in [PER t, PER (t + 1)) and its 16-byte chunk j sits at chunk index j * kClThreads + t.
 template <int NB>
-__device__ __forceinline__ void find_kth_bin(const uint32_t* h, const uint32_t (&own)[NB / kClThreads], uint32_t k,
-                                             uint32_t* warp_tot, uint32_t& bin, uint32_t& rank) {
-  constexpr int PER = NB / kClThreads;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ uint32_t swizzled_bin(uint32_t b) {
+  constexpr uint32_t PERC = NB / kClThreads / 4;  // 16-byte chunks per thread
+  const uint32_t rb = uint32_t(NB - 1) - b, q = rb >> 2;
+  return (((q % PERC) * kClThreads + q / PERC) << 2) | (rb & 3u);
+}
+
+template <int NB, bool kSwz = false>
+__device__ __forceinline__ void find_kth_bin(const uint32_t* h, uint32_t k, uint32_t* warp_tot, uint32_t* res) {
+  constexpr int PER = NB >= kClThreads ? NB / kClThreads : 1;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t cnt[PER];  // this thread's bins, highest first
+  if (kSwz) {
+    static_assert(!kSwz || PER >= 4, "the interleaved layout is for at least one chunk per thread");
+#pragma unroll
+    for (int i = 0; i < PER / 4; ++i) {
+      const uint4 x = reinterpret_cast<const uint4*>(h)[i * kClThreads + tid];
+      cnt[4 * i + 0] = x.x, cnt[4 * i + 1] = x.y, cnt[4 * i + 2] = x.z, cnt[4 * i + 3] = x.w;
+    }
+  } else if (PER >= 4) {
+    const uint4* mine = reinterpret_cast<const uint4*>(h + NB - PER * (tid + 1));
+#pragma unroll
+    for (int i = 0; i < PER / 4; ++i) {
+      const uint4 x = mine[PER / 4 - 1 - i];
+      cnt[4 * i + 0] = x.w, cnt[4 * i + 1] = x.z, cnt[4 * i + 2] = x.y, cnt[4 * i + 3] = x.x;
+    }
+  } else {
+    cnt[0] = tid < NB ? h[NB - 1 - tid] : 0u;
+  }
   uint32_t s = 0;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) s += own[i];
-  const uint32_t wsum = __reduce_add_sync(0xffffffffu, s);
-  if (lane == 0) warp_tot[warp] = wsum;
+  for (int i = 0; i < PER; ++i) s += cnt[i];
+  const uint32_t inc = warp_inclusive_scan(s);
+  if (lane == 31) warp_tot[warp] = inc;
+  if (tid == 0) res[0] = 0u, res[1] = 1u;  // stays if k exceeds the histogram's total (never with a consistent caller)
   __syncthreads();
-  const uint32_t wt = warp_tot[lane];
-  uint32_t inc = wt;
+  const uint32_t wt = lane < kClWarps ? warp_tot[lane] : 0u;
+  const uint32_t winc = warp_inclusive_scan(wt);
+  const uint32_t before_warp = __shfl_sync(0xffffffffu, winc - wt, warp);
+  const uint32_t k2 = k - before_warp;  // (wraps for the warps past the k-th element: they fail the test below)
+  if (before_warp < k && k2 <= __shfl_sync(0xffffffffu, inc, 31)) {  // this warp holds the k-th element
+    const uint32_t hit = __ballot_sync(0xffffffffu, inc >= k2);
+    if (lane == __ffs(hit) - 1) {
+      uint32_t running = inc - s, b = 0, rk = 1;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
-    if (lane >= o) inc += up;
-  }
-  const uint32_t hit = __ballot_sync(0xffffffffu, inc >= k);
-  const int W = hit ? __ffs(hit) - 1 : 31;
-  const uint32_t k2 = k - __shfl_sync(0xffffffffu, inc - wt, W);
-  const int top = NB - 1 - (W * 32 + lane) * PER;  // highest bin of this lane inside warp W's range
-  uint32_t c[PER];
-  uint32_t s2 = 0;
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    c[i] = h[top - i];
-    s2 += c[i];
-  }
-  uint32_t inc2 = s2;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t up = __shfl_up_sync(0xffffffffu, inc2, o);
-    if (lane >= o) inc2 += up;
-  }
-  const uint32_t hit2 = __ballot_sync(0xffffffffu, inc2 >= k2);
-  const int L = hit2 ? __ffs(hit2) - 1 : 31;
-  uint32_t running = inc2 - s2, b = uint32_t(top), rk = 1;
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    if (running < k2 && k2 <= running + c[i]) {
-      b = uint32_t(top - i);
-      rk = k2 - running;
+      for (int i = 0; i < PER; ++i) {
+        if (running < k2 && k2 <= running + cnt[i]) {
+          b = uint32_t(i);
+          rk = k2 - running;
+        }
+        running += cnt[i];
+      }
+      res[0] = uint32_t(NB - 1 - tid * PER) - b;
+      res[1] = rk;
     }
-    running += c[i];
   }
-  bin = __shfl_sync(0xffffffffu, b, L);
-  rank = __shfl_sync(0xffffffffu, rk, L);
+  __syncthreads();
 }
 
 __global__ void __launch_bounds__(kClThreads, 1)
-topk_cluster_kernel(const Params p, const int groups) {
-  extern __shared__ __align__(16) uint8_t topk_smem[];
-  ClShared& sh = *reinterpret_cast<ClShared*>(topk_smem);
+topk_cluster_kernel(const Params p, const int nk) {
+  extern __shared__ __align__(128) uint8_t topk_cl_smem[];
+  ClShared& sh = *reinterpret_cast<ClShared*>(topk_cl_smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = blockIdx.y;
   const uint32_t c = cluster_cta_rank(), C = cluster_num_ctas();
   const int stamp_cta = 512 + r * int(C) + int(c);
   DSA_KTIME_BEGIN(1);
   DSA_STAMP(stamp_cta, 0);
-  // ---- input-free set-up: clear the histograms, then tell the cluster they are clear
-  {
-    uint4* z = reinterpret_cast<uint4*>(&sh);
-    constexpr int kZero16 = int(offsetof(ClShared, keys) / 16);
-    for (int i = tid; i < kZero16; i += kClThreads) z[i] = make_uint4(0, 0, 0, 0);
+  const bool have_hist = p.hist != nullptr;
+  if (tid == 0) {
+    mbar_init(smem_u32(&sh.load_bar), 1);
+    mbar_fence_init();
   }
-  cluster_arrive();
   pdl_wait();
   pdl_launch_dependents();
   const float* row = p.logits + int64_t(r) * p.slab_stride;
-  int64_t len = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
-  len = len < 0 ? 0 : (len > p.n ? p.n : len);
+  int64_t len64 = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
+  len64 = len64 < 0 ? 0 : (len64 > p.n ? p.n : len64);
+  const int len = int(len64);
   const bool take_all = len <= p.topk;
-  const bool have_hist = p.hist != nullptr;
 
-  // ---- this CTA's slice as order-preserving keys (0 = not a visible position); thread
-  // (warp, lane) owns the 16-byte groups j * 32 + lane of its warp's run of `groups` * 128 positions
-  const int64_t base = int64_t(c) * (kClThreads * 4 * groups) + int64_t(warp) * (128 * groups) + lane * 4;
-  uint4* my_keys = sh.keys + warp * groups * 32 + lane;
-  {
-    // every load of the slice is issued before the first key is stored
-    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
-    float4 v[kClMaxGroups];
-#pragma unroll
-    for (int j = 0; j < kClMaxGroups; ++j) {
-      const int64_t p0 = base + j * 128;
-      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (j < groups && p0 < len) {
-        if (vec && p0 + 4 <= p.n) {
-          v[j] = *reinterpret_cast<const float4*>(row + p0);
-        } else {
-          v[j].x = row[p0];
-          if (p0 + 1 < len) v[j].y = row[p0 + 1];
-          if (p0 + 2 < len) v[j].z = row[p0 + 2];
-          if (p0 + 3 < len) v[j].w = row[p0 + 3];
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < kClMaxGroups; ++j) {
-      if (j < groups) {
-        const int64_t p0 = base + j * 128;
-        uint4 k;
-        k.x = p0 + 0 < len ? ordered_key(v[j].x) : 0u;
-        k.y = p0 + 1 < len ? ordered_key(v[j].y) : 0u;
-        k.z = p0 + 2 < len ? ordered_key(v[j].z) : 0u;
-        k.w = p0 + 3 < len ? ordered_key(v[j].w) : 0u;
-        my_keys[j * 32] = k;
-      }
-    }
+  // ---- loads. The CTA's slice (positions slice_base .. + span) comes into shared memory as it
+  // lies in global memory, by one bulk copy when the row is 16-byte aligned. Thread (warp, lane)
+  // then owns positions warp_off + i * 32 + lane of the slice, i < nk: conflict-free reads, and
+  // (i, lane) is ascending position order.
+  const int span = kClThreads * nk;
+  const int slice_base = int(c) * span;
+  const int warp_off = warp * (32 * nk);
+  uint32_t* flat = &sh.bits[0][0];
+  const int avail = max(0, min(int(p.n), slice_base + span) - slice_base);  // of the slice, inside the buffer
+  const int live = max(0, min(len - slice_base, span));                     // of the slice, visible
+  const bool bulk = live > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+  const int bulk_elems = bulk ? (avail & ~3) : 0;
+  const uint32_t bar = smem_u32(&sh.load_bar);
+  if (tid == 0 && bulk_elems > 0) {
+    mbar_arrive_expect_tx(bar, uint32_t(bulk_elems) * 4u);
+    bulk_g2s(smem_u32(flat), row + slice_base, uint32_t(bulk_elems) * 4u, bar);
   }
+  uint4 h1a = make_uint4(0, 0, 0, 0), h1b = h1a;
+  if (have_hist && !take_all) {  // this thread's 8 bins of the scan's histogram
+    const uint4* gh = reinterpret_cast<const uint4*>(p.hist + size_t(r) * kBins + (kBins - 8 * (tid + 1)));
+    h1a = __ldcg(gh);
+    h1b = __ldcg(gh + 1);
+  }
+  if (live > 0)
+    for (int i = bulk_elems + tid; i < live; i += kClThreads) flat[i] = __float_as_uint(row[slice_base + i]);
+  // ---- behind the loads: clear what is accumulated into, then tell the cluster it is clear
+  {
+    static_assert(offsetof(ClShared, warp_tot) % 16 == 0, "the cleared part is whole 16-byte words");
+    constexpr int kZero16 = int(offsetof(ClShared, warp_tot) / 16);  // the histograms and both masks
+    uint4* z = reinterpret_cast<uint4*>(&sh);
+    for (int i = (have_hist ? kBins / 4 : 0) + tid; i < kZero16; i += kClThreads)  // (a given hist1 is overwritten)
+      z[i] = make_uint4(0, 0, 0, 0);
+  }
+  cluster_arrive();
   DSA_STAMP(stamp_cta, 1);
 
-  uint32_t kstar = 0, ties_kept = 0;  // short rows keep every visible position: all keys exceed 0
+  // The slice is in shared memory once the bulk copy has landed; positions past the row's length
+  // then get a NaN, which fails every comparison below. Warp 0 waits (bounded), the others at the
+  // barrier; if the copy never lands the CTA goes on with an empty slice and the status word says so.
+  auto wait_slice = [&]() {
+    if (warp == 0 && bulk_elems > 0) {
+      if (!mbar_wait(bar, 0)) {
+        if (lane == 0) atomicOr(&g_device_status, kStatusSelectOverflow);
+        drain_after_timeout();
+      }
+    }
+    __syncthreads();
+    for (int i = live + tid; i < span; i += kClThreads) flat[i] = 0xFFFFFFFFu;
+    __syncthreads();
+  };
+
+  // Thresholds of the sweep as NUMBERS (floating-point compares issue at twice the rate of
+  // integer ones): a logit is certainly kept when v >= f_hi (its bin is above T) and a candidate
+  // when f_lo <= v < f_hi (its bin is T). Positions past the row's length hold a NaN and fail
+  // both. Short rows keep every visible position: f_hi = -inf.
+  float f_hi = __int_as_float(0xff800000), f_lo = f_hi;
+  uint32_t T = 0, need = 0;
   if (!take_all) {
     // ---- level 1: top 12 key bits
-    uint32_t own1[4];
-    if (have_hist) {  // from the scan: every CTA reads all of it (this thread's bins, highest first)
-      const uint4 h1 = __ldcg(reinterpret_cast<const uint4*>(p.hist + size_t(r) * kBins) + (kClThreads - 1 - tid));
-      reinterpret_cast<uint4*>(sh.hist1)[kClThreads - 1 - tid] = h1;
-      own1[0] = h1.w, own1[1] = h1.z, own1[2] = h1.y, own1[3] = h1.x;
+    if (have_hist) {
+      uint4* mine = reinterpret_cast<uint4*>(sh.hist1 + kBins - 8 * (tid + 1));
+      mine[0] = h1a;
+      mine[1] = h1b;
     } else {
+      // this CTA's own histogram, then its non-zero bins pushed into every CTA's hist1. It borrows
+      // the (still clear) first half of hist3 and clears it again before anybody pushes there.
+      uint32_t* local1 = sh.hist3;
+      wait_slice();
 #pragma unroll 1
-      for (int j = 0; j < groups; ++j) {
-        const uint4 k = my_keys[j * 32];
-        hist_add_warp(sh.local1, k.x != 0u, k.x >> kLowBits);
-        hist_add_warp(sh.local1, k.y != 0u, k.y >> kLowBits);
-        hist_add_warp(sh.local1, k.z != 0u, k.z >> kLowBits);
-        hist_add_warp(sh.local1, k.w != 0u, k.w >> kLowBits);
+      for (int i = 0; i < nk; ++i) {
+        const bool in = i * 32 + lane + warp_off < live;
+        const float v = in ? __uint_as_float(flat[warp_off + i * 32 + lane]) : 0.f;
+        hist_add_warp(local1, in, ordered_key(v) >> kLowBits);
       }
       __syncthreads();
-      cluster_wait();  // every CTA of the cluster has cleared its histograms: remote adds may start
-      push_bins<true>(sh.local1, sh.hist1, C);
+      cluster_wait();  // every CTA of the cluster runs and has cleared its histograms: remote adds may start
+      for (int i = tid; i < kBins; i += kClThreads) {
+        const uint32_t x = local1[i];
+        if (x) {
+          local1[i] = 0;
+          const uint32_t a = smem_u32(&sh.hist1[i]);
+#pragma unroll 1
+          for (uint32_t cc = 0; cc < C; ++cc) cluster_red_add(cluster_map(a, cc), x);
+        }
+      }
       cluster_arrive();
       cluster_wait();
-      const uint4 h1 = reinterpret_cast<const uint4*>(sh.hist1)[kClThreads - 1 - tid];
-      own1[0] = h1.w, own1[1] = h1.z, own1[2] = h1.y, own1[3] = h1.x;
     }
-    uint32_t T, need;
-    find_kth_bin<kBins>(sh.hist1, own1, uint32_t(p.topk), sh.warp_tot, T, need);
-    DSA_STAMP(stamp_cta, 2);
-    // ---- level 2: bits 19..10 of the keys in bin T
-#pragma unroll 1
-    for (int j = 0; j < groups; ++j) {
-      const uint4 k = my_keys[j * 32];
-      hist_add_warp(sh.local2, (k.x >> kLowBits) == T && k.x != 0u, (k.x >> 10) & (kRoundBins - 1));
-      hist_add_warp(sh.local2, (k.y >> kLowBits) == T && k.y != 0u, (k.y >> 10) & (kRoundBins - 1));
-      hist_add_warp(sh.local2, (k.z >> kLowBits) == T && k.z != 0u, (k.z >> 10) & (kRoundBins - 1));
-      hist_add_warp(sh.local2, (k.w >> kLowBits) == T && k.w != 0u, (k.w >> 10) & (kRoundBins - 1));
+    find_kth_bin<kBins>(sh.hist1, uint32_t(p.topk), sh.warp_tot, sh.res);
+    T = sh.res[0];
+    need = sh.res[1];
+    // bin T is [T << 20, (T + 1) << 20) in key space; bins below ordered_key(-inf) hold only NaNs
+    const uint32_t key_lo = max(T << kLowBits, 0x007FFFFFu);
+    f_lo = key_to_float(key_lo);
+    f_hi = T == uint32_t(kBins - 1) ? __int_as_float(0x7fc00000)  // top bin: nothing is above it
+                                    : key_to_float(max((T + 1) << kLowBits, 0x007FFFFFu));
+  }
+  DSA_STAMP(stamp_cta, 2);
+
+  // ---- the sweep: the warp's kept mask (lane i ends up with word i) and, per thread, which
+  // of its logits are candidates
+  if (have_hist || take_all) wait_slice();
+  uint32_t my_kept = 0, my_cand = 0;
+  const uint32_t* wbits = flat + warp_off;
+#pragma unroll
+  for (int i = 0; i < kClMaxKeys; ++i) {
+    if (i < nk) {
+      const float v = __uint_as_float(wbits[i * 32 + lane]);
+      const bool above = v >= f_hi;
+      const bool cand = v >= f_lo && !above && !take_all;
+      const uint32_t m = __ballot_sync(0xffffffffu, above);
+      if (lane == i) my_kept = m;
+      if (cand) my_cand |= 1u << i;
     }
+  }
+  if (lane < nk) sh.kept[warp][lane] = my_kept;
+  __syncwarp();
+  DSA_STAMP(stamp_cta, 3);
+
+  // One pass over this warp's candidates: every lane walks the set bits of its own mask, the
+  // warp stays converged (a lane that has run out takes part with live = false).
+  auto for_each_candidate = [&](auto&& fn) {
+    uint32_t rem = my_cand;
+    while (__any_sync(0xffffffffu, rem != 0u)) {
+      const bool live = rem != 0u;
+      const int i = live ? __ffs(rem) - 1 : 0;
+      rem &= rem - 1u;
+      fn(live, ordered_key(__uint_as_float(wbits[i * 32 + lane])), i);
+    }
+  };
+
+  uint32_t kstar = 0, ties_kept = 0;
+  if (!take_all) {
+    // ---- level 2: key bits 19..13 of the candidates
+    for_each_candidate([&](bool live, uint32_t key, int) {
+      hist_add_warp(sh.local2, live, (key >> kL3Bits) & (kL2Bins - 1));
+    });
+    DSA_STAMP(stamp_cta, 8);
     __syncthreads();
     if (have_hist) cluster_wait();  // (see above; without the scan's histogram it was taken at level 1)
-    push_bins<false>(sh.local2, sh.hist2, C);
-    cluster_arrive();
-    cluster_wait();
-    // every CTA has read the scan's histogram by now: re-arm it for the next scan
-    if (have_hist && c == 0)
-      reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins)[tid] = make_uint4(0, 0, 0, 0);
-    uint32_t d2, need2;
-    {
-      const uint32_t own2[1] = {sh.hist2[kRoundBins - 1 - tid]};
-      find_kth_bin<kRoundBins>(sh.hist2, own2, need, sh.warp_tot, d2, need2);
-    }
-    const uint32_t p22 = (T << 10) | d2;
-    DSA_STAMP(stamp_cta, 3);
-    // ---- level 3: the low 10 bits of the keys that share those 22 bits
+    DSA_STAMP(stamp_cta, 9);
+    if (tid < kL2Bins) {
+      const uint32_t x = sh.local2[tid];
+      if (x) {
+        const uint32_t a = smem_u32(&sh.hist2[tid]);
 #pragma unroll 1
-    for (int j = 0; j < groups; ++j) {
-      const uint4 k = my_keys[j * 32];
-      hist_add_warp(sh.local3, (k.x >> 10) == p22, k.x & (kRoundBins - 1));
-      hist_add_warp(sh.local3, (k.y >> 10) == p22, k.y & (kRoundBins - 1));
-      hist_add_warp(sh.local3, (k.z >> 10) == p22, k.z & (kRoundBins - 1));
-      hist_add_warp(sh.local3, (k.w >> 10) == p22, k.w & (kRoundBins - 1));
+        for (uint32_t cc = 0; cc < C; ++cc) cluster_red_add(cluster_map(a, cc), x);
+      }
     }
-    __syncthreads();
-    push_bins<false>(sh.local3, sh.hist3, C);
+    DSA_STAMP(stamp_cta, 10);
     cluster_arrive();
     cluster_wait();
-    uint32_t d3;
-    {
-      const uint32_t own3[1] = {sh.hist3[kRoundBins - 1 - tid]};
-      find_kth_bin<kRoundBins>(sh.hist3, own3, need2, sh.warp_tot, d3, ties_kept);
-    }
-    kstar = (p22 << 10) | d3;  // the k-th largest key of the row; ties_kept of its copies are kept
+    DSA_STAMP(stamp_cta, 11);
+    find_kth_bin<kL2Bins>(sh.hist2, need, sh.warp_tot, sh.res);
+    const uint32_t p19 = (T << kL2Bits) | sh.res[0];
+    const uint32_t need2 = sh.res[1];
     DSA_STAMP(stamp_cta, 4);
+    // ---- level 3: the low 13 bits of the candidates that share those 19 bits
+    for_each_candidate([&](bool live, uint32_t key, int) {
+      hist_push_warp(sh.hist3, live && (key >> kL3Bits) == p19, swizzled_bin<kL3Bins>(key & (kL3Bins - 1)), C);
+    });
+    DSA_STAMP(stamp_cta, 12);
+    cluster_arrive();
+    cluster_wait();
+    DSA_STAMP(stamp_cta, 13);
+    find_kth_bin<kL3Bins, true>(sh.hist3, need2, sh.warp_tot, sh.res);
+    kstar = (p19 << kL3Bits) | sh.res[0];  // the k-th largest key of the row
+    ties_kept = sh.res[1];                 // elements equal to it that are kept, lowest positions first
+    DSA_STAMP(stamp_cta, 5);
+    // ---- candidates above k* join the kept mask, those equal to it the tie mask
+    for_each_candidate([&](bool live, uint32_t key, int i) {
+      if (live && key > kstar) smem_red_or(&sh.kept[warp][i], 1u << lane);
+      else if (live && key == kstar) smem_red_or(&sh.ties[warp][i], 1u << lane);
+    });
+    __syncwarp();
   } else {
     cluster_wait();
-    if (have_hist && c == 0)
-      reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins)[tid] = make_uint4(0, 0, 0, 0);
   }
 
-  // ---- (larger, equal) counts, packed equal << 16 | larger: this warp's, then the warps and CTAs before it
-  auto count4 = [&](const uint4& k) -> uint32_t {
-    return (k.x > kstar ? 1u : 0u) + (k.y > kstar ? 1u : 0u) + (k.z > kstar ? 1u : 0u) + (k.w > kstar ? 1u : 0u) +
-           (((k.x == kstar ? 1u : 0u) + (k.y == kstar ? 1u : 0u) + (k.z == kstar ? 1u : 0u) + (k.w == kstar ? 1u : 0u)) << 16);
-  };
-  {
-    uint32_t tot = 0;
-#pragma unroll 1
-    for (int j = 0; j < groups; ++j) tot += count4(my_keys[j * 32]);
-    if (take_all) tot &= 0xFFFFu;  // key 0 marks the invisible positions, they are not ties
-    const uint32_t wsum = __reduce_add_sync(0xffffffffu, tot);  // at most 1024 of each kind per warp
-    __syncthreads();  // earlier readers of warp_tot are done
-    if (lane == 0) sh.warp_tot[warp] = wsum;
-  }
+  DSA_STAMP(stamp_cta, 14);
+  // ---- (kept, ties) counts in position order, packed ties << 16 | kept: words of a warp, warps, CTAs
+  const uint32_t gword = lane < nk ? sh.kept[warp][lane] : 0u;
+  const uint32_t qword = lane < nk ? sh.ties[warp][lane] : 0u;
+  const uint32_t cnt = uint32_t(__popc(gword)) | (uint32_t(__popc(qword)) << 16);
+  const uint32_t inc = warp_inclusive_scan(cnt);  // at most 1024 of each kind per warp
+  if (lane == 31) sh.warp_tot[warp] = inc;
   __syncthreads();
-  uint32_t before_warp, cta_sum;
-  {
-    const uint32_t w = sh.warp_tot[lane];
-    uint32_t inc = w;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += up;
-    }
-    before_warp = __shfl_sync(0xffffffffu, inc - w, warp);
-    cta_sum = __shfl_sync(0xffffffffu, inc, 31);  // at most 32768 of each kind per CTA
+  if (warp == 0) {
+    const uint32_t wt = lane < kClWarps ? sh.warp_tot[lane] : 0u;
+    const uint32_t winc = warp_inclusive_scan(wt);  // at most 16384 of each kind per CTA
+    if (lane < kClWarps) sh.warp_base[lane] = winc - wt;
+    const uint32_t cta_sum = __shfl_sync(0xffffffffu, winc, 31);
+    if (lane < int(C)) cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(lane)), cta_sum);
   }
-  if (tid < int(C)) cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(tid)), cta_sum);
   cluster_arrive();
   cluster_wait();
-  uint32_t gt_before = before_warp & 0xFFFFu, eq_before = before_warp >> 16, gt_total = 0, eq_total = 0;
-#pragma unroll 1
-  for (uint32_t cc = 0; cc < C; ++cc) {
-    const uint32_t t = sh.cta_tot[cc];
-    if (cc < c) {
-      gt_before += t & 0xFFFFu;
-      eq_before += t >> 16;
-    }
-    gt_total += t & 0xFFFFu;
-    eq_total += t >> 16;
+  uint32_t g_before, q_before, g_total, q_total;
+  {
+    const uint32_t t = lane < int(C) ? sh.cta_tot[lane] : 0u;
+    const uint32_t tg = t & 0xFFFFu, tq = t >> 16;
+    g_total = __reduce_add_sync(0xffffffffu, tg);
+    q_total = __reduce_add_sync(0xffffffffu, tq);
+    g_before = __reduce_add_sync(0xffffffffu, lane < int(c) ? tg : 0u);
+    q_before = __reduce_add_sync(0xffffffffu, lane < int(c) ? tq : 0u);
+    const uint32_t wb = sh.warp_base[warp];
+    g_before += (wb & 0xFFFFu) + ((inc - cnt) & 0xFFFFu);  // ... and the words before this lane's word
+    q_before += (wb >> 16) + ((inc - cnt) >> 16);
   }
-  DSA_STAMP(stamp_cta, 5);
+  DSA_STAMP(stamp_cta, 6);
 
-  // ---- emit: ascending positions, ties to the lower position
+  // ---- emit: lane i walks the set bits of its word i in ascending position order
   int32_t* out_idx = p.out_idx + int64_t(r) * p.topk;
   float* out_val = p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
   const int32_t* imap = p.index_map ? p.index_map + int64_t(r) * p.n : nullptr;
-  const uint32_t kNegInfKey = 0x007FFFFFu;  // ordered_key(-inf)
   const uint32_t topk_u = uint32_t(p.topk);
-#pragma unroll 1
-  for (int j = 0; j < groups; ++j) {
-    const uint4 k4 = my_keys[j * 32];
-    uint32_t cnt = count4(k4);
-    if (take_all) cnt &= 0xFFFFu;
-    if (__ballot_sync(0xffffffffu, cnt != 0u) == 0u) continue;  // nothing of this group is near the cutoff
-    uint32_t inc = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t up = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += up;
-    }
-    uint32_t g = gt_before + ((inc - cnt) & 0xFFFFu);
-    uint32_t q = eq_before + ((inc - cnt) >> 16);
-    const uint32_t ks[4] = {k4.x, k4.y, k4.z, k4.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const uint32_t k = ks[e];
-      const bool gt = k > kstar;
-      const bool eq = !take_all && k == kstar;
-      if (gt || (eq && q < ties_kept)) {
-        const uint32_t slot = g + min(q, ties_kept);
-        if (slot < topk_u) {
-          const int64_t pos = base + j * 128 + e;
-          const int32_t id = imap ? imap[pos] : int32_t(pos) + p.index_offset;
-          out_idx[slot] = (k == kNegInfKey) ? p.pad : id;
-          if (out_val) out_val[slot] = __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
-        }
-      }
-      g += gt ? 1u : 0u;
-      q += eq ? 1u : 0u;
-    }
-    const uint32_t wj = __shfl_sync(0xffffffffu, inc, 31);  // this group's total over the warp
-    gt_before += wj & 0xFFFFu;
-    eq_before += wj >> 16;
-  }
-  const uint32_t total = gt_total + min(eq_total, ties_kept);
   const float neg_inf = __int_as_float(0xff800000);
+  // a selected -inf can only appear when the row has fewer than topk finite logits
+  const bool need_value = out_val != nullptr || take_all || kstar <= 0x007FFFFFu;  // ordered_key(-inf)
+  {
+    uint32_t g = gword, q = qword, gb = g_before, qb = q_before;
+    const int word_base = slice_base + warp_off + lane * 32;
+    while (g | q) {
+      const int b = __ffs(g | q) - 1;
+      const uint32_t bit = 1u << b;
+      uint32_t slot = 0xFFFFFFFFu;
+      if (g & bit) {
+        slot = gb + min(qb, ties_kept);
+        ++gb;
+      } else {
+        if (qb < ties_kept) slot = gb + qb;
+        ++qb;
+      }
+      g &= ~bit;
+      q &= ~bit;
+      if (slot < topk_u) {
+        const int pos = word_base + b;
+        int32_t id = imap ? imap[pos] : pos + p.index_offset;
+        if (need_value) {
+          const float v = row[pos];
+          if (v == neg_inf) id = p.pad;
+          if (out_val) out_val[slot] = v;
+        }
+        out_idx[slot] = id;
+      }
+    }
+  }
+  const uint32_t total = g_total + min(q_total, ties_kept);
   for (uint32_t i = total + c * kClThreads + tid; i < topk_u; i += C * kClThreads) {
     out_idx[i] = p.pad;
     if (out_val) out_val[i] = neg_inf;
   }
-  DSA_STAMP(stamp_cta, 6);
+  // every CTA has read the scan's histogram long ago (before the first cluster barrier it
+  // passed): re-arm it for the next scan, away from the barriers
+  if (have_hist && c == 0) {
+    uint4* gh = reinterpret_cast<uint4*>(p.hist + size_t(r) * kBins);
+    gh[tid] = make_uint4(0, 0, 0, 0);
+    gh[tid + kClThreads] = make_uint4(0, 0, 0, 0);
+  }
+  DSA_STAMP(stamp_cta, 7);
   DSA_KTIME_END(1);
 }
 

@@ -38,7 +38,13 @@ def _bits(t: torch.Tensor) -> np.ndarray:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference repository")
+    ap.add_argument("--only", default="", help="comma-separated fixture names to (re)generate; default: all")
     args = ap.parse_args()
+    only = {x for x in args.only.split(",") if x}
+
+    def want(name: str) -> bool:
+        return not only or name in only
+
     ref = Path(args.reference)
     sys.path.insert(0, str(ref / "src"))
     sys.path.insert(0, str(ref / "kernels"))
@@ -56,8 +62,9 @@ def main() -> None:
     torch.manual_seed(0)
     x = torch.randn(37, 128) * torch.logspace(-3, 2, 37).unsqueeze(1)
     xq, xs = K.quantize_e4m3_rowwise(x)
-    np.savez_compressed(HERE / "fp8_formats.npz", e4m3_table=table.numpy(), x=x.numpy(),
-                        xq=_bits(xq), xs=xs.numpy())
+    if want("fp8_formats"):
+        np.savez_compressed(HERE / "fp8_formats.npz", e4m3_table=table.numpy(), x=x.numpy(),
+                            xq=_bits(xq), xs=xs.numpy())
 
     # ---- indexer logits on e4m3 operands (ref_indexer_logits_fp8)
     torch.manual_seed(0)
@@ -69,9 +76,10 @@ def main() -> None:
     ik8, sk = K.quantize_e4m3_rowwise(ik)
     wp = (sq * w).contiguous()
     logits = K.ref_indexer_logits_fp8(iq8, ik8, wp, sk)
-    np.savez_compressed(HERE / "indexer_fp8.npz", iq=iq.numpy(), ik=ik.numpy(), w=w.numpy(),
-                        iq8=_bits(iq8), ik8=_bits(ik8), wp=wp.numpy(), sk=sk.numpy(),
-                        logits=logits.numpy())
+    if want("indexer_fp8"):
+        np.savez_compressed(HERE / "indexer_fp8.npz", iq=iq.numpy(), ik=ik.numpy(), w=w.numpy(),
+                            iq8=_bits(iq8), ik8=_bits(ik8), wp=wp.numpy(), sk=sk.numpy(),
+                            logits=logits.numpy())
 
     # ---- sparse MLA decode (ref_sparse_mla) with the reference's causal random indices
     torch.manual_seed(0)
@@ -81,8 +89,9 @@ def main() -> None:
     indices = K.make_indices(S, N, topk, dev)
     sm_scale = 576 ** -0.5
     out = K.ref_sparse_mla(q, kv, indices, sm_scale, dev)
-    np.savez_compressed(HERE / "sparse_mla.npz", q=_bits(q), kv=_bits(kv), indices=indices.numpy(),
-                        sm_scale=np.float64(sm_scale), out=out.numpy())
+    if want("sparse_mla"):
+        np.savez_compressed(HERE / "sparse_mla.npz", q=_bits(q), kv=_bits(kv), indices=indices.numpy(),
+                            sm_scale=np.float64(sm_scale), out=out.numpy())
 
     # ---- fp32 core ops of the pure-PyTorch layer (attention_core.py)
     torch.manual_seed(0)
@@ -98,14 +107,15 @@ def main() -> None:
     mkv = torch.randn(b, s, vdim + rope)
     m_sparse = AC.sparse_mla_core(mq, mkv, c_idx, value_dim=vdim)
     m_dense = AC.dense_mla_core(mq, mkv, value_dim=vdim)
-    np.savez_compressed(HERE / "attention_core_f32.npz", q=cq.numpy(), k=ck.numpy(), w=cw.numpy(),
-                        logits=c_logits.numpy(), masked=c_masked.numpy(), idx=c_idx.numpy(),
-                        mq=mq.numpy(), mkv=mkv.numpy(), sparse=m_sparse.numpy(), dense=m_dense.numpy())
+    if want("attention_core_f32"):
+        np.savez_compressed(HERE / "attention_core_f32.npz", q=cq.numpy(), k=ck.numpy(), w=cw.numpy(),
+                            logits=c_logits.numpy(), masked=c_masked.numpy(), idx=c_idx.numpy(),
+                            mq=mq.numpy(), mkv=mkv.numpy(), sparse=m_sparse.numpy(), dense=m_dense.numpy())
 
     # ---- the three schedules on the SMALL preset (weights are re-created from the seed)
     cfg = L.SMALL_CONFIG
     rec = {}
-    for seed in (0, 7):
+    for seed in ((0, 7) if want("model_small") else ()):
         torch.manual_seed(seed)
         model = L.DSAModel(cfg).eval()
         torch.manual_seed(1000 + seed)
@@ -122,7 +132,8 @@ def main() -> None:
                         rec[f"used_{key}_{li}"] = u.numpy().astype(np.int32)
                     if p is not None:
                         rec[f"produced_{key}_{li}"] = p.numpy().astype(np.int32)
-    np.savez_compressed(HERE / "model_small.npz", **rec)
+    if want("model_small"):
+        np.savez_compressed(HERE / "model_small.npz", **rec)
 
     # ---- serving-form indexer staging (Indexer.stage_fp8_operands after its projections,
     # inference/modeling/transformer.py:1044-1066): the reference's own LayerNorm,
@@ -154,7 +165,8 @@ def main() -> None:
             k_rot.append(T.rotate_activation(k))
         rec[f"q_rot_{int(inter)}"] = _bits(torch.cat(q_rot).squeeze(1))
         rec[f"k_rot_{int(inter)}"] = _bits(torch.cat(k_rot).squeeze(1))
-    np.savez_compressed(HERE / "indexer_stage.npz", **rec)
+    if want("indexer_stage"):
+        np.savez_compressed(HERE / "indexer_stage.npz", **rec)
 
     # ---- serving-form latent append (MLA decode branch, transformer.py:3264-3267): the
     # reference's RMSNorm and apply_rotary_emb (interleaved, its default for MLA)
@@ -168,9 +180,68 @@ def main() -> None:
     kv_n = rn(kv_a[..., :512])
     pe = torch.cat([T.apply_rotary_emb(kv_a[b:b + 1, :, 512:].unsqueeze(2), torch.complex(cos[b:b + 1], sin[b:b + 1]))
                     .squeeze(2) for b in range(B)])
-    np.savez_compressed(HERE / "latent_append.npz", kv_a=_bits(kv_a.squeeze(1)), cos=cos.numpy(), sin=sin.numpy(),
-                        norm_w=rn.weight.data.numpy(), eps=np.float32(rn.eps), kv_norm=_bits(kv_n.squeeze(1)),
-                        k_pe=_bits(pe.squeeze(1)))
+    if want("latent_append"):
+        np.savez_compressed(HERE / "latent_append.npz", kv_a=_bits(kv_a.squeeze(1)), cos=cos.numpy(), sin=sin.numpy(),
+                            norm_w=rn.weight.data.numpy(), eps=np.float32(rn.eps), kv_norm=_bits(kv_n.squeeze(1)),
+                            k_pe=_bits(pe.squeeze(1)))
+
+    # ---- single-layer decode at the reference's own CPU-runnable size (fp32, seed 0): context
+    # 4096, 64 indexer heads x 128, top-2048, 16 MLA heads x 576, softmax scale 1/sqrt(192).
+    # Decode form of the pure-PyTorch layer: indexer_logits -> select_topk (one query at the
+    # last position: every key is causal) -> _selection_mask + _attend. The inputs are
+    # re-created from the seed by the test (their sums are stored to catch a generator change);
+    # the keys are rescaled by `key_scale` so that no logit lies near the rank-2048 cutoff.
+    if want("config1_decode"):
+        sys.path.insert(0, str(HERE.parent.parent))
+        from oracle import dsa_oracle as O  # margin enforcement only
+
+        torch.manual_seed(0)
+        n1, topk1 = 4096, 2048
+        iq1 = torch.randn(1, 1, 64, 128)
+        ik1 = torch.randn(1, n1, 128)
+        w1 = torch.randn(1, 1, 64) / 8
+        q1 = torch.randn(1, 1, 16, 576)
+        kv1 = torch.randn(1, n1, 576)
+        lg = AC.indexer_logits(iq1, ik1, w1)
+        key_scale, _ = O.enforce_topk_margin(lg[0, 0], torch.ones(n1), topk1)
+        ik1s = ik1 * key_scale.view(1, n1, 1)
+        lg = AC.indexer_logits(iq1, ik1s, w1)
+        idx1 = AC.select_topk(lg, topk1)
+        mask1 = AC._selection_mask(idx1, n1)
+        out1 = AC._attend(q1, kv1, mask1, 192 ** -0.5, 512)
+        np.savez_compressed(HERE / "config1_decode.npz", key_scale=key_scale.numpy(), logits=lg[0, 0].numpy(),
+                            idx=np.sort(idx1[0, 0].numpy()).astype(np.int32), out=out1[0, 0].numpy(),
+                            sums=np.array([iq1.double().sum(), ik1.double().sum(), w1.double().sum(),
+                                           q1.double().sum(), kv1.double().sum()]))
+
+    # ---- two layers of the full-size stack (hidden 7168, 128 heads, q_lora 1536, kv_lora 512,
+    # rope 64, v 128, indexer 64 x 128, MLP 18432) under the lagged schedule, fp32 on the CPU,
+    # 168 tokens, top-64 so that the selection is exercised at this short context. The weights
+    # are the seed's nn.Linear initialisation rounded to bf16 values, which is what the bf16
+    # decode path under test holds. Stored: the final hidden states of the last 8 positions and
+    # every index set those positions used / produced.
+    if want("model_full_dims"):
+        cfg3 = L.DSAConfig(num_hidden_layers=2, first_k_dense_replace=0, index_topk=64)
+        torch.manual_seed(3)
+        model3 = L.DSAModel(cfg3).eval()
+        with torch.no_grad():
+            for prm in model3.parameters():
+                prm.copy_(prm.to(torch.bfloat16).float())
+        torch.manual_seed(3003)
+        S3, tail = 168, 8
+        x3 = torch.randn(1, S3, cfg3.hidden_size).to(torch.bfloat16).float()
+        rec3 = {"x_sum": np.float64(x3.double().sum()), "S": np.int64(S3), "tail": np.int64(tail),
+                "w_sum": np.float64(sum(float(prm.double().sum()) for prm in model3.parameters()))}
+        with torch.no_grad():
+            tr3 = model3(x3, L.ScheduleMode.LAGGED_FUSED, cold_start=L.ColdStartPolicy.EAGER, record=True)
+        rec3["hidden_tail"] = tr3.final_hidden[0, S3 - tail:].numpy()
+        for li, (u, pr) in enumerate(zip(tr3.indices_used, tr3.indices_produced)):
+            if u is not None:
+                rec3[f"used_{li}"] = u[0, S3 - tail:].numpy().astype(np.int32)
+            if pr is not None:
+                rec3[f"produced_{li}"] = pr[0, S3 - tail:].numpy().astype(np.int32)
+        np.savez_compressed(HERE / "model_full_dims.npz", **rec3)
+        del model3
 
     for f in sorted(HERE.glob("*.npz")):
         print(f.name, f.stat().st_size, "bytes")

@@ -215,7 +215,7 @@ def production_config(D, layers=3):
 
 
 def test_production_geometry_fp8_bf16_path(D):
-    """FP8 scan + bf16 split-K attention behind the same model API: decode
+    """FP8 scan + bf16 split-K attention behind the same model API at reduced width: decode
     follows the fp32 kernels within bf16 tolerance and picks nearly the same keys."""
     cfg = production_config(D)
     torch.manual_seed(11)
@@ -245,6 +245,53 @@ def test_production_geometry_fp8_bf16_path(D):
                     sa, sb = set(ia[r].tolist()) - {-1}, set(ib[r].tolist()) - {-1}
                     overlaps.append(len(sa & sb) / max(1, len(sa | sb)))
     assert min(overlaps) > 0.6 and sum(overlaps) / len(overlaps) > 0.8
+
+
+def test_full_dimensions_decode_against_the_reference_model(D):
+    """Two layers with the full-size dimensions (hidden 7168, 128 MLA heads, q_lora 1536,
+    kv_lora 512, indexer 64 x 128, MLP 18432) under the lagged schedule: the bf16 / FP8 decode
+    path (cuBLAS projections, dsa_decode_prep, FP8 scan, top-k, split-K attention) against what
+    the reference's own fp32 DSAModel computed on the CPU from the same seed, with the same
+    bf16-rounded weights (tests/golden/model_full_dims.npz). 160 tokens are prefilled, the last
+    8 are decoded one by one. Tolerances: final hidden state within 6e-2 (bf16 activations against
+    fp32), selected sets overlapping by more than 0.8 on average (the cutoff of a 64-of-160
+    selection moves with bf16 / e4m3 rounding of the indexer operands)."""
+    g = load_golden("model_full_dims.npz")
+    cfg = D.DSAConfig(num_hidden_layers=2, first_k_dense_replace=0, index_topk=64)
+    torch.manual_seed(3)
+    model = D.DSAModel(cfg).eval()  # on the CPU, in the reference's construction order: the same weights
+    with torch.no_grad():
+        for prm in model.parameters():
+            prm.copy_(prm.to(torch.bfloat16).float())
+    w_sum = sum(float(prm.double().sum()) for prm in model.parameters())
+    assert w_sum == pytest.approx(float(g["w_sum"]), rel=1e-9), "seeded weights differ from the fixture's"
+    model = model.to(torch.bfloat16).cuda()
+    S, tail = int(g["S"]), int(g["tail"])
+    torch.manual_seed(3003)
+    x = torch.randn(1, S, cfg.hidden_size).to(torch.bfloat16)
+    assert float(x.float().double().sum()) == pytest.approx(float(g["x_sum"]), rel=1e-9)
+    mode, cold = D.ScheduleMode.LAGGED_FUSED, D.ColdStartPolicy.EAGER
+    st = model.init_decode(1, S + 8)
+    assert st.fp8
+    model.prefill(st, x[:, :S - tail].cuda(), mode, cold)
+    ref_h = torch.from_numpy(g["hidden_tail"])
+    overlaps, errs = [], []
+    for t in range(tail):
+        rec = {}
+        h = model.decode_step(st, x[:, S - tail + t].cuda(), mode, cold, record=rec)
+        errs.append(rel_err(h.float().cpu()[0], ref_h[t]))
+        for kind in ("used", "produced"):
+            for li, ours in enumerate(rec[kind]):
+                name = f"{kind}_{li}"
+                assert (ours is None) == (name not in g.files), name
+                if ours is not None:
+                    sa = set(int(v) for v in ours[0].tolist() if v >= 0)
+                    sb = set(int(v) for v in g[name][t].tolist() if 0 <= v < S)
+                    overlaps.append(len(sa & sb) / max(1, len(sa | sb)))
+    assert max(errs) < 6e-2, errs
+    assert min(overlaps) > 0.6 and sum(overlaps) / len(overlaps) > 0.8, overlaps
+    del model
+    torch.cuda.empty_cache()
 
 
 def test_fused_decode_prep_matches_the_unfused_chain(D):

@@ -4,6 +4,7 @@
 from __future__ import annotations
 
 import numpy as np
+import pytest
 import torch
 
 from conftest import bf16_from_bits, load_golden
@@ -228,3 +229,26 @@ def test_latent_append_matches_reference_and_packing():
     p2 = O.latent_append_rows(*args, "fp8", True)
     sc = p2[:, 512:528].contiguous().view(torch.float32)
     assert torch.equal(torch.log2(sc).round(), torch.log2(sc))
+
+
+def test_oracle_at_the_cpu_runnable_configuration():
+    """The oracle's fp32 decode path at the reference's own CPU-runnable size (context 4096,
+    64 x 128 indexer, top-2048, 16 heads x 576, scale 1/sqrt(192)) against what the reference's
+    indexer_logits / select_topk / _attend produced from the same seeded inputs."""
+    g = load_golden("config1_decode.npz")
+    torch.manual_seed(0)
+    n = 4096
+    iq = torch.randn(1, 1, 64, 128)
+    ik = torch.randn(1, n, 128)
+    w = torch.randn(1, 1, 64) / 8
+    q = torch.randn(1, 1, 16, 576)
+    kv = torch.randn(1, n, 576)
+    sums = [float(t.double().sum()) for t in (iq, ik, w, q, kv)]
+    assert sums == pytest.approx(g["sums"].tolist(), rel=1e-12)
+    ik = ik * torch.from_numpy(g["key_scale"]).view(1, -1, 1)
+    logits = O.indexer_logits_f32(iq, ik, w)[0]
+    assert torch.allclose(logits[0], torch.from_numpy(g["logits"]), rtol=1e-5, atol=1e-5)
+    idx = O.select_topk(logits, 2048, pad_value=-1)
+    assert torch.equal(idx[0].int(), torch.from_numpy(g["idx"]))
+    out = O.sparse_mla_decode(q[0], kv[0], idx, [n], 192 ** -0.5)
+    assert torch.allclose(out[0], torch.from_numpy(g["out"]), rtol=1e-4, atol=1e-5)
