@@ -35,6 +35,11 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_indexer_scan_f32": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _l, _l, _l, _p]),
     "dsa_topk_workspace_bytes": (_l, [_i, _l]),
     "dsa_topk_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _l, _i, _l, _l, _i, C.c_int32, C.c_int32, _p]),
+    "dsa_topk_select_push": (_i, [_p, _p, _p, _i, _l, _l, _i, C.c_int32, C.c_int32, _i, _i, _p, _p, _p, _p, _p]),
+    "dsa_topk_merge_wait": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, C.c_int32, _l, _p]),
+    "dsa_ipc_export": (_i, [_p, _p, _p]),
+    "dsa_ipc_open": (_i, [_p, _l, _p]),
+    "dsa_ipc_close": (_i, [_p, _l]),
     "dsa_topk_select_static": (_i, [_p, _p, _p, _p, _i, _l, _l, _i, C.c_int32, C.c_int32, _p]),
     "dsa_sparse_mla_partials": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _l, _i, _p]),
     "dsa_sparse_mla_combine": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
@@ -54,7 +59,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_quantize_e4m3_rowwise": (_i, [_p, _p, _p, _l, _i, _f, _p]),
 }
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 class DsaError(RuntimeError):

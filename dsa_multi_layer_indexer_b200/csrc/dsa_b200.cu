@@ -481,6 +481,110 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
   return DSA_OK;
 }
 
+// ------------------------------------------------------------------ candidate exchange between GPUs
+static int exchange_common(int R, int64_t n, int topk_k, int world) {
+  DSA_REQUIRE(R > 0 && R <= 65535, "candidate exchange: R=%d out of range", R);
+  DSA_REQUIRE(world >= 1 && world <= topk::kMaxRanks, "candidate exchange: world=%d out of range [1, %d]", world,
+              topk::kMaxRanks);
+  DSA_REQUIRE(topk_k > 0 && topk_k <= 65536, "candidate exchange: k=%d out of range [1, 65536]", topk_k);
+  if (n <= 0 || n > topk::kClMaxN)
+    return fail(DSA_ERR_UNSUPPORTED, "candidate exchange: rows of %lld logits (the limit is %lld)", (long long)n,
+                (long long)topk::kClMaxN);
+  return DSA_OK;
+}
+
+int dsa_topk_select_push(const float* logits, const int32_t* seq_lens, uint32_t* hist, int R, int64_t n,
+                         int64_t slab_stride, int topk_k, int32_t pad_value, int32_t index_offset, int world,
+                         int rank, void* const* gather_idx, void* const* gather_val, void* const* flags,
+                         uint32_t* sent, void* stream) {
+  int rc = exchange_common(R, n, topk_k, world);
+  if (rc) return rc;
+  DSA_REQUIRE(logits && gather_idx && gather_val && flags && sent, "topk push: null pointer");
+  DSA_REQUIRE(aligned16(logits) && slab_stride >= n, "topk push: logits must be 16-byte aligned, slab_stride >= n");
+  DSA_REQUIRE(rank >= 0 && rank < world, "topk push: rank=%d outside [0, %d)", rank, world);
+  topk::Params p{};
+  p.logits = logits;
+  p.seq_lens = seq_lens;
+  p.hist = hist;
+  p.n = n;
+  p.slab_stride = slab_stride;
+  p.topk = topk_k;
+  p.pad = pad_value;
+  p.index_offset = index_offset;
+  p.n_dest = world;
+  p.src_rank = rank;
+  for (int d = 0; d < world; ++d) {
+    DSA_REQUIRE(gather_idx[d] && gather_val[d] && flags[d], "topk push: null pointer for rank %d", d);
+    p.dest_idx[d] = static_cast<int32_t*>(gather_idx[d]);
+    p.dest_val[d] = static_cast<float*>(gather_val[d]);
+    p.dest_flag[d] = static_cast<uint32_t*>(flags[d]) + size_t(rank) * R;
+  }
+  p.sent = sent;
+  return launch_topk_cluster(p, R, n, static_cast<cudaStream_t>(stream));
+}
+
+int dsa_topk_merge_wait(const int32_t* gather_idx, const float* gather_val, const uint32_t* flags, uint32_t* seen,
+                        int32_t* out_idx, int R, int world, int topk_k, int32_t pad_value, int64_t wait_limit_ns,
+                        void* stream) {
+  const int64_t n = int64_t(world) * topk_k;
+  int rc = exchange_common(R, n, topk_k, world);
+  if (rc) return rc;
+  DSA_REQUIRE(gather_idx && gather_val && flags && seen && out_idx, "topk merge: null pointer");
+  DSA_REQUIRE(wait_limit_ns > 0, "topk merge: the wait needs a limit");
+  topk::Params p{};
+  p.logits = gather_val;  // [2][R][world][topk]: the kernel picks the parity of each row's step
+  p.index_map = gather_idx;
+  p.out_idx = out_idx;
+  p.n = n;
+  p.slab_stride = n;
+  p.topk = topk_k;
+  p.pad = pad_value;
+  p.n_src = world;
+  p.wait_flags = flags;
+  p.seen = seen;
+  p.wait_limit_ns = static_cast<unsigned long long>(wait_limit_ns);
+  return launch_topk_cluster(p, R, n, static_cast<cudaStream_t>(stream));
+}
+
+// Peer mapping of an exchange buffer (one process per GPU): the owner exports the CUDA IPC handle
+// of the allocation that contains `ptr`, every other process opens it and gets an address it can
+// store through. Set-up calls, not on any step's path.
+typedef CUresult (*GetAddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+int dsa_ipc_export(const void* ptr, void* handle_out, int64_t* offset_out) {
+  DSA_REQUIRE(ptr && handle_out && offset_out, "ipc export: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == DSA_IPC_HANDLE_BYTES, "handle size");
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  DSA_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &qres));
+  if (!sym || qres != cudaDriverEntryPointSuccess) return fail(DSA_ERR_CUDA, "ipc export: cuMemGetAddressRange unavailable");
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  CUresult res = reinterpret_cast<GetAddressRangeFn>(sym)(&base, &size, reinterpret_cast<CUdeviceptr>(ptr));
+  if (res != CUDA_SUCCESS) return fail(DSA_ERR_CUDA, "ipc export: cuMemGetAddressRange failed with CUresult %d", int(res));
+  cudaIpcMemHandle_t h;
+  DSA_CUDA(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(handle_out, &h, sizeof(h));
+  *offset_out = int64_t(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return DSA_OK;
+}
+
+int dsa_ipc_open(const void* handle, int64_t offset, void** ptr_out) {
+  DSA_REQUIRE(handle && ptr_out && offset >= 0, "ipc open: bad argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* base = nullptr;
+  DSA_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr_out = static_cast<char*>(base) + offset;
+  return DSA_OK;
+}
+
+int dsa_ipc_close(void* ptr, int64_t offset) {
+  DSA_REQUIRE(ptr && offset >= 0, "ipc close: bad argument");
+  DSA_CUDA(cudaIpcCloseMemHandle(static_cast<char*>(ptr) - offset));
+  return DSA_OK;
+}
+
 // ------------------------------------------------------------------ top-k without caller scratch
 }  // extern "C"
 

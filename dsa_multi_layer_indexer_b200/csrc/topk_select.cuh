@@ -43,6 +43,7 @@ constexpr int kFinWarps = kFinThreads / 32;
 constexpr int kCandCap = 8192;                  // candidates held in shared memory (more: re-read from L2)
 constexpr int kTinyCap = 1024;                  // candidates sharing the threshold's top 22 key bits
 constexpr int64_t kMaxN = 1 << 20;              // the selection mask of one row lives in shared memory
+constexpr int kMaxRanks = 8;                    // GPUs of one candidate exchange
 
 struct Params {
   const float* logits;
@@ -63,6 +64,22 @@ struct Params {
   int topk;
   int32_t pad;
   int32_t index_offset;
+  // ---- candidate exchange between the GPUs of a sequence-sharded indexer (cluster kernel only)
+  // Push side (n_dest > 0): the selection of row r goes, as (index, logit), into slot `src_rank`
+  // of every rank's gather buffers [2 parities][R][n_dest][topk], then flag word
+  // dest_flag[d][r] of every rank d gets this row's step number.
+  int n_dest;
+  int src_rank;
+  int32_t* dest_idx[kMaxRanks];
+  float* dest_val[kMaxRanks];
+  uint32_t* dest_flag[kMaxRanks];  // this rank's [R] flag words inside rank d's flag array
+  uint32_t* sent;                  // [R] steps pushed so far (local)
+  // Merge side (n_src > 0): logits / index_map are this rank's gather buffers; the kernel first
+  // waits, bounded, until wait_flags[s * R + r] of every source s reaches this row's next step.
+  int n_src;
+  const uint32_t* wait_flags;      // [n_src][R], written by the sources
+  uint32_t* seen;                  // [R] steps merged so far (local)
+  unsigned long long wait_limit_ns;
 };
 
 // Workspace layout in 32-bit words: [R][words] mask | [R][slots] counts |
@@ -684,11 +701,33 @@ topk_cluster_kernel(const Params p, const int nk) {
   }
   pdl_wait();
   pdl_launch_dependents();
-  const float* row = p.logits + int64_t(r) * p.slab_stride;
+  const int R = int(gridDim.y);
+  // Candidate exchange: this row's step number picks one of the two gather buffers, so that a
+  // rank already pushing step e + 1 does not overwrite what a slower rank still merges for step e.
+  const uint32_t step = p.n_dest > 0 ? p.sent[r] + 1u : (p.n_src > 0 ? p.seen[r] + 1u : 0u);
+  const int64_t gather_row = int64_t(step & 1u) * R + r;  // (= r outside an exchange)
+  const float* row = p.logits + (p.n_src > 0 ? gather_row : int64_t(r)) * p.slab_stride;
   int64_t len64 = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len64 = len64 < 0 ? 0 : (len64 > p.n ? p.n : len64);
   const int len = int(len64);
   const bool take_all = len <= p.topk;
+  if (p.n_src > 0) {
+    // Merge side: the candidates of every source must have landed. One thread polls the flags the
+    // sources set behind their data; the wait is bounded by wall time, and when it runs out the
+    // kernel says so in the status word and goes on with whatever is there (the host raises).
+    if (tid == 0) {
+      const unsigned long long t0 = wall_ns();
+      bool ok = false;
+      for (uint32_t spin = 0; !ok; ++spin) {
+        ok = true;
+        for (int src = 0; src < p.n_src; ++src)
+          ok = ok && int32_t(ld_acquire_sys(p.wait_flags + size_t(src) * R + r) - step) >= 0;
+        if (!ok && (spin & 63u) == 63u && wall_ns() - t0 > p.wait_limit_ns) break;
+      }
+      if (!ok) atomicOr(&g_device_status, kStatusExchangeTimeout);
+    }
+    __syncthreads();
+  }
 
   // ---- loads. The CTA's slice (positions slice_base .. + span) comes into shared memory as it
   // lies in global memory, by one bulk copy when the row is 16-byte aligned. Thread (warp, lane)
@@ -700,7 +739,8 @@ topk_cluster_kernel(const Params p, const int nk) {
   uint32_t* flat = &sh.bits[0][0];
   const int avail = max(0, min(int(p.n), slice_base + span) - slice_base);  // of the slice, inside the buffer
   const int live = max(0, min(len - slice_base, span));                     // of the slice, visible
-  const bool bulk = live > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+  // (candidates another GPU wrote are read with plain loads, not by the copy engine)
+  const bool bulk = live > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.n_src == 0;
   const int bulk_elems = bulk ? (avail & ~3) : 0;
   const uint32_t bar = smem_u32(&sh.load_bar);
   if (tid == 0 && bulk_elems > 0) {
@@ -901,13 +941,15 @@ topk_cluster_kernel(const Params p, const int nk) {
   DSA_STAMP(stamp_cta, 6);
 
   // ---- emit: lane i walks the set bits of its word i in ascending position order
-  int32_t* out_idx = p.out_idx + int64_t(r) * p.topk;
+  int32_t* out_idx = p.out_idx ? p.out_idx + int64_t(r) * p.topk : nullptr;
   float* out_val = p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
-  const int32_t* imap = p.index_map ? p.index_map + int64_t(r) * p.n : nullptr;
+  const int32_t* imap = p.index_map ? p.index_map + (p.n_src > 0 ? gather_row : int64_t(r)) * p.n : nullptr;
   const uint32_t topk_u = uint32_t(p.topk);
   const float neg_inf = __int_as_float(0xff800000);
+  const int n_dest = p.n_dest;
+  const int64_t dest_off = (gather_row * n_dest + p.src_rank) * int64_t(p.topk);  // this rank's slot of row r
   // a selected -inf can only appear when the row has fewer than topk finite logits
-  const bool need_value = out_val != nullptr || take_all || kstar <= 0x007FFFFFu;  // ordered_key(-inf)
+  const bool need_value = out_val != nullptr || n_dest > 0 || take_all || kstar <= 0x007FFFFFu;  // ordered_key(-inf)
   {
     uint32_t g = gword, q = qword, gb = g_before, qb = q_before;
     const int word_base = slice_base + warp_off + lane * 32;
@@ -927,20 +969,41 @@ topk_cluster_kernel(const Params p, const int nk) {
       if (slot < topk_u) {
         const int pos = word_base + b;
         int32_t id = imap ? imap[pos] : pos + p.index_offset;
+        float v = 0.f;
         if (need_value) {
-          const float v = row[pos];
+          v = row[pos];
           if (v == neg_inf) id = p.pad;
           if (out_val) out_val[slot] = v;
         }
-        out_idx[slot] = id;
+        if (out_idx) out_idx[slot] = id;
+        for (int d = 0; d < n_dest; ++d) {  // plain stores into every rank's gather buffers (peer memory)
+          p.dest_idx[d][dest_off + slot] = id;
+          p.dest_val[d][dest_off + slot] = v;
+        }
       }
     }
   }
   const uint32_t total = g_total + min(q_total, ties_kept);
   for (uint32_t i = total + c * kClThreads + tid; i < topk_u; i += C * kClThreads) {
-    out_idx[i] = p.pad;
+    if (out_idx) out_idx[i] = p.pad;
     if (out_val) out_val[i] = neg_inf;
+    for (int d = 0; d < n_dest; ++d) {
+      p.dest_idx[d][dest_off + i] = p.pad;
+      p.dest_val[d][dest_off + i] = neg_inf;
+    }
   }
+  if (n_dest > 0) {
+    // Every thread's stores are ordered before the barrier at system scope; behind the barrier one
+    // thread posts the row's step number to every rank (release): whoever reads it sees the data.
+    __threadfence_system();
+    cluster_arrive();
+    cluster_wait();
+    if (c == 0 && tid == 0) {
+      for (int d = 0; d < n_dest; ++d) st_release_sys(p.dest_flag[d] + r, step);
+      p.sent[r] = step;
+    }
+  }
+  if (p.n_src > 0 && c == 0 && tid == 0) p.seen[r] = step;
   // every CTA has read the scan's histogram long ago (before the first cluster barrier it
   // passed): re-arm it for the next scan, away from the barriers
   if (have_hist && c == 0) {

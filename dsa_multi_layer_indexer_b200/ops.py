@@ -624,3 +624,122 @@ def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, ml
         _ptr(mla_cos), _ptr(mla_sin), _ptr(idx_cos), _ptr(idx_sin), _ptr(positions), _ptr(index_q), _ptr(index_w),
         _ptr(q_full), _ptr(cache_index_k), _ptr(cache_k_scale), _ptr(cache_kv), B, H, n_idx, cap,
         1 if interleave else 0, float(eps), _stream()))
+
+
+# --------------------------------------------------------------------------- candidate exchange between GPUs
+class CandidateExchange:
+    """One rank's side of the candidate exchange of a KV-sequence-sharded indexer
+    (``dsa_topk_select_push`` / ``dsa_topk_merge_wait``).
+
+    Holds this rank's gather buffers ``[2, rows, world, topk]`` (index and logit), the flag
+    words the other ranks post to, and the two step counters, all in ONE zeroed allocation,
+    plus the addresses under which this process reaches every other rank's copy. Those come
+    from CUDA IPC (``connect``: one process per GPU, handles exchanged over the process group)
+    or, for ranks emulated on one GPU, are simply the other objects' own pointers
+    (``local_group``). After set-up a step is two launches and touches no host state."""
+
+    def __init__(self, rows: int, topk: int, world: int, rank: int, device, wait_limit_s: float = 2.0) -> None:
+        import ctypes as C
+
+        _need(1 <= world <= 8 and 0 <= rank < world, "world must be 1..8 and rank inside it")
+        self.rows, self.topk, self.world, self.rank = rows, topk, world, rank
+        self.wait_limit_ns = int(wait_limit_s * 1e9)
+        n_gather = 2 * rows * world * topk
+        self._off_val = n_gather * 4
+        self._off_flags = 2 * n_gather * 4
+        self._off_sent = self._off_flags + world * rows * 4
+        self._off_seen = self._off_sent + rows * 4
+        total = self._off_seen + rows * 4
+        self.arena = torch.zeros((total + 255) // 256 * 256, dtype=torch.uint8, device=device)
+        a = self.arena
+        self.gather_idx = a[:self._off_val].view(torch.int32).view(2, rows, world, topk)
+        self.gather_val = a[self._off_val:self._off_flags].view(torch.float32).view(2, rows, world, topk)
+        self.flags = a[self._off_flags:self._off_sent].view(torch.int32).view(world, rows)
+        self.sent = a[self._off_sent:self._off_seen].view(torch.int32)
+        self.seen = a[self._off_seen:self._off_seen + rows * 4].view(torch.int32)
+        self._bases = [None] * world       # every rank's arena as this process addresses it
+        self._bases[rank] = a.data_ptr()
+        self._opened = []                  # (mapped pointer, offset) of the peers' allocations
+        self._ptr_arrays = None
+        self._C = C
+
+    # -- set-up ------------------------------------------------------------------
+    def _finish(self) -> None:
+        C = self._C
+        _need(all(b is not None for b in self._bases), "not every rank's buffer is mapped")
+        mk = lambda off: (C.c_void_p * self.world)(*[b + off for b in self._bases])
+        self._ptr_arrays = (mk(0), mk(self._off_val), mk(self._off_flags))
+
+    def connect(self, group=None) -> "CandidateExchange":
+        """One process per GPU: exchanges CUDA IPC handles of the arenas over ``group`` and maps
+        the peers' arenas. Collective: every rank of the group calls it."""
+        import torch.distributed as dist
+
+        C = self._C
+        if self.world == 1:
+            self._finish()
+            return self
+        handle = (C.c_ubyte * 64)()
+        offset = C.c_int64(0)
+        _lib.check(_lib.lib().dsa_ipc_export(self.arena.data_ptr(), handle, C.byref(offset)))
+        mine = (bytes(handle), int(offset.value))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        for r, (h, off) in enumerate(everyone):
+            if r == self.rank:
+                continue
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            out = C.c_void_p(0)
+            _lib.check(_lib.lib().dsa_ipc_open(buf, off, C.byref(out)))
+            self._bases[r] = int(out.value)
+            self._opened.append((int(out.value), off))
+        self._finish()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # nobody pushes before every arena is zeroed and mapped
+        return self
+
+    @classmethod
+    def local_group(cls, rows: int, topk: int, world: int, device, wait_limit_s: float = 2.0):
+        """``world`` ranks emulated on ONE GPU (tests, single-GPU checks): every "peer" buffer is
+        an ordinary local allocation. The ranks' launches must then be enqueued one after the
+        other on one stream, every push before the first merge."""
+        xs = [cls(rows, topk, world, r, device, wait_limit_s) for r in range(world)]
+        for x in xs:
+            x._bases = [y.arena.data_ptr() for y in xs]
+            x._finish()
+        return xs
+
+    def close(self) -> None:
+        for ptr, off in self._opened:
+            _lib.lib().dsa_ipc_close(ptr, off)
+        self._opened = []
+
+    # -- the two launches of a step ------------------------------------------------
+    def push(self, logits: torch.Tensor, seq_lens: Optional[torch.Tensor] = None, *,
+             hist: Optional[torch.Tensor] = None, index_offset: int = 0, pad_value: int = -1) -> None:
+        """Local top-k of ``logits[rows, n]`` whose (position + index_offset, logit) pairs are
+        stored into every rank's gather buffers, then the step is posted to every rank."""
+        _need(self._ptr_arrays is not None, "call connect() (or build the ranks with local_group) first")
+        _need(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1,
+              "logits must be CUDA fp32 [rows, n] with dense rows")
+        R, n = logits.shape
+        _need(R == self.rows, f"logits has {R} rows, the exchange was built for {self.rows}")
+        seq_lens = _lens(seq_lens, R)
+        if hist is not None:
+            _cuda_contig(hist, "hist", (torch.int32, torch.uint32))
+            _need(hist.numel() == R * HIST_BINS, "hist must be [R, 4096]")
+        gi, gv, fl = self._ptr_arrays
+        slab_stride = logits.stride(0) if R > 1 else max(logits.stride(0), n)
+        _lib.check(_lib.lib().dsa_topk_select_push(
+            _ptr(logits), _ptr(seq_lens), _ptr(hist), R, n, slab_stride, self.topk, int(pad_value),
+            int(index_offset), self.world, self.rank, gi, gv, fl, _ptr(self.sent), _stream()))
+
+    def merge(self, out_idx: torch.Tensor, pad_value: int = -1) -> torch.Tensor:
+        """Waits (on the device, bounded) for this step's candidates of every rank, then writes the
+        exact global top-k into ``out_idx[rows, topk]``."""
+        _cuda_contig(out_idx, "out_idx", (torch.int32,))
+        _need(tuple(out_idx.shape) == (self.rows, self.topk), "out_idx must be [rows, topk]")
+        _lib.check(_lib.lib().dsa_topk_merge_wait(
+            _ptr(self.gather_idx), _ptr(self.gather_val), _ptr(self.flags), _ptr(self.seen), _ptr(out_idx),
+            self.rows, self.world, self.topk, int(pad_value), self.wait_limit_ns, _stream()))
+        return out_idx

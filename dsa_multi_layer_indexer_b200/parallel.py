@@ -12,15 +12,15 @@ Two independent shardings:
 * **KV-sequence-sharded indexer** (not in the reference; its closest relative is
   the per-slice top-m + exact merge inside one GPU,
   kernels/cuda_fused_sparse_splitk.py:1914-2015): rank r scans keys
-  ``key_range(r)``, keeps its local top-k as (global position, logit), one NCCL
-  all-gather moves ``world * topk * 8`` bytes, and every rank merges the
-  candidates with the same exact top-k kernel. The global top-k is a subset of
+  ``key_range(r)``, keeps its local top-k as (global position, logit), one exchange
+  step moves ``world * topk * 8`` bytes (stores through peer-mapped pointers, or one
+  NCCL all-gather), and every rank merges the candidates with the same exact top-k kernel. The global top-k is a subset of
   the union of the local ones, and candidates arrive in ascending position
   order, so the merged set (ties to the lower position) equals the single-GPU
   selection bit for bit.
 
-No kernel here reads a peer's memory: the gathered candidates land in local HBM
-through NCCL before the merge kernel runs.
+No kernel here reads a peer's memory: candidates are stored into the peers' buffers (or
+gathered by NCCL) and land in local HBM before the merge kernel reads them.
 """
 
 from __future__ import annotations
@@ -66,37 +66,57 @@ def all_reduce_hidden(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None
 class SeqShardedIndexer:
     """Indexer over a KV cache sharded by sequence range across ``group``.
 
-    Each rank holds only its slice of the index keys (``local_ctx`` keys starting
-    at global position ``key_lo``). ``select`` returns the global top-k
-    positions, identical on every rank. Buffers are persistent: ``capture`` turns the
-    call into two CUDA graphs with the one NCCL all-gather enqueued between them."""
+    Each rank holds only its slice of the index keys (``local_ctx`` keys starting at global
+    position ``key_lo``). ``select`` returns the global top-k positions, identical on every
+    rank and equal to the single-GPU selection bit for bit. Two ways to move the candidates:
+
+    * ``exchange="p2p"`` (default): the local top-k stores its (position, logit) pairs straight
+      into every rank's gather buffers through peer-mapped pointers and posts a flag; the merge
+      kernel waits for the flags on the device, with a limit (``ops.CandidateExchange``). A step
+      is kernels in stream order, so it can be captured in ONE CUDA graph together with the
+      attention behind it.
+    * ``exchange="nccl"``: local top-k, one ``all_gather_into_tensor`` of the packed candidates,
+      merge. ``capture`` then makes two graphs with the eager NCCL call between the replays."""
 
     def __init__(self, rows: int, topk: int, local_ctx: int, key_lo: int, device,
-                 group: Optional[dist.ProcessGroup] = None) -> None:
+                 group: Optional[dist.ProcessGroup] = None, exchange: str = "p2p",
+                 wait_limit_s: float = 2.0) -> None:
         from . import ops
 
+        if exchange not in ("p2p", "nccl"):
+            raise ValueError("exchange must be 'p2p' or 'nccl'")
         self.ops = ops
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.rows, self.topk, self.local_ctx, self.key_lo = rows, topk, local_ctx, key_lo
+        self.exchange = exchange
         dev = torch.device(device)
         slab = (max(local_ctx, 1) + 3) // 4 * 4
         self.logits = torch.empty(rows, slab, dtype=torch.float32, device=dev)
         self.hist = torch.zeros(rows, ops.HIST_BINS, dtype=torch.int32, device=dev)
         self.local_ws = ops.topk_workspace(rows, max(local_ctx, 1), dev)
-        # (index, logit) candidates travel as ONE buffer: [2, rows, topk] 32-bit words per rank
-        self.cand = torch.empty(2, rows, topk, dtype=torch.int32, device=dev)
-        self.cand_idx = self.cand[0]
-        self.cand_val = self.cand[1].view(torch.float32)
-        self.gath = torch.empty(self.world, 2, rows, topk, dtype=torch.int32, device=dev)
-        self.merge_ws = ops.topk_workspace(rows, self.world * topk, dev)
         self.indices = torch.empty(rows, topk, dtype=torch.int32, device=dev)
+        self.xchg = None
+        if exchange == "p2p":
+            self.xchg = ops.CandidateExchange(rows, topk, self.world, self.rank, dev, wait_limit_s).connect(group)
+            if local_ctx <= 0:  # an empty shard pushes a row of -inf: every entry comes out as padding
+                self._empty = torch.full((rows, 4), float("-inf"), dtype=torch.float32, device=dev)
+        else:
+            # (index, logit) candidates travel as ONE buffer: [2, rows, topk] 32-bit words per rank
+            self.cand = torch.empty(2, rows, topk, dtype=torch.int32, device=dev)
+            self.cand_idx = self.cand[0]
+            self.cand_val = self.cand[1].view(torch.float32)
+            self.gath = torch.empty(self.world, 2, rows, topk, dtype=torch.int32, device=dev)
+            self.merge_ws = ops.topk_workspace(rows, self.world * topk, dev)
 
     def select(self, index_q: torch.Tensor, index_w: torch.Tensor, index_k: torch.Tensor,
                k_scale: torch.Tensor, local_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """index_k / k_scale: this rank's slice ``[n_seq, local_ctx(, 128)]``;
         local_lens: visible keys inside the slice per row (None = all)."""
         self._local(index_q, index_w, index_k, k_scale, local_lens)
+        if self.exchange == "p2p":
+            return self.xchg.merge(self.indices)
         if self.world == 1:
             self.indices.copy_(self.cand_idx)
             return self.indices
@@ -107,22 +127,31 @@ class SeqShardedIndexer:
     def capture(self, index_q: torch.Tensor, index_w: torch.Tensor, index_k: torch.Tensor,
                 k_scale: torch.Tensor, local_lens: Optional[torch.Tensor] = None,
                 after: Optional[Callable[[torch.Tensor], None]] = None) -> Callable[[], torch.Tensor]:
-        """``select`` on fixed buffers as two CUDA graphs around the one NCCL call: the
-        local scan + top-k before it, the merge (and ``after(indices)``, e.g. this rank's
-        attention over the merged set) behind it. The all-gather itself is enqueued
-        between the two replays, outside any graph. Returns the step function."""
-        self._local(index_q, index_w, index_k, k_scale, local_lens)  # warm-up, also of lazy state
-        if self.world > 1:
-            self._exchange()
-            self._merge()
-        else:
-            self.indices.copy_(self.cand_idx)
+        """``select`` (and ``after(indices)``, e.g. this rank's attention over the merged set) on
+        fixed buffers as CUDA graphs. With the p2p exchange that is ONE graph. With NCCL it is two
+        graphs around the one all-gather, which is enqueued between the two replays, outside any
+        graph. Every rank must call it (the warm-up runs one real step). Returns the step function."""
+        args = (index_q, index_w, index_k, k_scale, local_lens)
+        self.select(*args)  # warm-up, also of lazy state
         if after is not None:
             after(self.indices)
         torch.cuda.synchronize()
+        if self.exchange == "p2p":
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.select(*args)
+                if after is not None:
+                    after(self.indices)
+            self._graphs = (graph,)
+
+            def step() -> torch.Tensor:
+                graph.replay()
+                return self.indices
+
+            return step
         g_local, g_merge = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_local):
-            self._local(index_q, index_w, index_k, k_scale, local_lens)
+            self._local(*args)
         with torch.cuda.graph(g_merge):
             if self.world > 1:
                 self._merge()
@@ -155,8 +184,13 @@ class SeqShardedIndexer:
         if self.local_ctx > 0:
             logits = ops.indexer_scan_fp8(index_q, index_w, index_k, k_scale, local_lens,
                                           ctx=self.local_ctx, out=self.logits, hist=self.hist)
-            ops.topk_select(logits, self.topk, local_lens, hist=self.hist, out_idx=self.cand_idx,
-                            out_val=self.cand_val, index_offset=self.key_lo, workspace=self.local_ws)
+            if self.exchange == "p2p":
+                self.xchg.push(logits, local_lens, hist=self.hist, index_offset=self.key_lo)
+            else:
+                ops.topk_select(logits, self.topk, local_lens, hist=self.hist, out_idx=self.cand_idx,
+                                out_val=self.cand_val, index_offset=self.key_lo, workspace=self.local_ws)
+        elif self.exchange == "p2p":
+            self.xchg.push(self._empty)
         else:  # an empty shard contributes only padding
             self.cand_idx.fill_(-1)
             self.cand_val.fill_(float("-inf"))

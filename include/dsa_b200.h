@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 5
+#define DSA_ABI_VERSION 6
 
 enum dsa_status {
   DSA_OK = 0,
@@ -144,6 +144,48 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
                     void* workspace, int64_t workspace_bytes,
                     int R, int64_t n, int64_t slab_stride, int topk,
                     int32_t pad_value, int32_t index_offset, void* stream);
+
+/* ---- candidate exchange of the KV-sequence-sharded indexer -------------------
+ * One process per GPU, each scanning its own range of the keys. The reference has no
+ * multi-GPU indexer; its closest relative is the per-slice top-m followed by an exact merge
+ * inside one GPU (kernels/cuda_fused_sparse_splitk.py:1914-2015), and its serving overlay
+ * states the rules for collectives inside a captured graph (persistent buffers, in-place,
+ * sglang_overlay/mli-sglang-v0.5.16.patch:2478-2487). Here the exchange is part of the two
+ * top-k launches themselves, so a whole sharded step is kernels in stream order:
+ *
+ *   dsa_topk_select_push   the local top-k of each row; every selected (index + index_offset,
+ *                          logit) pair is STORED into slot `rank` of every rank's gather buffers
+ *                          (plain stores through peer-mapped pointers over NVLink, no loads from
+ *                          peer memory, no multicast), then the row's step number is posted, with
+ *                          release at system scope, to flag word [rank][r] of every rank.
+ *   dsa_topk_merge_wait    waits until all `world` flags of a row carry its next step number
+ *                          (acquire; BOUNDED by wait_limit_ns of wall time: when it runs out the
+ *                          kernel sets DSA_STATUS_EXCHANGE_TIMEOUT and finishes, and
+ *                          dsa_check_device_status returns DSA_ERR_DEVICE_TIMEOUT), then selects
+ *                          the exact top-k of the world * topk candidates, ties to the lower rank /
+ *                          position, so every rank ends with the single-GPU selection bit for bit.
+ *
+ * Buffers of one rank (all zero before the first step, never touched by the host afterwards):
+ *   gather_idx int32 / gather_val fp32  [2][R][world][topk]   two step parities
+ *   flags  uint32 [world][R]   written by the sources        sent, seen  uint32 [R]  local
+ * gather_idx / gather_val / flags given to dsa_topk_select_push are arrays of `world`
+ * pointers: entry d is rank d's buffer as THIS process can address it (its own pointer for
+ * d == rank, else from dsa_ipc_open). The two launches of a step must be enqueued in this
+ * order on every rank, the same number of times; rows of up to 131072 logits. */
+int dsa_topk_select_push(const float* logits, const int32_t* seq_lens, uint32_t* hist, int R, int64_t n,
+                         int64_t slab_stride, int topk, int32_t pad_value, int32_t index_offset, int world,
+                         int rank, void* const* gather_idx, void* const* gather_val, void* const* flags,
+                         uint32_t* sent, void* stream);
+int dsa_topk_merge_wait(const int32_t* gather_idx, const float* gather_val, const uint32_t* flags,
+                        uint32_t* seen, int32_t* out_idx, int R, int world, int topk, int32_t pad_value,
+                        int64_t wait_limit_ns, void* stream);
+/* Set-up of the peer mapping (CUDA IPC; one call per buffer and peer, outside any step):
+ * export gives the handle of the allocation that holds `ptr` and ptr's offset inside it,
+ * open maps a peer's allocation and returns the address of the same byte, close unmaps it. */
+#define DSA_IPC_HANDLE_BYTES 64
+int dsa_ipc_export(const void* ptr, void* handle_out /* DSA_IPC_HANDLE_BYTES */, int64_t* offset_out);
+int dsa_ipc_open(const void* handle, int64_t offset, void** ptr_out);
+int dsa_ipc_close(void* ptr, int64_t offset);
 
 /* ---- top-k for callers that cannot allocate ---------------------------------
  * This entry point has no counterpart in the reference. It is dsa_topk_select

@@ -77,6 +77,18 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert rc == -1 and b"num_pages" in h.dsa_last_error()
     rc = h.dsa_latent_append(addr, addr, 1e-6, addr, addr, addr, addr, addr, 1, 128, 16, 1, 3, 0, None)
     assert rc == -1 and b"format" in h.dsa_last_error()
+    # the candidate exchange: world and rank ranges, row length limit, a wait without a limit
+    ptrs = (ctypes.c_void_p * 8)(*([addr] * 8))
+    rc = h.dsa_topk_select_push(addr, None, None, 1, 4096, 4096, 2048, -1, 0, 9, 0, ptrs, ptrs, ptrs, addr, None)
+    assert rc == -1 and b"world" in h.dsa_last_error()
+    rc = h.dsa_topk_select_push(addr, None, None, 1, 4096, 4096, 2048, -1, 0, 2, 2, ptrs, ptrs, ptrs, addr, None)
+    assert rc == -1 and b"rank" in h.dsa_last_error()
+    rc = h.dsa_topk_select_push(addr, None, None, 1, 1 << 18, 1 << 18, 2048, -1, 0, 2, 0, ptrs, ptrs, ptrs, addr, None)
+    assert rc == -2
+    rc = h.dsa_topk_merge_wait(addr, addr, addr, addr, addr, 1, 2, 2048, -1, 0, None)
+    assert rc == -1 and b"limit" in h.dsa_last_error()
+    rc = h.dsa_ipc_open(None, 0, None)
+    assert rc == -1
 
 
 def test_staging_wrappers_reject_host_tensors():

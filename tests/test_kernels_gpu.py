@@ -336,28 +336,12 @@ def test_bad_arguments_raise(ops):
         ops.topk_select(torch.zeros(1, (1 << 20) + 1, device="cuda"), 2048)
 
 
-def test_fused_cluster_attention_in_a_fresh_process():
-    """DSA_MLA_FUSED=1 selects the cluster/DSMEM form of dsa_sparse_mla_decode; the
-    switch is read once per process, so the attention tests are re-run in a child."""
-    import os
-    import subprocess
-    import sys
-
-    env = dict(os.environ, DSA_MLA_FUSED="1")
-    here = os.path.dirname(os.path.abspath(__file__))
-    proc = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_kernels_gpu.py"), "-m", "gpu", "-x",
-                           "-q", "-k", "sparse_mla and not fresh_process"], env=env, capture_output=True, text=True,
-                          timeout=600)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
-
-
 # ----------------------------------------------------------------------------- fused launch
 @pytest.mark.parametrize("B,H,n,topk,nsplit", [(1, 128, 20000, 2048, 32), (3, 32, 5000, 1024, 8), (2, 16, 700, 64, 1)])
-def test_fused_indexer_attention_launch_equals_separate_launches(ops, monkeypatch, B, H, n, topk, nsplit):
+def test_fused_indexer_attention_launch_equals_separate_launches(ops, B, H, n, topk, nsplit):
     """One role-split launch (attention over a given selection + the indexer scan)
     returns bit for bit what the two separate launches return (the role-split launch
-    contains the mma.sync attention body, so the separate launch is pinned to it)."""
-    monkeypatch.setenv("DSA_MLA_TC", "0")
+    contains the mma.sync attention body; at these sizes the separate launch takes it too)."""
     torch.manual_seed(B * 1000 + H)
     q = dev(torch.randn(B, H, 576).to(torch.bfloat16))
     kv = dev(torch.randn(B, n, 576).to(torch.bfloat16))

@@ -98,6 +98,69 @@ def test_sequence_sharded_selection_emulated_on_one_gpu():
     assert torch.equal(merged, full)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_store_exchange_emulated_on_one_gpu(world):
+    """The exchange kernels with every "rank" on one GPU: each rank's local top-k stores its
+    candidates into all ranks' gather buffers and posts its flags, then each rank's merge finds
+    the flags already there and selects. Three steps with different logits (the two buffer
+    parities, then the first one again), ragged rows, one empty shard: every rank ends with the
+    oracle's global selection. The ranks' launches are enqueued one after the other on one
+    stream, every push before the first merge, so no kernel ever waits for a later one."""
+    from dsa_multi_layer_indexer_b200 import _lib, ops
+    from dsa_multi_layer_indexer_b200.parallel import key_range
+
+    rows, topk, n = 3, 512, 20000
+    xs = ops.CandidateExchange.local_group(rows, topk, world, "cuda")
+    outs = [torch.full((rows, topk), -7, dtype=torch.int32, device="cuda") for _ in range(world)]
+    lens = [n, n // 2 + 17, 300]  # row 2: only the first shard sees any key
+    for step in range(3):
+        g = torch.Generator().manual_seed(100 + step)
+        logits = torch.randn(rows, n, generator=g)
+        logits[1, ::5] = logits[1, 0]  # ties across shards
+        want = O.select_topk(O.mask_beyond(logits, lens), topk, pad_value=-1)
+        dl = logits.cuda()
+        for r in range(world):
+            lo, hi = key_range(r, world, n)
+            local = dl[:, lo:hi].contiguous()
+            local_lens = torch.tensor([max(0, min(l, hi) - lo) for l in lens], dtype=torch.int32, device="cuda")
+            xs[r].push(local, local_lens, index_offset=lo)
+        for r in range(world):
+            xs[r].merge(outs[r])
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        for r in range(world):
+            assert torch.equal(outs[r].cpu().long(), want), f"step {step} rank {r}"
+        assert xs[0].sent.tolist() == [step + 1] * rows and xs[0].seen.tolist() == [step + 1] * rows
+
+
+@pytest.mark.gpu
+def test_merge_wait_runs_out_when_a_rank_never_posts():
+    """Failure detection without a fault: rank 1 of a two-rank exchange never pushes. Rank 0's merge
+    waits for that flag with a limit of two milliseconds, gives up, sets the status word and returns;
+    the host call that reads the status raises, and the context stays usable."""
+    from dsa_multi_layer_indexer_b200 import _lib, ops
+
+    rows, topk = 2, 64
+    xs = ops.CandidateExchange.local_group(rows, topk, 2, "cuda", wait_limit_s=0.002)
+    out = torch.full((rows, topk), -7, dtype=torch.int32, device="cuda")
+    xs[0].push(torch.randn(rows, 1000, device="cuda"))
+    _lib.check_device_status()
+    xs[0].merge(out)  # rank 1 posted nothing
+    with pytest.raises(_lib.DsaError) as err:
+        _lib.check_device_status()
+    assert err.value.status == -4
+    _lib.check_device_status()  # read and cleared
+    # the context is alive: rank 1 catches up, the next step completes in time
+    xs[1].push(torch.randn(rows, 1000, device="cuda"))
+    xs[1].merge(out)
+    xs[0].push(torch.randn(rows, 1000, device="cuda"))
+    xs[1].push(torch.randn(rows, 1000, device="cuda"))
+    xs[0].merge(out)
+    _lib.check_device_status()
+    assert int((out >= 0).sum()) == rows * topk
+
+
 def _nccl_worker(rank: int, world: int, port: int, n: int, topk: int, out_path: str):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -113,18 +176,28 @@ def _nccl_worker(rank: int, world: int, port: int, n: int, topk: int, out_path: 
         kv = torch.randn(n, 576).to(torch.bfloat16)
         iq8, ik8, wp, sk, q, kv = (t.cuda() for t in (iq8, ik8, wp, sk, q, kv))
         lo, hi = key_range(rank, world, n)
-        idxr = SeqShardedIndexer(2, topk, hi - lo, lo, "cuda")
         keys = ik8[lo:hi].unsqueeze(0).expand(2, -1, -1).contiguous()
         scales = sk[lo:hi].unsqueeze(0).expand(2, -1).contiguous()
-        sel = idxr.select(iq8, wp, keys, scales).clone()
-        # the same step as two graphs around the all-gather, with a consumer behind the merge
-        seen = torch.zeros_like(sel)
-        step = idxr.capture(iq8, wp, keys, scales, after=lambda idx: seen.copy_(idx))
-        seen.zero_()
-        idxr.indices.fill_(-7)
-        sel_g = step().clone()
-        torch.cuda.synchronize()
-        assert torch.equal(sel_g, sel) and torch.equal(seen, sel)
+        picked = []
+        for exchange in ("p2p", "nccl"):
+            idxr = SeqShardedIndexer(2, topk, hi - lo, lo, "cuda", exchange=exchange)
+            sel = idxr.select(iq8, wp, keys, scales).clone()
+            # the same step captured (one graph with the peer-store exchange, two graphs around the
+            # all-gather with NCCL), with a consumer behind the merge
+            seen = torch.zeros_like(sel)
+            step = idxr.capture(iq8, wp, keys, scales, after=lambda idx: seen.copy_(idx))
+            for _ in range(3):
+                seen.zero_()
+                idxr.indices.fill_(-7)
+                sel_g = step().clone()
+                torch.cuda.synchronize()
+                assert torch.equal(sel_g, sel) and torch.equal(seen, sel), exchange
+            picked.append(sel)
+            dist.barrier()
+        from dsa_multi_layer_indexer_b200 import _lib
+        _lib.check_device_status()
+        assert torch.equal(picked[0], picked[1])
+        sel = picked[0]
         h0, h1 = head_range(rank, world, 32)
         kv2 = kv.unsqueeze(0).expand(2, -1, -1).contiguous()
         part = ops.sparse_mla_decode(q[:, h0:h1].contiguous(), kv2, sel, 0.07, nsplit=8)
