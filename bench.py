@@ -10,10 +10,12 @@ Prints ONE JSON line (rank 0). With --impl reference the CPU oracle (a port of
 the reference's PyTorch path) is timed on the host cores instead.
 
 Under torchrun (N > 1) MLA heads are split tensor-parallel across ranks and the
-indexer is replicated, as the reference does under TP
-(src/lagged_indexer_dsa/inference/modeling/transformer.py:673-677, :1323); with
---seq-shard the scan is split by KV range instead and the per-rank top-2048
-candidates are merged after an NCCL all-gather.
+two forms are timed and the faster one is the line's value: the indexer
+replicated, as the reference does under TP
+(src/lagged_indexer_dsa/inference/modeling/transformer.py:673-677, :1323), and
+the scan split by KV range with the per-rank top-2048 candidates exchanged by
+peer stores inside the step's graph and merged. Before the timed region the
+N-rank result is checked against the one-GPU result on the same inputs.
 """
 
 from __future__ import annotations
@@ -55,7 +57,6 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=16, help="distinct per-layer caches cycled through")
     ap.add_argument("--graph-per-layer", action="store_true",
                     help="one CUDA graph per step instead of one graph over --layers consecutive steps")
-    ap.add_argument("--seq-shard", action="store_true", help="N>1: shard the scan by KV range + all-gather merge")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--scan-impl", type=int, default=0, help="0 tcgen05, 1 legacy mma.sync")
     ap.add_argument("--tp-emulate", type=int, default=1,
@@ -72,16 +73,15 @@ def workload_config(args, world):
         "batch": 1, "context": args.ctx, "index_heads": INDEX_HEADS, "index_dim": 128,
         "index_key_dtype": "e4m3+fp32 scale", "topk": TOPK, "mla_heads": HEADS, "latent_dim": 576,
         "latent_dtype": "bf16", "sm_scale": "1/sqrt(192)",
-        "parallelism": ("tp%d_heads" % world) + ("+seq_sharded_indexer" if args.seq_shard and world > 1 else "+replicated_indexer" if world > 1 else ""),
+        "parallelism": "tp%d_heads" % world if world == 1 else "tp%d_heads: the faster of +replicated_indexer and +seq_sharded_indexer" % world,
         "l2": "%d distinct per-layer caches cycled (%.0f MB of index keys + %.0f MB of latent rows): "
               "inputs larger than the 126 MB L2" % (args.layers, args.layers * args.ctx * 132 / 1e6,
                                                     args.layers * args.ctx * 1152 / 1e6),
-        "launch": ("eager launches (NCCL all-gather between the local and the merged selection)"
-                   if args.seq_shard and world > 1 else
-                   "one CUDA graph per layer step (5 kernels: scan, classify, finish, attention partials, combine)"
+        "launch": ("one CUDA graph per layer step (4 kernels: scan, top-k, attention partials, combine)"
                    if args.graph_per_layer or args.layers <= 1 else
                    "one CUDA graph over %d consecutive layer steps, as a model's decode step is captured "
-                   "(5 kernels per step: scan, classify, finish, attention partials, combine); "
+                   "(4 kernels per step: scan, top-k, attention partials, combine; 5 with the sequence-sharded "
+                   "indexer: scan, local top-k + peer stores, merge, partials, combine); "
                    "steps beyond a multiple of %d share one more graph" % (args.layers, args.layers)),
     }
 
@@ -202,7 +202,7 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    warmup = max(0, args.warmup)
+    warmup = max(3, args.warmup)  # (the GPU arm never runs fewer than three warm-ups either)
     steps = max(1, args.steps)
     capped = ""
     if warmup + steps > REF_MAX_STEPS:  # honour the arguments up to the cap, and say so
@@ -248,12 +248,153 @@ def event_time_ms(fn, iters):
     return st.elapsed_time(en) / iters
 
 
+class LayerSet:
+    """Per-layer caches and step buffers of one form of the hot path on this rank.
+
+    form "replicated": every rank scans the whole key cache (the reference's scheme under TP,
+    src/lagged_indexer_dsa/inference/modeling/transformer.py:673-677) and attends its own heads.
+    form "sharded": rank r scans keys [r * ctx / N, (r + 1) * ctx / N); the ranks' local top-2048
+    candidates are exchanged and merged (parallel.SeqShardedIndexer), then each rank attends its
+    own heads over the merged selection."""
+
+    def __init__(self, form, ctx, L, world, rank, dev, inputs, exchange="p2p"):
+        from dsa_multi_layer_indexer_b200 import ops
+        from dsa_multi_layer_indexer_b200.decode import HotPathState, LayerCache
+        from dsa_multi_layer_indexer_b200.parallel import SeqShardedIndexer
+
+        self.form, self.ctx, self.L, self.world, self.rank, self.dev = form, ctx, L, world, rank, dev
+        self.sharded = form == "sharded" and world > 1
+        self.heads_local = HEADS // world
+        self.ctx_local = ctx // world if self.sharded else ctx
+        key_lo = rank * self.ctx_local if self.sharded else 0
+        h_iq8, h_w, h_q = inputs
+        gen = torch.Generator(device=dev).manual_seed(1234)  # the same caches on every rank
+        self.caches, self.states, self.indexers = [], [], []
+        for _ in range(L):
+            ik = torch.randn(ctx, 128, device=dev, generator=gen)
+            ik8, sk = ops.quantize_e4m3_rowwise(ik)
+            kv = torch.randn(ctx, 576, device=dev, generator=gen).to(torch.bfloat16)
+            self.caches.append(LayerCache(ik8[key_lo:key_lo + self.ctx_local].unsqueeze(0).contiguous(),
+                                          sk[key_lo:key_lo + self.ctx_local].unsqueeze(0).contiguous(), kv.unsqueeze(0)))
+            del ik, ik8, sk
+            st = HotPathState(1, self.heads_local, INDEX_HEADS, self.ctx_local, TOPK, dev)
+            st.index_q.copy_(h_iq8)
+            st.index_w.copy_(h_w)
+            st.q.copy_(h_q[:, rank * self.heads_local:(rank + 1) * self.heads_local])
+            if self.sharded:
+                st.seq_lens.fill_(ctx)  # the attention sees the whole (replicated) latent cache
+                self.indexers.append(SeqShardedIndexer(1, TOPK, self.ctx_local, key_lo, dev, exchange=exchange))
+            self.states.append(st)
+        torch.cuda.synchronize()
+
+    def select(self, l, impl=0):
+        st, cache = self.states[l], self.caches[l]
+        if not self.sharded:
+            return st.run_indexer(cache, impl)
+        return self.indexers[l].select(st.index_q, st.index_w, cache.index_k, cache.k_scale)
+
+    def step(self, l, impl=0):
+        idx = self.select(l, impl)
+        return self.states[l].run_attention(self.caches[l], idx, SM_SCALE)
+
+    def free(self):
+        for x in self.indexers:
+            if x.xchg is not None:
+                x.xchg.close()
+        self.caches, self.states, self.indexers = [], [], []
+        torch.cuda.empty_cache()
+
+
+def time_steps(layers, steps, warmup, barrier, impl=0, graph_per_layer=False):
+    """ms per step of `steps` consecutive layer steps, device-timed. A model's decode step is ONE
+    graph over all its layers, so the timed loop replays a graph that holds L consecutive layer
+    steps (L steps per replay, distinct caches); the steps beyond a multiple of L share one more."""
+    L = layers.L
+    for l in range(L):
+        layers.step(l, impl)  # eager warm-up (opt-ins, lazy state)
+    torch.cuda.synchronize()
+
+    def capture(count):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for l in range(count):
+                layers.step(l % L, impl)
+        torch.cuda.synchronize()
+        return g
+
+    if graph_per_layer or L == 1:
+        singles = [capture_one(layers, l, impl) for l in range(L)]
+        plan = [(singles[i % L], 1) for i in range(steps)]
+        warm = [singles[i % L] for i in range(max(warmup, 3))]
+    else:
+        n_big, rem = divmod(steps, L)
+        big = capture(L) if n_big else None
+        tail = capture(rem) if rem else None
+        plan = [(big, L)] * n_big + ([(tail, rem)] if rem else [])
+        warm = [g for g in (big, tail) if g is not None] * max(1, -(-max(warmup, 3) // L))
+    barrier()
+    for g in warm:
+        g.replay()
+    barrier()
+    st_ev, en_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    st_ev.record()
+    for g, _ in plan:
+        g.replay()
+    en_ev.record()
+    barrier()
+    return st_ev.elapsed_time(en_ev) / steps
+
+
+def capture_one(layers, l, impl=0):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        layers.step(l, impl)
+    return g
+
+
+def parity_check(world, rank, dev, ctx, inputs, dist):
+    """Before anything is timed at N > 1: the N-rank result must be the one-GPU result on the same
+    seeded inputs (the reference's own gate of this kind: batched == rows, bitwise,
+    kernels/cuda_fused_sparse_splitk.py:3536-3668). Every rank runs both forms on one layer; rank 0
+    also runs the whole layer alone and compares: selections exactly, the concatenated attention
+    output within the 2e-2 bound (the split count of the attention depends on the head count, so
+    its fp32 summation order differs). Returns (ok, max relative error of the attention)."""
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    worst, ok = 0.0, True
+    alone = None
+    if rank == 0:
+        ref = LayerSet("replicated", ctx, 1, 1, 0, dev, inputs)
+        alone = (ref.select(0).clone(), ref.step(0).clone())
+        ref.free()
+    for form in ("replicated", "sharded"):
+        ls = LayerSet(form, ctx, 1, world, rank, dev, inputs)
+        sel = ls.select(0).clone()
+        out = ls.states[0].run_attention(ls.caches[0], sel, SM_SCALE).clone()
+        torch.cuda.synchronize()
+        sels = [torch.empty_like(sel) for _ in range(world)]
+        outs = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(sels, sel)
+        dist.all_gather(outs, out)
+        if rank == 0:
+            ok = ok and all(torch.equal(s_, alone[0]) for s_ in sels)
+            full = torch.cat(outs, dim=1).float()
+            err = float((full - alone[1].float()).abs().max() / alone[1].float().abs().max())
+            worst = max(worst, err)
+            ok = ok and err < 2e-2
+        ls.free()
+        dist.barrier()
+    _lib.check_device_status()
+    flag = torch.tensor([1.0 if ok else 0.0, worst], dtype=torch.float64, device=dev)
+    dist.broadcast(flag, 0)
+    return bool(flag[0].item() > 0.5), float(flag[1].item())
+
+
 def run_ours(args):
     import torch.distributed as dist
 
     from dsa_multi_layer_indexer_b200 import _lib, ops
-    from dsa_multi_layer_indexer_b200.decode import HostDecoder, HotPathState, LayerCache
-    from dsa_multi_layer_indexer_b200.parallel import SeqShardedIndexer
+    from dsa_multi_layer_indexer_b200.decode import HostDecoder
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -264,22 +405,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     _lib.lib()
     assert HEADS % world == 0
-    heads_local = HEADS // world
     ctx, L = args.ctx, args.layers
-    seq_shard = args.seq_shard and world > 1
-    ctx_local = ctx // world if seq_shard else ctx
-    key_lo = rank * ctx_local if seq_shard else 0
 
-    # ---- per-layer caches, generated and quantised on the device (seeded)
-    gen = torch.Generator(device=dev).manual_seed(1234)
-    caches = []
-    for _ in range(L):
-        ik = torch.randn(ctx, 128, device=dev, generator=gen)
-        ik8, sk = ops.quantize_e4m3_rowwise(ik)
-        kv = torch.randn(ctx, 576, device=dev, generator=gen).to(torch.bfloat16)
-        caches.append(LayerCache(ik8[key_lo:key_lo + ctx_local].unsqueeze(0).contiguous(),
-                                 sk[key_lo:key_lo + ctx_local].unsqueeze(0).contiguous(), kv.unsqueeze(0)))
-        del ik
     # ---- the step's query operands come from (pinned) host memory
     hgen = torch.Generator().manual_seed(99)
     iq = torch.randn(1, INDEX_HEADS, 128, generator=hgen)
@@ -288,110 +415,73 @@ def run_ours(args):
     iq8, sq = ops.quantize_e4m3_rowwise(iq.to(dev))
     h_iq8 = iq8.view(torch.uint8).cpu()
     h_w = (sq.cpu() * w).contiguous()
-    h_q = q_all[:, rank * heads_local:(rank + 1) * heads_local].contiguous()
-
-    states, graphs = [], []
-    shard_indexers = []
-
-    def hot_path(state, cache, l=None):
-        if not seq_shard:
-            state.run(cache, SM_SCALE, impl=args.scan_impl)
-            return
-        idx = shard_indexers[l].select(state.index_q, state.index_w, cache.index_k, cache.k_scale)
-        state.run_attention(cache, idx, SM_SCALE)
-
-    for l in range(L):
-        st = HotPathState(1, heads_local, INDEX_HEADS, ctx_local, TOPK, dev)
-        st.index_q.copy_(h_iq8)
-        st.index_w.copy_(h_w)
-        st.q.copy_(h_q)
-        if seq_shard:
-            st.seq_lens.fill_(ctx)  # attention sees the whole (replicated) latent cache
-            shard_indexers.append(SeqShardedIndexer(1, TOPK, ctx_local, key_lo, dev))
-        states.append(st)
-    torch.cuda.synchronize()
-    # eager warm-up (also the NCCL communicator), then one graph per layer
-    for l in range(L):
-        hot_path(states[l], caches[l], l)
-    torch.cuda.synchronize()
-    class _TwoGraphs:  # same interface as a captured graph
-        def __init__(self, step):
-            self.step = step
-
-        def replay(self):
-            self.step()
-
-    for l in range(L):
-        if seq_shard:
-            # The NCCL all-gather stays outside CUDA graphs (a capture that contained it did
-            # not finish on this software stack): local scan + top-k are one graph, merge +
-            # attention another, and the all-gather is enqueued between the two replays.
-            st, cache = states[l], caches[l]
-            graphs.append(_TwoGraphs(shard_indexers[l].capture(
-                st.index_q, st.index_w, cache.index_k, cache.k_scale,
-                after=lambda idx, st=st, cache=cache: st.run_attention(cache, idx, SM_SCALE))))
-            continue
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            hot_path(states[l], caches[l])
-        graphs.append(g)
-    torch.cuda.synchronize()
+    inputs = (h_iq8.to(dev), h_w.to(dev), q_all.to(dev))
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # A decode step of a real model is ONE graph over all its layers, so the timed loop
-    # replays a graph that holds the hot paths of L consecutive layers (L steps per
-    # replay, distinct caches); --graph-per-layer launches one graph per step instead.
-    big = tail = None
-    n_big, rem = 0, args.steps
-    if not seq_shard and not args.graph_per_layer and L > 1:
-        n_big, rem = divmod(args.steps, L)
+    parity = None
+    if world > 1:
+        ok, err = parity_check(world, rank, dev, ctx, inputs, dist)
+        parity = {"parity_checked": ok, "parity_max_rel_err_attention": err,
+                  "parity_note": "N-rank selection == one-GPU selection (exact) and concatenated attention output "
+                                 "within 2e-2 of the one-GPU output, both forms, before the timed region"}
+        if not ok:
+            if rank == 0:
+                print(json.dumps({"error": "the N-rank result differs from the one-GPU result", **parity}))
+            dist.destroy_process_group()
+            sys.exit(1)
 
-        def capture_steps(count):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                for l in range(count):
-                    hot_path(states[l], caches[l])
-            torch.cuda.synchronize()
-            return g
-
-        if n_big:
-            big = capture_steps(L)
-        if rem > 1:  # the steps beyond a multiple of L share a graph too
-            tail = capture_steps(rem)
-
-    def run_steps():
-        for _ in range(n_big):
-            big.replay()
-        if tail is not None:
-            tail.replay()
-        else:
-            for i in range(rem):
-                graphs[i % L].replay()
-
-    # the clock sampler starts before the warm-up (nvidia-smi needs ~0.1 s to deliver its first
-    # sample), so that its samples cover the timed region and the per-kernel legs behind it
+    # the clock sampler starts early (nvidia-smi needs ~0.1 s to deliver its first sample)
     sampler = ClockSampler(local)
     sampler.start()
-    for i in range(max(args.warmup, 3)):
-        graphs[i % L].replay()
-    for g in (big, tail):
-        if g is not None:
-            g.replay()
-    barrier()
-    st_ev, en_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    st_ev.record()
-    run_steps()
-    en_ev.record()
-    barrier()
-    ms_step = st_ev.elapsed_time(en_ev) / args.steps
 
-    # ---- the dominant kernel alone, same rotation: average launch duration with CUDA events
-    # One graph holds the kernel once per layer cache (L launches back to back), so the
-    # figure is the kernel's own duration plus the in-graph launch gap, not host launch rate.
+    forms = {}
+    main = LayerSet("replicated", ctx, L, world, rank, dev, inputs)
+    ms_rep = time_steps(main, args.steps, args.warmup, barrier, args.scan_impl, args.graph_per_layer)
+    forms["tp_heads+replicated_indexer"] = ms_rep
+    ms_shard = ms_shard2 = coll_ms = None
+    if world > 1:
+        sh = LayerSet("sharded", ctx, L, world, rank, dev, inputs)
+        ms_shard = time_steps(sh, args.steps, args.warmup, barrier, args.scan_impl)
+        # the exchange by itself: local top-k with the peer stores + the merge behind the bounded wait
+        def xchg_only(l):
+            x = sh.indexers[l]
+            x.xchg.push(x.logits[:, :sh.ctx_local], None, hist=None, index_offset=x.key_lo)
+            x.xchg.merge(x.indices)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for l in range(L):
+                xchg_only(l)
+        barrier()
+        g.replay()
+        barrier()
+        reps = max(4, args.steps // L)
+        st_ev, en_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st_ev.record()
+        for _ in range(reps):
+            g.replay()
+        en_ev.record()
+        barrier()
+        coll_ms = st_ev.elapsed_time(en_ev) / (reps * L)
+        del g
+        sh.free()
+        forms["tp_heads+seq_sharded_indexer"] = ms_shard
+        if args.ctx == CTX:  # BASELINE config 5: the same step at twice the context
+            sh2 = LayerSet("sharded", 2 * ctx, min(L, 8), world, rank, dev, inputs)
+            ms_shard2 = time_steps(sh2, args.steps, args.warmup, barrier, args.scan_impl)
+            sh2.free()
+            forms["tp_heads+seq_sharded_indexer_ctx262144"] = ms_shard2
+    ms_step = min(ms_rep, ms_shard) if ms_shard is not None else ms_rep
+    best_form = "tp_heads+seq_sharded_indexer" if (ms_shard is not None and ms_shard < ms_rep) else \
+        ("tp_heads+replicated_indexer" if world > 1 else "tp1_heads")
+
+    # ---- each kernel alone, same rotation of caches: L launches back to back inside one graph, so the
+    # figure is the kernel's own duration plus the in-graph launch gap, not the host's launch rate
+    states, caches = main.states, main.caches
+
     def time_graphs(build):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
@@ -401,22 +491,38 @@ def run_ours(args):
         reps = max(4, (max(args.steps, 64) + L - 1) // L)
         return event_time_ms(lambda i: g.replay(), reps) / L
 
-    def scan_only(l):
+    def scan_as_run(l):  # with its histogram epilogue, as the step runs it (each layer has its own histogram)
         s = states[l]
         ops.indexer_scan_fp8(s.index_q, s.index_w, caches[l].index_k, caches[l].k_scale, None,
-                             ctx=ctx_local, out=s.logits, hist=s.hist, impl=args.scan_impl)
-        s.hist.zero_()  # the select normally re-arms it; a memset node stands in here
+                             ctx=ctx, out=s.logits, hist=s.hist, impl=args.scan_impl)
 
     def scan_nohist(l):
         s = states[l]
         ops.indexer_scan_fp8(s.index_q, s.index_w, caches[l].index_k, caches[l].k_scale, None,
-                             ctx=ctx_local, out=s.logits, hist=None, impl=args.scan_impl)
+                             ctx=ctx, out=s.logits, hist=None, impl=args.scan_impl)
 
-    scan_ms = time_graphs(scan_nohist)
-    scan_hist_ms = time_graphs(scan_only)
-    topk_ms = time_graphs(lambda l: ops.topk_select(states[l].logits[:, :ctx_local], TOPK, None,
-                                                    out_idx=states[l].indices, workspace=states[l].topk_ws))
+    scan_ms = time_graphs(scan_as_run)
+    for s in states:
+        s.hist.zero_()  # (nothing re-armed them between those launches)
+    scan_nohist_ms = time_graphs(scan_nohist)
+    for s in states:  # a consistent histogram for the top-k leg below
+        ops.indexer_scan_fp8(s.index_q, s.index_w, caches[0].index_k, caches[0].k_scale, None, ctx=ctx,
+                             out=s.logits, hist=s.hist)
+    torch.cuda.synchronize()
+
+    def topk_as_run(l):  # consumes the scan's histogram and re-arms it: refill it by a copy node
+        s = states[l]
+        ops.topk_select(s.logits[:, :ctx], TOPK, None, hist=s.hist, out_idx=s.indices, workspace=s.topk_ws)
+        s.hist.copy_(hist_keep[l])
+
+    hist_keep = [s.hist.clone() for s in states]
+    topk_copy_ms = time_graphs(topk_as_run)
+    copy_ms = time_graphs(lambda l: states[l].hist.copy_(hist_keep[l]))
+    topk_ms = topk_copy_ms - copy_ms
+    for s in states:
+        s.hist.zero_()
     attn_ms = time_graphs(lambda l: states[l].run_attention(caches[l], states[l].indices, SM_SCALE))
+
     def attn_stage(l, stage):
         s = states[l]
         ops.sparse_mla_decode(s.q, caches[l].kv, s.indices, SM_SCALE, s.seq_lens, scratch=s.scratch,
@@ -425,111 +531,127 @@ def run_ours(args):
     comb_ms = time_graphs(lambda l: attn_stage(l, "combine"))
     # the lagged schedule's pair (attention over a given selection, this layer's indexer), as the
     # reference's own harness reports it (kernels/cuda_fused_sparse_splitk.py:4080-4094)
-    lag = None
-    if not seq_shard:
-        attend = [s.indices.clone() for s in states]
+    attend = [s.indices.clone() for s in states]
 
-        def indexer_only(l):
+    def indexer_only(l):
+        states[l].run_indexer(caches[l], impl=args.scan_impl)
+
+    def serial_pair(l):
+        states[l].run_attention(caches[l], attend[l], SM_SCALE)
+        states[l].run_indexer(caches[l], impl=args.scan_impl)
+
+    def fused_pair(l):
+        states[l].run_lagged_fused(caches[l], attend[l], SM_SCALE)
+
+    side = torch.cuda.Stream()
+
+    def two_stream_pair(l):  # the default realisation: the indexer forks to a second stream and is joined
+        cur = torch.cuda.current_stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
             states[l].run_indexer(caches[l], impl=args.scan_impl)
+        states[l].run_attention(caches[l], attend[l], SM_SCALE)
+        cur.wait_stream(side)
 
-        def serial_pair(l):
-            states[l].run_attention(caches[l], attend[l], SM_SCALE)
-            states[l].run_indexer(caches[l], impl=args.scan_impl)
-
-        def fused_pair(l):
-            states[l].run_lagged_fused(caches[l], attend[l], SM_SCALE)
-
-        side = torch.cuda.Stream()
-
-        def two_stream_pair(l):  # the default realisation: the indexer forks to a second stream and is joined
-            main = torch.cuda.current_stream()
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                states[l].run_indexer(caches[l], impl=args.scan_impl)
-            states[l].run_attention(caches[l], attend[l], SM_SCALE)
-            main.wait_stream(side)
-
-        idx_ms, ser_ms, fus_ms = time_graphs(indexer_only), time_graphs(serial_pair), time_graphs(fused_pair)
-        two_ms = time_graphs(two_stream_pair)
-        ideal = max(attn_ms, idx_ms)
-        lag = {"attn_only_ms": attn_ms, "indexer_only_ms": idx_ms, "serial_ms": ser_ms, "fused_ms": fus_ms,
-               "two_stream_ms": two_ms, "ideal_overlap_ms": ideal,
-               "fused_vs_ideal_pct": 100.0 * (fus_ms / ideal - 1.0),
-               "two_stream_vs_ideal_pct": 100.0 * (two_ms / ideal - 1.0),
-               "saved_vs_serial_pct": 100.0 * (1.0 - min(fus_ms, two_ms) / ser_ms),
-               "note": "fused = one role-split launch (attention partials + indexer scan), then merge and top-k; "
-                       "two_stream = indexer forked to a second stream inside the graph (default realisation)"}
+    idx_ms, ser_ms, fus_ms = time_graphs(indexer_only), time_graphs(serial_pair), time_graphs(fused_pair)
+    two_ms = time_graphs(two_stream_pair)
+    ideal = max(attn_ms, idx_ms)
+    lag = {"attn_only_ms": attn_ms, "indexer_only_ms": idx_ms, "serial_ms": ser_ms, "fused_ms": fus_ms,
+           "two_stream_ms": two_ms, "ideal_overlap_ms": ideal,
+           "fused_vs_ideal_pct": 100.0 * (fus_ms / ideal - 1.0),
+           "two_stream_vs_ideal_pct": 100.0 * (two_ms / ideal - 1.0),
+           "saved_vs_serial_pct": 100.0 * (1.0 - min(fus_ms, two_ms) / ser_ms),
+           "note": "fused = one role-split launch (attention partials + indexer scan), then merge and top-k; "
+                   "two_stream = indexer forked to a second stream inside the graph (default realisation)"}
     clocks = sampler.stop()
 
-    # ---- end to end with host buffers (rank-local operands in pinned memory)
-    e2e = None
-    if not seq_shard:
-        dec = [HostDecoder(states[l], caches[l], SM_SCALE, kernel_copies=os.environ.get("DSA_E2E_KERNEL_COPIES", "1") != "0",
-                            poll=os.environ.get("DSA_E2E_POLL", "1") != "0")
-               for l in range(min(L, 4))]
-        for d in dec:
-            d.h_index_q.copy_(h_iq8)
-            d.h_index_w.copy_(h_w)
-            d.h_q.copy_(h_q)
-        for i in range(8):
-            dec[i % len(dec)].step()
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            dec[i % len(dec)].step()
-        barrier()
-        e2e_dt = (time.perf_counter() - t0) / args.steps
-        e2e = {"value": 1.0 / e2e_dt, "unit": UNIT, "ms_per_step": e2e_dt * 1e3,
-               "h2d_bytes_per_step": dec[0].h2d_bytes, "d2h_bytes_per_step": dec[0].d2h_bytes,
-               "note": "one graph per step: index_q / index_w pinned host -> device by a kernel node, q by the copy engine beside the scan, kernels, selection -> pinned host by a kernel node on a forked stream, attention output written straight into pinned host memory; the host polls the epoch word the graph's last node posts, every step"}
+    # ---- end to end with host buffers (rank-local operands in pinned memory), over ALL the layer
+    # caches, so that a step's keys are as cold as in the device-timed loop
+    dec = [HostDecoder(states[l], caches[l], SM_SCALE) for l in range(L)]
+    for d in dec:
+        d.h_index_q.copy_(h_iq8)
+        d.h_index_w.copy_(h_w)
+        d.h_q.copy_(q_all[:, rank * main.heads_local:(rank + 1) * main.heads_local])
+    for i in range(2 * L):
+        dec[i % L].step()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        dec[i % L].step()
+    barrier()
+    e2e_dt = (time.perf_counter() - t0) / args.steps
+    e2e = {"value": 1.0 / e2e_dt, "unit": UNIT, "ms_per_step": e2e_dt * 1e3,
+           "h2d_bytes_per_step": dec[0].h2d_bytes, "d2h_bytes_per_step": dec[0].d2h_bytes,
+           "form": "tp%d_heads%s" % (world, "+replicated_indexer" if world > 1 else ""),
+           "note": "one graph per step, cycling over all %d layer caches: index_q / index_w pinned host -> device by a "
+                   "kernel node, q by the copy engine beside the scan, kernels, selection -> pinned host by a kernel node "
+                   "on a forked stream, attention output written straight into pinned host memory; the host polls the "
+                   "epoch word the graph's last node posts, every step" % L}
 
     _lib.check_device_status()
-    times = torch.tensor([ms_step, scan_ms, topk_ms, attn_ms, e2e["ms_per_step"] if e2e else 0.0],
-                         dtype=torch.float64, device=dev)
+    vals = [ms_step, scan_ms, topk_ms, attn_ms, e2e["ms_per_step"], ms_rep, ms_shard or 0.0, ms_shard2 or 0.0,
+            coll_ms or 0.0]
+    times = torch.tensor(vals, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_step, scan_ms, topk_ms, attn_ms, e2e_ms = times.tolist()
-    if e2e:
-        e2e["ms_per_step"] = e2e_ms
-        e2e["value"] = 1e3 / e2e_ms
+    ms_step, scan_ms, topk_ms, attn_ms, e2e_ms, ms_rep, ms_shard_m, ms_shard2_m, coll_m = times.tolist()
+    e2e["ms_per_step"] = e2e_ms
+    e2e["value"] = 1e3 / e2e_ms
+    if world > 1:
+        ms_step = min(ms_rep, ms_shard_m)
 
     if rank == 0:
         peak, peak_src = measured_peaks()
-        scan_bytes = ctx_local * SCAN_BYTES_PER_KEY
+        scan_bytes = ctx * SCAN_BYTES_PER_KEY
         achieved = scan_bytes / (scan_ms * 1e-3) / 1e9
+        cfg = workload_config(args, world)
         out = {
             "metric": METRIC, "value": 1e3 / ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8 e4m3 (indexer MMA) + bf16 (MLA), fp32 accumulate",
-            "data": "synthetic", "config": workload_config(args, world),
+            "data": "synthetic", "config": cfg, "form": best_form,
             "layer_us": ms_step * 1e3,
-            "breakdown_us": {"indexer_scan": scan_ms * 1e3, "indexer_scan_with_hist_plus_memset": scan_hist_ms * 1e3,
+            "breakdown_us": {"indexer_scan": scan_ms * 1e3, "indexer_scan_without_histogram": scan_nohist_ms * 1e3,
                              "topk_select": topk_ms * 1e3,
                              "sparse_mla_partials_plus_combine": attn_ms * 1e3,
                              "sparse_mla_partials": part_ms * 1e3, "sparse_mla_combine": comb_ms * 1e3,
-                             "note": "each kernel alone: L back-to-back launches (one per layer cache) inside one graph, includes the in-graph launch gap"},
+                             "note": "each kernel alone, as the step runs it (the scan with its histogram epilogue, the "
+                                     "top-k consuming that histogram): L back-to-back launches (one per layer cache) inside "
+                                     "one graph, includes the in-graph launch gap; measured on the replicated form"},
             "roofline": {"kernel": "indexer_scan_tc_kernel" if args.scan_impl == 0 else "indexer_scan_legacy_kernel",
+                         "variant": "as the step runs it: with the histogram epilogue",
                          "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_src,
                          "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "frac_without_histogram": scan_bytes / (scan_nohist_ms * 1e-3) / 1e9 / peak,
                          "algorithmic_bytes_per_launch": scan_bytes,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from an ncu capture of
-                         # this kernel at 131072 keys x 64 heads; other shapes were not captured
-                         "traffic": SCAN_TRAFFIC_CTX128K if (args.ctx == 131072 and args.scan_impl == 0
-                                                              and not seq_shard) else None},
+                         "traffic": SCAN_TRAFFIC_CTX128K if (args.ctx == 131072 and args.scan_impl == 0) else None,
+                         "traffic_source": "constant: dram__bytes_read.sum + dram__bytes_write.sum of one launch over "
+                                           "131072 keys x 64 heads from an ncu capture (profiles/), not measured in this run"},
             "lagged_pair": lag,
-            "gpu_launches": args.steps * (8 if seq_shard else 5),
+            "gpu_launches": args.steps * (4 if best_form != "tp_heads+seq_sharded_indexer" else 5),
             "clocks": clocks,
+            "e2e": e2e,
         }
-        if e2e:
-            out["e2e"] = e2e
+        if world > 1:
+            out["forms_ms_per_step"] = {k: v for k, v in
+                                        (("tp_heads+replicated_indexer", ms_rep), ("tp_heads+seq_sharded_indexer", ms_shard_m),
+                                         ("tp_heads+seq_sharded_indexer_ctx262144", ms_shard2_m)) if v}
+            out["collective_us"] = coll_m * 1e3
+            out["comm"] = ("sharded form: every step stores this rank's 2048 (index, logit) candidates into all ranks' gather "
+                           "buffers over NVLink (peer stores, no NCCL call, no multicast) and waits on the device for the "
+                           "others' flags: inside the timed region, inside the graph; collective_us = local top-k + stores + "
+                           "wait + merge per step. Replicated form: no collective (the selection is deterministic)")
+            out.update(parity)
         if not args.no_cpu_baseline and world == 1:
             dt, cores, kind = time_cpu(ctx, 10, 2)
             out["cpu_baseline"] = {"value": 1.0 / dt, "unit": UNIT, "cores": cores, "kind": kind,
                                    "sample": f"10 full steps (ctx {ctx}, 128 heads) after 2 warm-ups, torch CPU"}
         print(json.dumps(out))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
 
 # ------------------------------------------------------------------------------ other BASELINE configs
 # (parity-test cases, measured on request; the default line above stays config 2)
