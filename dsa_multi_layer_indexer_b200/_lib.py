@@ -37,6 +37,8 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_topk_select": (_i, [_p, _p, _p, _p, _p, _p, _p, _l, _i, _l, _l, _i, C.c_int32, C.c_int32, _p]),
     "dsa_topk_select_push": (_i, [_p, _p, _p, _i, _l, _l, _i, C.c_int32, C.c_int32, _i, _i, _p, _p, _p, _p, _p]),
     "dsa_topk_merge_wait": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, C.c_int32, _l, _p]),
+    "dsa_allreduce_push": (_i, [_p, _i, _l, _i, _i, _p, _p, _p, _p]),
+    "dsa_allreduce_wait_sum": (_i, [_p, _p, _p, _p, _p, _i, _l, _i, _l, _p]),
     "dsa_ipc_export": (_i, [_p, _p, _p]),
     "dsa_ipc_open": (_i, [_p, _l, _p]),
     "dsa_ipc_close": (_i, [_p, _l]),
@@ -59,7 +61,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_quantize_e4m3_rowwise": (_i, [_p, _p, _p, _l, _i, _f, _p]),
 }
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 
 class DsaError(RuntimeError):

@@ -18,7 +18,7 @@ PKG = CSRC.parent
 LIB = PKG / "libdsa_b200.so"
 SOURCES = ["dsa_b200.cu"]
 HEADERS = ["common.cuh", "indexer_scan.cuh", "topk_select.cuh", "sparse_mla.cuh", "sparse_mla_tc.cuh",
-           "fused_decode.cuh", "decode_prep.cuh"]
+           "fused_decode.cuh", "decode_prep.cuh", "peer_allreduce.cuh"]
 PUBLIC_HEADER = PKG.parent / "include" / "dsa_b200.h"
 
 NVCC_FLAGS = [

@@ -12,6 +12,7 @@
 #include "decode_prep.cuh"
 #include "fused_decode.cuh"
 #include "indexer_scan.cuh"
+#include "peer_allreduce.cuh"
 #include "sparse_mla.cuh"
 #include "sparse_mla_tc.cuh"
 #include "topk_select.cuh"
@@ -544,6 +545,54 @@ int dsa_topk_merge_wait(const int32_t* gather_idx, const float* gather_val, cons
   p.seen = seen;
   p.wait_limit_ns = static_cast<unsigned long long>(wait_limit_ns);
   return launch_topk_cluster(p, R, n, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------ all-reduce of a decode activation
+int dsa_allreduce_push(const void* src, int src_bf16, int64_t n, int world, int rank, void* const* slots,
+                       void* const* flags, uint32_t* sent, void* stream) {
+  DSA_REQUIRE(src && slots && flags && sent, "all-reduce push: null pointer");
+  DSA_REQUIRE(world >= 1 && world <= ar::kMaxRanks && rank >= 0 && rank < world,
+              "all-reduce push: world=%d / rank=%d out of range", world, rank);
+  DSA_REQUIRE(n > 0 && n % 4 == 0 && n <= (int64_t(1) << 20), "all-reduce push: n=%lld must be a multiple of 4, at most 2^20",
+              (long long)n);
+  DSA_REQUIRE(aligned16(src), "all-reduce push: src must be 16-byte aligned");
+  ar::PushParams p{};
+  p.src = src;
+  p.src_bf16 = src_bf16 ? 1 : 0;
+  p.n = n;
+  p.n_dest = world;
+  p.src_rank = rank;
+  for (int d = 0; d < world; ++d) {
+    DSA_REQUIRE(slots[d] && flags[d] && aligned16(slots[d]), "all-reduce push: bad buffer of rank %d", d);
+    p.dest[d] = static_cast<float*>(slots[d]);
+    p.dest_flag[d] = static_cast<uint32_t*>(flags[d]) + rank;
+  }
+  p.sent = sent;
+  DSA_CUDA(launch_pdl(ar::allreduce_push_kernel, dim3(1), dim3(ar::kThreads), 0, static_cast<cudaStream_t>(stream), p));
+  return DSA_OK;
+}
+
+int dsa_allreduce_wait_sum(const float* slots, const uint32_t* flags, uint32_t* seen, const void* residual, void* out,
+                           int out_bf16, int64_t n, int world, int64_t wait_limit_ns, void* stream) {
+  DSA_REQUIRE(slots && flags && seen && out, "all-reduce sum: null pointer");
+  DSA_REQUIRE(world >= 1 && world <= ar::kMaxRanks, "all-reduce sum: world=%d out of range", world);
+  DSA_REQUIRE(n > 0 && n % 4 == 0 && n <= (int64_t(1) << 20), "all-reduce sum: n=%lld must be a multiple of 4, at most 2^20",
+              (long long)n);
+  DSA_REQUIRE(aligned16(slots) && aligned16(out) && (!residual || aligned16(residual)),
+              "all-reduce sum: pointers must be 16-byte aligned");
+  DSA_REQUIRE(wait_limit_ns > 0, "all-reduce sum: the wait needs a limit");
+  ar::SumParams p{};
+  p.slots = slots;
+  p.flags = flags;
+  p.seen = seen;
+  p.residual = residual;
+  p.out = out;
+  p.out_bf16 = out_bf16 ? 1 : 0;
+  p.n = n;
+  p.n_src = world;
+  p.wait_limit_ns = static_cast<unsigned long long>(wait_limit_ns);
+  DSA_CUDA(launch_pdl(ar::allreduce_wait_sum_kernel, dim3(1), dim3(ar::kThreads), 0, static_cast<cudaStream_t>(stream), p));
+  return DSA_OK;
 }
 
 // Peer mapping of an exchange buffer (one process per GPU): the owner exports the CUDA IPC handle

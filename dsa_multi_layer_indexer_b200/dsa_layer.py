@@ -135,6 +135,12 @@ class DSALayer(nn.Module):
         self.gate_proj = nn.Linear(c.hidden_size, c.intermediate_size, bias=False)
         self.up_proj = nn.Linear(c.hidden_size, c.intermediate_size, bias=False)
         self.down_proj = nn.Linear(c.intermediate_size, c.hidden_size, bias=False)
+        # Set by DSAModel.tensor_parallel: this module then holds one rank's heads and MLP columns,
+        # and the outputs of o_proj / down_proj are partial sums that `tp.reduce` completes.
+        self.tp = None
+
+    def _reduced(self, partial: torch.Tensor) -> torch.Tensor:
+        return partial if self.tp is None else self.tp.reduce(partial)
 
     # ------------------------------------------------------------------ helpers
     def _fast_path(self, t: torch.Tensor) -> bool:
@@ -202,7 +208,7 @@ class DSALayer(nn.Module):
         c = self.config
         _, w_uv = self._w_uk_uv()
         o = torch.einsum("bshl,hdl->bshd", o_latent, w_uv)
-        return self.o_proj(o.reshape(o.shape[0], o.shape[1], c.num_attention_heads * c.v_head_dim))
+        return self._reduced(self.o_proj(o.reshape(o.shape[0], o.shape[1], c.num_attention_heads * c.v_head_dim)))
 
     def _indexer_qkw(self, x_norm, c_q, rope: RopeCaches):
         c = self.config
@@ -276,11 +282,11 @@ class DSALayer(nn.Module):
         if (h_norm.is_cuda and h_norm.dtype == torch.bfloat16 and h_norm.dim() == 2 and h_norm.shape[0] <= 2
                 and not torch.is_grad_enabled()):
             gate, up = ops.gemv(h_norm, self.gate_proj.weight), ops.gemv(h_norm, self.up_proj.weight)
-            return self.down_proj(ops.silu_mul(gate, up))
+            return self._reduced(self.down_proj(ops.silu_mul(gate, up)))
         gate, up = self.gate_proj(h_norm), self.up_proj(h_norm)
         if gate.is_cuda and gate.dtype == torch.bfloat16 and not torch.is_grad_enabled():
-            return self.down_proj(ops.silu_mul(gate, up))  # one launch instead of two
-        return self.down_proj(torch.nn.functional.silu(gate) * up)
+            return self._reduced(self.down_proj(ops.silu_mul(gate, up)))  # one launch instead of two
+        return self._reduced(self.down_proj(torch.nn.functional.silu(gate) * up))
 
     # ------------------------------------------------------------------ decode form
     def new_cache(self, n_seq: int, capacity: int, device, fp8: bool) -> LayerDecodeCache:
@@ -408,4 +414,4 @@ class DSALayer(nn.Module):
                                    seq_lens).to(q.dtype)
         _, w_uv = self._w_uk_uv()
         ov = torch.einsum("bhl,hdl->bhd", o, w_uv)
-        return self.o_proj(ov.reshape(ov.shape[0], c.num_attention_heads * c.v_head_dim))
+        return self._reduced(self.o_proj(ov.reshape(ov.shape[0], c.num_attention_heads * c.v_head_dim)))

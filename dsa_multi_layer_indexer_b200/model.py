@@ -85,6 +85,42 @@ class DSAModel(nn.Module):
         self.layers = nn.ModuleList([DSALayer(config) for _ in range(config.num_hidden_layers)])
         self.final_norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
 
+    # ------------------------------------------------------------------ tensor parallelism
+    @classmethod
+    def tensor_parallel(cls, full_config: DSAConfig, full_state: dict, device, dtype=None, group=None,
+                        peers=None) -> "DSAModel":
+        """This rank's part of a model that is tensor-parallel over the process group: MLA heads
+        and MLP columns are split (``parallel.tp_config`` / ``shard_state_dict``), the indexer,
+        the low-rank down-projections and the norms are replicated, and every layer sums the
+        partial outputs of its row-parallel ``o_proj`` / ``down_proj`` over the ranks
+        (``parallel.TensorParallel``; the reference's RowParallelLinear,
+        src/lagged_indexer_dsa/inference/modeling/transformer.py:361-377). The indexer is
+        deterministic, so every rank selects the same keys without the reference's rank-0
+        broadcast (:1157-1164). ``full_state`` is the state_dict of the unsharded model (every
+        rank passes the same one); None leaves this rank's shard at its random initialisation,
+        created on ``device`` (benchmarks with random weights: no rank ever holds the full model).
+        ``peers`` = (PeerAllReduce, world, rank) emulates the ranks on one GPU."""
+        from .parallel import TensorParallel, shard_state_dict, tp_config
+        import torch.distributed as dist
+
+        if peers is not None:
+            _, world, rank = peers
+        else:
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+            rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if full_state is None:
+            with torch.device(device):
+                model = cls(tp_config(full_config, world))
+        else:
+            model = cls(tp_config(full_config, world))
+            model.load_state_dict(shard_state_dict(full_state, full_config, rank, world))
+        model = model.to(device=device, dtype=dtype).eval()
+        tp = TensorParallel(full_config.hidden_size, device, group, peers=peers)
+        for layer in model.layers:
+            layer.tp = tp  # the layers run one after the other: one set of buffers serves them all
+        model.tp = tp
+        return model
+
     # ------------------------------------------------------------------ shared helpers
     def _build_rope(self, seq_len: int, device, dtype) -> RopeCaches:
         c = self.config

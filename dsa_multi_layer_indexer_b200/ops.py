@@ -626,93 +626,105 @@ def decode_prep(iq_raw, w_raw, ik_raw, kv_a, q_abs, q_pe, kv_norm_w, mla_cos, ml
         1 if interleave else 0, float(eps), _stream()))
 
 
-# --------------------------------------------------------------------------- candidate exchange between GPUs
-class CandidateExchange:
-    """One rank's side of the candidate exchange of a KV-sequence-sharded indexer
-    (``dsa_topk_select_push`` / ``dsa_topk_merge_wait``).
+# --------------------------------------------------------------------------- exchanges between GPUs
+class PeerArena:
+    """ONE zeroed device allocation per rank that the other ranks of a node store into, plus the
+    addresses under which this process reaches every rank's copy. Those come from CUDA IPC
+    (``connect``: one process per GPU, handles exchanged over the process group) or, for ranks
+    emulated on one GPU, are simply the other objects' own pointers (``local_group``)."""
 
-    Holds this rank's gather buffers ``[2, rows, world, topk]`` (index and logit), the flag
-    words the other ranks post to, and the two step counters, all in ONE zeroed allocation,
-    plus the addresses under which this process reaches every other rank's copy. Those come
-    from CUDA IPC (``connect``: one process per GPU, handles exchanged over the process group)
-    or, for ranks emulated on one GPU, are simply the other objects' own pointers
-    (``local_group``). After set-up a step is two launches and touches no host state."""
-
-    def __init__(self, rows: int, topk: int, world: int, rank: int, device, wait_limit_s: float = 2.0) -> None:
+    def __init__(self, nbytes: int, world: int, rank: int, device) -> None:
         import ctypes as C
 
         _need(1 <= world <= 8 and 0 <= rank < world, "world must be 1..8 and rank inside it")
-        self.rows, self.topk, self.world, self.rank = rows, topk, world, rank
-        self.wait_limit_ns = int(wait_limit_s * 1e9)
-        n_gather = 2 * rows * world * topk
-        self._off_val = n_gather * 4
-        self._off_flags = 2 * n_gather * 4
-        self._off_sent = self._off_flags + world * rows * 4
-        self._off_seen = self._off_sent + rows * 4
-        total = self._off_seen + rows * 4
-        self.arena = torch.zeros((total + 255) // 256 * 256, dtype=torch.uint8, device=device)
-        a = self.arena
-        self.gather_idx = a[:self._off_val].view(torch.int32).view(2, rows, world, topk)
-        self.gather_val = a[self._off_val:self._off_flags].view(torch.float32).view(2, rows, world, topk)
-        self.flags = a[self._off_flags:self._off_sent].view(torch.int32).view(world, rows)
-        self.sent = a[self._off_sent:self._off_seen].view(torch.int32)
-        self.seen = a[self._off_seen:self._off_seen + rows * 4].view(torch.int32)
+        self.world, self.rank = world, rank
+        self.arena = torch.zeros((nbytes + 255) // 256 * 256, dtype=torch.uint8, device=device)
         self._bases = [None] * world       # every rank's arena as this process addresses it
-        self._bases[rank] = a.data_ptr()
+        self._bases[rank] = self.arena.data_ptr()
         self._opened = []                  # (mapped pointer, offset) of the peers' allocations
-        self._ptr_arrays = None
         self._C = C
 
-    # -- set-up ------------------------------------------------------------------
-    def _finish(self) -> None:
-        C = self._C
-        _need(all(b is not None for b in self._bases), "not every rank's buffer is mapped")
-        mk = lambda off: (C.c_void_p * self.world)(*[b + off for b in self._bases])
-        self._ptr_arrays = (mk(0), mk(self._off_val), mk(self._off_flags))
+    def _peer_pointers(self, offset: int):
+        """ctypes array of ``world`` pointers: byte ``offset`` of every rank's arena."""
+        _need(all(b is not None for b in self._bases), "not every rank's buffer is mapped: call connect() first")
+        return (self._C.c_void_p * self.world)(*[b + offset for b in self._bases])
 
-    def connect(self, group=None) -> "CandidateExchange":
+    def _mapped(self) -> None:
+        """Hook: called once every rank's arena is addressable."""
+
+    def connect(self, group=None):
         """One process per GPU: exchanges CUDA IPC handles of the arenas over ``group`` and maps
         the peers' arenas. Collective: every rank of the group calls it."""
         import torch.distributed as dist
 
         C = self._C
-        if self.world == 1:
-            self._finish()
-            return self
-        handle = (C.c_ubyte * 64)()
-        offset = C.c_int64(0)
-        _lib.check(_lib.lib().dsa_ipc_export(self.arena.data_ptr(), handle, C.byref(offset)))
-        mine = (bytes(handle), int(offset.value))
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=group)
-        for r, (h, off) in enumerate(everyone):
-            if r == self.rank:
-                continue
-            buf = (C.c_ubyte * 64).from_buffer_copy(h)
-            out = C.c_void_p(0)
-            _lib.check(_lib.lib().dsa_ipc_open(buf, off, C.byref(out)))
-            self._bases[r] = int(out.value)
-            self._opened.append((int(out.value), off))
-        self._finish()
-        torch.cuda.synchronize()
-        dist.barrier(group=group)  # nobody pushes before every arena is zeroed and mapped
+        if self.world > 1:
+            handle = (C.c_ubyte * 64)()
+            offset = C.c_int64(0)
+            _lib.check(_lib.lib().dsa_ipc_export(self.arena.data_ptr(), handle, C.byref(offset)))
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, (bytes(handle), int(offset.value)), group=group)
+            for r, (h, off) in enumerate(everyone):
+                if r == self.rank:
+                    continue
+                buf = (C.c_ubyte * 64).from_buffer_copy(h)
+                out = C.c_void_p(0)
+                _lib.check(_lib.lib().dsa_ipc_open(buf, off, C.byref(out)))
+                self._bases[r] = int(out.value)
+                self._opened.append((int(out.value), off))
+        self._mapped()
+        if self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=group)  # nobody stores before every arena is zeroed and mapped
         return self
 
     @classmethod
-    def local_group(cls, rows: int, topk: int, world: int, device, wait_limit_s: float = 2.0):
+    def local_group(cls, *args, world: int, **kwargs):
         """``world`` ranks emulated on ONE GPU (tests, single-GPU checks): every "peer" buffer is
         an ordinary local allocation. The ranks' launches must then be enqueued one after the
-        other on one stream, every push before the first merge."""
-        xs = [cls(rows, topk, world, r, device, wait_limit_s) for r in range(world)]
+        other on one stream, every push before the first wait."""
+        xs = [cls(*args, world=world, rank=r, **kwargs) for r in range(world)]
         for x in xs:
             x._bases = [y.arena.data_ptr() for y in xs]
-            x._finish()
+            x._mapped()
         return xs
 
     def close(self) -> None:
         for ptr, off in self._opened:
             _lib.lib().dsa_ipc_close(ptr, off)
         self._opened = []
+
+
+class CandidateExchange(PeerArena):
+    """One rank's side of the candidate exchange of a KV-sequence-sharded indexer
+    (``dsa_topk_select_push`` / ``dsa_topk_merge_wait``): this rank's gather buffers
+    ``[2, rows, world, topk]`` (index and logit), the flag words the other ranks post to and
+    the two step counters. After set-up a step is two launches and touches no host state."""
+
+    def __init__(self, rows: int, topk: int, world: int, rank: int, device, wait_limit_s: float = 2.0) -> None:
+        self.rows, self.topk = rows, topk
+        self.wait_limit_ns = int(wait_limit_s * 1e9)
+        n_gather = 2 * rows * world * topk
+        self._off_val = n_gather * 4
+        self._off_flags = 2 * n_gather * 4
+        self._off_sent = self._off_flags + world * rows * 4
+        self._off_seen = self._off_sent + rows * 4
+        super().__init__(self._off_seen + rows * 4, world, rank, device)
+        a = self.arena
+        self.gather_idx = a[:self._off_val].view(torch.int32).view(2, rows, world, topk)
+        self.gather_val = a[self._off_val:self._off_flags].view(torch.float32).view(2, rows, world, topk)
+        self.flags = a[self._off_flags:self._off_sent].view(torch.int32).view(world, rows)
+        self.sent = a[self._off_sent:self._off_seen].view(torch.int32)
+        self.seen = a[self._off_seen:self._off_seen + rows * 4].view(torch.int32)
+        self._ptr_arrays = None
+
+    def _mapped(self) -> None:
+        self._ptr_arrays = (self._peer_pointers(0), self._peer_pointers(self._off_val),
+                            self._peer_pointers(self._off_flags))
+
+    @classmethod
+    def local_group(cls, rows: int, topk: int, world: int, device, wait_limit_s: float = 2.0):
+        return super().local_group(rows, topk, world=world, device=device, wait_limit_s=wait_limit_s)
 
     # -- the two launches of a step ------------------------------------------------
     def push(self, logits: torch.Tensor, seq_lens: Optional[torch.Tensor] = None, *,
@@ -743,3 +755,61 @@ class CandidateExchange:
             _ptr(self.gather_idx), _ptr(self.gather_val), _ptr(self.flags), _ptr(self.seen), _ptr(out_idx),
             self.rows, self.world, self.topk, int(pad_value), self.wait_limit_ns, _stream()))
         return out_idx
+
+
+class PeerAllReduce(PeerArena):
+    """Sum of a small activation (up to ``max_elems`` values: the [B, hidden] output of a
+    row-parallel projection at decode) over the ranks of a tensor-parallel group, as two small
+    launches in stream order (``dsa_allreduce_push`` / ``dsa_allreduce_wait_sum``): capturable
+    in a CUDA graph, deterministic (rank order), with a bounded wait on the device."""
+
+    def __init__(self, max_elems: int, world: int, rank: int, device, wait_limit_s: float = 2.0) -> None:
+        _need(max_elems > 0 and max_elems % 4 == 0, "max_elems must be a positive multiple of 4")
+        self.max_elems = max_elems
+        self.wait_limit_ns = int(wait_limit_s * 1e9)
+        self._off_flags = 2 * world * max_elems * 4
+        self._off_sent = self._off_flags + 64
+        self._off_seen = self._off_sent + 16
+        super().__init__(self._off_seen + 16, world, rank, device)
+        a = self.arena
+        self.flags = a[self._off_flags:self._off_flags + world * 4].view(torch.int32)
+        self.sent = a[self._off_sent:self._off_sent + 4].view(torch.int32)
+        self.seen = a[self._off_seen:self._off_seen + 4].view(torch.int32)
+        self._ptr_arrays = None
+
+    def _mapped(self) -> None:
+        self._ptr_arrays = (self._peer_pointers(0), self._peer_pointers(self._off_flags))
+
+    @classmethod
+    def local_group(cls, max_elems: int, world: int, device, wait_limit_s: float = 2.0):
+        return super().local_group(max_elems, world=world, device=device, wait_limit_s=wait_limit_s)
+
+    def push(self, x: torch.Tensor) -> None:
+        """Stores this rank's partial ``x`` (bf16 or fp32, contiguous) into every rank's slots."""
+        _need(self._ptr_arrays is not None, "call connect() (or build the ranks with local_group) first")
+        _cuda_contig(x, "x", (torch.bfloat16, torch.float32))
+        n = x.numel()
+        _need(n % 4 == 0 and n <= self.max_elems, f"x has {n} elements: a multiple of 4, at most {self.max_elems}")
+        self._n = n
+        slots, flags = self._ptr_arrays
+        # the slot stride is the element count of THIS call: every rank passes the same shape
+        _lib.check(_lib.lib().dsa_allreduce_push(_ptr(x), 1 if x.dtype == torch.bfloat16 else 0, n, self.world,
+                                                 self.rank, slots, flags, _ptr(self.sent), _stream()))
+
+    def wait_sum(self, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``out = sum over ranks (+ residual)``, once every rank's partial of this step is there."""
+        _cuda_contig(out, "out", (torch.bfloat16, torch.float32))
+        n = out.numel()
+        _need(n == getattr(self, "_n", n), "out must have the element count that was pushed")
+        if residual is not None:
+            _cuda_contig(residual, "residual", (out.dtype,))
+            _need(residual.numel() == n, "residual must have out's element count")
+        _lib.check(_lib.lib().dsa_allreduce_wait_sum(
+            _ptr(self.arena), _ptr(self.flags), _ptr(self.seen), _ptr(residual), _ptr(out),
+            1 if out.dtype == torch.bfloat16 else 0, n, self.world, self.wait_limit_ns, _stream()))
+        return out
+
+    def all_reduce(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        self.push(x)
+        return self.wait_sum(torch.empty_like(x) if out is None else out, residual)

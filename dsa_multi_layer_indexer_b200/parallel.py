@@ -8,7 +8,7 @@ Two independent shardings:
   and the selection are replicated. The indexer is replicated too and is
   deterministic, so every rank selects the same set without the reference's
   rank-0 broadcast (transformer.py:1157-1164). The only collective is the
-  all-reduce of the row-parallel output projection (``all_reduce_hidden``).
+  all-reduce of the row-parallel projections' partial outputs (``TensorParallel``).
 * **KV-sequence-sharded indexer** (not in the reference; its closest relative is
   the per-slice top-m + exact merge inside one GPU,
   kernels/cuda_fused_sparse_splitk.py:1914-2015): rank r scans keys
@@ -56,11 +56,79 @@ def interleave_gathered(gathered: torch.Tensor, world: int, rows: int, topk: int
     return gathered.reshape(world, rows, topk).permute(1, 0, 2).reshape(rows, world * topk).contiguous()
 
 
-def all_reduce_hidden(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """Sums the per-rank partial outputs of a row-parallel projection in place."""
-    if dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(x, group=group)
-    return x
+def tp_config(config, world: int):
+    """The per-rank shapes of a layer that is tensor-parallel over ``world`` ranks: each rank owns
+    ``num_attention_heads / world`` MLA heads and ``intermediate_size / world`` MLP columns
+    (the reference's ColumnParallelLinear / RowParallelLinear split,
+    src/lagged_indexer_dsa/inference/modeling/transformer.py:293-377, :1323). The indexer, the
+    low-rank down-projections and the norms are replicated."""
+    import dataclasses
+
+    if config.num_attention_heads % world or config.intermediate_size % world:
+        raise ValueError(f"{config.num_attention_heads} heads / {config.intermediate_size} MLP columns do not split "
+                         f"over {world} ranks")
+    return dataclasses.replace(config, num_attention_heads=config.num_attention_heads // world,
+                               intermediate_size=config.intermediate_size // world)
+
+
+def shard_state_dict(state: dict, config, rank: int, world: int) -> dict:
+    """Rank ``rank``'s slice of a full model's ``state_dict``: rows of the column-parallel
+    projections (q_b_proj and kv_b_proj per head, gate_proj / up_proj per MLP column), columns of
+    the row-parallel ones (o_proj per head, down_proj per MLP column); everything else whole."""
+    h0, h1 = head_range(rank, world, config.num_attention_heads)
+    per_i = config.intermediate_size // world
+    i0, i1 = rank * per_i, (rank + 1) * per_i
+    dq = config.qk_nope_head_dim + config.qk_rope_head_dim
+    dkv = config.qk_nope_head_dim + config.v_head_dim
+    dv = config.v_head_dim
+    out = {}
+    for name, t in state.items():
+        leaf = name.rsplit(".", 2)[-2] if name.endswith(".weight") else ""
+        if leaf == "q_b_proj":
+            t = t[h0 * dq:h1 * dq]
+        elif leaf == "kv_b_proj":
+            t = t[h0 * dkv:h1 * dkv]
+        elif leaf == "o_proj":
+            t = t[:, h0 * dv:h1 * dv]
+        elif leaf in ("gate_proj", "up_proj"):
+            t = t[i0:i1]
+        elif leaf == "down_proj":
+            t = t[:, i0:i1]
+        out[name] = t.contiguous()
+    return out
+
+
+class TensorParallel:
+    """The collective of a tensor-parallel layer: the sum of the row-parallel projections' partial
+    outputs over the ranks (the reference's ``dist.all_reduce`` in RowParallelLinear,
+    transformer.py:361-377). A decode activation (a few rows of ``hidden``) goes through
+    ``ops.PeerAllReduce`` -- peer stores and a bounded wait, two small launches, capturable --
+    larger tensors (prefill) through NCCL in fp32, as the reference does."""
+
+    def __init__(self, hidden_size: int, device, group: Optional[dist.ProcessGroup] = None,
+                 max_decode_rows: int = 4, wait_limit_s: float = 2.0, peers=None) -> None:
+        from . import ops
+
+        self.group = group
+        if peers is not None:          # ranks emulated on one GPU: (PeerAllReduce of this rank, world, rank)
+            self.ar, self.world, self.rank = peers
+        else:
+            self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+            self.ar = ops.PeerAllReduce(max_decode_rows * hidden_size, self.world, self.rank, device,
+                                        wait_limit_s).connect(group)
+        self.max_decode_elems = max_decode_rows * hidden_size
+
+    def reduce(self, partial: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Sum of ``partial`` over the ranks (plus ``residual``)."""
+        if self.world == 1:
+            return partial if residual is None else partial + residual
+        if partial.dim() == 2 and partial.numel() <= self.max_decode_elems and partial.numel() % 4 == 0:
+            return self.ar.all_reduce(partial.contiguous(), None if residual is None else residual.contiguous())
+        y = partial.float()
+        dist.all_reduce(y, group=self.group)
+        y = y.to(partial.dtype)
+        return y if residual is None else y + residual
 
 
 class SeqShardedIndexer:

@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 6
+#define DSA_ABI_VERSION 7
 
 enum dsa_status {
   DSA_OK = 0,
@@ -179,6 +179,27 @@ int dsa_topk_select_push(const float* logits, const int32_t* seq_lens, uint32_t*
 int dsa_topk_merge_wait(const int32_t* gather_idx, const float* gather_val, const uint32_t* flags,
                         uint32_t* seen, int32_t* out_idx, int R, int world, int topk, int32_t pad_value,
                         int64_t wait_limit_ns, void* stream);
+/* ---- all-reduce of a decode activation across the GPUs of a tensor-parallel layer ----
+ * The reference sums the partial outputs of its row-parallel projections with
+ * dist.all_reduce in fp32 (src/lagged_indexer_dsa/inference/modeling/transformer.py:361-377
+ * RowParallelLinear, :3965 MoE / MLP output). At decode that is a [B, hidden] vector of tens
+ * of kilobytes; here it is two one-CTA launches in stream order, the same store-and-flag
+ * protocol as the candidate exchange above:
+ *   dsa_allreduce_push      src [n] (bf16 when src_bf16, else fp32) -> fp32, stored into slot
+ *                           `rank` of every rank's slots [2][world][n], then the step number
+ *                           is posted to flag word [rank] of every rank.
+ *   dsa_allreduce_wait_sum  bounded wait for all `world` flags, then
+ *                           out = (residual ? residual : 0) + sum over ranks in rank order
+ *                           (bit-identical on every rank); out / residual bf16 when out_bf16.
+ *                           With a bf16 residual the sum is rounded to bf16 before the addition.
+ * slots / flags given to the push are arrays of `world` pointers as for the candidate
+ * exchange; n a multiple of 4. Buffers start zeroed; flags uint32 [world], sent / seen one
+ * uint32 each. */
+int dsa_allreduce_push(const void* src, int src_bf16, int64_t n, int world, int rank, void* const* slots,
+                       void* const* flags, uint32_t* sent, void* stream);
+int dsa_allreduce_wait_sum(const float* slots, const uint32_t* flags, uint32_t* seen, const void* residual,
+                           void* out, int out_bf16, int64_t n, int world, int64_t wait_limit_ns, void* stream);
+
 /* Set-up of the peer mapping (CUDA IPC; one call per buffer and peer, outside any step):
  * export gives the handle of the allocation that holds `ptr` and ptr's offset inside it,
  * open maps a peer's allocation and returns the address of the same byte, close unmaps it. */

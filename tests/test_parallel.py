@@ -98,6 +98,83 @@ def test_sequence_sharded_selection_emulated_on_one_gpu():
     assert torch.equal(merged, full)
 
 
+def _tp_gloo_worker(rank: int, world: int, port: int):
+    """Sharding arithmetic of the tensor-parallel layer on the CPU: the column-parallel slices
+    give this rank's heads / MLP columns, and the row-parallel partial outputs summed over the
+    ranks (all_reduce) equal the unsharded projection."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import torch.nn.functional as F
+
+        import dsa_multi_layer_indexer_b200 as D
+        from dsa_multi_layer_indexer_b200.parallel import head_range, shard_state_dict, tp_config
+
+        cfg = D.SMALL_CONFIG
+        torch.manual_seed(0)  # the same full model on every rank
+        full = {k: v.double() for k, v in D.DSAModel(cfg).state_dict().items()}
+        mine = shard_state_dict(full, cfg, rank, world)
+        local_cfg = tp_config(cfg, world)
+        assert local_cfg.num_attention_heads * world == cfg.num_attention_heads
+        assert local_cfg.intermediate_size * world == cfg.intermediate_size
+        D.DSAModel(local_cfg).load_state_dict({k: v.float() for k, v in mine.items()})  # shapes fit
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(3, cfg.hidden_size, generator=g, dtype=torch.float64)
+        c_q = torch.randn(3, cfg.q_lora_rank, generator=g, dtype=torch.float64)
+        h0, h1 = head_range(rank, world, cfg.num_attention_heads)
+        pre = "layers.1."
+        dq = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+        q_full = F.linear(c_q, full[pre + "q_b_proj.weight"]).view(3, cfg.num_attention_heads, dq)
+        q_mine = F.linear(c_q, mine[pre + "q_b_proj.weight"]).view(3, h1 - h0, dq)
+        assert torch.equal(q_mine, q_full[:, h0:h1])
+        attn = torch.randn(3, cfg.num_attention_heads, cfg.v_head_dim, generator=g, dtype=torch.float64)
+        part = F.linear(attn[:, h0:h1].reshape(3, -1), mine[pre + "o_proj.weight"])
+        dist.all_reduce(part)
+        assert torch.allclose(part, F.linear(attn.reshape(3, -1), full[pre + "o_proj.weight"]), rtol=1e-12, atol=1e-12)
+        mlp = lambda sd: F.linear(F.silu(F.linear(x, sd[pre + "gate_proj.weight"])) * F.linear(x, sd[pre + "up_proj.weight"]),
+                                  sd[pre + "down_proj.weight"])
+        part = mlp(mine)
+        dist.all_reduce(part)
+        assert torch.allclose(part, mlp(full), rtol=1e-12, atol=1e-12)
+        for name in ("index_q_proj", "index_k_proj", "index_weights_proj", "q_a_proj", "kv_a_proj"):
+            assert torch.equal(mine[pre + name + ".weight"], full[pre + name + ".weight"])  # replicated
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_sharding_arithmetic_gloo(world):
+    mp.spawn(_tp_gloo_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,dtype", [(2, torch.bfloat16), (4, torch.float32), (8, torch.bfloat16)])
+def test_peer_all_reduce_emulated_on_one_gpu(world, dtype):
+    """The all-reduce kernels with every "rank" on one GPU: all pushes, then every rank's sum. The
+    result is the fp32 sum in rank order (plus the residual), identical on every rank; three steps
+    exercise both slot parities."""
+    from dsa_multi_layer_indexer_b200 import _lib, ops
+
+    n = 2 * 7168
+    ars = ops.PeerAllReduce.local_group(4 * 7168, world, "cuda")
+    for step in range(3):
+        g = torch.Generator().manual_seed(step)
+        parts = [torch.randn(2, 7168, generator=g).to(dtype) for _ in range(world)]
+        res = torch.randn(2, 7168, generator=g).to(dtype)
+        want = parts[0].float()
+        for t in parts[1:]:
+            want = want + t.float()
+        want = (want.to(dtype).float() + res.float()).to(dtype) if dtype == torch.bfloat16 else want + res
+        for r in range(world):
+            ars[r].push(parts[r].cuda())
+        outs = [ars[r].wait_sum(torch.empty(2, 7168, dtype=dtype, device="cuda"), res.cuda()) for r in range(world)]
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        for o in outs:
+            assert torch.equal(o.cpu(), want), f"step {step}"
+    assert n == parts[0].numel()
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_store_exchange_emulated_on_one_gpu(world):
@@ -221,4 +298,74 @@ def test_sequence_sharded_indexer_and_tp_heads_nccl(tmp_path):
         pytest.skip("needs two GPUs")
     out = tmp_path / "result.txt"
     mp.spawn(_nccl_worker, args=(2, _free_port(), 30000, 2048, str(out)), nprocs=2, join=True)
+    assert out.read_text() == "ok"
+
+
+def _tp_model_worker(rank: int, world: int, port: int, out_path: str):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import dataclasses
+
+        import dsa_multi_layer_indexer_b200 as D
+        from dsa_multi_layer_indexer_b200 import _lib
+
+        cfg = dataclasses.replace(D.SMALL_CONFIG, num_hidden_layers=8)
+        torch.manual_seed(4)  # the same full model on every rank
+        full = D.DSAModel(cfg).eval()
+        tp_model = D.DSAModel.tensor_parallel(cfg, full.state_dict(), "cuda")
+        B, S0, steps = 2, 24, 4
+        g = torch.Generator().manual_seed(9)
+        prompt = torch.randn(B, S0, cfg.hidden_size, generator=g).cuda()
+        toks = torch.randn(steps, B, cfg.hidden_size, generator=g).cuda()
+        mode, cold = D.ScheduleMode.LAGGED_FUSED, D.ColdStartPolicy.EAGER
+        st = tp_model.init_decode(B, 32, fp8=False)
+        h_pre = tp_model.prefill(st, prompt, mode, cold)
+        outs, sets = [h_pre], []
+        for t in range(steps - 1):
+            rec = {}
+            outs.append(tp_model.decode_step(st, toks[t], mode, cold, record=rec).clone())
+            sets.append([None if p is None else p.clone() for p in rec["produced"]])
+        # the last step through a captured graph: the all-reduces are kernels inside it
+        graph, x_in, x_out = tp_model.capture_decode(st, mode, cold, overlap=True)
+        x_in.copy_(toks[steps - 1])
+        graph.replay()
+        torch.cuda.synchronize()
+        outs.append(x_out.clone())
+        _lib.check_device_status()
+        ok = True
+        if rank == 0:
+            one = full.cuda()
+            s1 = one.init_decode(B, 32, fp8=False)
+            refs, ref_sets = [one.prefill(s1, prompt, mode, cold)], []
+            for t in range(steps):
+                rec = {}
+                refs.append(one.decode_step(s1, toks[t], mode, cold, record=rec).clone())
+                ref_sets.append([None if p is None else p.clone() for p in rec["produced"]])
+            for a, b in zip(outs, refs):
+                err = float((a - b).abs().max() / b.abs().max())
+                ok = ok and err < 1e-4
+            for got, want in zip(sets, ref_sets):
+                for p, q in zip(got, want):
+                    ok = ok and ((p is None) == (q is None)) and (p is None or torch.equal(p, q))
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.broadcast(flag, 0)
+        if rank == 0:
+            with open(out_path, "w") as f:
+                f.write("ok" if ok else "mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_tensor_parallel_model_equals_the_unsharded_one(tmp_path):
+    """Eight layers of the small configuration, tensor-parallel over two GPUs (heads and MLP columns
+    split, o_proj / down_proj partial sums all-reduced by peer stores, indexer replicated): prefill
+    and decode hidden states equal the one-GPU model's within 1e-4 (fp32), every produced index set
+    is identical, and a decode step captured in a CUDA graph contains its all-reduces."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = tmp_path / "result.txt"
+    mp.spawn(_tp_model_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
     assert out.read_text() == "ok"

@@ -16,7 +16,9 @@ ATTN_TOL = 2e-2
 LOGIT_TOL = 1e-2
 
 
-def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=31, lens=None):
+def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=31, lens=None, lat_rows=None):
+    """lat_rows: build the latent pool from this many distinct random rows, repeated (a pool of
+    two million distinct rows would only cost host time and memory)."""
     g = torch.Generator().manual_seed(seed)
     lens = [cap, 700, 1300][:B] if lens is None else list(lens)
     B = len(lens)
@@ -30,7 +32,8 @@ def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=
     wp = torch.empty(B, hidx)
     ref_logits = torch.full((B, cap), float("-inf"))
     # latent rows live in one pool addressed by KV slot = page * 64 + offset
-    lat = torch.randn(num_pages * 64, 576, generator=g)
+    n_slots = num_pages * 64
+    lat = torch.randn(lat_rows or n_slots, 576, generator=g)
     for b in range(B):
         ik = torch.randn(cap, 128, generator=g)
         q8, k8, wf, sk = O.make_fp8_indexer_inputs(iq[b:b + 1], ik, w[b:b + 1])
@@ -45,6 +48,8 @@ def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=
     pos2slot = (perm.long().repeat_interleave(64, dim=1) * 64 + torch.arange(64).repeat(pages_per)).int()
     kv_pool = O.pack_fp8_latent(lat) if fp8_pool else lat.to(torch.bfloat16)
     kv_ref = O.unpack_fp8_latent(kv_pool) if fp8_pool else kv_pool
+    if lat_rows:  # slot s holds distinct row s % lat_rows
+        kv_pool = kv_pool[torch.arange(n_slots) % lat_rows].contiguous()
     q = torch.randn(1, B, heads, 576, generator=g).to(torch.bfloat16)
     inc = torch.stack([pos2slot[b, torch.randperm(lens[b], generator=g)[:topk].sort().values.long()
                                   if lens[b] >= topk else
@@ -55,7 +60,8 @@ def build_case(fp8_pool: bool, B=3, cap=2048, heads=16, hidx=64, topk=512, seed=
             inc[b, lens[b]:] = -1
     inc[:, 5::37] = -1  # padding entries are skipped
     return dict(B=B, cap=cap, heads=heads, hidx=hidx, topk=topk, lens=lens, q=q, kv_pool=kv_pool, kv_ref=kv_ref,
-                inc=inc, iq8=iq8, wp=wp, pages=pool_pages, pt=perm, pos2slot=pos2slot, ref_logits=ref_logits)
+                inc=inc, iq8=iq8, wp=wp, pages=pool_pages, pt=perm, pos2slot=pos2slot, ref_logits=ref_logits,
+                lat_rows=lat_rows, n_slots=n_slots)
 
 
 def call(case, **kw):
@@ -70,9 +76,17 @@ def call(case, **kw):
 
 def ref_attention(c):
     out = torch.zeros(c["B"], c["heads"], 512)
-    n = c["kv_ref"].shape[0]
+    n = c["n_slots"]
     for b in range(c["B"]):
-        out[b] = O.sparse_mla_decode(c["q"][0, b:b + 1], c["kv_ref"], c["inc"][b:b + 1], [n], 192 ** -0.5)[0]
+        inc = c["inc"][b:b + 1]
+        if c["lat_rows"]:  # the rows this sequence selected, gathered from the distinct ones
+            live = (inc[0] >= 0) & (inc[0] < n)
+            rows = c["kv_ref"][inc[0][live].long() % c["lat_rows"]]
+            local = torch.full_like(inc, -1)
+            local[0, live] = torch.arange(int(live.sum()), dtype=inc.dtype)
+            out[b] = O.sparse_mla_decode(c["q"][0, b:b + 1], rows, local, [rows.shape[0]], 192 ** -0.5)[0]
+        else:
+            out[b] = O.sparse_mla_decode(c["q"][0, b:b + 1], c["kv_ref"], inc, [n], 192 ** -0.5)[0]
     return out
 
 
@@ -178,6 +192,32 @@ def test_ragged_batch_at_serving_size():
     got = [sorted(v for v in row if v >= 0) for row in nxt.cpu().tolist()]
     assert got == ref_next(c)
     _lib.check_device_status()
+
+
+def test_batch32_ragged_paged_fp8_at_its_full_size():
+    """The batched configuration at its own size: 32 rows, lengths drawn as the benchmark draws them
+    (torch.randint(16384, 65537) under seed 0), page-64 FP8 index keys behind a shuffled page table,
+    FP8-packed 656-byte latent rows, 128 heads, top-2048, through the serving entry: every row's
+    selected set bit-exact (scales with a margin around the cutoff), attention within 2e-2."""
+    from dsa_multi_layer_indexer_b200 import _lib, serving
+
+    serving.clear_scratch()
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(16384, 65537, (32,), generator=g, dtype=torch.int32).tolist()
+    c = build_case(True, cap=65536, heads=128, topk=2048, seed=44, lens=lens, lat_rows=1 << 16)
+    attn, nxt, logits = call(c, return_logits=True)
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    lg = logits.cpu()
+    for b, ln in enumerate(lens):
+        assert rel_err(lg[b:b + 1, :ln], c["ref_logits"][b:b + 1, :ln]) < LOGIT_TOL
+        assert torch.isinf(lg[b, ln:]).all()
+    got = [sorted(v for v in row if v >= 0) for row in nxt.cpu().tolist()]
+    assert got == ref_next(c)
+    ref = ref_attention(c)
+    assert rel_err(attn[0].float().cpu(), ref) < ATTN_TOL
+    assert corr_diff(attn[0].float().cpu(), ref) < 1e-3
+    serving.clear_scratch()
 
 
 def test_forward_hide_operands_stages_and_feeds_the_paged_scan():
