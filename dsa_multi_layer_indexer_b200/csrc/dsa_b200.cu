@@ -394,8 +394,10 @@ int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
 static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStream_t st) {
   int rc = opt_in_smem(topk::topk_cluster_kernel, sizeof(topk::ClShared), g_opt_topk_cluster);
   if (rc) return rc;
-  int ctas = 1;  // at least 4 logits per thread before another CTA is added
-  while (ctas < topk::kClMaxCtas && int64_t(ctas) * topk::kClThreads * 4 < n) ctas *= 2;
+  // As few CTAs as hold the row at 32 logits per thread: every CTA added costs cluster barriers and
+  // remote reductions, and a row of up to 16384 logits needs none of either.
+  int ctas = 1;
+  while (ctas < topk::kClMaxCtas && int64_t(ctas) * topk::kClThreads * topk::kClMaxKeys < n) ctas *= 2;
   const int64_t per_key = int64_t(ctas) * topk::kClThreads;
   const int nk = int((n + per_key - 1) / per_key);
   cudaLaunchConfig_t cfg{};

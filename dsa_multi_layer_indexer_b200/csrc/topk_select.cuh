@@ -598,9 +598,13 @@ __device__ __forceinline__ void hist_push_warp(uint32_t* whole, bool pred, uint3
   uint32_t add = 0;
   if (pred) add = digit != first ? 1u : (int(threadIdx.x & 31) == leader ? uint32_t(__popc(same)) : 0u);
   if (add) {
-    const uint32_t a = smem_u32(whole + digit);
+    if (n_ctas == 1) {
+      smem_red_add(whole + digit, add);
+    } else {
+      const uint32_t a = smem_u32(whole + digit);
 #pragma unroll 1
-    for (uint32_t cc = 0; cc < n_ctas; ++cc) cluster_red_add(cluster_map(a, cc), add);
+      for (uint32_t cc = 0; cc < n_ctas; ++cc) cluster_red_add(cluster_map(a, cc), add);
+    }
   }
 }
 
@@ -684,6 +688,17 @@ __device__ __forceinline__ void find_kth_bin(const uint32_t* h, uint32_t k, uint
   __syncthreads();
 }
 
+// Barrier over the whole cluster (release / acquire), or over the CTA alone when the cluster
+// is a single CTA: rows of up to 16384 logits run without any cluster operation.
+__device__ __forceinline__ void cluster_sync_all(bool solo) {
+  if (solo) {
+    __syncthreads();
+  } else {
+    cluster_arrive();
+    cluster_wait();
+  }
+}
+
 __global__ void __launch_bounds__(kClThreads, 1)
 topk_cluster_kernel(const Params p, const int nk) {
   extern __shared__ __align__(128) uint8_t topk_cl_smem[];
@@ -691,6 +706,7 @@ topk_cluster_kernel(const Params p, const int nk) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = blockIdx.y;
   const uint32_t c = cluster_cta_rank(), C = cluster_num_ctas();
+  const bool solo = C == 1;
   const int stamp_cta = 512 + r * int(C) + int(c);
   DSA_KTIME_BEGIN(1);
   DSA_STAMP(stamp_cta, 0);
@@ -763,7 +779,7 @@ topk_cluster_kernel(const Params p, const int nk) {
     for (int i = (have_hist ? kBins / 4 : 0) + tid; i < kZero16; i += kClThreads)  // (a given hist1 is overwritten)
       z[i] = make_uint4(0, 0, 0, 0);
   }
-  cluster_arrive();
+  if (!solo) cluster_arrive();
   DSA_STAMP(stamp_cta, 1);
 
   // The slice is in shared memory once the bulk copy has landed; positions past the row's length
@@ -805,18 +821,21 @@ topk_cluster_kernel(const Params p, const int nk) {
         hist_add_warp(local1, in, ordered_key(v) >> kLowBits);
       }
       __syncthreads();
-      cluster_wait();  // every CTA of the cluster runs and has cleared its histograms: remote adds may start
+      if (!solo) cluster_wait();  // every CTA of the cluster runs and has cleared its histograms: remote adds may start
       for (int i = tid; i < kBins; i += kClThreads) {
         const uint32_t x = local1[i];
         if (x) {
           local1[i] = 0;
-          const uint32_t a = smem_u32(&sh.hist1[i]);
+          if (solo) {
+            sh.hist1[i] = x;
+          } else {
+            const uint32_t a = smem_u32(&sh.hist1[i]);
 #pragma unroll 1
-          for (uint32_t cc = 0; cc < C; ++cc) cluster_red_add(cluster_map(a, cc), x);
+            for (uint32_t cc = 0; cc < C; ++cc) cluster_red_add(cluster_map(a, cc), x);
+          }
         }
       }
-      cluster_arrive();
-      cluster_wait();
+      cluster_sync_all(solo);
     }
     find_kth_bin<kBins>(sh.hist1, uint32_t(p.topk), sh.warp_tot, sh.res);
     T = sh.res[0];
@@ -869,19 +888,20 @@ topk_cluster_kernel(const Params p, const int nk) {
     });
     DSA_STAMP(stamp_cta, 8);
     __syncthreads();
-    if (have_hist) cluster_wait();  // (see above; without the scan's histogram it was taken at level 1)
+    if (have_hist && !solo) cluster_wait();  // (see above; without the scan's histogram it was taken at level 1)
     DSA_STAMP(stamp_cta, 9);
     if (tid < kL2Bins) {
       const uint32_t x = sh.local2[tid];
-      if (x) {
+      if (x && solo) {
+        sh.hist2[tid] = x;
+      } else if (x) {
         const uint32_t a = smem_u32(&sh.hist2[tid]);
 #pragma unroll 1
         for (uint32_t cc = 0; cc < C; ++cc) cluster_red_add(cluster_map(a, cc), x);
       }
     }
     DSA_STAMP(stamp_cta, 10);
-    cluster_arrive();
-    cluster_wait();
+    cluster_sync_all(solo);
     DSA_STAMP(stamp_cta, 11);
     find_kth_bin<kL2Bins>(sh.hist2, need, sh.warp_tot, sh.res);
     const uint32_t p19 = (T << kL2Bits) | sh.res[0];
@@ -892,8 +912,7 @@ topk_cluster_kernel(const Params p, const int nk) {
       hist_push_warp(sh.hist3, live && (key >> kL3Bits) == p19, swizzled_bin<kL3Bins>(key & (kL3Bins - 1)), C);
     });
     DSA_STAMP(stamp_cta, 12);
-    cluster_arrive();
-    cluster_wait();
+    cluster_sync_all(solo);
     DSA_STAMP(stamp_cta, 13);
     find_kth_bin<kL3Bins, true>(sh.hist3, need2, sh.warp_tot, sh.res);
     kstar = (p19 << kL3Bits) | sh.res[0];  // the k-th largest key of the row
@@ -905,7 +924,7 @@ topk_cluster_kernel(const Params p, const int nk) {
       else if (live && key == kstar) smem_red_or(&sh.ties[warp][i], 1u << lane);
     });
     __syncwarp();
-  } else {
+  } else if (!solo) {
     cluster_wait();
   }
 
@@ -922,10 +941,13 @@ topk_cluster_kernel(const Params p, const int nk) {
     const uint32_t winc = warp_inclusive_scan(wt);  // at most 16384 of each kind per CTA
     if (lane < kClWarps) sh.warp_base[lane] = winc - wt;
     const uint32_t cta_sum = __shfl_sync(0xffffffffu, winc, 31);
-    if (lane < int(C)) cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(lane)), cta_sum);
+    if (solo) {
+      if (lane == 0) sh.cta_tot[0] = cta_sum;
+    } else if (lane < int(C)) {
+      cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(lane)), cta_sum);
+    }
   }
-  cluster_arrive();
-  cluster_wait();
+  cluster_sync_all(solo);
   uint32_t g_before, q_before, g_total, q_total;
   {
     const uint32_t t = lane < int(C) ? sh.cta_tot[lane] : 0u;
@@ -996,8 +1018,7 @@ topk_cluster_kernel(const Params p, const int nk) {
     // Every thread's stores are ordered before the barrier at system scope; behind the barrier one
     // thread posts the row's step number to every rank (release): whoever reads it sees the data.
     __threadfence_system();
-    cluster_arrive();
-    cluster_wait();
+    cluster_sync_all(solo);
     if (c == 0 && tid == 0) {
       for (int d = 0; d < n_dest; ++d) st_release_sys(p.dest_flag[d] + r, step);
       p.sent[r] = step;

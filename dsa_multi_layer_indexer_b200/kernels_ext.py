@@ -34,6 +34,19 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
+_LENS = {}
+
+
+def _causal_lens(S: int, Skv: int, device) -> torch.Tensor:
+    """Visible keys of each of the S query rows of one sequence (row s sees Skv - S + s + 1),
+    built once per (S, Skv, device): a launch then allocates nothing and stays capturable."""
+    key = (S, Skv, str(device))
+    lens = _LENS.get(key)
+    if lens is None:
+        lens = _LENS[key] = torch.arange(Skv - S + 1, Skv + 1, dtype=torch.int32, device=device)
+    return lens
+
+
 def _check_modes(with_select: int, win: int) -> None:
     if with_select not in (0, 1, 2):
         raise RuntimeError("with_select >= 3 (tap cascade) is not provided by this build")
@@ -50,7 +63,7 @@ class FusedSparseSplitK:
         """One sequence, S query rows; row s sees keys [0, Skv - S + s]."""
         _check_modes(with_select, win)
         lib = _lib.lib()
-        lens = torch.arange(Skv - S + 1, Skv + 1, dtype=torch.int32, device=Q.device)
+        lens = _causal_lens(S, Skv, Q.device)
         if attn_on:
             _lib.check(lib.dsa_sparse_mla_decode(_p(Q), _p(KV), _p(Indices), _p(lens), _p(PartAcc), _p(PartM),
                                                  _p(PartL), _p(Out), S, S, H, topk, nsplit, float(sm_scale), Skv, 0,
