@@ -150,6 +150,9 @@ __device__ __forceinline__ void cluster_red_add(uint32_t cluster_addr, uint32_t 
 __device__ __forceinline__ void cluster_st(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void cluster_st2(uint32_t cluster_addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared::cluster.v2.u32 [%0], {%1, %2};" ::"r"(cluster_addr), "r"(a), "r"(b) : "memory");
+}
 // Hardware barrier over every thread of the cluster (the CTAs of a cluster are
 // co-scheduled, so this is not a wait on another launch). Split in two so that work
 // can sit between the arrival and the wait.

@@ -557,19 +557,31 @@ constexpr int64_t kClMaxN = int64_t(kClMaxCtas) * kClThreads * kClMaxKeys;  // 1
 constexpr int kL2Bits = 7, kL2Bins = 1 << kL2Bits;            // key bits 19..13
 constexpr int kL3Bits = 13, kL3Bins = 1 << kL3Bits;           // key bits 12..0
 constexpr int kWarpKeys = 32 * kClMaxKeys;                    // 1024: a warp's share of the slice
+constexpr int kListCap = 256;                                 // candidates a CTA may list (else: histograms)
+constexpr int kSurvCap = 256;                                 // candidates ranked by comparison (else: histograms)
 
 struct ClShared {
   uint32_t hist1[kBins];         // level 1: whole row (copy of the scan's, or pushed by the CTAs)
   uint32_t hist3[kL3Bins];       // level 3: whole row, pushed; stored as swizzled_bin<kL3Bins> says
   uint32_t hist2[kL2Bins];       // level 2: whole row, pushed
   uint32_t local2[kL2Bins];      // level 2: this CTA's part
+  uint32_t cand_kept[kClMaxCtas];  // per CTA of the cluster: its candidates that are kept (list path)
+  uint32_t surv_n;               // entries of surv[]
+  uint32_t list_n;               // this CTA's candidates (slots handed out in its region of the list)
+  uint32_t above_n;              // this CTA's certainly kept logits
+  uint32_t pad0;
   uint32_t kept[kClWarps][kClMaxKeys];   // bit (w, i, l): position w * 32 * nk + i * 32 + l of the slice is kept
   uint32_t ties[kClWarps][kClMaxKeys];   // same, for the elements equal to k*
   uint32_t warp_tot[kClWarps];
   uint32_t warp_base[kClWarps];
   uint32_t cta_tot[kClMaxCtas];  // (ties << 16 | kept) of every CTA of the cluster
+  uint32_t cnts[kClMaxCtas];     // (certainly kept << 16 | candidates) of every CTA, pushed with the list
   uint32_t res[4];
+  uint64_t surv[kSurvCap + 4];   // key << 32 | ~place of the candidates sharing the k-th key's top 19 bits (+ 4 zeros)
+  alignas(16) uint32_t tbl[kClMaxCtas][kL2Bins];  // level 2: every CTA's histogram of its candidates, pushed
   uint64_t load_bar;                       // mbarrier of the slice's bulk copy
+  uint2 list[kClMaxCtas][kListCap];        // (key, place) of every CTA's candidates, pushed; place =
+                                           // CTA << 14 | warp << 10 | word << 5 | bit orders like the position
   alignas(128) uint32_t bits[kClWarps][kWarpKeys];  // (a bulk copy's destination must be 16-byte aligned)      // the slice's raw logits: word (w, i * 32 + l) is thread (w, l)'s i-th
 };
 static_assert(kL3Bins >= kBins, "hist3 doubles as the local level-1 histogram");
@@ -636,6 +648,77 @@ __device__ __forceinline__ uint32_t swizzled_bin(uint32_t b) {
   return (((q % PERC) * kClThreads + q / PERC) << 2) | (rb & 3u);
 }
 
+// The same for a 128-bin histogram (16-byte aligned), by one warp: lane l owns bins
+// 127 - 4 l down to 124 - 4 l; one warp scan, one barrier.
+template <int NB>
+__device__ __forceinline__ void find_kth_bin_warp(const uint32_t* h, uint32_t k, uint32_t* res) {
+  static_assert(NB == 128, "four bins per lane");
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const uint4 x = reinterpret_cast<const uint4*>(h)[31 - lane];
+    const uint32_t cnt[4] = {x.w, x.z, x.y, x.x};  // highest bin first
+    const uint32_t s = cnt[0] + cnt[1] + cnt[2] + cnt[3];
+    const uint32_t inc = warp_inclusive_scan(s);
+    const uint32_t hit = __ballot_sync(0xffffffffu, inc >= k);
+    if (hit == 0u) {
+      if (lane == 0) res[0] = 0u, res[1] = 1u;  // k exceeds the total (never with a consistent caller)
+    } else if (lane == __ffs(hit) - 1) {
+      uint32_t running = inc - s, b = 0, rk = 1;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (running < k && k <= running + cnt[i]) {
+          b = uint32_t(i);
+          rk = k - running;
+        }
+        running += cnt[i];
+      }
+      res[0] = uint32_t(NB - 1 - 4 * lane) - b;
+      res[1] = rk;
+    }
+  }
+  __syncthreads();
+}
+
+// The same over the sum of n_tbl 128-bin tables that lie one after the other; res[2] gets the
+// size of the bin found.
+__device__ __forceinline__ void find_kth_bin_tables(const uint32_t* tbl, int n_tbl, uint32_t k, uint32_t* res) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    uint32_t cnt[4] = {0u, 0u, 0u, 0u};  // highest bin first
+#pragma unroll
+    for (int t = 0; t < kClMaxCtas; ++t) {
+      if (t < n_tbl) {
+        const uint4 x = reinterpret_cast<const uint4*>(tbl + t * kL2Bins)[31 - lane];
+        cnt[0] += x.w, cnt[1] += x.z, cnt[2] += x.y, cnt[3] += x.x;
+      }
+    }
+    const uint32_t s = cnt[0] + cnt[1] + cnt[2] + cnt[3];
+    const uint32_t inc = warp_inclusive_scan(s);
+    const uint32_t hit = __ballot_sync(0xffffffffu, inc >= k);
+    if (hit == 0u) {
+      if (lane == 0) res[0] = 0u, res[1] = 1u, res[2] = 0u;  // k exceeds the total (never with a consistent caller)
+    } else if (lane == __ffs(hit) - 1) {
+      uint32_t running = inc - s, b = 0, rk = 1, size = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (running < k && k <= running + cnt[i]) {
+          b = uint32_t(i);
+          rk = k - running;
+          size = cnt[i];
+        }
+        running += cnt[i];
+      }
+      res[0] = uint32_t(kL2Bins - 1 - 4 * lane) - b;
+      res[1] = rk;
+      res[2] = size;
+    }
+  }
+  __syncthreads();
+}
+
+template <int NB, int PER>
+__device__ __forceinline__ void find_kth_in_registers(const uint32_t (&cnt)[PER], uint32_t k, uint32_t* warp_tot, uint32_t* res);
+
 template <int NB, bool kSwz = false>
 __device__ __forceinline__ void find_kth_bin(const uint32_t* h, uint32_t k, uint32_t* warp_tot, uint32_t* res) {
   constexpr int PER = NB >= kClThreads ? NB / kClThreads : 1;
@@ -658,18 +741,25 @@ __device__ __forceinline__ void find_kth_bin(const uint32_t* h, uint32_t k, uint
   } else {
     cnt[0] = tid < NB ? h[NB - 1 - tid] : 0u;
   }
+  find_kth_in_registers<NB, PER>(cnt, k, warp_tot, res);
+}
+
+// The search proper: thread t holds its PER bins (highest first) in registers.
+template <int NB, int PER>
+__device__ __forceinline__ void find_kth_in_registers(const uint32_t (&cnt)[PER], uint32_t k, uint32_t* warp_tot, uint32_t* res) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint32_t s = 0;
 #pragma unroll
   for (int i = 0; i < PER; ++i) s += cnt[i];
-  const uint32_t inc = warp_inclusive_scan(s);
-  if (lane == 31) warp_tot[warp] = inc;
+  const uint32_t wsum = __reduce_add_sync(0xffffffffu, s);
+  if (lane == 0) warp_tot[warp] = wsum;
   if (tid == 0) res[0] = 0u, res[1] = 1u;  // stays if k exceeds the histogram's total (never with a consistent caller)
   __syncthreads();
   const uint32_t wt = lane < kClWarps ? warp_tot[lane] : 0u;
-  const uint32_t winc = warp_inclusive_scan(wt);
-  const uint32_t before_warp = __shfl_sync(0xffffffffu, winc - wt, warp);
-  const uint32_t k2 = k - before_warp;  // (wraps for the warps past the k-th element: they fail the test below)
-  if (before_warp < k && k2 <= __shfl_sync(0xffffffffu, inc, 31)) {  // this warp holds the k-th element
+  const uint32_t before_warp = __reduce_add_sync(0xffffffffu, lane < warp ? wt : 0u);
+  if (before_warp < k && k - before_warp <= wsum) {  // this warp holds the k-th element: only it scans
+    const uint32_t k2 = k - before_warp;
+    const uint32_t inc = warp_inclusive_scan(s);
     const uint32_t hit = __ballot_sync(0xffffffffu, inc >= k2);
     if (lane == __ffs(hit) - 1) {
       uint32_t running = inc - s, b = 0, rk = 1;
@@ -715,18 +805,55 @@ topk_cluster_kernel(const Params p, const int nk) {
     mbar_init(smem_u32(&sh.load_bar), 1);
     mbar_fence_init();
   }
+  // ---- before anything of the previous launch is needed: clear what is accumulated into and tell
+  // the cluster it is clear (shared memory only, so this runs while the previous launch drains)
+  {
+    static_assert(offsetof(ClShared, warp_tot) % 16 == 0, "the cleared part is whole 16-byte words");
+    constexpr int kZero16 = int(offsetof(ClShared, warp_tot) / 16);  // the histograms and both masks
+    uint4* z = reinterpret_cast<uint4*>(&sh);
+    for (int i = (have_hist ? kBins / 4 : 0) + tid; i < kZero16; i += kClThreads)  // (a given hist1 is overwritten)
+      z[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (!solo) cluster_arrive();
   pdl_wait();
+  DSA_STAMP(stamp_cta, 15);
   pdl_launch_dependents();
   const int R = int(gridDim.y);
+  // ---- loads. The CTA's slice (positions slice_base .. + span) comes into shared memory as it
+  // lies in global memory, by one bulk copy when the row is 16-byte aligned. Thread (warp, lane)
+  // then owns positions warp_off + i * 32 + lane of the slice, i < nk: conflict-free reads, and
+  // (i, lane) is ascending position order. The copy and the histogram loads do not wait for the
+  // row's length: what lies past it is overwritten after the copy has landed.
+  const int span = kClThreads * nk;
+  const int slice_base = int(c) * span;
+  const int warp_off = warp * (32 * nk);
+  uint32_t* flat = &sh.bits[0][0];
+  const int avail = max(0, min(int(p.n), slice_base + span) - slice_base);  // of the slice, inside the buffer
+  const float* row = p.logits + int64_t(r) * p.slab_stride;
+  // (candidates another GPU wrote are read with plain loads, not by the copy engine)
+  const bool bulk = avail > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.n_src == 0;
+  const int bulk_elems = bulk ? (avail & ~3) : 0;
+  const uint32_t bar = smem_u32(&sh.load_bar);
+  if (tid == 0 && bulk_elems > 0) {
+    mbar_arrive_expect_tx(bar, uint32_t(bulk_elems) * 4u);
+    bulk_g2s(smem_u32(flat), row + slice_base, uint32_t(bulk_elems) * 4u, bar);
+  }
+  uint4 h1a = make_uint4(0, 0, 0, 0), h1b = h1a;
+  if (have_hist) {  // this thread's 8 bins of the scan's histogram
+    const uint4* gh = reinterpret_cast<const uint4*>(p.hist + size_t(r) * kBins + (kBins - 8 * (tid + 1)));
+    h1a = __ldcg(gh);
+    h1b = __ldcg(gh + 1);
+  }
   // Candidate exchange: this row's step number picks one of the two gather buffers, so that a
   // rank already pushing step e + 1 does not overwrite what a slower rank still merges for step e.
   const uint32_t step = p.n_dest > 0 ? p.sent[r] + 1u : (p.n_src > 0 ? p.seen[r] + 1u : 0u);
   const int64_t gather_row = int64_t(step & 1u) * R + r;  // (= r outside an exchange)
-  const float* row = p.logits + (p.n_src > 0 ? gather_row : int64_t(r)) * p.slab_stride;
+  if (p.n_src > 0) row = p.logits + gather_row * p.slab_stride;
   int64_t len64 = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len64 = len64 < 0 ? 0 : (len64 > p.n ? p.n : len64);
   const int len = int(len64);
   const bool take_all = len <= p.topk;
+  const int live = max(0, min(len - slice_base, span));  // of the slice, visible
   if (p.n_src > 0) {
     // Merge side: the candidates of every source must have landed. One thread polls the flags the
     // sources set behind their data; the wait is bounded by wall time, and when it runs out the
@@ -744,42 +871,8 @@ topk_cluster_kernel(const Params p, const int nk) {
     }
     __syncthreads();
   }
-
-  // ---- loads. The CTA's slice (positions slice_base .. + span) comes into shared memory as it
-  // lies in global memory, by one bulk copy when the row is 16-byte aligned. Thread (warp, lane)
-  // then owns positions warp_off + i * 32 + lane of the slice, i < nk: conflict-free reads, and
-  // (i, lane) is ascending position order.
-  const int span = kClThreads * nk;
-  const int slice_base = int(c) * span;
-  const int warp_off = warp * (32 * nk);
-  uint32_t* flat = &sh.bits[0][0];
-  const int avail = max(0, min(int(p.n), slice_base + span) - slice_base);  // of the slice, inside the buffer
-  const int live = max(0, min(len - slice_base, span));                     // of the slice, visible
-  // (candidates another GPU wrote are read with plain loads, not by the copy engine)
-  const bool bulk = live > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.n_src == 0;
-  const int bulk_elems = bulk ? (avail & ~3) : 0;
-  const uint32_t bar = smem_u32(&sh.load_bar);
-  if (tid == 0 && bulk_elems > 0) {
-    mbar_arrive_expect_tx(bar, uint32_t(bulk_elems) * 4u);
-    bulk_g2s(smem_u32(flat), row + slice_base, uint32_t(bulk_elems) * 4u, bar);
-  }
-  uint4 h1a = make_uint4(0, 0, 0, 0), h1b = h1a;
-  if (have_hist && !take_all) {  // this thread's 8 bins of the scan's histogram
-    const uint4* gh = reinterpret_cast<const uint4*>(p.hist + size_t(r) * kBins + (kBins - 8 * (tid + 1)));
-    h1a = __ldcg(gh);
-    h1b = __ldcg(gh + 1);
-  }
   if (live > 0)
     for (int i = bulk_elems + tid; i < live; i += kClThreads) flat[i] = __float_as_uint(row[slice_base + i]);
-  // ---- behind the loads: clear what is accumulated into, then tell the cluster it is clear
-  {
-    static_assert(offsetof(ClShared, warp_tot) % 16 == 0, "the cleared part is whole 16-byte words");
-    constexpr int kZero16 = int(offsetof(ClShared, warp_tot) / 16);  // the histograms and both masks
-    uint4* z = reinterpret_cast<uint4*>(&sh);
-    for (int i = (have_hist ? kBins / 4 : 0) + tid; i < kZero16; i += kClThreads)  // (a given hist1 is overwritten)
-      z[i] = make_uint4(0, 0, 0, 0);
-  }
-  if (!solo) cluster_arrive();
   DSA_STAMP(stamp_cta, 1);
 
   // The slice is in shared memory once the bulk copy has landed; positions past the row's length
@@ -806,9 +899,8 @@ topk_cluster_kernel(const Params p, const int nk) {
   if (!take_all) {
     // ---- level 1: top 12 key bits
     if (have_hist) {
-      uint4* mine = reinterpret_cast<uint4*>(sh.hist1 + kBins - 8 * (tid + 1));
-      mine[0] = h1a;
-      mine[1] = h1b;
+      const uint32_t cnt[8] = {h1b.w, h1b.z, h1b.y, h1b.x, h1a.w, h1a.z, h1a.y, h1a.x};  // highest bin first
+      find_kth_in_registers<kBins, 8>(cnt, uint32_t(p.topk), sh.warp_tot, sh.res);
     } else {
       // this CTA's own histogram, then its non-zero bins pushed into every CTA's hist1. It borrows
       // the (still clear) first half of hist3 and clears it again before anybody pushes there.
@@ -836,8 +928,8 @@ topk_cluster_kernel(const Params p, const int nk) {
         }
       }
       cluster_sync_all(solo);
+      find_kth_bin<kBins>(sh.hist1, uint32_t(p.topk), sh.warp_tot, sh.res);
     }
-    find_kth_bin<kBins>(sh.hist1, uint32_t(p.topk), sh.warp_tot, sh.res);
     T = sh.res[0];
     need = sh.res[1];
     // bin T is [T << 20, (T + 1) << 20) in key space; bins below ordered_key(-inf) hold only NaNs
@@ -851,20 +943,28 @@ topk_cluster_kernel(const Params p, const int nk) {
   // ---- the sweep: the warp's kept mask (lane i ends up with word i) and, per thread, which
   // of its logits are candidates
   if (have_hist || take_all) wait_slice();
+  DSA_STAMP(stamp_cta, 4);
+  // Lane l of a warp owns word l of the warp's share: 32 consecutive positions, read as eight
+  // 16-byte chunks. The lanes start at different chunks ((j + l) mod 8), so that the eight lanes
+  // served together touch all 32 banks. Bit b of my_kept / my_cand is position 32 l + b.
   uint32_t my_kept = 0, my_cand = 0;
   const uint32_t* wbits = flat + warp_off;
+  if (lane < nk) {
+    const uint4* chunks = reinterpret_cast<const uint4*>(wbits + lane * 32);
+    uint32_t ge_lo = 0;
 #pragma unroll
-  for (int i = 0; i < kClMaxKeys; ++i) {
-    if (i < nk) {
-      const float v = __uint_as_float(wbits[i * 32 + lane]);
-      const bool above = v >= f_hi;
-      const bool cand = v >= f_lo && !above && !take_all;
-      const uint32_t m = __ballot_sync(0xffffffffu, above);
-      if (lane == i) my_kept = m;
-      if (cand) my_cand |= 1u << i;
+    for (int j = 0; j < 8; ++j) {
+      const int q = (j + lane) & 7;
+      const uint4 x = chunks[q];
+      const float v0 = __uint_as_float(x.x), v1 = __uint_as_float(x.y), v2 = __uint_as_float(x.z), v3 = __uint_as_float(x.w);
+      const uint32_t hi4 = (v0 >= f_hi ? 1u : 0u) | (v1 >= f_hi ? 2u : 0u) | (v2 >= f_hi ? 4u : 0u) | (v3 >= f_hi ? 8u : 0u);
+      const uint32_t lo4 = (v0 >= f_lo ? 1u : 0u) | (v1 >= f_lo ? 2u : 0u) | (v2 >= f_lo ? 4u : 0u) | (v3 >= f_lo ? 8u : 0u);
+      my_kept |= hi4 << (4 * q);
+      ge_lo |= lo4 << (4 * q);
     }
+    my_cand = take_all ? 0u : ge_lo & ~my_kept;
+    sh.kept[warp][lane] = my_kept;
   }
-  if (lane < nk) sh.kept[warp][lane] = my_kept;
   __syncwarp();
   DSA_STAMP(stamp_cta, 3);
 
@@ -876,20 +976,167 @@ topk_cluster_kernel(const Params p, const int nk) {
       const bool live = rem != 0u;
       const int i = live ? __ffs(rem) - 1 : 0;
       rem &= rem - 1u;
-      fn(live, ordered_key(__uint_as_float(wbits[i * 32 + lane])), i);
+      fn(live, ordered_key(__uint_as_float(wbits[lane * 32 + i])), i);
     }
   };
 
   uint32_t kstar = 0, ties_kept = 0;
+  bool totals_known = false;  // the list path leaves every CTA's kept count in cnts[] / cand_kept[]
   if (!take_all) {
-    // ---- level 2: key bits 19..13 of the candidates
-    for_each_candidate([&](bool live, uint32_t key, int) {
-      hist_add_warp(sh.local2, live, (key >> kL3Bits) & (kL2Bins - 1));
-    });
-    DSA_STAMP(stamp_cta, 8);
+    // ---- the candidates (bin T) of the whole row go to every CTA as a list of (key, position),
+    // with the CTA's level-2 histogram of them (key bits 19..13) and its count of certainly kept
+    // logits: one cluster barrier, and everything after it is local. A CTA with more than
+    // kListCap candidates sends only its counts, and the whole cluster (which sees the same
+    // counts) takes the histogram path below instead.
+    const uint32_t n_cand = uint32_t(__popc(my_cand));
+    const uint32_t cinc = warp_inclusive_scan(n_cand);
+    const uint32_t wabove = __reduce_add_sync(0xffffffffu, uint32_t(__popc(my_kept)));
+    uint32_t slot = 0;
+    if (lane == 31) {
+      slot = atomicAdd(&sh.list_n, cinc);  // the warp's slots in this CTA's region of the list
+      smem_red_add(&sh.above_n, wabove);
+    }
+    if (have_hist && !solo) cluster_wait();  // every CTA of the cluster runs (without the scan's histogram: taken at level 1)
+    slot = __shfl_sync(0xffffffffu, slot, 31);
+    if (slot + __shfl_sync(0xffffffffu, cinc, 31) <= uint32_t(kListCap)) {  // (else the region overflows: see below)
+      slot += cinc - n_cand;
+      uint32_t rem = my_cand;
+      while (rem) {  // into this CTA's own copy of its region first
+        const int i = __ffs(rem) - 1;
+        rem &= rem - 1u;
+        const uint32_t key = ordered_key(__uint_as_float(wbits[lane * 32 + i]));
+        smem_red_add(&sh.local2[(key >> kL3Bits) & (kL2Bins - 1)], 1u);
+        // place = (CTA, warp, word, bit): orders like the position
+        sh.list[c][slot++] = make_uint2(key, (c << 14) | uint32_t((warp << 10) | (lane << 5) | i));
+      }
+    }
     __syncthreads();
-    if (have_hist && !solo) cluster_wait();  // (see above; without the scan's histogram it was taken at level 1)
+    const uint32_t listed_here = sh.list_n;
+    const bool fits = listed_here <= uint32_t(kListCap);
+    if (!solo) {
+      // ... then one entry per thread to the other CTAs, the level-2 counts and the totals
+      if (fits) {
+        for (uint32_t j = tid; j < listed_here; j += kClThreads) {
+          const uint2 e = sh.list[c][j];
+          const uint32_t a = smem_u32(&sh.list[c][j]);
+#pragma unroll
+          for (uint32_t cc = 0; cc < uint32_t(kClMaxCtas); ++cc)
+            if (cc < C && cc != c) cluster_st2(cluster_map(a, cc), e.x, e.y);
+        }
+        if (tid >= kClThreads - kL2Bins) {
+          const int bin = tid - (kClThreads - kL2Bins);
+          const uint32_t x = sh.local2[bin];
+          const uint32_t a = smem_u32(&sh.tbl[c][bin]);
+#pragma unroll
+          for (uint32_t cc = 0; cc < uint32_t(kClMaxCtas); ++cc)
+            if (cc < C) cluster_st(cluster_map(a, cc), x);
+        }
+      }
+      if (warp == kClWarps / 2 && lane < int(C))
+        cluster_st(cluster_map(smem_u32(&sh.cnts[c]), uint32_t(lane)), listed_here | (sh.above_n << 16));  // at most 16384 of each
+    } else {
+      if (tid < kL2Bins) sh.tbl[0][tid] = sh.local2[tid];
+      if (tid == kL2Bins) sh.cnts[0] = listed_here | (sh.above_n << 16);
+    }
+    DSA_STAMP(stamp_cta, 8);
+    cluster_sync_all(solo);
     DSA_STAMP(stamp_cta, 9);
+
+    bool listed;
+    {
+      const uint32_t pk = lane < int(C) ? sh.cnts[lane] & 0xFFFFu : 0u;
+      listed = !__any_sync(0xffffffffu, pk > uint32_t(kListCap));
+    }
+    uint32_t p19 = 0, need2 = 0, n_surv = 0, b2 = 0;
+    if (listed) {
+      // ---- level 2 (key bits 19..13): the sum of the CTAs' tables, searched by one warp
+      find_kth_bin_tables(&sh.tbl[0][0], int(C), need, sh.res);
+      b2 = sh.res[0];
+      p19 = (T << kL2Bits) | b2;
+      need2 = sh.res[1];
+      n_surv = sh.res[2];
+      listed = n_surv <= uint32_t(kSurvCap);
+    }
+    DSA_STAMP(stamp_cta, 10);
+    if (listed) {
+      // ---- (a) this CTA's own candidates above those 19 bits are kept; (b) how many such
+      // candidates every CTA has, from its table; (c) the few candidates that share the 19 bits
+      // ("survivors") are collected from the whole list: warp w looks at region w % C, 32 entries
+      // at a time.
+      if (my_cand) {  // (a word has one owner; the survivors' bits come later, behind a barrier)
+        uint32_t rem = my_cand;
+        while (rem) {
+          const int i = __ffs(rem) - 1;
+          rem &= rem - 1u;
+          if ((ordered_key(__uint_as_float(wbits[lane * 32 + i])) >> kL3Bits) > p19) my_kept |= 1u << i;
+        }
+        sh.kept[warp][lane] = my_kept;
+      }
+      if (warp < int(C)) {
+        const uint4 x = reinterpret_cast<const uint4*>(sh.tbl[warp])[lane];  // bins 4 lane .. 4 lane + 3
+        const uint32_t b0 = uint32_t(4 * lane);
+        const uint32_t sum = (b0 > b2 ? x.x : 0u) + (b0 + 1 > b2 ? x.y : 0u) + (b0 + 2 > b2 ? x.z : 0u) + (b0 + 3 > b2 ? x.w : 0u);
+        const uint32_t tot = __reduce_add_sync(0xffffffffu, sum);
+        if (lane == 0) smem_red_add(&sh.cand_kept[warp], tot);
+      }
+      {
+        const int region = warp & int(C - 1u), chunk_step = (kClWarps / int(C)) * 32;
+        const uint2* rlist = sh.list[region];
+        const int rcnt = int(sh.cnts[region] & 0xFFFFu);
+        for (int j = (warp / int(C)) * 32 + lane; j - lane < rcnt; j += chunk_step) {
+          const uint2 e = j < rcnt ? rlist[j] : make_uint2(0u, 0u);
+          const bool is = j < rcnt && (e.x >> kL3Bits) == p19;
+          const uint32_t m = __ballot_sync(0xffffffffu, is);
+          if (m) {
+            const int leader = __ffs(m) - 1;
+            uint32_t base = 0;
+            if (lane == leader) base = atomicAdd(&sh.surv_n, uint32_t(__popc(m)));
+            base = __shfl_sync(0xffffffffu, base, leader);
+            if (is) sh.surv[base + __popc(m & ((1u << lane) - 1u))] = (uint64_t(e.x) << 32) | uint64_t(~e.y);
+          }
+        }
+      }
+      if (tid >= kClThreads - 4) sh.surv[n_surv + uint32_t(tid - (kClThreads - 4))] = 0ull;  // below every survivor
+      __syncthreads();
+      DSA_STAMP(stamp_cta, 11);
+      // ---- a survivor is kept when fewer than need2 survivors come before it (larger key, or the
+      // same key at a lower position); k* is the key of the need2-th
+      if (warp * 32 < int(n_surv)) {  // (whole warps, for the ballots)
+        const bool have = tid < int(n_surv);
+        const uint64_t mine = sh.surv[have ? tid : 0];  // larger = earlier in (key descending, position ascending)
+        uint32_t before = 0;
+#pragma unroll 1
+        for (uint32_t j = 0; j < n_surv; j += 4) {
+          const uint64_t o0 = sh.surv[j], o1 = sh.surv[j + 1], o2 = sh.surv[j + 2], o3 = sh.surv[j + 3];
+          before += uint32_t(o0 > mine) + uint32_t(o1 > mine) + uint32_t(o2 > mine) + uint32_t(o3 > mine);
+        }
+        const uint32_t key = uint32_t(mine >> 32), place = ~uint32_t(mine);
+        if (have && before + 1u == need2) sh.res[3] = key;
+        const bool keep = have && before < need2;
+        const uint32_t owner = place >> 14;
+        // kept survivors per owning CTA: eight 8-bit counters (at most 32 each) in two warp sums
+        const uint32_t one = keep ? 1u << (8u * (owner & 3u)) : 0u;
+        const uint32_t lo = __reduce_add_sync(0xffffffffu, owner < 4u ? one : 0u);
+        const uint32_t hi = __reduce_add_sync(0xffffffffu, owner < 4u ? 0u : one);
+        if (lane < int(C)) {
+          const uint32_t n = ((lane < 4 ? lo : hi) >> (8 * (lane & 3))) & 0xFFu;
+          if (n) smem_red_add(&sh.cand_kept[lane], n);
+        }
+        if (keep && owner == c) smem_red_or(&sh.kept[(place >> 10) & 15u][(place >> 5) & 31u], 1u << (place & 31u));
+      }
+      __syncthreads();
+      kstar = sh.res[3];
+      totals_known = true;  // (ties_kept stays 0: the ties are already in the kept mask)
+    } else {
+    // ---- level 2: key bits 19..13 of the candidates
+    if (!fits) {  // (a CTA that listed its candidates has counted them already; one that could not starts over)
+      if (tid < kL2Bins) sh.local2[tid] = 0u;
+      __syncthreads();
+      for_each_candidate([&](bool live, uint32_t key, int) {
+        hist_add_warp(sh.local2, live, (key >> kL3Bits) & (kL2Bins - 1));
+      });
+    }
+    __syncthreads();
     if (tid < kL2Bins) {
       const uint32_t x = sh.local2[tid];
       if (x && solo) {
@@ -900,12 +1147,10 @@ topk_cluster_kernel(const Params p, const int nk) {
         for (uint32_t cc = 0; cc < C; ++cc) cluster_red_add(cluster_map(a, cc), x);
       }
     }
-    DSA_STAMP(stamp_cta, 10);
     cluster_sync_all(solo);
-    DSA_STAMP(stamp_cta, 11);
-    find_kth_bin<kL2Bins>(sh.hist2, need, sh.warp_tot, sh.res);
-    const uint32_t p19 = (T << kL2Bits) | sh.res[0];
-    const uint32_t need2 = sh.res[1];
+    find_kth_bin_warp<kL2Bins>(sh.hist2, need, sh.res);
+    p19 = (T << kL2Bits) | sh.res[0];
+    need2 = sh.res[1];
     DSA_STAMP(stamp_cta, 4);
     // ---- level 3: the low 13 bits of the candidates that share those 19 bits
     for_each_candidate([&](bool live, uint32_t key, int) {
@@ -920,10 +1165,11 @@ topk_cluster_kernel(const Params p, const int nk) {
     DSA_STAMP(stamp_cta, 5);
     // ---- candidates above k* join the kept mask, those equal to it the tie mask
     for_each_candidate([&](bool live, uint32_t key, int i) {
-      if (live && key > kstar) smem_red_or(&sh.kept[warp][i], 1u << lane);
-      else if (live && key == kstar) smem_red_or(&sh.ties[warp][i], 1u << lane);
+      if (live && key > kstar) sh.kept[warp][lane] |= 1u << i;  // (a word has one owner)
+      else if (live && key == kstar) sh.ties[warp][lane] |= 1u << i;
     });
     __syncwarp();
+    }
   } else if (!solo) {
     cluster_wait();
   }
@@ -931,32 +1177,35 @@ topk_cluster_kernel(const Params p, const int nk) {
   DSA_STAMP(stamp_cta, 14);
   // ---- (kept, ties) counts in position order, packed ties << 16 | kept: words of a warp, warps, CTAs
   const uint32_t gword = lane < nk ? sh.kept[warp][lane] : 0u;
-  const uint32_t qword = lane < nk ? sh.ties[warp][lane] : 0u;
+  const uint32_t qword = lane < nk && !totals_known ? sh.ties[warp][lane] : 0u;
   const uint32_t cnt = uint32_t(__popc(gword)) | (uint32_t(__popc(qword)) << 16);
   const uint32_t inc = warp_inclusive_scan(cnt);  // at most 1024 of each kind per warp
   if (lane == 31) sh.warp_tot[warp] = inc;
   __syncthreads();
-  if (warp == 0) {
-    const uint32_t wt = lane < kClWarps ? sh.warp_tot[lane] : 0u;
-    const uint32_t winc = warp_inclusive_scan(wt);  // at most 16384 of each kind per CTA
-    if (lane < kClWarps) sh.warp_base[lane] = winc - wt;
-    const uint32_t cta_sum = __shfl_sync(0xffffffffu, winc, 31);
-    if (solo) {
-      if (lane == 0) sh.cta_tot[0] = cta_sum;
-    } else if (lane < int(C)) {
-      cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(lane)), cta_sum);
-    }
-  }
-  cluster_sync_all(solo);
   uint32_t g_before, q_before, g_total, q_total;
   {
-    const uint32_t t = lane < int(C) ? sh.cta_tot[lane] : 0u;
+    const uint32_t wt = lane < kClWarps ? sh.warp_tot[lane] : 0u;  // at most 16384 of each kind per CTA
+    const uint32_t wb = __reduce_add_sync(0xffffffffu, lane < warp ? wt : 0u);
+    uint32_t t;
+    if (totals_known) {
+      t = lane < int(C) ? (sh.cnts[lane] >> 16) + sh.cand_kept[lane] : 0u;
+    } else {
+      const uint32_t cta_sum = __reduce_add_sync(0xffffffffu, wt);
+      if (warp == 0) {
+        if (solo) {
+          if (lane == 0) sh.cta_tot[0] = cta_sum;
+        } else if (lane < int(C)) {
+          cluster_st(cluster_map(smem_u32(&sh.cta_tot[c]), uint32_t(lane)), cta_sum);
+        }
+      }
+      cluster_sync_all(solo);
+      t = lane < int(C) ? sh.cta_tot[lane] : 0u;
+    }
     const uint32_t tg = t & 0xFFFFu, tq = t >> 16;
     g_total = __reduce_add_sync(0xffffffffu, tg);
     q_total = __reduce_add_sync(0xffffffffu, tq);
     g_before = __reduce_add_sync(0xffffffffu, lane < int(c) ? tg : 0u);
     q_before = __reduce_add_sync(0xffffffffu, lane < int(c) ? tq : 0u);
-    const uint32_t wb = sh.warp_base[warp];
     g_before += (wb & 0xFFFFu) + ((inc - cnt) & 0xFFFFu);  // ... and the words before this lane's word
     q_before += (wb >> 16) + ((inc - cnt) >> 16);
   }
