@@ -527,28 +527,41 @@ topk_finish_kernel(const Params p) {
 // ------------------------------------------------------------------------------
 // One launch for rows of up to kClMaxN logits: a thread-block cluster per row.
 //
-// Each CTA of the cluster owns a contiguous slice of the row and looks at every
-// logit of it exactly once. With the threshold bin T of the 12-bit histogram
-// (the indexer scan's, when the caller passes it) one sweep over the slice
-// leaves, per warp, a bit mask of the positions that are certainly kept (bin
-// above T) and a compact list of the few candidates in bin T. Everything after
-// that touches only mask words and candidates:
-//   * two more radix levels (7 + 13 bits) over the candidates find the k-th
-//     largest key k* exactly. A level's counts are PUSHED into every CTA's
-//     histogram (distributed-shared-memory reductions), and one cluster barrier
-//     later each CTA finds the threshold bin by itself;
-//   * candidates above k* join the kept mask, those equal to k* a tie mask;
+// Each CTA of the cluster owns a contiguous slice of the row (brought into shared
+// memory by one bulk copy) and looks at every logit of it exactly once. With the
+// threshold bin T of the 12-bit histogram (the indexer scan's, when the caller
+// passes it) one sweep over the slice leaves, per thread, a 32-bit mask of the
+// positions that are certainly kept (bin above T) and one of the few candidates
+// in bin T. Everything after that touches only mask words and candidates:
+//   * the usual case: every CTA sends its candidates as (key, place) pairs, with
+//     its 128-bin histogram of their next 7 key bits and its count of certainly
+//     kept logits, to every CTA of the cluster (distributed-shared-memory
+//     stores). ONE cluster barrier later each CTA holds the whole candidate
+//     list: it searches the summed histograms for the level-2 bin, collects the
+//     handful of candidates that share the k-th key's top 19 bits, ranks them by
+//     comparison (larger key first, lower position first among equal keys), and
+//     knows from the tables and the ranks how many candidates every CTA keeps:
+//     no further exchange;
+//   * a CTA with more than kListCap candidates, or more than kSurvCap candidates
+//     sharing the 19 bits (rows with many equal logits): two more radix levels
+//     (7 + 13 bits) as histograms PUSHED into every CTA (distributed-shared-
+//     memory reductions), a cluster barrier after each, candidates equal to k*
+//     in a tie mask, the CTAs' totals exchanged behind a last barrier;
 //   * one prefix sum over the pair (kept, tie) in position order gives each
 //     element its slot in the ascending output:
 //       slot(x) = kept_before(x) + min(ties_before(x), ties_kept)
 //     so ties go to the lower positions.
-// No scratch in global memory, no capacity limit (a warp's candidate list holds
-// the warp's whole share), no wait on another launch.
+// No scratch in global memory, no wait on another launch.
 //
-// Cost model that shaped it: a CTA's warps share four issue ports, so every
-// instruction a thread executes costs (warps per port) cycles of wall time.
-// Hence 512 threads, one heavy sweep, sections that only one warp needs to run
-// are run by one warp while the others wait at a barrier, and loops are rolled.
+// Cost model that shaped it: the kernel is a chain of short dependent phases, each
+// paced by instruction and shared-memory latency, not by throughput. A CTA's
+// warps share four issue ports, shared-memory atomics retire about one per cycle
+// per SM (so nothing adds per element, only per candidate), a cluster barrier
+// costs about 1500 cycles where it stands, a block barrier about 100. Hence 512
+// threads, one sweep without warp votes, a single cluster barrier on the usual
+// path, warp reductions instead of scans where only a total is needed, and
+// whatever needs no data of the previous launch (clearing shared memory, the
+// first cluster arrival) ahead of the dependency wait.
 constexpr int kClThreads = 512;
 constexpr int kClWarps = kClThreads / 32;
 constexpr int kClMaxKeys = 32;                                // logits per thread (= mask words per warp)
@@ -940,8 +953,7 @@ topk_cluster_kernel(const Params p, const int nk) {
   }
   DSA_STAMP(stamp_cta, 2);
 
-  // ---- the sweep: the warp's kept mask (lane i ends up with word i) and, per thread, which
-  // of its logits are candidates
+  // ---- the sweep: per thread, which of its 32 logits are certainly kept and which are candidates
   if (have_hist || take_all) wait_slice();
   DSA_STAMP(stamp_cta, 4);
   // Lane l of a warp owns word l of the warp's share: 32 consecutive positions, read as eight
@@ -1151,7 +1163,6 @@ topk_cluster_kernel(const Params p, const int nk) {
     find_kth_bin_warp<kL2Bins>(sh.hist2, need, sh.res);
     p19 = (T << kL2Bits) | sh.res[0];
     need2 = sh.res[1];
-    DSA_STAMP(stamp_cta, 4);
     // ---- level 3: the low 13 bits of the candidates that share those 19 bits
     for_each_candidate([&](bool live, uint32_t key, int) {
       hist_push_warp(sh.hist3, live && (key >> kL3Bits) == p19, swizzled_bin<kL3Bins>(key & (kL3Bins - 1)), C);
