@@ -570,7 +570,7 @@ constexpr int64_t kClMaxN = int64_t(kClMaxCtas) * kClThreads * kClMaxKeys;  // 1
 constexpr int kL2Bits = 7, kL2Bins = 1 << kL2Bits;            // key bits 19..13
 constexpr int kL3Bits = 13, kL3Bins = 1 << kL3Bits;           // key bits 12..0
 constexpr int kWarpKeys = 32 * kClMaxKeys;                    // 1024: a warp's share of the slice
-constexpr int kListCap = 256;                                 // candidates a CTA may list (else: histograms)
+constexpr int kListCap = 1024;                                // candidates a CTA may list (else: histograms)
 constexpr int kSurvCap = 256;                                 // candidates ranked by comparison (else: histograms)
 
 struct ClShared {
