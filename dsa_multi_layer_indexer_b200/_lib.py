@@ -30,6 +30,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_status_string": (C.c_char_p, [_i]),
     "dsa_check_device_status": (_i, [C.POINTER(C.c_uint32)]),
     "dsa_debug_read_stamps": (_i, [_p, _i]),
+    "dsa_debug_wait_timeout": (_i, [C.c_uint64, _p]),
     "dsa_indexer_scan_fp8": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _l, _l, _l, _l, _l, _i, _p]),
     "dsa_indexer_scan_fp8_paged": (_i, [_p, _p, _p, _l, _p, _l, _p, _p, _p, _i, _i, _l, _l, _p]),
     "dsa_indexer_scan_f32": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _l, _l, _l, _p]),
@@ -61,7 +62,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_quantize_e4m3_rowwise": (_i, [_p, _p, _p, _l, _i, _f, _p]),
 }
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 
 class DsaError(RuntimeError):

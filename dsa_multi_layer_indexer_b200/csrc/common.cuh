@@ -200,7 +200,12 @@ __device__ __forceinline__ unsigned long long wall_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, unsigned long long limit_ns);
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  return mbar_wait_for(bar, parity, kWaitLimitNs);
+}
+// Waits for the phase with the given parity, at most limit_ns of wall time (and kWaitLimit probes).
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
   unsigned long long t0 = 0;
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     uint32_t done;
@@ -215,7 +220,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if ((i & 255u) == 255u) {
       const unsigned long long now = wall_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
   return false;

@@ -185,6 +185,27 @@ int dsa_check_device_status(uint32_t* detail) {
   return DSA_OK;
 }
 
+// One CTA waits on a transaction barrier that nobody completes, for at most limit_ns: the wait
+// runs out, the CTA agrees on that (one vote), sets the attention time-out bit and returns.
+__global__ void wait_probe_kernel(unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = mbar_wait_for(smem_u32(&bar), 0, limit_ns);
+  if (__syncthreads_or(!ok) && threadIdx.x == 0) atomicOr(&g_device_status, kStatusAttnTimeout);
+}
+
+int dsa_debug_wait_timeout(uint64_t limit_ns, void* stream) {
+  DSA_REQUIRE(limit_ns > 0 && limit_ns <= 10ull * 1000 * 1000, "wait probe: limit_ns=%llu outside (0, 10 ms]",
+              (unsigned long long)limit_ns);
+  wait_probe_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+  DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
 int dsa_debug_read_stamps(uint64_t* host_out, int max_words) {
 #ifdef DSA_STAMPS
   const int n = max_words < kStampCtas * kStampSlots ? max_words : kStampCtas * kStampSlots;

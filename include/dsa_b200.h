@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 7
+#define DSA_ABI_VERSION 8
 
 enum dsa_status {
   DSA_OK = 0,
@@ -74,6 +74,14 @@ int dsa_check_device_status(uint32_t* detail);
  * clears them; returns the number of words or DSA_ERR_UNSUPPORTED. Counterpart
  * of hide_debug_read (kernels/cuda_fused_sparse_splitk.py:2329-2349). */
 int dsa_debug_read_stamps(uint64_t* host_out, int max_words);
+
+/* Test aid for the bounded waits: launches one CTA that waits, for at most
+ * limit_ns (0 < limit_ns <= 10 ms) of wall time, on a shared-memory barrier that
+ * nothing completes. The wait runs out, the kernel sets DSA_STATUS_ATTN_TIMEOUT
+ * and returns; dsa_check_device_status then reports DSA_ERR_DEVICE_TIMEOUT once
+ * and clears the word. Nothing faults or hangs: this is the path every kernel of
+ * the library takes when one of its waits runs out. */
+int dsa_debug_wait_timeout(uint64_t limit_ns, void* stream);
 
 /* ---- (a1) lightning-indexer scan ------------------------------------------
  * logits[r, s] = (sum_h w[r,h] * relu(q[r,h,:] . k[s,:])) * k_scale[s],

@@ -364,3 +364,22 @@ def test_fused_indexer_attention_launch_equals_separate_launches(ops, B, H, n, t
     assert torch.equal(hist_a, hist_b)
     sel = ops.topk_select(logits_f, topk, lens, hist=hist_a)
     assert torch.equal(sel, ops.topk_select(logits_s, topk, lens))
+
+
+def test_a_wait_that_runs_out_reports_and_clears(ops):
+    """Every wait in the library's kernels is bounded. One CTA waits 1 ms on a barrier that
+    nothing completes: the kernel returns, the status call reports the time-out once, and the
+    word is clear again afterwards (nothing faults or hangs; the context stays usable)."""
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    _lib.check(_lib.lib().dsa_debug_wait_timeout(1_000_000, torch.cuda.current_stream().cuda_stream))
+    with pytest.raises(_lib.DsaError) as err:
+        _lib.check_device_status()
+    assert err.value.status == -4  # DSA_ERR_DEVICE_TIMEOUT
+    _lib.check_device_status()  # cleared
+    with pytest.raises(_lib.DsaError):  # the limit is capped at 10 ms
+        _lib.check(_lib.lib().dsa_debug_wait_timeout(10_000_001, torch.cuda.current_stream().cuda_stream))
+    x = torch.arange(8, device="cuda").sum().item()  # the context still works
+    assert x == 28
