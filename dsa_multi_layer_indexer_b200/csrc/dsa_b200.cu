@@ -417,8 +417,12 @@ static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStre
   if (rc) return rc;
   // As few CTAs as hold the row at 32 logits per thread: every CTA added costs cluster barriers and
   // remote reductions, and a row of up to 16384 logits needs none of either.
+  // A row that comes without the scan's histogram counts its own first level with shared-memory
+  // atomics, about one per cycle per SM: it is spread over as many SMs as the cluster has (2048 logits
+  // per CTA or more).
   int ctas = 1;
-  while (ctas < topk::kClMaxCtas && int64_t(ctas) * topk::kClThreads * topk::kClMaxKeys < n) ctas *= 2;
+  const int64_t per_cta = p.hist ? int64_t(topk::kClThreads) * topk::kClMaxKeys : 2048;
+  while (ctas < topk::kClMaxCtas && int64_t(ctas) * per_cta < n) ctas *= 2;
   const int64_t per_key = int64_t(ctas) * topk::kClThreads;
   const int nk = int((n + per_key - 1) / per_key);
   cudaLaunchConfig_t cfg{};

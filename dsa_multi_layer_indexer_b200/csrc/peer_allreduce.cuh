@@ -57,10 +57,13 @@ allreduce_push_kernel(const PushParams p) {
     }
     for (int d = 0; d < p.n_dest; ++d) *reinterpret_cast<float4*>(p.dest[d] + off + i) = v;
   }
-  __threadfence_system();  // this thread's stores are ordered, at system scope, before the barrier
+  // Behind the block barrier ONE thread fences at system scope and posts the step number to every
+  // rank: a release that, being cumulative, also orders the stores of the other threads (which
+  // reached this thread through the barrier) before the flags.
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int d = 0; d < p.n_dest; ++d) st_release_sys(p.dest_flag[d], step);
+    fence_acq_rel_sys();
+    for (int d = 0; d < p.n_dest; ++d) st_relaxed_sys(p.dest_flag[d], step);
     *p.sent = step;
   }
 }

@@ -886,6 +886,12 @@ topk_cluster_kernel(const Params p, const int nk) {
   }
   if (live > 0)
     for (int i = bulk_elems + tid; i < live; i += kClThreads) flat[i] = __float_as_uint(row[slice_base + i]);
+  // A short slice leaves room for its part of the index map behind it: the emission then reads
+  // shared memory instead of making one trip to global memory per selected element.
+  const int32_t* imap = p.index_map ? p.index_map + (p.n_src > 0 ? gather_row : int64_t(r)) * p.n : nullptr;
+  const bool imap_staged = imap != nullptr && 2 * span <= kClWarps * kWarpKeys;
+  if (imap_staged)
+    for (int i = tid; i < live; i += kClThreads) flat[span + i] = uint32_t(imap[slice_base + i]);
   DSA_STAMP(stamp_cta, 1);
 
   // The slice is in shared memory once the bulk copy has landed; positions past the row's length
@@ -1225,7 +1231,6 @@ topk_cluster_kernel(const Params p, const int nk) {
   // ---- emit: lane i walks the set bits of its word i in ascending position order
   int32_t* out_idx = p.out_idx ? p.out_idx + int64_t(r) * p.topk : nullptr;
   float* out_val = p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
-  const int32_t* imap = p.index_map ? p.index_map + (p.n_src > 0 ? gather_row : int64_t(r)) * p.n : nullptr;
   const uint32_t topk_u = uint32_t(p.topk);
   const float neg_inf = __int_as_float(0xff800000);
   const int n_dest = p.n_dest;
@@ -1233,34 +1238,71 @@ topk_cluster_kernel(const Params p, const int nk) {
   // a selected -inf can only appear when the row has fewer than topk finite logits
   const bool need_value = out_val != nullptr || n_dest > 0 || take_all || kstar <= 0x007FFFFFu;  // ordered_key(-inf)
   {
-    uint32_t g = gword, q = qword, gb = g_before, qb = q_before;
-    const int word_base = slice_base + warp_off + lane * 32;
+    // Four set bits at a time: their index-map loads are issued together (each is a trip to
+    // global memory), the logit values come from the slice in shared memory.
+    // A short row fills only the first nk words of a warp: each word is then shared by G lanes
+    // (G = 32 / nk rounded down to a power of two), every lane taking 32 / G of its bits, so that
+    // the emission is spread over all lanes whatever the row's length.
+    int G = 1;
+    while (2 * G * nk <= 32) G *= 2;
+    const int wsel = lane / G, width = 32 / G, lo = (lane % G) * width;
+    const uint32_t gw = __shfl_sync(0xffffffffu, gword, wsel), qw = __shfl_sync(0xffffffffu, qword, wsel);
+    uint32_t gb = __shfl_sync(0xffffffffu, g_before, wsel), qb = __shfl_sync(0xffffffffu, q_before, wsel);
+    const uint32_t below = (1u << lo) - 1u;  // (lo < 32)
+    const uint32_t mine = (width == 32 ? 0xFFFFFFFFu : (1u << width) - 1u) << lo;
+    gb += uint32_t(__popc(gw & below));
+    qb += uint32_t(__popc(qw & below));
+    uint32_t g = gw & mine, q = qw & mine;
+    const int word_base = slice_base + warp_off + wsel * 32;
+    const uint32_t* wvals = wbits + wsel * 32;
     while (g | q) {
-      const int b = __ffs(g | q) - 1;
-      const uint32_t bit = 1u << b;
-      uint32_t slot = 0xFFFFFFFFu;
-      if (g & bit) {
-        slot = gb + min(qb, ties_kept);
-        ++gb;
-      } else {
-        if (qb < ties_kept) slot = gb + qb;
-        ++qb;
-      }
-      g &= ~bit;
-      q &= ~bit;
-      if (slot < topk_u) {
-        const int pos = word_base + b;
-        int32_t id = imap ? imap[pos] : pos + p.index_offset;
-        float v = 0.f;
-        if (need_value) {
-          v = row[pos];
-          if (v == neg_inf) id = p.pad;
-          if (out_val) out_val[slot] = v;
+      bool ok[4];
+      int bitv[4];
+      uint32_t slotv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        ok[u] = false;
+        bitv[u] = 0;
+        slotv[u] = 0;
+        if (g | q) {
+          const int b = __ffs(g | q) - 1;
+          const uint32_t bit = 1u << b;
+          uint32_t slot = 0xFFFFFFFFu;
+          if (g & bit) {
+            slot = gb + min(qb, ties_kept);
+            ++gb;
+          } else {
+            if (qb < ties_kept) slot = gb + qb;
+            ++qb;
+          }
+          g &= ~bit;
+          q &= ~bit;
+          ok[u] = slot < topk_u;
+          bitv[u] = b;
+          slotv[u] = slot;
         }
-        if (out_idx) out_idx[slot] = id;
-        for (int d = 0; d < n_dest; ++d) {  // plain stores into every rank's gather buffers (peer memory)
-          p.dest_idx[d][dest_off + slot] = id;
-          p.dest_val[d][dest_off + slot] = v;
+      }
+      int32_t idv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int pos = word_base + bitv[u];
+        idv[u] = !ok[u] ? 0 : imap_staged ? int32_t(wvals[span + bitv[u]]) : imap ? imap[pos] : pos + p.index_offset;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (ok[u]) {
+          int32_t id = idv[u];
+          float v = 0.f;
+          if (need_value) {
+            v = __uint_as_float(wvals[bitv[u]]);
+            if (v == neg_inf) id = p.pad;
+            if (out_val) out_val[slotv[u]] = v;
+          }
+          if (out_idx) out_idx[slotv[u]] = id;
+          for (int d = 0; d < n_dest; ++d) {  // plain stores into every rank's gather buffers (peer memory)
+            p.dest_idx[d][dest_off + slotv[u]] = id;
+            p.dest_val[d][dest_off + slotv[u]] = v;
+          }
         }
       }
     }
@@ -1275,12 +1317,14 @@ topk_cluster_kernel(const Params p, const int nk) {
     }
   }
   if (n_dest > 0) {
-    // Every thread's stores are ordered before the barrier at system scope; behind the barrier one
-    // thread posts the row's step number to every rank (release): whoever reads it sees the data.
-    __threadfence_system();
+    // Every thread's stores come before the barrier; behind it ONE thread posts the row's step number
+    // to every rank behind one fence at system scope (a release). The release is cumulative: it orders the stores
+    // that reached this thread through the barrier too, so whoever acquires the flag sees the data
+    // (no fence per thread: 4096 system-scope fences cost microseconds per destination).
     cluster_sync_all(solo);
     if (c == 0 && tid == 0) {
-      for (int d = 0; d < n_dest; ++d) st_release_sys(p.dest_flag[d] + r, step);
+      fence_acq_rel_sys();
+      for (int d = 0; d < n_dest; ++d) st_relaxed_sys(p.dest_flag[d] + r, step);
       p.sent[r] = step;
     }
   }
