@@ -925,12 +925,13 @@ topk_cluster_kernel(const Params p, const int nk) {
       // the (still clear) first half of hist3 and clears it again before anybody pushes there.
       uint32_t* local1 = sh.hist3;
       wait_slice();
-#pragma unroll 1
+#pragma unroll 4
       for (int i = 0; i < nk; ++i) {
         const bool in = i * 32 + lane + warp_off < live;
         const float v = in ? __uint_as_float(flat[warp_off + i * 32 + lane]) : 0.f;
         hist_add_warp(local1, in, ordered_key(v) >> kLowBits);
       }
+      DSA_STAMP(stamp_cta, 12);
       __syncthreads();
       if (!solo) cluster_wait();  // every CTA of the cluster runs and has cleared its histograms: remote adds may start
       for (int i = tid; i < kBins; i += kClThreads) {
@@ -946,7 +947,9 @@ topk_cluster_kernel(const Params p, const int nk) {
           }
         }
       }
+      DSA_STAMP(stamp_cta, 13);
       cluster_sync_all(solo);
+      DSA_STAMP(stamp_cta, 5);
       find_kth_bin<kBins>(sh.hist1, uint32_t(p.topk), sh.warp_tot, sh.res);
     }
     T = sh.res[0];
