@@ -3,6 +3,7 @@
 // device code. Host code here only validates arguments, encodes tensor maps
 // and launches; it never allocates device memory and never synchronises,
 // except dsa_check_device_status which exists to do exactly that.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -91,11 +92,6 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, con
   return DSA_OK;
 }
 
-static int env_int(const char* name, int fallback) {
-  const char* v = getenv(name);
-  return (v && *v) ? atoi(v) : fallback;
-}
-
 // Raises a kernel's dynamic shared-memory limit, once per device.
 template <typename K>
 static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
@@ -106,7 +102,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_scan2[64], g_opt_scan3[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_topk_cluster[64], g_opt_gemv[4][64];
+static bool g_opt_fused[64], g_opt_scan2[64], g_opt_scan3[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_topk_cluster[64], g_opt_topk_cluster_any[64], g_opt_gemv[4][64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -256,7 +252,7 @@ static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
 
 // Two CTAs per SM with a 4-slot ring. Tiles in their epilogue at once per CTA: three for a
 // batch (measured 1.5-2 % faster than two on 32 rows), two for one row (three is 0.15 us
-// slower there). A ragged batch works on its long rows first.
+// slower there). A ragged batch is spread so that every CTA gets about the same number of tiles.
 static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p_in, int R, cudaStream_t st) {
   scan::Params p = p_in;
   p.balance_rows = (R > 1 && R <= 32 && p.seq_lens) ? R : 0;
@@ -264,8 +260,10 @@ static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p_in, int
   if (R > 1) {
     int rc3 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>, smem, g_opt_scan3);
     if (rc3) return rc3;
-    DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>,
-                        dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(64 + 128 * 3), smem, st, tmap, p));
+    // a ragged batch of up to 32 rows: one resident wave on a 1-D grid, the rows' CTA counts settled on the device
+    const dim3 grid = p.balance_rows ? dim3(std::max(R, 2 * sm_count()), 1) : dim3(scan_grid_x(R, p.tiles_per_row, 2), R);
+    DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>, grid, dim3(64 + 128 * 3), smem, st,
+                        tmap, p));
     return DSA_OK;
   }
   int rc2 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>, smem, g_opt_scan2);
@@ -413,7 +411,9 @@ int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
 
 // Rows of up to kClMaxN logits: one cluster of 1..8 CTAs per row, no scratch.
 static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStream_t st) {
-  int rc = opt_in_smem(topk::topk_cluster_kernel, sizeof(topk::ClShared), g_opt_topk_cluster);
+  const bool plain = p.hist && !p.n_src && !p.n_dest && !p.index_map && !p.out_val;
+  int rc = plain ? opt_in_smem(topk::topk_cluster_kernel<true>, sizeof(topk::ClShared), g_opt_topk_cluster)
+                 : opt_in_smem(topk::topk_cluster_kernel<false>, sizeof(topk::ClShared), g_opt_topk_cluster_any);
   if (rc) return rc;
   // As few CTAs as hold the row at 32 logits per thread: every CTA added costs cluster barriers and
   // remote reductions, and a row of up to 16384 logits needs none of either.
@@ -439,7 +439,8 @@ static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStre
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel, p, nk));
+  if (plain) DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel<true>, p, nk));
+  else DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel<false>, p, nk));
   return DSA_OK;
 }
 

@@ -56,7 +56,7 @@ struct Params {
   int n_heads;
   int tiles_per_row;
   int paged;
-  int balance_rows;  // > 1: CTAs of grid row y work on the row with the y-th longest sequence (rows <= 32)
+  int balance_rows;  // > 1: the number of rows (<= 32) of a ragged batch on a 1-D grid, see balanced_share
 };
 
 template <int kStages>
@@ -100,13 +100,37 @@ __device__ __forceinline__ int row_of_rank(const Params& p, int y, int R) {
   return hit ? __ffs(hit) - 1 : y;
 }
 
+// Ragged batch on a 1-D grid of N CTAs: row j gets one CTA plus its share of the other N - R in
+// proportion to its number of key tiles, so that every CTA works through about the same number
+// of tiles whatever the rows' lengths (R <= 32: one lane per row; every warp computes the same
+// answer by itself). Gives the row of CTA b, its index among the row's CTAs and their count.
+__device__ __forceinline__ void balanced_share(const Params& p, int b, int N, int R, int& r, int& bx, int& G) {
+  const int lane = threadIdx.x & 31;
+  const int tiles = lane < R ? (row_len(p, lane) + kTileKeys - 1) / kTileKeys : 0;
+  int cum = tiles;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, cum, o);
+    if (lane >= o) cum += up;
+  }
+  const int total = __shfl_sync(0xffffffffu, cum, 31), spare = N - R;
+  const int start = lane + (total > 0 ? int(int64_t(cum - tiles) * spare / total) : 0);
+  const int end = lane + 1 + (total > 0 ? int(int64_t(cum) * spare / total) : 0);
+  const uint32_t hit = __ballot_sync(0xffffffffu, lane < R && b >= start && b < end);
+  const int j = hit ? __ffs(hit) - 1 : 0;
+  r = j;
+  bx = b - __shfl_sync(0xffffffffu, start, j);
+  G = __shfl_sync(0xffffffffu, end - start, j);
+}
+
 // Body of the scan for CTA `bx` of `G` working on row `r` (the kernel below
 // passes its block indices; the fused indexer + attention launch passes indices
 // of its scan partition). `tmap_ptr` must point at a __grid_constant__ kernel
 // parameter; `smem_raw` is the CTA's dynamic shared memory.
 template <int kStages, int kEpiGroups = 1>
-__device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const Params& p, const int bx,
-                                             const int G, const int r_grid, uint8_t* smem_raw) {
+__device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const Params& p, const int bx_in,
+                                             const int G_in, const int r_grid, uint8_t* smem_raw) {
+  int bx = bx_in, G = G_in;  // (a balanced ragged batch settles them after the dependency wait)
   const CUtensorMap& tmap = *tmap_ptr;
   constexpr int kBodyThreads = 64 + 128 * kEpiGroups;  // threads that take part (the caller's CTA may not be larger)
   constexpr int kAcc = kEpiGroups < 2 ? 2 : kEpiGroups;  // tile `it` accumulates in buffer it % kAcc
@@ -127,13 +151,21 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   const int lane = tid & 31;
   int r = r_grid, seq = 0, len = 0;  // settled after the dependency wait below
   const bool want_hist = p.hist != nullptr;
-  const int stamp_cta = r_grid * G + bx;
+  const int stamp_cta = r_grid * G_in + bx_in;
   DSA_STAMP(stamp_cta, 0);
   DSA_KTIME_BEGIN(0);
   if (tid == 0) prefetch_tensor_map(&tmap);
 
   // One tile's TMA load into ring slot (it % kStages); the caller has made sure the slot is free.
-  auto issue_tile = [&](int it, int t) {
+  // (paged layout: the tile's two page ids are read by the caller, ahead of the moment the slot
+  // is free, so that the loads from the page table are not on the producer's critical path)
+  auto tile_pages = [&](int t) -> int2 {
+    if (!p.paged) return make_int2(0, 0);
+    const int32_t* pt = p.page_table + int64_t(r) * p.pt_stride + 2 * t;
+    const bool second = int64_t(2 * t + 1) * DSA_PAGE_TOKENS < len;
+    return make_int2(pt[0], second ? pt[1] : -1);
+  };
+  auto issue_tile = [&](int it, int t, int2 pages) {
     const int s = it % kStages;
     const uint32_t dst = smem_u32(s_tiles + size_t(s) * kTileBytes);
     const uint32_t bar = smem_u32(&bars->full[s]);
@@ -141,11 +173,10 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       mbar_arrive_expect_tx(bar, kTileBytes);
       tma_load_2d(dst, &tmap, 0, static_cast<int>(int64_t(seq) * p.k_seq_stride + int64_t(t) * kTileKeys), bar);
     } else {
-      const int32_t* pt = p.page_table + int64_t(r) * p.pt_stride + 2 * t;
       const bool second = int64_t(2 * t + 1) * DSA_PAGE_TOKENS < len;
       mbar_arrive_expect_tx(bar, second ? kTileBytes : kTileBytes / 2);
-      tma_load_3d(dst, &tmap, 0, 0, pt[0], bar);
-      if (second) tma_load_3d(dst + kTileBytes / 2, &tmap, 0, 0, pt[1], bar);
+      tma_load_3d(dst, &tmap, 0, 0, pages.x, bar);
+      if (second) tma_load_3d(dst + kTileBytes / 2, &tmap, 0, 0, pages.y, bar);
     }
   };
 
@@ -174,7 +205,9 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   pdl_wait();  // keys, query, weights and lengths may come from the previous kernel
   pdl_launch_dependents();
   DSA_STAMP(stamp_cta, 13);
-  if (p.balance_rows > 1) r = row_of_rank(p, r_grid, p.balance_rows);
+  if constexpr (kEpiGroups > 2) {  // (batches run the three-group form)
+    if (p.balance_rows > 1) balanced_share(p, bx_in, G_in, p.balance_rows, r, bx, G);
+  }
   seq = r / p.rows_per_seq;
   len = row_len(p, r);
   // q[r] is [n_heads][128 B]. Its loads (and the head weights') are issued before
@@ -200,11 +233,25 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   // Thread 0 starts the key loads right after its own query loads were issued
   // (the other warps issue theirs within the same few cycles).
   if (tid == 0) {
-    int it = 0;
+    if (p.paged) {
+      int2 pages[kStages];
+#pragma unroll
+      for (int i = 0; i < kStages; ++i) {  // all page-table loads first: one latency, not one per tile
+        const int t = bx + i * G;
+        pages[i] = (t < p.tiles_per_row && int64_t(t) * kTileKeys < len) ? tile_pages(t) : make_int2(0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < kStages; ++i) {
+        const int t = bx + i * G;
+        if (t < p.tiles_per_row && int64_t(t) * kTileKeys < len) issue_tile(i, t, pages[i]);
+      }
+    } else {  // (kept as a short rolled loop: the kernel's time inside a decode step follows its code size)
+      int it = 0;
 #pragma unroll 1
-    for (int t = bx; t < p.tiles_per_row && it < kStages; t += G, ++it) {
-      if (int64_t(t) * kTileKeys >= len) break;
-      issue_tile(it, t);
+      for (int t = bx; t < p.tiles_per_row && it < kStages; t += G, ++it) {
+        if (int64_t(t) * kTileKeys >= len) break;
+        issue_tile(it, t, make_int2(0, 0));
+      }
     }
   }
   DSA_STAMP(stamp_cta, 15);
@@ -237,13 +284,14 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
       for (int t = bx; t < p.tiles_per_row; t += G, ++it) {
         if (int64_t(t) * kTileKeys >= len || *abort_flag) break;
         if (it < kStages) continue;
+        const int2 pages = tile_pages(t);  // (in flight during the wait for the slot)
         const uint32_t ph = (it / kStages) & 1;
         if (!mbar_wait(smem_u32(&bars->empty[it % kStages]), ph ^ 1)) {
           atomicOr(&g_device_status, kStatusScanTimeout);
           *abort_flag = 1;
           break;
         }
-        issue_tile(it, t);
+        issue_tile(it, t, pages);
       }
     }
   } else if (warp == 1) {
@@ -304,11 +352,29 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
                                              DSA_PAGE_TOKENS * kKeyBytes + (g & 63) * 4);
     };
     float next_scale = load_scale(bx + grp * G);
+    {
+      // Columns past the row's last live tile are -inf: one pass of 16-byte stores by the epilogue
+      // threads of the row's G CTAs, while they would otherwise wait for the first accumulator.
+      const int64_t dead0 = (int64_t(len) + kTileKeys - 1) / kTileKeys * kTileKeys;
+      const int et = tid - 64, n_epi = 128 * kEpiGroups;
+      if ((reinterpret_cast<uintptr_t>(out_row) & 15u) == 0) {
+        const float4 ninf4 = make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
+        for (int64_t i = dead0 + (int64_t(bx) * n_epi + et) * 4; i < p.ctx; i += int64_t(G) * n_epi * 4) {
+          if (i + 3 < p.ctx) {
+            *reinterpret_cast<float4*>(out_row + i) = ninf4;
+          } else {
+            for (int64_t k = i; k < p.ctx; ++k) out_row[k] = neg_inf;
+          }
+        }
+      } else {
+        for (int64_t i = dead0 + int64_t(bx) * n_epi + et; i < p.ctx; i += int64_t(G) * n_epi) out_row[i] = neg_inf;
+      }
+    }
 #pragma unroll 1
-    for (int t = bx, j = 0; t < p.tiles_per_row; t += G, ++j) {
+    for (int t = bx, j = 0; int64_t(t) * kTileKeys < len; t += G, ++j) {
       if ((j % kEpiGroups) != grp) continue;  // the other group's tile
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
-      if (int64_t(t) * kTileKeys >= len || dead) {  // no visible key in this tile
+      if (dead) {  // a wait ran out: what is left of the row's live part reads -inf
         if (g < p.ctx) out_row[g] = neg_inf;
         continue;
       }

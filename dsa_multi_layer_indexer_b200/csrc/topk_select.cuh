@@ -735,7 +735,7 @@ __device__ __forceinline__ void find_kth_in_registers(const uint32_t (&cnt)[PER]
 template <int NB, bool kSwz = false>
 __device__ __forceinline__ void find_kth_bin(const uint32_t* h, uint32_t k, uint32_t* warp_tot, uint32_t* res) {
   constexpr int PER = NB >= kClThreads ? NB / kClThreads : 1;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   uint32_t cnt[PER];  // this thread's bins, highest first
   if (kSwz) {
     static_assert(!kSwz || PER >= 4, "the interleaved layout is for at least one chunk per thread");
@@ -802,6 +802,11 @@ __device__ __forceinline__ void cluster_sync_all(bool solo) {
   }
 }
 
+// kPlain = the decode step's call: the scan's histogram is there, no candidate exchange, no index
+// map, indices only. It is the same code with those features compiled out, so that the kernel
+// every decode step runs is small (it alternates with three other kernels on the same SMs, and
+// its time in a step follows its size; alone, both forms take the same time).
+template <bool kPlain>
 __global__ void __launch_bounds__(kClThreads, 1)
 topk_cluster_kernel(const Params p, const int nk) {
   extern __shared__ __align__(128) uint8_t topk_cl_smem[];
@@ -813,7 +818,9 @@ topk_cluster_kernel(const Params p, const int nk) {
   const int stamp_cta = 512 + r * int(C) + int(c);
   DSA_KTIME_BEGIN(1);
   DSA_STAMP(stamp_cta, 0);
-  const bool have_hist = p.hist != nullptr;
+  const bool have_hist = kPlain || p.hist != nullptr;
+  const int n_src = kPlain ? 0 : p.n_src, n_dest = kPlain ? 0 : p.n_dest;
+  const int32_t* const index_map = kPlain ? nullptr : p.index_map;
   if (tid == 0) {
     mbar_init(smem_u32(&sh.load_bar), 1);
     mbar_fence_init();
@@ -844,7 +851,7 @@ topk_cluster_kernel(const Params p, const int nk) {
   const int avail = max(0, min(int(p.n), slice_base + span) - slice_base);  // of the slice, inside the buffer
   const float* row = p.logits + int64_t(r) * p.slab_stride;
   // (candidates another GPU wrote are read with plain loads, not by the copy engine)
-  const bool bulk = avail > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0 && p.n_src == 0;
+  const bool bulk = avail > 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0 && n_src == 0;
   const int bulk_elems = bulk ? (avail & ~3) : 0;
   const uint32_t bar = smem_u32(&sh.load_bar);
   if (tid == 0 && bulk_elems > 0) {
@@ -859,15 +866,15 @@ topk_cluster_kernel(const Params p, const int nk) {
   }
   // Candidate exchange: this row's step number picks one of the two gather buffers, so that a
   // rank already pushing step e + 1 does not overwrite what a slower rank still merges for step e.
-  const uint32_t step = p.n_dest > 0 ? p.sent[r] + 1u : (p.n_src > 0 ? p.seen[r] + 1u : 0u);
+  const uint32_t step = n_dest > 0 ? p.sent[r] + 1u : (n_src > 0 ? p.seen[r] + 1u : 0u);
   const int64_t gather_row = int64_t(step & 1u) * R + r;  // (= r outside an exchange)
-  if (p.n_src > 0) row = p.logits + gather_row * p.slab_stride;
+  if (n_src > 0) row = p.logits + gather_row * p.slab_stride;
   int64_t len64 = p.seq_lens ? int64_t(p.seq_lens[r]) : p.n;
   len64 = len64 < 0 ? 0 : (len64 > p.n ? p.n : len64);
   const int len = int(len64);
   const bool take_all = len <= p.topk;
   const int live = max(0, min(len - slice_base, span));  // of the slice, visible
-  if (p.n_src > 0) {
+  if (n_src > 0) {
     // Merge side: the candidates of every source must have landed. One thread polls the flags the
     // sources set behind their data; the wait is bounded by wall time, and when it runs out the
     // kernel says so in the status word and goes on with whatever is there (the host raises).
@@ -876,7 +883,7 @@ topk_cluster_kernel(const Params p, const int nk) {
       bool ok = false;
       for (uint32_t spin = 0; !ok; ++spin) {
         ok = true;
-        for (int src = 0; src < p.n_src; ++src)
+        for (int src = 0; src < n_src; ++src)
           ok = ok && int32_t(ld_acquire_sys(p.wait_flags + size_t(src) * R + r) - step) >= 0;
         if (!ok && (spin & 63u) == 63u && wall_ns() - t0 > p.wait_limit_ns) break;
       }
@@ -888,7 +895,7 @@ topk_cluster_kernel(const Params p, const int nk) {
     for (int i = bulk_elems + tid; i < live; i += kClThreads) flat[i] = __float_as_uint(row[slice_base + i]);
   // A short slice leaves room for its part of the index map behind it: the emission then reads
   // shared memory instead of making one trip to global memory per selected element.
-  const int32_t* imap = p.index_map ? p.index_map + (p.n_src > 0 ? gather_row : int64_t(r)) * p.n : nullptr;
+  const int32_t* imap = index_map ? index_map + (n_src > 0 ? gather_row : int64_t(r)) * p.n : nullptr;
   const bool imap_staged = imap != nullptr && 2 * span <= kClWarps * kWarpKeys;
   if (imap_staged)
     for (int i = tid; i < live; i += kClThreads) flat[span + i] = uint32_t(imap[slice_base + i]);
@@ -1233,80 +1240,86 @@ topk_cluster_kernel(const Params p, const int nk) {
 
   // ---- emit: lane i walks the set bits of its word i in ascending position order
   int32_t* out_idx = p.out_idx ? p.out_idx + int64_t(r) * p.topk : nullptr;
-  float* out_val = p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
+  float* out_val = !kPlain && p.out_val ? p.out_val + int64_t(r) * p.topk : nullptr;
   const uint32_t topk_u = uint32_t(p.topk);
   const float neg_inf = __int_as_float(0xff800000);
-  const int n_dest = p.n_dest;
   const int64_t dest_off = (gather_row * n_dest + p.src_rank) * int64_t(p.topk);  // this rank's slot of row r
   // a selected -inf can only appear when the row has fewer than topk finite logits
   const bool need_value = out_val != nullptr || n_dest > 0 || take_all || kstar <= 0x007FFFFFu;  // ordered_key(-inf)
   {
-    // Four set bits at a time: their index-map loads are issued together (each is a trip to
-    // global memory), the logit values come from the slice in shared memory.
     // A short row fills only the first nk words of a warp: each word is then shared by G lanes
     // (G = 32 / nk rounded down to a power of two), every lane taking 32 / G of its bits, so that
     // the emission is spread over all lanes whatever the row's length.
-    int G = 1;
-    while (2 * G * nk <= 32) G *= 2;
-    const int wsel = lane / G, width = 32 / G, lo = (lane % G) * width;
-    const uint32_t gw = __shfl_sync(0xffffffffu, gword, wsel), qw = __shfl_sync(0xffffffffu, qword, wsel);
-    uint32_t gb = __shfl_sync(0xffffffffu, g_before, wsel), qb = __shfl_sync(0xffffffffu, q_before, wsel);
-    const uint32_t below = (1u << lo) - 1u;  // (lo < 32)
-    const uint32_t mine = (width == 32 ? 0xFFFFFFFFu : (1u << width) - 1u) << lo;
-    gb += uint32_t(__popc(gw & below));
-    qb += uint32_t(__popc(qw & below));
-    uint32_t g = gw & mine, q = qw & mine;
+    uint32_t g = gword, q = qword, gb = g_before, qb = q_before;
+    int wsel = lane;
+    if (2 * nk <= 32) {
+      int G = 2;
+      while (2 * G * nk <= 32) G *= 2;
+      wsel = lane / G;
+      const int width = 32 / G, lo = (lane % G) * width;
+      const uint32_t gw = __shfl_sync(0xffffffffu, gword, wsel), qw = __shfl_sync(0xffffffffu, qword, wsel);
+      gb = __shfl_sync(0xffffffffu, g_before, wsel);
+      qb = __shfl_sync(0xffffffffu, q_before, wsel);
+      const uint32_t below = (1u << lo) - 1u, mine = ((1u << width) - 1u) << lo;  // (width <= 16)
+      gb += uint32_t(__popc(gw & below));
+      qb += uint32_t(__popc(qw & below));
+      g = gw & mine;
+      q = qw & mine;
+    }
     const int word_base = slice_base + warp_off + wsel * 32;
-    const uint32_t* wvals = wbits + wsel * 32;
-    while (g | q) {
-      bool ok[4];
-      int bitv[4];
-      uint32_t slotv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        ok[u] = false;
-        bitv[u] = 0;
-        slotv[u] = 0;
-        if (g | q) {
-          const int b = __ffs(g | q) - 1;
-          const uint32_t bit = 1u << b;
-          uint32_t slot = 0xFFFFFFFFu;
-          if (g & bit) {
-            slot = gb + min(qb, ties_kept);
-            ++gb;
-          } else {
-            if (qb < ties_kept) slot = gb + qb;
-            ++qb;
-          }
-          g &= ~bit;
-          q &= ~bit;
-          ok[u] = slot < topk_u;
-          bitv[u] = b;
-          slotv[u] = slot;
-        }
+    const uint32_t* wvals = wbits + wsel * 32;  // the word's logits (and, staged behind the slice, its index-map entries)
+    // next set bit of the word and its output slot (>= topk: a tie that is not kept)
+    auto next_bit = [&](int& b, uint32_t& slot) {
+      b = __ffs(g | q) - 1;
+      const uint32_t bit = 1u << b;
+      slot = 0xFFFFFFFFu;
+      if (g & bit) {
+        slot = gb + min(qb, ties_kept);
+        ++gb;
+      } else {
+        if (qb < ties_kept) slot = gb + qb;
+        ++qb;
       }
-      int32_t idv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int pos = word_base + bitv[u];
-        idv[u] = !ok[u] ? 0 : imap_staged ? int32_t(wvals[span + bitv[u]]) : imap ? imap[pos] : pos + p.index_offset;
+      g &= ~bit;
+      q &= ~bit;
+    };
+    auto store = [&](int b, uint32_t slot, int32_t id) {
+      float v = 0.f;
+      if (need_value) {
+        v = __uint_as_float(wvals[b]);
+        if (v == neg_inf) id = p.pad;
+        if (out_val) out_val[slot] = v;
       }
+      if (out_idx) out_idx[slot] = id;
+      for (int d = 0; d < n_dest; ++d) {  // plain stores into every rank's gather buffers (peer memory)
+        p.dest_idx[d][dest_off + slot] = id;
+        p.dest_val[d][dest_off + slot] = v;
+      }
+    };
+    if (imap == nullptr || imap_staged) {
+      while (g | q) {
+        int b;
+        uint32_t slot;
+        next_bit(b, slot);
+        if (slot < topk_u) store(b, slot, imap_staged ? int32_t(wvals[span + b]) : word_base + b + p.index_offset);
+      }
+    } else {
+      // index map in global memory: four set bits at a time, so that their loads travel together
+      while (g | q) {
+        int bv[4];
+        uint32_t sv[4];
+        int32_t idv[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (ok[u]) {
-          int32_t id = idv[u];
-          float v = 0.f;
-          if (need_value) {
-            v = __uint_as_float(wvals[bitv[u]]);
-            if (v == neg_inf) id = p.pad;
-            if (out_val) out_val[slotv[u]] = v;
-          }
-          if (out_idx) out_idx[slotv[u]] = id;
-          for (int d = 0; d < n_dest; ++d) {  // plain stores into every rank's gather buffers (peer memory)
-            p.dest_idx[d][dest_off + slotv[u]] = id;
-            p.dest_val[d][dest_off + slotv[u]] = v;
-          }
+        for (int u = 0; u < 4; ++u) {
+          bv[u] = 0;
+          sv[u] = 0xFFFFFFFFu;
+          if (g | q) next_bit(bv[u], sv[u]);
         }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) idv[u] = sv[u] < topk_u ? imap[word_base + bv[u]] : 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (sv[u] < topk_u) store(bv[u], sv[u], idv[u]);
       }
     }
   }
@@ -1331,7 +1344,7 @@ topk_cluster_kernel(const Params p, const int nk) {
       p.sent[r] = step;
     }
   }
-  if (p.n_src > 0 && c == 0 && tid == 0) p.seen[r] = step;
+  if (n_src > 0 && c == 0 && tid == 0) p.seen[r] = step;
   // every CTA has read the scan's histogram long ago (before the first cluster barrier it
   // passed): re-arm it for the next scan, away from the barriers
   if (have_hist && c == 0) {
