@@ -102,7 +102,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_scan2[64], g_opt_scan3[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_topk_cluster[64], g_opt_topk_cluster_any[64], g_opt_gemv[4][64];
+static bool g_opt_fused[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_topk_cluster[64], g_opt_topk_cluster_any[64], g_opt_gemv[4][64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -253,24 +253,29 @@ static int scan_grid_x(int R, int tiles_per_row, int ctas_per_sm) {
 // Two CTAs per SM with a 4-slot ring. Tiles in their epilogue at once per CTA: three for a
 // batch (measured 1.5-2 % faster than two on 32 rows), two for one row (three is 0.15 us
 // slower there). A ragged batch is spread so that every CTA gets about the same number of tiles.
+extern "C++" {
+template <int kEpiGroups, bool kPaged>
+static int launch_scan_tc_as(const CUtensorMap& tmap, const scan::Params& p, dim3 grid, cudaStream_t st) {
+  static bool done[64];
+  constexpr size_t smem = scan::smem_bytes<scan::kStagesTwoPerSm>();
+  auto kernel = scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, kEpiGroups, kPaged>;
+  int rc = opt_in_smem(kernel, smem, done);
+  if (rc) return rc;
+  DSA_CUDA(launch_pdl(kernel, grid, dim3(64 + 128 * kEpiGroups), smem, st, tmap, p));
+  return DSA_OK;
+}
+}  // extern "C++"
+
 static int launch_scan_tc(const CUtensorMap& tmap, const scan::Params& p_in, int R, cudaStream_t st) {
   scan::Params p = p_in;
   p.balance_rows = (R > 1 && R <= 32 && p.seq_lens) ? R : 0;
-  constexpr size_t smem = scan::smem_bytes<scan::kStagesTwoPerSm>();
   if (R > 1) {
-    int rc3 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>, smem, g_opt_scan3);
-    if (rc3) return rc3;
     // a ragged batch of up to 32 rows: one resident wave on a 1-D grid, the rows' CTA counts settled on the device
     const dim3 grid = p.balance_rows ? dim3(std::max(R, 2 * sm_count()), 1) : dim3(scan_grid_x(R, p.tiles_per_row, 2), R);
-    DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 3>, grid, dim3(64 + 128 * 3), smem, st,
-                        tmap, p));
-    return DSA_OK;
+    return p.paged ? launch_scan_tc_as<3, true>(tmap, p, grid, st) : launch_scan_tc_as<3, false>(tmap, p, grid, st);
   }
-  int rc2 = opt_in_smem(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>, smem, g_opt_scan2);
-  if (rc2) return rc2;
-  DSA_CUDA(launch_pdl(scan::indexer_scan_tc_kernel<scan::kStagesTwoPerSm, 2>,
-                      dim3(scan_grid_x(R, p.tiles_per_row, 2), R), dim3(scan::kThreads2), smem, st, tmap, p));
-  return DSA_OK;
+  const dim3 grid(scan_grid_x(R, p.tiles_per_row, 2), R);
+  return p.paged ? launch_scan_tc_as<2, true>(tmap, p, grid, st) : launch_scan_tc_as<2, false>(tmap, p, grid, st);
 }
 
 int dsa_indexer_scan_fp8(const uint8_t* index_q, const float* index_w, const uint8_t* index_k,
@@ -421,8 +426,9 @@ static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStre
   // atomics, about one per cycle per SM: it is spread over as many SMs as the cluster has (2048 logits
   // per CTA or more).
   int ctas = 1;
-  const int64_t per_cta = p.hist ? int64_t(topk::kClThreads) * topk::kClMaxKeys : 2048;
-  while (ctas < topk::kClMaxCtas && int64_t(ctas) * per_cta < n) ctas *= 2;
+  while (ctas < topk::kClMaxCtas && int64_t(ctas) * topk::kClThreads * topk::kClMaxKeys < n) ctas *= 2;
+  if (!p.hist)  // (as long as the launch still fits the device in one wave)
+    while (ctas < topk::kClMaxCtas && int64_t(ctas) * 2048 < n && 2 * ctas * R <= sm_count()) ctas *= 2;
   const int64_t per_key = int64_t(ctas) * topk::kClThreads;
   const int nk = int((n + per_key - 1) / per_key);
   cudaLaunchConfig_t cfg{};

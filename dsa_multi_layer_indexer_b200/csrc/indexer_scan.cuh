@@ -127,7 +127,7 @@ __device__ __forceinline__ void balanced_share(const Params& p, int b, int N, in
 // passes its block indices; the fused indexer + attention launch passes indices
 // of its scan partition). `tmap_ptr` must point at a __grid_constant__ kernel
 // parameter; `smem_raw` is the CTA's dynamic shared memory.
-template <int kStages, int kEpiGroups = 1>
+template <int kStages, int kEpiGroups = 1, bool kPaged = false>
 __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const Params& p, const int bx_in,
                                              const int G_in, const int r_grid, uint8_t* smem_raw) {
   int bx = bx_in, G = G_in;  // (a balanced ragged batch settles them after the dependency wait)
@@ -160,7 +160,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   // (paged layout: the tile's two page ids are read by the caller, ahead of the moment the slot
   // is free, so that the loads from the page table are not on the producer's critical path)
   auto tile_pages = [&](int t) -> int2 {
-    if (!p.paged) return make_int2(0, 0);
+    if (!kPaged) return make_int2(0, 0);
     const int32_t* pt = p.page_table + int64_t(r) * p.pt_stride + 2 * t;
     const bool second = int64_t(2 * t + 1) * DSA_PAGE_TOKENS < len;
     return make_int2(pt[0], second ? pt[1] : -1);
@@ -169,7 +169,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
     const int s = it % kStages;
     const uint32_t dst = smem_u32(s_tiles + size_t(s) * kTileBytes);
     const uint32_t bar = smem_u32(&bars->full[s]);
-    if (!p.paged) {
+    if (!kPaged) {
       mbar_arrive_expect_tx(bar, kTileBytes);
       tma_load_2d(dst, &tmap, 0, static_cast<int>(int64_t(seq) * p.k_seq_stride + int64_t(t) * kTileKeys), bar);
     } else {
@@ -233,7 +233,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   // Thread 0 starts the key loads right after its own query loads were issued
   // (the other warps issue theirs within the same few cycles).
   if (tid == 0) {
-    if (p.paged) {
+    if (kPaged) {
       int2 pages[kStages];
 #pragma unroll
       for (int i = 0; i < kStages; ++i) {  // all page-table loads first: one latency, not one per tile
@@ -340,7 +340,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
     auto load_scale = [&](int t) -> float {
       const int64_t g = int64_t(t) * kTileKeys + quad * 32 + lane;
       if (t >= p.tiles_per_row || g >= len) return 0.f;
-      if (!p.paged) return kscale_row[int64_t(seq) * p.scale_seq_stride + g];
+      if (!kPaged) return kscale_row[int64_t(seq) * p.scale_seq_stride + g];
       // The tensor-map load of a page outside the pool is zero-filled; this plain load would
       // not be, so a bad entry is not followed: the key's logit becomes -inf (NaN scale marks it).
       const int page = p.page_table[int64_t(r) * p.pt_stride + (g >> 6)];
@@ -454,11 +454,13 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   }
 }
 
-template <int kStages, int kEpiGroups = 1>
+// (the dense and the paged cache layout are separate instantiations: what a decode step runs
+// carries no code of the other layout)
+template <int kStages, int kEpiGroups = 1, bool kPaged = false>
 __global__ void __launch_bounds__(64 + 128 * kEpiGroups, kStages <= kStagesTwoPerSm ? 2 : 1)
 indexer_scan_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
   extern __shared__ uint8_t scan_smem[];
-  scan_tc_body<kStages, kEpiGroups>(&tmap, p, blockIdx.x, gridDim.x, blockIdx.y, scan_smem);
+  scan_tc_body<kStages, kEpiGroups, kPaged>(&tmap, p, blockIdx.x, gridDim.x, blockIdx.y, scan_smem);
 }
 
 // ------------------------------------------------------------------------------
