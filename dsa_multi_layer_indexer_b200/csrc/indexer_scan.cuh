@@ -104,9 +104,10 @@ __device__ __forceinline__ int row_of_rank(const Params& p, int y, int R) {
 // proportion to its number of key tiles, so that every CTA works through about the same number
 // of tiles whatever the rows' lengths (R <= 32: one lane per row; every warp computes the same
 // answer by itself). Gives the row of CTA b, its index among the row's CTAs and their count.
-__device__ __forceinline__ void balanced_share(const Params& p, int b, int N, int R, int& r, int& bx, int& G) {
+__device__ __forceinline__ void balanced_share(const Params& p, int b, int N, int R, int& r, int& bx, int& G, int& len) {
   const int lane = threadIdx.x & 31;
-  const int tiles = lane < R ? (row_len(p, lane) + kTileKeys - 1) / kTileKeys : 0;
+  const int my_len = lane < R ? row_len(p, lane) : 0;
+  const int tiles = (my_len + kTileKeys - 1) / kTileKeys;
   int cum = tiles;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -121,6 +122,7 @@ __device__ __forceinline__ void balanced_share(const Params& p, int b, int N, in
   r = j;
   bx = b - __shfl_sync(0xffffffffu, start, j);
   G = __shfl_sync(0xffffffffu, end - start, j);
+  len = __shfl_sync(0xffffffffu, my_len, j);  // (saves the row's own length a second trip to global memory)
 }
 
 // Body of the scan for CTA `bx` of `G` working on row `r` (the kernel below
@@ -205,11 +207,15 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   pdl_wait();  // keys, query, weights and lengths may come from the previous kernel
   pdl_launch_dependents();
   DSA_STAMP(stamp_cta, 13);
+  bool have_len = false;
   if constexpr (kEpiGroups > 2) {  // (batches run the three-group form)
-    if (p.balance_rows > 1) balanced_share(p, bx_in, G_in, p.balance_rows, r, bx, G);
+    if (p.balance_rows > 1) {
+      balanced_share(p, bx_in, G_in, p.balance_rows, r, bx, G, len);
+      have_len = true;
+    }
   }
   seq = r / p.rows_per_seq;
-  len = row_len(p, r);
+  if (!have_len) len = row_len(p, r);
   // q[r] is [n_heads][128 B]. Its loads (and the head weights') are issued before
   // the key tiles' so they are not queued behind 64 KB of TMA traffic per CTA.
   constexpr int kQChunks = (kMaxHeads * 8 + kBodyThreads - 1) / kBodyThreads;
