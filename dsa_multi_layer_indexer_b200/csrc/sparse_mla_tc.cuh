@@ -22,7 +22,10 @@
 // Warp roles (512 threads): a warp reaches the TMEM lane quadrant (warp % 4).
 // Warps 0,1 and 4,5 run the softmax on the 64 real S rows (thread = head; warps 0,1
 // take key columns 0..31, warps 4,5 columns 32..63); warps 0-3 rescale and write
-// O^T; warp 6 allocates TMEM and issues every MMA from one lane; warps 8-15 gather
+// O^T; warp 6 allocates TMEM and issues the score MMAs from one lane, warp 7 the value MMAs (one
+// issuing thread for both made each product wait behind the other's 36 / 16 instructions: 57.2 -> 55.9 us
+// at batch 32; what remains is the instructions' own rate, ~63 cycles per score MMA and ~95 per value MMA
+// at N = 64, i.e. ~3800 of a tile's ~4900 cycles); warps 8-15 gather
 // rows (eight threads per row; with four gather warps the fp8 conversion paced the
 // kernel: 63 us against 56 us at batch 32, bf16 rows unchanged): 16-byte asynchronous copies straight into the swizzled image (bf16 rows)
 // or load / dequantise / store (fp8 rows, fp8 -> f32, x group scale, round to
@@ -58,7 +61,8 @@ constexpr int kTileBytes = kChunks * kChunkBytes;  // 73,728
 constexpr int kProdWarps = DSA_MLA_TC_PROD_WARPS;  // gather warps: 4 or 8
 constexpr int kThreads = 256 + 32 * kProdWarps;
 constexpr int kSoftThreads = 192;              // warps 0-5: softmax / rescale group
-constexpr int kMmaWarp = 6;
+constexpr int kMmaWarp = 6;                    // issues the score products (and owns the tensor-memory allocation)
+constexpr int kPvWarp = 7;                     // issues the value products
 constexpr int kProducerWarp0 = 8;
 constexpr int kProducers = 32 * kProdWarps;
 constexpr int kRowsPerPass = 4 * kProdWarps;    // 8 threads per row
@@ -67,7 +71,6 @@ constexpr float kRescaleLog2 = 40.f;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;                  // two S buffers of 64 columns
 constexpr uint32_t kColO = 128;                // four O^T blocks of 64 columns
-constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr int kMinTiles = 128;                 // fewer 64x64 tiles than this: the mma.sync kernel is faster
 
 struct Smem {
@@ -315,54 +318,59 @@ sparse_mla_tc_kernel(const mla::Params p) {
       if (!p.kv_fp8 && n_tiles > 0) mbar_arrive(bar(kBarKFull + ((n_tiles - 1) & 1)));
     }
   } else if (warp == kMmaWarp) {
-    // ===================================================================== MMA issue
+    // ===================================================================== MMA issue: scores
+    // Two issuing threads, one per product, so that neither waits behind the other's instructions:
+    // this one issues S(t) = Q K(t)^T as soon as the rows of tile t have landed. (S(t) reuses the
+    // buffer of S(t-2); that tile's softmax has read it, since rows(t) could only be written after
+    // the value product of t-2, which needed P(t-2).)
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = idesc_bf16_f32(128, kBN, false, false);
-      constexpr uint32_t idesc_pv = idesc_bf16_f32(128, kHG, true, false);
       if (!mbar_wait(bar(kBarQ), 0)) failed = true;
-      // The value product of tile t is issued as soon as P(t) is ready, the score
-      // product of tile t as soon as its rows have landed, whichever comes first;
-      // S(t) reuses the buffer of S(t-2), so it follows the value product of t-2.
-      int qk = 0, pv = 0;
-      uint32_t spins = 0;
-      while (pv < n_tiles && !failed) {
-        if (pv < qk && mbar_test(bar(kBarPFull), pv & 1)) {
-          tc_fence_after();
-          const uint32_t stage = s_k + uint32_t(pv & 1) * kTileBytes;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-#pragma unroll
-            for (int ks = 0; ks < kBN / 16; ++ks) {
-              const uint64_t a = smem_desc_mn128(stage + uint32_t(2 * j) * kChunkBytes + uint32_t(ks) * 2048u,
-                                                 kChunkBytes, 1024);
-              const uint64_t b = smem_desc_k128(s_p) + uint64_t(2 * ks);
-              tc_mma_f16(tmem + kColO + 64u * j, a, b, idesc_pv, (pv > 0 || ks > 0) ? 1u : 0u);
-            }
-          }
-          tc_commit(bar(kBarKFree + (pv & 1)));
-          DSA_STAMP_IF(pv == 4, scta, 8);
-          ++pv;
-          spins = 0;
-        } else if (qk < n_tiles && qk <= pv + 1 && mbar_test(bar(kBarKFull + (qk & 1)), (qk >> 1) & 1)) {
-          tc_fence_after();
-          DSA_STAMP_IF(qk == 4, scta, 5);
-          const uint32_t stage = s_k + uint32_t(qk & 1) * kTileBytes;
-#pragma unroll
-          for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const uint64_t a = smem_desc_k128(s_q + uint32_t(c) * kChunkBytes) + uint64_t(2 * ks);
-              const uint64_t b = smem_desc_k128(stage + uint32_t(c) * kChunkBytes) + uint64_t(2 * ks);
-              tc_mma_f16(tmem + kColS + 64u * (qk & 1), a, b, idesc_qk, (c | ks) ? 1u : 0u);
-            }
-          }
-          tc_commit(bar(kBarSFull + (qk & 1)));
-          DSA_STAMP_IF(qk == 4, scta, 6);
-          ++qk;
-          spins = 0;
-        } else if (++spins > kSpinLimit) {
+      for (int t = 0; t < n_tiles && !failed; ++t) {
+        if (!mbar_wait(bar(kBarKFull + (t & 1)), (t >> 1) & 1)) {
           failed = true;
+          break;
         }
+        tc_fence_after();
+        DSA_STAMP_IF(t == 4, scta, 5);
+        const uint32_t stage = s_k + uint32_t(t & 1) * kTileBytes;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t a = smem_desc_k128(s_q + uint32_t(c) * kChunkBytes) + uint64_t(2 * ks);
+            const uint64_t b = smem_desc_k128(stage + uint32_t(c) * kChunkBytes) + uint64_t(2 * ks);
+            tc_mma_f16(tmem + kColS + 64u * (t & 1), a, b, idesc_qk, (c | ks) ? 1u : 0u);
+          }
+        }
+        tc_commit(bar(kBarSFull + (t & 1)));
+        DSA_STAMP_IF(t == 4, scta, 6);
+      }
+    }
+  } else if (warp == kPvWarp) {
+    // ===================================================================== MMA issue: values
+    // O^T += V(t)^T P(t)^T as soon as P(t) is in shared memory; its completion frees the tile's slot.
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_pv = idesc_bf16_f32(128, kHG, true, false);
+      for (int t = 0; t < n_tiles && !failed; ++t) {
+        if (!mbar_wait(bar(kBarPFull), t & 1)) {
+          failed = true;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t stage = s_k + uint32_t(t & 1) * kTileBytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks) {
+            const uint64_t a = smem_desc_mn128(stage + uint32_t(2 * j) * kChunkBytes + uint32_t(ks) * 2048u,
+                                               kChunkBytes, 1024);
+            const uint64_t b = smem_desc_k128(s_p) + uint64_t(2 * ks);
+            tc_mma_f16(tmem + kColO + 64u * j, a, b, idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+          }
+        }
+        tc_commit(bar(kBarKFree + (t & 1)));
+        DSA_STAMP_IF(t == 4, scta, 8);
       }
       if (!failed) tc_commit(bar(kBarOFull));
     }
