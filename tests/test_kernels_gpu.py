@@ -83,6 +83,34 @@ def test_scan_ragged_batch_and_mask(ops):
     assert (out[:, 1500:] == 7.0).all()  # columns past ctx are not written
 
 
+def test_scan_ragged_batch_of_32_rows_on_the_shared_out_grid(ops):
+    """32 rows of very different lengths (empty ones among them) on the 1-D grid whose CTAs are
+    shared out by tile count; an output slab whose rows are not 16-byte aligned (the dead tail is
+    then filled by scalar stores); the per-row histogram counts exactly the visible logits."""
+    B, cap, stride = 32, 3000, 3001
+    g = torch.Generator().manual_seed(11)
+    lens = torch.randint(0, cap + 1, (B,), generator=g).tolist()
+    lens[0], lens[5], lens[31] = 0, cap, 1
+    iq8, sq = O.quantize_e4m3_rowwise(torch.randn(B, 64, 128, generator=g))
+    ik8, sk = O.quantize_e4m3_rowwise(torch.randn(B, cap, 128, generator=g))
+    wp = sq * (torch.randn(B, 64, generator=g) / 8)
+    seq_lens = torch.tensor(lens, dtype=torch.int32)
+    out = torch.full((B, stride), 7.0, device="cuda")
+    hist = torch.zeros(B, ops.HIST_BINS, dtype=torch.int32, device="cuda")
+    got = ops.indexer_scan_fp8(dev(iq8), dev(wp), dev(ik8), dev(sk), dev(seq_lens), out=out, hist=hist).cpu()
+    hist = hist.cpu()
+    for b in range(B):
+        n = lens[b]
+        if n:
+            ref = O.indexer_logits_fp8(iq8[b:b + 1], ik8[b], wp[b:b + 1], sk[b])[0]
+            assert rel_err(got[b, :n], ref[:n]) < 1e-5, b
+        assert torch.isinf(got[b, n:cap]).all() and (got[b, n:cap] < 0).all(), b
+        bits = got[b, :n].contiguous().view(torch.int32).long() & 0xFFFFFFFF
+        key = torch.where(bits >> 31 != 0, ~bits & 0xFFFFFFFF, bits | 0x80000000)
+        assert torch.equal(hist[b].long(), torch.bincount(key >> 20, minlength=ops.HIST_BINS)), b
+    assert (out[:, cap:] == 7.0).all()  # columns past ctx are not written
+
+
 def test_scan_full_context_128k(ops):
     n = 131072
     iq8, ik8, wp, sk = make_indexer(0, 1, 64, n)
