@@ -207,10 +207,11 @@ class DSAModel(nn.Module):
             positions=torch.zeros(batch, dtype=torch.int64, device=dev),
             seq_lens=torch.zeros(batch, dtype=torch.int32, device=dev),
             batch_index=torch.arange(batch, device=dev),
-            # the indexer branch runs on a high-priority stream (the reference's HH_LAG_STREAM_PRIORITY,
-            # sglang_overlay/mli-sglang-v0.5.16.patch:1795-1800): its kernels get SM slots ahead of the
-            # attention's, which then fills in behind the scan and beside the 8-CTA top-k
-            side_stream=torch.cuda.Stream(device=dev, priority=-1),
+            # (default priority: a high-priority stream, the reference's HH_LAG_STREAM_PRIORITY,
+            # sglang_overlay/mli-sglang-v0.5.16.patch:1795-1800, shortens the bare attention + indexer
+            # pair by 2 us but measured 0.5 us per layer slower inside the full stack, where the
+            # main stream's projections and all-reduces are the critical path)
+            side_stream=torch.cuda.Stream(device=dev),
             runs_indexer=parse_retention(retention, len(self.layers)), fp8=fp8,
             workspaces=[IndexerWorkspace.create(batch, capacity, self.config.index_topk, dev, fp8)
                         for _ in self.layers])
