@@ -85,21 +85,6 @@ __device__ __forceinline__ int row_len(const Params& p, int r) {
   return static_cast<int>(len);
 }
 
-// Row with the y-th longest sequence among rows [0, R), R <= 32 (ties: lower row
-// first). Called by whole warps. A grid is scheduled in block order, so a ragged
-// batch starts its long rows first and the short rows fill the tail.
-__device__ __forceinline__ int row_of_rank(const Params& p, int y, int R) {
-  const int lane = threadIdx.x & 31;
-  const int mine = lane < R ? row_len(p, lane) : -1;
-  int rank = 0;
-  for (int j = 0; j < R; ++j) {
-    const int other = __shfl_sync(0xffffffffu, mine, j);
-    rank += (other > mine || (other == mine && j < lane)) ? 1 : 0;
-  }
-  const uint32_t hit = __ballot_sync(0xffffffffu, lane < R && rank == y);
-  return hit ? __ffs(hit) - 1 : y;
-}
-
 // Ragged batch on a 1-D grid of N CTAs: row j gets one CTA plus its share of the other N - R in
 // proportion to its number of key tiles, so that every CTA works through about the same number
 // of tiles whatever the rows' lengths (R <= 32: one lane per row; every warp computes the same
@@ -154,6 +139,7 @@ __device__ __forceinline__ void scan_tc_body(const CUtensorMap* tmap_ptr, const 
   int r = r_grid, seq = 0, len = 0;  // settled after the dependency wait below
   const bool want_hist = p.hist != nullptr;
   const int stamp_cta = r_grid * G_in + bx_in;
+  (void)stamp_cta;  // (used by the tracing build only)
   DSA_STAMP(stamp_cta, 0);
   DSA_KTIME_BEGIN(0);
   if (tid == 0) prefetch_tensor_map(&tmap);

@@ -816,6 +816,7 @@ topk_cluster_kernel(const Params p, const int nk) {
   const uint32_t c = cluster_cta_rank(), C = cluster_num_ctas();
   const bool solo = C == 1;
   const int stamp_cta = 512 + r * int(C) + int(c);
+  (void)stamp_cta;  // (used by the tracing build only)
   DSA_KTIME_BEGIN(1);
   DSA_STAMP(stamp_cta, 0);
   const bool have_hist = kPlain || p.hist != nullptr;
