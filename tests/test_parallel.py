@@ -369,3 +369,69 @@ def test_tensor_parallel_model_equals_the_unsharded_one(tmp_path):
     out = tmp_path / "result.txt"
     mp.spawn(_tp_model_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
     assert out.read_text() == "ok"
+
+
+def _stress_worker(rank: int, world: int, port: int, out_path: str):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from dsa_multi_layer_indexer_b200 import _lib, ops
+        from dsa_multi_layer_indexer_b200.parallel import SeqShardedIndexer, key_range
+
+        torch.manual_seed(0)
+        R, topk, n = 2, 2048, 40000
+        iq8, sq = ops.quantize_e4m3_rowwise(torch.randn(R, 64, 128, device="cuda"))
+        ik8, sk = ops.quantize_e4m3_rowwise(torch.randn(n, 128, device="cuda"))
+        wp_base = (sq * torch.randn(R, 64, device="cuda") / 8).contiguous()
+        wp = wp_base.clone()
+        lo, hi = key_range(rank, world, n)
+        keys = ik8[lo:hi].unsqueeze(0).expand(R, -1, -1).contiguous()
+        scales = sk[lo:hi].unsqueeze(0).expand(R, -1).contiguous()
+        idxr = SeqShardedIndexer(R, topk, hi - lo, lo, "cuda", exchange="p2p")
+        step = idxr.capture(iq8, wp, keys, scales)
+        ik2 = ik8.unsqueeze(0).expand(R, -1, -1).contiguous()
+        sk2 = sk.unsqueeze(0).expand(R, -1).contiguous()
+        expected = []
+        for s in range(16):  # sixteen different inputs, each checked against the unsharded selection
+            wp.copy_(wp_base.roll(s, dims=1))
+            expected.append(ops.topk_select(ops.indexer_scan_fp8(iq8, wp, ik2, sk2), topk).clone())
+        bad = torch.zeros((), dtype=torch.int64, device="cuda")
+        for s in range(3000):  # every step compared on the device, no host round trip in between
+            wp.copy_(wp_base.roll(s % 16, dims=1))
+            bad += (step() != expected[s % 16]).any()
+        # the all-reduce: partial sums that differ per rank, compared with NCCL's result
+        ar = ops.PeerAllReduce(7168, world, rank, "cuda")
+        ar.connect()
+        torch.manual_seed(100 + rank)
+        xs = [torch.randn(7168, device="cuda") for _ in range(8)]
+        want = []
+        for x in xs:
+            y = x.clone()
+            dist.all_reduce(y)
+            want.append(y)
+        out = torch.empty(7168, device="cuda")
+        for s in range(5000):
+            ar.all_reduce(xs[s % 8], out=out)
+            bad += ((out - want[s % 8]).abs() > 1e-4 * want[s % 8].abs().clamp_min(1.0)).any()
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        flag = torch.tensor([int(bad)], device="cuda")
+        dist.all_reduce(flag)
+        if rank == 0:
+            with open(out_path, "w") as f:
+                f.write("ok" if int(flag) == 0 else f"{int(flag)} mismatches")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_exchange_and_all_reduce_hold_over_thousands_of_steps(tmp_path):
+    """The release pattern of the peer-store protocol (stores, a barrier, ONE system-scope fence
+    by one thread, relaxed flag stores) under load: 3000 captured steps of the sequence-sharded
+    selection and 5000 all-reduces on two GPUs, every result compared on the device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = tmp_path / "result.txt"
+    mp.spawn(_stress_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    assert out.read_text() == "ok"
