@@ -71,7 +71,10 @@ constexpr float kRescaleLog2 = 40.f;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;                  // two S buffers of 64 columns
 constexpr uint32_t kColO = 128;                // four O^T blocks of 64 columns
-constexpr int kMinTiles = 128;                 // fewer 64x64 tiles than this: the mma.sync kernel is faster
+#ifndef DSA_MLA_TC_MIN_TILES
+#define DSA_MLA_TC_MIN_TILES 128  // (a build flag, for measuring the crossover)
+#endif
+constexpr int kMinTiles = DSA_MLA_TC_MIN_TILES;  // fewer 64x64 tiles than this: the mma.sync kernel is faster
 
 struct Smem {
   static constexpr int q_off = 0;
