@@ -196,6 +196,55 @@ def test_topk_short_rows_and_neg_inf(ops):
     assert int((got < 0).sum()) == 64 - 20
 
 
+def test_topk_mixed_rows_repeated(ops):
+    """Twelve rows of one launch that take every path of the cluster kernel (random, heavy ties,
+    all equal, sorted so that the candidates sit in one CTA, short and boundary lengths), with and
+    without the 12-bit histogram, against a stable descending sort; the launch is then replayed
+    500 times from a graph and every result compared (a race between CTAs would show as a rare miss)."""
+    torch.manual_seed(1)
+    R, n, topk = 12, 60000, 2048
+    logits = torch.randn(R, n, device="cuda") * 5
+    logits[1] = torch.randint(0, 40, (n,), device="cuda").float()
+    logits[2] = torch.randint(0, 3, (n,), device="cuda").float()
+    logits[3] = 1.0
+    logits[4, ::3] = logits[4, 0]
+    logits[5] = torch.sort(logits[5]).values
+    lens = torch.tensor([n, n, n, n, n, n, 100, 2048, 2049, 30000, 16384, 16385], dtype=torch.int32, device="cuda")
+
+    def reference(row, ln):
+        order = torch.sort(row[:ln], descending=True, stable=True).indices[:topk]
+        out = torch.full((topk,), -1, dtype=torch.int32, device="cuda")
+        out[:order.numel()] = torch.sort(order).values.int()
+        return out
+
+    want = torch.stack([reference(logits[r], int(lens[r])) for r in range(R)])
+    key = logits.view(torch.int32)
+    bins = ((torch.where(key < 0, ~key, key | -2147483648) >> 20) & 0xFFF).long()
+    hist0 = torch.stack([torch.bincount(bins[r, :int(lens[r])], minlength=ops.HIST_BINS) for r in range(R)]).int()
+    for use_hist in (False, True):
+        hist = hist0.clone() if use_hist else None
+        out = torch.empty(R, topk, dtype=torch.int32, device="cuda")
+        ops.topk_select(logits, topk, lens, hist=hist, out_idx=out)
+        assert torch.equal(out, want), use_hist
+        if use_hist:
+            assert int(hist.abs().sum()) == 0  # consumed and re-armed
+            hist.copy_(hist0)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph):
+                ops.topk_select(logits, topk, lens, hist=hist, out_idx=out)
+                if use_hist:
+                    hist.copy_(hist0)
+        torch.cuda.current_stream().wait_stream(side)
+        bad = torch.zeros((), dtype=torch.int64, device="cuda")
+        for _ in range(500):
+            graph.replay()
+            bad += (out != want).any()
+        assert int(bad) == 0, use_hist
+
+
 def test_topk_strided_slab_offset_and_map(ops):
     torch.manual_seed(4)
     slab = torch.randn(3, 8192)
