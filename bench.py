@@ -439,7 +439,7 @@ def run_ours(args):
     main = LayerSet("replicated", ctx, L, world, rank, dev, inputs)
     ms_rep = time_steps(main, args.steps, args.warmup, barrier, args.scan_impl, args.graph_per_layer)
     forms["tp_heads+replicated_indexer"] = ms_rep
-    ms_shard = ms_shard2 = coll_ms = None
+    ms_shard = ms_shard2 = ms_rep2 = coll_ms = None
     if world > 1:
         sh = LayerSet("sharded", ctx, L, world, rank, dev, inputs)
         ms_shard = time_steps(sh, args.steps, args.warmup, barrier, args.scan_impl)
@@ -471,6 +471,10 @@ def run_ours(args):
             ms_shard2 = time_steps(sh2, args.steps, args.warmup, barrier, args.scan_impl)
             sh2.free()
             forms["tp_heads+seq_sharded_indexer_ctx262144"] = ms_shard2
+            rep2 = LayerSet("replicated", 2 * ctx, min(L, 8), world, rank, dev, inputs)  # the same length, every rank scanning all of it
+            ms_rep2 = time_steps(rep2, args.steps, args.warmup, barrier, args.scan_impl)
+            rep2.free()
+            forms["tp_heads+replicated_indexer_ctx262144"] = ms_rep2
     ms_step = min(ms_rep, ms_shard) if ms_shard is not None else ms_rep
     best_form = "tp_heads+seq_sharded_indexer" if (ms_shard is not None and ms_shard < ms_rep) else \
         ("tp_heads+replicated_indexer" if world > 1 else "tp1_heads")
@@ -588,11 +592,11 @@ def run_ours(args):
 
     _lib.check_device_status()
     vals = [ms_step, scan_ms, topk_ms, attn_ms, e2e["ms_per_step"], ms_rep, ms_shard or 0.0, ms_shard2 or 0.0,
-            coll_ms or 0.0]
+            coll_ms or 0.0, ms_rep2 or 0.0]
     times = torch.tensor(vals, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_step, scan_ms, topk_ms, attn_ms, e2e_ms, ms_rep, ms_shard_m, ms_shard2_m, coll_m = times.tolist()
+    ms_step, scan_ms, topk_ms, attn_ms, e2e_ms, ms_rep, ms_shard_m, ms_shard2_m, coll_m, ms_rep2_m = times.tolist()
     e2e["ms_per_step"] = e2e_ms
     e2e["value"] = 1e3 / e2e_ms
     if world > 1:
@@ -634,7 +638,8 @@ def run_ours(args):
         if world > 1:
             out["forms_ms_per_step"] = {k: v for k, v in
                                         (("tp_heads+replicated_indexer", ms_rep), ("tp_heads+seq_sharded_indexer", ms_shard_m),
-                                         ("tp_heads+seq_sharded_indexer_ctx262144", ms_shard2_m)) if v}
+                                         ("tp_heads+seq_sharded_indexer_ctx262144", ms_shard2_m),
+                                         ("tp_heads+replicated_indexer_ctx262144", ms_rep2_m)) if v}
             out["collective_us"] = coll_m * 1e3
             out["comm"] = ("sharded form: every step stores this rank's 2048 (index, logit) candidates into all ranks' gather "
                            "buffers over NVLink (peer stores, no NCCL call, no multicast) and waits on the device for the "

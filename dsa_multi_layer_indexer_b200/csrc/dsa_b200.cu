@@ -102,7 +102,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_topk_cluster[64], g_opt_topk_cluster_any[64], g_opt_gemv[4][64];
+static bool g_opt_fused[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_gemv[4][64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -415,27 +415,24 @@ int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
 }
 
 // Rows of up to kClMaxN logits: one cluster of 1..8 CTAs per row, no scratch.
-static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStream_t st) {
-  const bool plain = p.hist && !p.n_src && !p.n_dest && !p.index_map && !p.out_val;
-  int rc = plain ? opt_in_smem(topk::topk_cluster_kernel<true>, sizeof(topk::ClShared), g_opt_topk_cluster)
-                 : opt_in_smem(topk::topk_cluster_kernel<false>, sizeof(topk::ClShared), g_opt_topk_cluster_any);
+extern "C++" {
+template <bool kPlain, int kMaxC>
+static int launch_topk_cluster_as(const topk::Params& p, int R, int ctas, int nk, cudaStream_t st) {
+  static bool done[64];
+  auto kernel = topk::topk_cluster_kernel<kPlain, kMaxC>;
+  constexpr size_t smem = sizeof(topk::ClSharedT<kMaxC>);
+  int dev = 0;
+  DSA_CUDA(cudaGetDevice(&dev));
+  const bool first = !(dev >= 0 && dev < 64 && done[dev]);
+  int rc = opt_in_smem(kernel, smem, done);
   if (rc) return rc;
-  // As few CTAs as hold the row at 32 logits per thread: every CTA added costs cluster barriers and
-  // remote reductions, and a row of up to 16384 logits needs none of either.
-  // A row that comes without the scan's histogram counts its own first level with shared-memory
-  // atomics, about one per cycle per SM: it is spread over as many SMs as the cluster has (2048 logits
-  // per CTA or more).
-  int ctas = 1;
-  while (ctas < topk::kClMaxCtas && int64_t(ctas) * topk::kClThreads * topk::kClMaxKeys < n) ctas *= 2;
-  if (!p.hist)  // (as long as the launch still fits the device in one wave)
-    while (ctas < topk::kClMaxCtas && int64_t(ctas) * 2048 < n && 2 * ctas * R <= sm_count()) ctas *= 2;
-  const int64_t per_key = int64_t(ctas) * topk::kClThreads;
-  const int nk = int((n + per_key - 1) / per_key);
+  if (first && kMaxC > 8)  // sixteen CTAs per cluster is not a portable size: the kernel opts in
+    DSA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[2];
   cfg.gridDim = dim3(ctas, R);
   cfg.blockDim = dim3(topk::kClThreads);
-  cfg.dynamicSmemBytes = sizeof(topk::ClShared);
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = ctas;
@@ -445,9 +442,29 @@ static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStre
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  if (plain) DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel<true>, p, nk));
-  else DSA_CUDA(cudaLaunchKernelEx(&cfg, topk::topk_cluster_kernel<false>, p, nk));
+  DSA_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, nk));
   return DSA_OK;
+}
+}  // extern "C++"
+
+static int launch_topk_cluster(const topk::Params& p, int R, int64_t n, cudaStream_t st) {
+  const bool plain = p.hist && !p.n_src && !p.n_dest && !p.index_map && !p.out_val;
+  // As few CTAs as hold the row at 32 logits per thread: every CTA added costs cluster barriers and
+  // remote stores, and a row of up to 16384 logits needs none of either.
+  // A row that comes without the scan's histogram counts its own first level with shared-memory
+  // atomics, about one per cycle per SM: it is spread over as many SMs as the cluster has (2048 logits
+  // per CTA or more).
+  int ctas = 1;
+  while (ctas < topk::kClMaxCtasBig && int64_t(ctas) * topk::kClThreads * topk::kClMaxKeys < n) ctas *= 2;
+  if (!p.hist)  // (as long as the launch still fits the device in one wave)
+    while (ctas < topk::kClMaxCtas && int64_t(ctas) * 2048 < n && 2 * ctas * R <= sm_count()) ctas *= 2;
+  const int64_t per_key = int64_t(ctas) * topk::kClThreads;
+  const int nk = int((n + per_key - 1) / per_key);
+  if (ctas > topk::kClMaxCtas)
+    return plain ? launch_topk_cluster_as<true, topk::kClMaxCtasBig>(p, R, ctas, nk, st)
+                 : launch_topk_cluster_as<false, topk::kClMaxCtasBig>(p, R, ctas, nk, st);
+  return plain ? launch_topk_cluster_as<true, topk::kClMaxCtas>(p, R, ctas, nk, st)
+               : launch_topk_cluster_as<false, topk::kClMaxCtas>(p, R, ctas, nk, st);
 }
 
 int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist,

@@ -525,7 +525,8 @@ topk_finish_kernel(const Params p) {
 }
 
 // ------------------------------------------------------------------------------
-// One launch for rows of up to kClMaxN logits: a thread-block cluster per row.
+// One launch for rows of up to kClMaxN logits: a thread-block cluster per row (1-8 CTAs up to
+// 131072 logits; 16 CTAs, a cluster size the kernel opts into, up to 262144).
 //
 // Each CTA of the cluster owns a contiguous slice of the row (brought into shared
 // memory by one bulk copy) and looks at every logit of it exactly once. With the
@@ -542,7 +543,7 @@ topk_finish_kernel(const Params p) {
 //     comparison (larger key first, lower position first among equal keys), and
 //     knows from the tables and the ranks how many candidates every CTA keeps:
 //     no further exchange;
-//   * a CTA with more than kListCap candidates, or more than kSurvCap candidates
+//   * a CTA with more candidates than its region of the list holds (8192 / C), or more than kSurvCap candidates
 //     sharing the 19 bits (rows with many equal logits): two more radix levels
 //     (7 + 13 bits) as histograms PUSHED into every CTA (distributed-shared-
 //     memory reductions), a cluster barrier after each, candidates equal to k*
@@ -565,20 +566,23 @@ topk_finish_kernel(const Params p) {
 constexpr int kClThreads = 512;
 constexpr int kClWarps = kClThreads / 32;
 constexpr int kClMaxKeys = 32;                                // logits per thread (= mask words per warp)
-constexpr int kClMaxCtas = 8;                                 // portable cluster size
-constexpr int64_t kClMaxN = int64_t(kClMaxCtas) * kClThreads * kClMaxKeys;  // 131072
+constexpr int kClMaxCtas = 8;                                 // portable cluster size: rows of up to 131072 logits
+constexpr int kClMaxCtasBig = 16;                             // non-portable cluster size (an opt-in of the kernel): up to 262144
+constexpr int64_t kClPortableN = int64_t(kClMaxCtas) * kClThreads * kClMaxKeys;   // 131072
+constexpr int64_t kClMaxN = int64_t(kClMaxCtasBig) * kClThreads * kClMaxKeys;     // 262144
 constexpr int kL2Bits = 7, kL2Bins = 1 << kL2Bits;            // key bits 19..13
 constexpr int kL3Bits = 13, kL3Bins = 1 << kL3Bits;           // key bits 12..0
 constexpr int kWarpKeys = 32 * kClMaxKeys;                    // 1024: a warp's share of the slice
-constexpr int kListCap = 1024;                                // candidates a CTA may list (else: histograms)
+constexpr int kListTotal = 8192;                              // list entries per CTA image: a region of kListTotal / C per CTA of the cluster (more candidates in one CTA: histograms)
 constexpr int kSurvCap = 256;                                 // candidates ranked by comparison (else: histograms)
 
-struct ClShared {
+template <int kMaxC>
+struct ClSharedT {
   uint32_t hist1[kBins];         // level 1: whole row (copy of the scan's, or pushed by the CTAs)
   uint32_t hist3[kL3Bins];       // level 3: whole row, pushed; stored as swizzled_bin<kL3Bins> says
   uint32_t hist2[kL2Bins];       // level 2: whole row, pushed
   uint32_t local2[kL2Bins];      // level 2: this CTA's part
-  uint32_t cand_kept[kClMaxCtas];  // per CTA of the cluster: its candidates that are kept (list path)
+  uint32_t cand_kept[kMaxC];  // per CTA of the cluster: its candidates that are kept (list path)
   uint32_t surv_n;               // entries of surv[]
   uint32_t list_n;               // this CTA's candidates (slots handed out in its region of the list)
   uint32_t above_n;              // this CTA's certainly kept logits
@@ -587,18 +591,22 @@ struct ClShared {
   uint32_t ties[kClWarps][kClMaxKeys];   // same, for the elements equal to k*
   uint32_t warp_tot[kClWarps];
   uint32_t warp_base[kClWarps];
-  uint32_t cta_tot[kClMaxCtas];  // (ties << 16 | kept) of every CTA of the cluster
-  uint32_t cnts[kClMaxCtas];     // (certainly kept << 16 | candidates) of every CTA, pushed with the list
+  uint32_t cta_tot[kMaxC];  // (ties << 16 | kept) of every CTA of the cluster
+  uint32_t cnts[kMaxC];     // (certainly kept << 16 | candidates) of every CTA, pushed with the list
   uint32_t res[4];
   uint64_t surv[kSurvCap + 4];   // key << 32 | ~place of the candidates sharing the k-th key's top 19 bits (+ 4 zeros)
-  alignas(16) uint32_t tbl[kClMaxCtas][kL2Bins];  // level 2: every CTA's histogram of its candidates, pushed
+  alignas(16) uint32_t tbl[kMaxC][kL2Bins];  // level 2: every CTA's histogram of its candidates, pushed
   uint64_t load_bar;                       // mbarrier of the slice's bulk copy
-  uint2 list[kClMaxCtas][kListCap];        // (key, place) of every CTA's candidates, pushed; place =
+  uint2 list[kListTotal];                  // (key, place) of every CTA's candidates, region c at c * kListTotal / C, pushed; place =
                                            // CTA << 14 | warp << 10 | word << 5 | bit orders like the position
   alignas(128) uint32_t bits[kClWarps][kWarpKeys];  // (a bulk copy's destination must be 16-byte aligned)      // the slice's raw logits: word (w, i * 32 + l) is thread (w, l)'s i-th
 };
+using ClShared = ClSharedT<kClMaxCtas>;
+using ClSharedBig = ClSharedT<kClMaxCtasBig>;
 static_assert(kL3Bins >= kBins, "hist3 doubles as the local level-1 histogram");
-static_assert(offsetof(ClShared, bits) % 128 == 0 && offsetof(ClShared, load_bar) % 8 == 0, "alignment of the copy target and its barrier");
+static_assert(offsetof(ClShared, bits) % 128 == 0 && offsetof(ClShared, load_bar) % 8 == 0 &&
+              offsetof(ClSharedBig, bits) % 128 == 0 && offsetof(ClSharedBig, load_bar) % 8 == 0,
+              "alignment of the copy target and its barrier");
 
 // Adds `amount` of 1s to h[digit] for the lanes with `pred`. The lanes that share the first
 // such lane's digit add once, so a row of equal logits does not serialise on one address.
@@ -694,12 +702,13 @@ __device__ __forceinline__ void find_kth_bin_warp(const uint32_t* h, uint32_t k,
 
 // The same over the sum of n_tbl 128-bin tables that lie one after the other; res[2] gets the
 // size of the bin found.
+template <int kMaxC>
 __device__ __forceinline__ void find_kth_bin_tables(const uint32_t* tbl, int n_tbl, uint32_t k, uint32_t* res) {
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
     uint32_t cnt[4] = {0u, 0u, 0u, 0u};  // highest bin first
 #pragma unroll
-    for (int t = 0; t < kClMaxCtas; ++t) {
+    for (int t = 0; t < kMaxC; ++t) {
       if (t < n_tbl) {
         const uint4 x = reinterpret_cast<const uint4*>(tbl + t * kL2Bins)[31 - lane];
         cnt[0] += x.w, cnt[1] += x.z, cnt[2] += x.y, cnt[3] += x.x;
@@ -806,11 +815,12 @@ __device__ __forceinline__ void cluster_sync_all(bool solo) {
 // map, indices only. It is the same code with those features compiled out, so that the kernel
 // every decode step runs is small (it alternates with three other kernels on the same SMs, and
 // its time in a step follows its size; alone, both forms take the same time).
-template <bool kPlain>
+template <bool kPlain, int kMaxC = kClMaxCtas>
 __global__ void __launch_bounds__(kClThreads, 1)
 topk_cluster_kernel(const Params p, const int nk) {
   extern __shared__ __align__(128) uint8_t topk_cl_smem[];
-  ClShared& sh = *reinterpret_cast<ClShared*>(topk_cl_smem);
+  using Shared = ClSharedT<kMaxC>;
+  Shared& sh = *reinterpret_cast<Shared*>(topk_cl_smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r = blockIdx.y;
   const uint32_t c = cluster_cta_rank(), C = cluster_num_ctas();
@@ -829,8 +839,8 @@ topk_cluster_kernel(const Params p, const int nk) {
   // ---- before anything of the previous launch is needed: clear what is accumulated into and tell
   // the cluster it is clear (shared memory only, so this runs while the previous launch drains)
   {
-    static_assert(offsetof(ClShared, warp_tot) % 16 == 0, "the cleared part is whole 16-byte words");
-    constexpr int kZero16 = int(offsetof(ClShared, warp_tot) / 16);  // the histograms and both masks
+    static_assert(offsetof(Shared, warp_tot) % 16 == 0, "the cleared part is whole 16-byte words");
+    constexpr int kZero16 = int(offsetof(Shared, warp_tot) / 16);  // the histograms and both masks
     uint4* z = reinterpret_cast<uint4*>(&sh);
     for (int i = (have_hist ? kBins / 4 : 0) + tid; i < kZero16; i += kClThreads)  // (a given hist1 is overwritten)
       z[i] = make_uint4(0, 0, 0, 0);
@@ -1015,8 +1025,9 @@ topk_cluster_kernel(const Params p, const int nk) {
     // ---- the candidates (bin T) of the whole row go to every CTA as a list of (key, position),
     // with the CTA's level-2 histogram of them (key bits 19..13) and its count of certainly kept
     // logits: one cluster barrier, and everything after it is local. A CTA with more than
-    // kListCap candidates sends only its counts, and the whole cluster (which sees the same
+    // kListTotal / C candidates sends only its counts, and the whole cluster (which sees the same
     // counts) takes the histogram path below instead.
+    const uint32_t list_cap = uint32_t(kListTotal) / C;  // entries per CTA's region of the list
     const uint32_t n_cand = uint32_t(__popc(my_cand));
     const uint32_t cinc = warp_inclusive_scan(n_cand);
     const uint32_t wabove = __reduce_add_sync(0xffffffffu, uint32_t(__popc(my_kept)));
@@ -1027,7 +1038,7 @@ topk_cluster_kernel(const Params p, const int nk) {
     }
     if (have_hist && !solo) cluster_wait();  // every CTA of the cluster runs (without the scan's histogram: taken at level 1)
     slot = __shfl_sync(0xffffffffu, slot, 31);
-    if (slot + __shfl_sync(0xffffffffu, cinc, 31) <= uint32_t(kListCap)) {  // (else the region overflows: see below)
+    if (slot + __shfl_sync(0xffffffffu, cinc, 31) <= list_cap) {  // (else the region overflows: see below)
       slot += cinc - n_cand;
       uint32_t rem = my_cand;
       while (rem) {  // into this CTA's own copy of its region first
@@ -1036,20 +1047,20 @@ topk_cluster_kernel(const Params p, const int nk) {
         const uint32_t key = ordered_key(__uint_as_float(wbits[lane * 32 + i]));
         smem_red_add(&sh.local2[(key >> kL3Bits) & (kL2Bins - 1)], 1u);
         // place = (CTA, warp, word, bit): orders like the position
-        sh.list[c][slot++] = make_uint2(key, (c << 14) | uint32_t((warp << 10) | (lane << 5) | i));
+        sh.list[c * list_cap + slot++] = make_uint2(key, (c << 14) | uint32_t((warp << 10) | (lane << 5) | i));
       }
     }
     __syncthreads();
     const uint32_t listed_here = sh.list_n;
-    const bool fits = listed_here <= uint32_t(kListCap);
+    const bool fits = listed_here <= list_cap;
     if (!solo) {
       // ... then one entry per thread to the other CTAs, the level-2 counts and the totals
       if (fits) {
         for (uint32_t j = tid; j < listed_here; j += kClThreads) {
-          const uint2 e = sh.list[c][j];
-          const uint32_t a = smem_u32(&sh.list[c][j]);
+          const uint2 e = sh.list[c * list_cap + j];
+          const uint32_t a = smem_u32(&sh.list[c * list_cap + j]);
 #pragma unroll
-          for (uint32_t cc = 0; cc < uint32_t(kClMaxCtas); ++cc)
+          for (uint32_t cc = 0; cc < uint32_t(kMaxC); ++cc)
             if (cc < C && cc != c) cluster_st2(cluster_map(a, cc), e.x, e.y);
         }
         if (tid >= kClThreads - kL2Bins) {
@@ -1057,7 +1068,7 @@ topk_cluster_kernel(const Params p, const int nk) {
           const uint32_t x = sh.local2[bin];
           const uint32_t a = smem_u32(&sh.tbl[c][bin]);
 #pragma unroll
-          for (uint32_t cc = 0; cc < uint32_t(kClMaxCtas); ++cc)
+          for (uint32_t cc = 0; cc < uint32_t(kMaxC); ++cc)
             if (cc < C) cluster_st(cluster_map(a, cc), x);
         }
       }
@@ -1074,12 +1085,12 @@ topk_cluster_kernel(const Params p, const int nk) {
     bool listed;
     {
       const uint32_t pk = lane < int(C) ? sh.cnts[lane] & 0xFFFFu : 0u;
-      listed = !__any_sync(0xffffffffu, pk > uint32_t(kListCap));
+      listed = !__any_sync(0xffffffffu, pk > list_cap);
     }
     uint32_t p19 = 0, need2 = 0, n_surv = 0, b2 = 0;
     if (listed) {
       // ---- level 2 (key bits 19..13): the sum of the CTAs' tables, searched by one warp
-      find_kth_bin_tables(&sh.tbl[0][0], int(C), need, sh.res);
+      find_kth_bin_tables<kMaxC>(&sh.tbl[0][0], int(C), need, sh.res);
       b2 = sh.res[0];
       p19 = (T << kL2Bits) | b2;
       need2 = sh.res[1];
@@ -1110,7 +1121,7 @@ topk_cluster_kernel(const Params p, const int nk) {
       }
       {
         const int region = warp & int(C - 1u), chunk_step = (kClWarps / int(C)) * 32;
-        const uint2* rlist = sh.list[region];
+        const uint2* rlist = sh.list + uint32_t(region) * list_cap;
         const int rcnt = int(sh.cnts[region] & 0xFFFFu);
         for (int j = (warp / int(C)) * 32 + lane; j - lane < rcnt; j += chunk_step) {
           const uint2 e = j < rcnt ? rlist[j] : make_uint2(0u, 0u);
@@ -1143,14 +1154,17 @@ topk_cluster_kernel(const Params p, const int nk) {
         if (have && before + 1u == need2) sh.res[3] = key;
         const bool keep = have && before < need2;
         const uint32_t owner = place >> 14;
-        // kept survivors per owning CTA: eight 8-bit counters (at most 32 each) in two warp sums
+        // kept survivors per owning CTA: 8-bit counters (at most 32 each), four to a warp sum
         const uint32_t one = keep ? 1u << (8u * (owner & 3u)) : 0u;
-        const uint32_t lo = __reduce_add_sync(0xffffffffu, owner < 4u ? one : 0u);
-        const uint32_t hi = __reduce_add_sync(0xffffffffu, owner < 4u ? 0u : one);
-        if (lane < int(C)) {
-          const uint32_t n = ((lane < 4 ? lo : hi) >> (8 * (lane & 3))) & 0xFFu;
-          if (n) smem_red_add(&sh.cand_kept[lane], n);
+        uint32_t mine_n = 0;
+#pragma unroll
+        for (uint32_t w4 = 0; w4 < uint32_t(kMaxC) / 4; ++w4) {
+          if (4 * w4 < C) {
+            const uint32_t sum = __reduce_add_sync(0xffffffffu, (owner >> 2) == w4 ? one : 0u);
+            if (uint32_t(lane) >> 2 == w4) mine_n = (sum >> (8 * (lane & 3))) & 0xFFu;
+          }
         }
+        if (lane < int(C) && mine_n) smem_red_add(&sh.cand_kept[lane], mine_n);
         if (keep && owner == c) smem_red_or(&sh.kept[(place >> 10) & 15u][(place >> 5) & 31u], 1u << (place & 31u));
       }
       __syncthreads();

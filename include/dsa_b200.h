@@ -179,7 +179,7 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
  * gather_idx / gather_val / flags given to dsa_topk_select_push are arrays of `world`
  * pointers: entry d is rank d's buffer as THIS process can address it (its own pointer for
  * d == rank, else from dsa_ipc_open). The two launches of a step must be enqueued in this
- * order on every rank, the same number of times; rows of up to 131072 logits. */
+ * order on every rank, the same number of times; rows of up to 262144 logits. */
 int dsa_topk_select_push(const float* logits, const int32_t* seq_lens, uint32_t* hist, int R, int64_t n,
                          int64_t slab_stride, int topk, int32_t pad_value, int32_t index_offset, int world,
                          int rank, void* const* gather_idx, void* const* gather_val, void* const* flags,
@@ -221,15 +221,14 @@ int dsa_ipc_close(void* ptr, int64_t offset);
  * (no histogram input, no index map) for hosts that have no way to obtain device
  * memory for scratch: a runtime whose memory pool is closed once serving starts,
  * a plugin that is handed only its input and output buffers, or code running at
- * a point where cudaMalloc is forbidden. Rows of up to 131072 logits need no
+ * a point where cudaMalloc is forbidden. Rows of up to 262144 logits need no
  * scratch at all (one cluster kernel, shared memory only); for longer rows the
  * scratch is a fixed DSA_TOPK_STATIC_SCRATCH_BYTES array inside the library's
  * device image, so each GPU that loads the library gives up that much memory
  * until the process exits; the call itself performs no cudaMalloc / cudaFree
  * and calls no allocating routine.
  *   - Limit: dsa_topk_workspace_bytes(R, n) <= DSA_TOPK_STATIC_SCRATCH_BYTES
- *     (for rows longer than 131072: one row of up to ~480k logits, or two of
- *     ~240k); larger requests return DSA_ERR_UNSUPPORTED with a message naming
+ *     (for rows longer than 262144: one row of up to ~480k logits); larger requests return DSA_ERR_UNSUPPORTED with a message naming
  *     both sizes. Every argument is checked before anything is enqueued.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call before starting any stream

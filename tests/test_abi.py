@@ -83,7 +83,7 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert rc == -1 and b"world" in h.dsa_last_error()
     rc = h.dsa_topk_select_push(addr, None, None, 1, 4096, 4096, 2048, -1, 0, 2, 2, ptrs, ptrs, ptrs, addr, None)
     assert rc == -1 and b"rank" in h.dsa_last_error()
-    rc = h.dsa_topk_select_push(addr, None, None, 1, 1 << 18, 1 << 18, 2048, -1, 0, 2, 0, ptrs, ptrs, ptrs, addr, None)
+    rc = h.dsa_topk_select_push(addr, None, None, 1, 1 << 19, 1 << 19, 2048, -1, 0, 2, 0, ptrs, ptrs, ptrs, addr, None)
     assert rc == -2
     rc = h.dsa_topk_merge_wait(addr, addr, addr, addr, addr, 1, 2, 2048, -1, 0, None)
     assert rc == -1 and b"limit" in h.dsa_last_error()

@@ -170,7 +170,8 @@ def check_topk(ops, logits, topk, lens=None, pad=-1):
 
 
 @pytest.mark.parametrize("n,topk", [(100, 16), (2048, 2048), (4096, 2048), (5000, 64), (32768, 2048),
-                                    (40000, 2048), (131072, 2048), (200000, 2048), (262144, 2048), (1 << 20, 4096)])
+                                    (40000, 2048), (131072, 2048), (131073, 2048), (200000, 2048), (262144, 2048),
+                                    (262145, 2048), (1 << 20, 4096)])
 def test_topk_random(ops, n, topk):
     torch.manual_seed(n)
     check_topk(ops, torch.randn(2, n), topk)

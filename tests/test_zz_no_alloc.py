@@ -35,11 +35,14 @@ def test_static_scratch_topk_matches_regular_entry_point():
 
     lib = _lib.lib()
     torch.manual_seed(0)
-    # Rows longer than 131072 logits are the ones that use the built-in scratch. Call 1: one long
-    # row; call 2: two shorter ragged rows with ties, laid out differently in the scratch; call 3:
-    # rows short enough for the scratch-free kernel, which must not mind the leftovers either.
+    # Rows longer than 262144 logits are the ones that use the built-in scratch. Call 1: one long
+    # row; call 2: a longer ragged row with ties, laid out differently in the scratch; call 3: two
+    # rows for the 16-CTA cluster kernel and call 4 three short ones for the 1-8-CTA form, neither of
+    # which uses the scratch or minds the leftovers.
     cases = [
         (torch.randn(1, 300000, device="cuda"), None, 2048),
+        ((torch.randint(-6, 6, (1, 450000), device="cuda").float() * 0.5).contiguous(),
+         torch.tensor([440001], dtype=torch.int32, device="cuda"), 2048),
         ((torch.randint(-6, 6, (2, 150000), device="cuda").float() * 0.5).contiguous(),
          torch.tensor([150000, 140001], dtype=torch.int32, device="cuda"), 2048),
         ((torch.randint(-6, 6, (3, 40000), device="cuda").float() * 0.5).contiguous(),
@@ -64,7 +67,7 @@ def test_static_scratch_topk_rejects_what_does_not_fit():
     from dsa_multi_layer_indexer_b200 import _lib
 
     lib = _lib.lib()
-    logits = torch.zeros(4, 200000, device="cuda")  # 4 rows of 200000 need 6.6 MB of scratch, the array holds 4 MiB
+    logits = torch.zeros(2, 300000, device="cuda")  # 2 rows of 300000 need more scratch than the 4 MiB the array holds
     rc, _, _ = _static_topk(lib, logits, None, 2048, pad=-1, offset=0)
     assert rc == -2
     msg = lib.dsa_last_error().decode()
