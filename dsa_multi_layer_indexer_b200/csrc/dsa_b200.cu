@@ -408,13 +408,49 @@ int dsa_indexer_scan_f32(const float* index_q, const float* index_w, const float
 }
 
 // ------------------------------------------------------------------ top-k
+// Longest row the one-launch cluster kernel takes on the current device: 262144 logits where a
+// cluster of 16 CTAs with its shared memory can be scheduled (asked of the runtime once per
+// device), else the portable 8-CTA limit of 131072. Without a device: the portable limit.
+static int64_t topk_cluster_max_n() {
+  static int state[64];  // 0 unknown, 1 portable only, 2 sixteen CTAs
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return topk::kClPortableN;
+  }
+  if (state[dev] == 0) {
+    auto kernel = topk::topk_cluster_kernel<false, topk::kClMaxCtasBig>;
+    constexpr size_t smem = sizeof(topk::ClSharedBig);
+    int clusters = 0;
+    bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) == cudaSuccess &&
+              cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (ok) {
+      cudaLaunchConfig_t cfg{};
+      cudaLaunchAttribute attr[1];
+      cfg.gridDim = dim3(topk::kClMaxCtasBig, 1);
+      cfg.blockDim = dim3(topk::kClThreads);
+      cfg.dynamicSmemBytes = smem;
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = topk::kClMaxCtasBig;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      ok = cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters >= 1;
+    }
+    cudaGetLastError();  // (a refusal is an answer, not an error of the caller)
+    state[dev] = ok ? 2 : 1;
+  }
+  return state[dev] == 2 ? topk::kClMaxN : topk::kClPortableN;
+}
+
 int64_t dsa_topk_workspace_bytes(int R, int64_t n) {
   if (R <= 0 || n <= 0) return 0;
-  if (n <= topk::kClMaxN) return 16;  // the cluster kernel keeps everything in shared memory
+  if (n <= topk_cluster_max_n()) return 16;  // the cluster kernel keeps everything in shared memory
   return topk::workspace_words(R, n) * 4;
 }
 
-// Rows of up to kClMaxN logits: one cluster of 1..8 CTAs per row, no scratch.
+// Rows of up to topk_cluster_max_n() logits: one cluster of 1..8 (or 16) CTAs per row, no scratch.
 extern "C++" {
 template <bool kPlain, int kMaxC>
 static int launch_topk_cluster_as(const topk::Params& p, int R, int ctas, int nk, cudaStream_t st) {
@@ -482,7 +518,7 @@ int dsa_topk_select(const float* logits, const int32_t* seq_lens, uint32_t* hist
   DSA_REQUIRE(workspace_bytes >= dsa_topk_workspace_bytes(R, n),
               "topk: workspace of %lld bytes is smaller than dsa_topk_workspace_bytes = %lld",
               (long long)workspace_bytes, (long long)dsa_topk_workspace_bytes(R, n));
-  if (n <= topk::kClMaxN) {
+  if (n <= topk_cluster_max_n()) {
     topk::Params p{};
     p.logits = logits;
     p.seq_lens = seq_lens;
@@ -539,9 +575,9 @@ static int exchange_common(int R, int64_t n, int topk_k, int world) {
   DSA_REQUIRE(world >= 1 && world <= topk::kMaxRanks, "candidate exchange: world=%d out of range [1, %d]", world,
               topk::kMaxRanks);
   DSA_REQUIRE(topk_k > 0 && topk_k <= 65536, "candidate exchange: k=%d out of range [1, 65536]", topk_k);
-  if (n <= 0 || n > topk::kClMaxN)
+  if (n <= 0 || n > topk_cluster_max_n())
     return fail(DSA_ERR_UNSUPPORTED, "candidate exchange: rows of %lld logits (the limit is %lld)", (long long)n,
-                (long long)topk::kClMaxN);
+                (long long)topk_cluster_max_n());
   return DSA_OK;
 }
 
@@ -732,7 +768,7 @@ int dsa_topk_select_static(const float* logits, const int32_t* seq_lens, int32_t
   void* scratch = nullptr;
   int rc = topk_static_scratch(&scratch);
   if (rc) return rc;
-  if (n > topk::kClMaxN) {
+  if (n > topk_cluster_max_n()) {
     // The array still holds whatever the previous call left, possibly laid out for
     // another (R, n): the histograms of this call's layout have to start at zero.
     const int64_t words = topk::mask_words(n), slots = words / 4;

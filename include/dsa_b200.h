@@ -221,8 +221,9 @@ int dsa_ipc_close(void* ptr, int64_t offset);
  * (no histogram input, no index map) for hosts that have no way to obtain device
  * memory for scratch: a runtime whose memory pool is closed once serving starts,
  * a plugin that is handed only its input and output buffers, or code running at
- * a point where cudaMalloc is forbidden. Rows of up to 262144 logits need no
- * scratch at all (one cluster kernel, shared memory only); for longer rows the
+ * a point where cudaMalloc is forbidden. Rows of up to 262144 logits (131072
+ * on a device that cannot schedule a cluster of 16 CTAs) need no scratch at all
+ * (one cluster kernel, shared memory only); for longer rows the
  * scratch is a fixed DSA_TOPK_STATIC_SCRATCH_BYTES array inside the library's
  * device image, so each GPU that loads the library gives up that much memory
  * until the process exits; the call itself performs no cudaMalloc / cudaFree
