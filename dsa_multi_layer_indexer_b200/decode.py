@@ -204,9 +204,21 @@ class HostDecoder:
         ``h_indices`` is valid) once the step has completed. With ``poll`` the host
         waits on the epoch word the graph's last node posts to pinned memory (falling
         back to a stream synchronise after 2 s) instead of a stream synchronise."""
+        self.launch()
+        return self.wait()
+
+    def launch(self) -> None:
+        """Enqueues the step and returns at once. A caller with several decoders (one per
+        layer cache, each with its own pinned buffers) may launch the next one before it
+        waits for this one, which hides the host's launch cost behind the device's work."""
         self.graph.replay()
         if self.poll:
             self._expected = (self._expected + 1) & 0xFFFFFFFF
+
+    def wait(self) -> torch.Tensor:
+        """Blocks until the step enqueued by the last :meth:`launch` has put its results into
+        ``h_out`` / ``h_indices``."""
+        if self.poll:
             word, want = self._flag_word, self._expected
             deadline = None
             spins = 0
