@@ -599,9 +599,9 @@ def run_ours(args):
            "form": "tp%d_heads%s" % (world, "+replicated_indexer" if world > 1 else ""),
            "pipelined_depth2_ms_per_step": e2e_pipe_dt * 1e3,
            "note": "one graph per step, cycling over all %d layer caches: index_q / index_w pinned host -> device by a "
-                   "kernel node, q by the copy engine beside the scan, kernels, selection -> pinned host by a kernel node "
-                   "on a forked stream, attention output written straight into pinned host memory; the host polls the "
-                   "epoch word the graph's last node posts, every step; pipelined_depth2 = the same steps with the next "
+                   "kernel node, q by the copy engine beside the scan, kernels, attention output written straight into pinned "
+                   "host memory, selection -> pinned host by the graph's last node, which then posts the epoch word the "
+                   "host polls, every step; pipelined_depth2 = the same steps with the next "
                    "step's graph enqueued before the host waits for the current one (this rank's wall clock)" % L}
 
     _lib.check_device_status()

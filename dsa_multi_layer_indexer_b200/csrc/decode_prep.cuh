@@ -175,6 +175,18 @@ copy16_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n1
   for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n16; i += int64_t(gridDim.x) * 256) dst[i] = src[i];
 }
 
+// The same copy for data that the kernel enqueued just before it neither produces nor reads
+// (a step's queries coming from the host while the selection is still being computed): it
+// copies at once, beside that kernel, and only then waits for it, so it still completes after
+// it and the kernel enqueued next, whose own wait is for this grid, sees both. A copy in the
+// stream's chain of programmatic dependents, where a copy on a forked stream would cost a join.
+__global__ void __launch_bounds__(256)
+copy16_beside_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n16) {
+  pdl_launch_dependents();
+  for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n16; i += int64_t(gridDim.x) * 256) dst[i] = src[i];
+  pdl_wait();
+}
+
 // Completion signal for a host that polls instead of synchronising: bumps a device-side
 // epoch counter and posts the new value to a word of pinned host memory, after a
 // system-wide fence so that everything the stream wrote to host memory before this
@@ -185,6 +197,25 @@ __global__ void post_epoch_kernel(uint32_t* __restrict__ counter, volatile uint3
   *counter = e;
   __threadfence_system();
   *host_flag = e;
+}
+
+// The same signal with a last small copy in front of it (a step's selection, a few KB, into
+// pinned host memory): one node at the end of a step's graph instead of a copy on a forked
+// stream, a join and the signal. One CTA; the block barrier orders every thread's copy before
+// thread 0's system-wide fence. Launched as a programmatic dependent: it is resident and waiting
+// when the kernel before it retires.
+__global__ void __launch_bounds__(512)
+copy_post_epoch_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n16,
+                       uint32_t* __restrict__ counter, volatile uint32_t* __restrict__ host_flag) {
+  pdl_wait();
+  for (int64_t i = threadIdx.x; i < n16; i += 512) dst[i] = src[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t e = *counter + 1;
+    *counter = e;
+    __threadfence_system();
+    *host_flag = e;
+  }
 }
 
 // ------------------------------------------------------------------ skinny GEMV

@@ -937,11 +937,34 @@ int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream) {
   return DSA_OK;
 }
 
+int dsa_copy_bytes_beside(void* dst, const void* src, int64_t bytes, void* stream) {
+  DSA_REQUIRE(dst && src, "copy: null pointer");
+  DSA_REQUIRE(bytes > 0 && bytes % 16 == 0 && aligned16(dst) && aligned16(src),
+              "copy: size and both pointers must be multiples of 16 bytes");
+  const int64_t n16 = bytes / 16;
+  int64_t blocks = (n16 + 255) / 256;
+  if (blocks > sm_count()) blocks = sm_count();  // its CTAs stay resident until the kernel before it has completed
+  DSA_CUDA(launch_pdl(prep::copy16_beside_kernel, dim3(unsigned(blocks)), dim3(256), 0,
+                      static_cast<cudaStream_t>(stream), static_cast<uint4*>(dst), static_cast<const uint4*>(src), n16));
+  return DSA_OK;
+}
+
 int dsa_post_epoch(uint32_t* counter, uint32_t* host_flag, void* stream) {
   DSA_REQUIRE(counter && host_flag, "post epoch: null pointer");
   // an ordinary launch (no programmatic overlap): it must start after everything before it has completed
   prep::post_epoch_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter, host_flag);
   DSA_CUDA(cudaGetLastError());
+  return DSA_OK;
+}
+
+int dsa_copy_post_epoch(void* dst, const void* src, int64_t bytes, uint32_t* counter, uint32_t* host_flag,
+                        void* stream) {
+  DSA_REQUIRE(dst && src && counter && host_flag, "copy + post epoch: null pointer");
+  DSA_REQUIRE(bytes > 0 && bytes <= (int64_t(1) << 20) && bytes % 16 == 0 && aligned16(dst) && aligned16(src),
+              "copy + post epoch: at most 1 MiB; size and both pointers must be multiples of 16 bytes");
+  DSA_CUDA(launch_pdl(prep::copy_post_epoch_kernel, dim3(1), dim3(512), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<uint4*>(dst), static_cast<const uint4*>(src), bytes / 16, counter,
+                      static_cast<volatile uint32_t*>(host_flag)));
   return DSA_OK;
 }
 

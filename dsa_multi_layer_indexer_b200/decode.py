@@ -164,29 +164,42 @@ class HostDecoder:
     def _body(self, sm_scale: float) -> None:
         s = self.state
         main, side = torch.cuda.current_stream(), self._side
-        # H2D in two pieces: index_q | index_w (8 KB, needed by the scan at once) on the
-        # main stream, q (needed only by the attention) on a forked stream beside the scan.
+        # H2D in two pieces: index_q | index_w (8 KB, needed by the scan at once) in front of the
+        # scan, q (needed only by the attention) while the indexer runs: by a kernel that copies
+        # beside the top-k and completes after it, which keeps the whole step one chain of
+        # programmatic dependents, or else by the copy engine on a forked stream joined before the
+        # attention (a join gives the attention's node full dependencies).
         small = s.index_q.numel() + s.index_w.numel() * 4
-        side.wait_stream(main)
-        if self.kernel_copies and small % 16 == 0:
+        chained = self.kernel_copies and small % 16 == 0 and (self.h_in.numel() - small) % 16 == 0
+        if chained:
             ops.copy_bytes(s.in_arena[:small], self.h_in[:small])  # a kernel node: starts sooner than a copy node
+            s.run_indexer(self.cache)
+            ops.copy_bytes(s.in_arena[small:], self.h_in[small:], beside_previous=True)
         else:
+            side.wait_stream(main)
             s.in_arena[:small].copy_(self.h_in[:small], non_blocking=True)
-        with torch.cuda.stream(side):
-            s.in_arena[small:].copy_(self.h_in[small:], non_blocking=True)  # copy engine (a kernel copy measured no better)
-        s.run_indexer(self.cache)
-        main.wait_stream(side)
-        # The selection goes back on the forked stream while the attention runs, and the
-        # attention's merge kernel writes its output straight into the pinned host
-        # buffer, so no device-to-host copy is left on the step's critical path.
-        side.wait_stream(main)
-        with torch.cuda.stream(side):
-            if self.kernel_copies:
-                ops.copy_bytes(self.h_indices, s.indices)
-            else:
-                self.h_indices.copy_(s.indices, non_blocking=True)
+            with torch.cuda.stream(side):
+                s.in_arena[small:].copy_(self.h_in[small:], non_blocking=True)
+            s.run_indexer(self.cache)
+            main.wait_stream(side)
+        # The attention's merge kernel writes its output straight into the pinned host buffer. The
+        # selection (a few KB) goes back in the step's last node, which also posts the completion
+        # word: one programmatic dependent of the merge kernel instead of a copy on the forked
+        # stream, a join and a separate signal (a join gives its node full dependencies).
+        sel_bytes = self.h_indices.numel() * 4
+        fused_tail = self.poll and self.kernel_copies and sel_bytes % 16 == 0 and sel_bytes <= 1 << 20
+        if not fused_tail:
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                if self.kernel_copies:
+                    ops.copy_bytes(self.h_indices, s.indices)
+                else:
+                    self.h_indices.copy_(s.indices, non_blocking=True)
         ops.sparse_mla_decode(s.q, self.cache.kv, s.indices, sm_scale, s.seq_lens, scratch=s.scratch,
                               out=self.h_out)
+        if fused_tail:
+            ops.copy_post_epoch(self.h_indices, s.indices, self._epoch_dev, self._flag)
+            return
         main.wait_stream(side)
         if self.poll:
             ops.post_epoch(self._epoch_dev, self._flag)  # after the join: every output is in host memory

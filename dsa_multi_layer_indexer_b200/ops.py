@@ -480,14 +480,17 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def copy_bytes(dst: torch.Tensor, src: torch.Tensor) -> None:
+def copy_bytes(dst: torch.Tensor, src: torch.Tensor, beside_previous: bool = False) -> None:
     """``dst <- src`` (same byte count, a multiple of 16) by a kernel on the current stream.
-    Each side is a contiguous CUDA tensor or pinned host memory."""
+    Each side is a contiguous CUDA tensor or pinned host memory. With ``beside_previous`` the
+    copy runs beside the kernel enqueued just before it (which must neither write nor read
+    these bytes) and completes after it; what is enqueued next sees both."""
     for t, name in ((dst, "dst"), (src, "src")):
         _need((t.is_cuda or t.is_pinned()) and t.is_contiguous(), f"{name} must be contiguous CUDA or pinned memory")
     nbytes = dst.numel() * dst.element_size()
     _need(nbytes == src.numel() * src.element_size() and nbytes % 16 == 0, "byte counts must match and be a multiple of 16")
-    _lib.check(_lib.lib().dsa_copy_bytes(_ptr(dst), _ptr(src), nbytes, _stream()))
+    fn = _lib.lib().dsa_copy_bytes_beside if beside_previous else _lib.lib().dsa_copy_bytes
+    _lib.check(fn(_ptr(dst), _ptr(src), nbytes, _stream()))
 
 
 def post_epoch(counter: torch.Tensor, host_flag: torch.Tensor) -> None:
@@ -498,6 +501,20 @@ def post_epoch(counter: torch.Tensor, host_flag: torch.Tensor) -> None:
     _need(host_flag.is_pinned() and host_flag.dtype == torch.int32 and host_flag.numel() == 1,
           "host_flag: one pinned int32")
     _lib.check(_lib.lib().dsa_post_epoch(_ptr(counter), _ptr(host_flag), _stream()))
+
+
+def copy_post_epoch(dst: torch.Tensor, src: torch.Tensor, counter: torch.Tensor, host_flag: torch.Tensor) -> None:
+    """:func:`copy_bytes` of at most 1 MiB followed by :func:`post_epoch`, as one launch: the last
+    node of a step when a few KB (the selection) still have to reach the host before the signal."""
+    for t, name in ((dst, "dst"), (src, "src")):
+        _need((t.is_cuda or t.is_pinned()) and t.is_contiguous(), f"{name} must be contiguous CUDA or pinned memory")
+    nbytes = dst.numel() * dst.element_size()
+    _need(nbytes == src.numel() * src.element_size() and nbytes % 16 == 0 and nbytes <= 1 << 20,
+          "byte counts must match, be a multiple of 16 and at most 1 MiB")
+    _need(counter.is_cuda and counter.dtype == torch.int32 and counter.numel() == 1, "counter: one CUDA int32")
+    _need(host_flag.is_pinned() and host_flag.dtype == torch.int32 and host_flag.numel() == 1,
+          "host_flag: one pinned int32")
+    _lib.check(_lib.lib().dsa_copy_post_epoch(_ptr(dst), _ptr(src), nbytes, _ptr(counter), _ptr(host_flag), _stream()))
 
 
 def gemv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

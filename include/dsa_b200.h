@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define DSA_ABI_VERSION 8
+#define DSA_ABI_VERSION 9
 
 enum dsa_status {
   DSA_OK = 0,
@@ -336,12 +336,26 @@ int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, v
  * node starts sooner than a copy-engine node, which matters for the few KB a decode step
  * brings from the host. No counterpart in the reference. */
 int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream);
+/* The same copy, run BESIDE the kernel enqueued just before it on the stream instead of after
+ * it: for data that kernel neither writes nor reads (a step's queries arriving from the host
+ * while the selection is being computed). The copy still completes after that kernel, and
+ * whatever is enqueued next on the stream sees both. It keeps the stream's chain of
+ * programmatic dependents intact where a copy on a forked stream would cost a join. The
+ * kernel before it must be one of this library's (they release their dependents early);
+ * behind any other work it behaves like dsa_copy_bytes. No counterpart in the reference. */
+int dsa_copy_bytes_beside(void* dst, const void* src, int64_t bytes, void* stream);
 
 /* Completion signal for a host that polls instead of calling a stream synchronise:
  * *counter (device) is incremented and its new value posted to *host_flag (pinned
  * host memory) once everything enqueued before it on the stream has completed and its
  * writes to host memory are visible. No counterpart in the reference. */
 int dsa_post_epoch(uint32_t* counter, uint32_t* host_flag, void* stream);
+/* dsa_copy_bytes (at most 1 MiB, by one CTA) followed by dsa_post_epoch in ONE launch: the
+ * last node of a step's graph when a few KB (the selection) still have to reach the host
+ * before the signal. It starts as a programmatic dependent of the kernel enqueued before
+ * it on the stream and runs once that kernel has completed. No counterpart in the reference. */
+int dsa_copy_post_epoch(void* dst, const void* src, int64_t bytes, uint32_t* counter, uint32_t* host_flag,
+                        void* stream);
 
 /* y[b, n] = sum_k w[n, k] x[b, k] for a decode batch of 1..4 rows: bf16 operands, fp32
  * accumulation, w [n, k] row-major streamed once (the projection GEMVs of

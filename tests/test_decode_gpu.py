@@ -87,6 +87,38 @@ def test_copy_bytes_between_pinned_host_and_device():
         ops.copy_bytes(dst, torch.zeros(4096, dtype=torch.int32))  # pageable host memory
 
 
+def test_copy_beside_the_previous_kernel_and_copy_with_epoch():
+    """The copy that runs beside the kernel enqueued before it completes after that kernel, and
+    the next launch sees both: a top-k, then a copy from pinned memory beside it, then a kernel
+    copy that reads what the two wrote. The final node copies and posts the epoch word in one launch."""
+    from dsa_multi_layer_indexer_b200 import ops
+
+    torch.manual_seed(3)
+    n = 65536
+    src = torch.empty(36864, dtype=torch.int32).pin_memory()
+    dst = torch.zeros(36864, dtype=torch.int32, device="cuda")
+    sel = torch.empty(1, 2048, dtype=torch.int32, device="cuda")
+    seen = torch.zeros(36864 + 2048, dtype=torch.int32, device="cuda")
+    back = torch.zeros(36864 + 2048, dtype=torch.int32).pin_memory()
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    for it in range(20):
+        logits = torch.randn(1, n, device="cuda")
+        src.copy_(torch.randint(0, 1 << 30, (36864,), dtype=torch.int32))
+        ops.topk_select(logits, 2048, out_idx=sel)
+        ops.copy_bytes(dst, src, beside_previous=True)
+        ops.copy_bytes(seen[:36864], dst)
+        ops.copy_bytes(seen[36864:], sel.view(-1))
+        ops.copy_post_epoch(back, seen, counter, flag)
+        torch.cuda.synchronize()
+        assert int(flag.item()) == it + 1
+        assert torch.equal(back[:36864], src)
+        want = torch.topk(logits[0], 2048).indices.sort().values.int().cpu()
+        assert torch.equal(back[36864:].sort().values, want)
+    with pytest.raises(ValueError):
+        ops.copy_post_epoch(back[:3], seen[:3], counter, flag)
+
+
 def test_host_decoder_stream_sync_mode_agrees_with_polling():
     from dsa_multi_layer_indexer_b200.decode import HostDecoder
 
