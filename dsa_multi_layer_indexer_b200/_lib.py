@@ -47,6 +47,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_sparse_mla_partials": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _l, _i, _p]),
     "dsa_sparse_mla_combine": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "dsa_sparse_mla_decode": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _l, _i, _p]),
+    "dsa_sparse_mla_decode_beside": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _l, _i, _p]),
     "dsa_fused_decode": (_i, [_p] * 15 + [_i, _i, _i, _i, _i, _f, _l, _i, _l, _l, _l, _l, _l, _p]),
     "dsa_sparse_mla_f32": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _l, _p]),
     "dsa_rmsnorm": (_i, [_p, _p, _p, _l, _i, _f, _i, _p]),

@@ -102,7 +102,7 @@ static int opt_in_smem(K kernel, size_t bytes, bool (&done)[64]) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return DSA_OK;
 }
-static bool g_opt_fused[64], g_opt_mla[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_gemv[4][64];
+static bool g_opt_fused[64], g_opt_mla[64], g_opt_mla_beside[64], g_opt_mla_tc[64], g_opt_scan_f32[64], g_opt_topk[64], g_opt_gemv[4][64];
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled
 // while its predecessor in the stream is still draining; it calls
@@ -822,10 +822,10 @@ static int mla_prepare(const void* q, const void* kv, const int32_t* indices, co
   return DSA_OK;
 }
 
-int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
-                            const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
-                            int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
-                            int64_t kv_seq_stride, int kv_fp8, void* stream) {
+static int mla_partials_launch(const void* q, const void* kv, const int32_t* indices,
+                               const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
+                               int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
+                               int64_t kv_seq_stride, int kv_fp8, bool beside, void* stream) {
   mla::Params p;
   int rc0 = mla_prepare(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
                         nsplit, sm_scale, kv_seq_stride, kv_fp8, true, &p);
@@ -844,6 +844,13 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
     return DSA_OK;
   }
   const size_t smem = kv_fp8 ? mla::SmemLayout::bytes_fp8 : mla::SmemLayout::bytes_bf16;
+  if (beside) {
+    int rc = opt_in_smem(mla::sparse_mla_partials_beside_kernel, mla::SmemLayout::bytes_fp8, g_opt_mla_beside);
+    if (rc) return rc;
+    DSA_CUDA(launch_pdl(mla::sparse_mla_partials_beside_kernel, dim3(nsplit, H / DSA_HEAD_BLOCK, R),
+                        dim3(mla::kThreads), smem, static_cast<cudaStream_t>(stream), p));
+    return DSA_OK;
+  }
   {
     int rc = opt_in_smem(mla::sparse_mla_partials_kernel, mla::SmemLayout::bytes_fp8, g_opt_mla);
     if (rc) return rc;
@@ -851,6 +858,14 @@ int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indice
   DSA_CUDA(launch_pdl(mla::sparse_mla_partials_kernel, dim3(nsplit, H / DSA_HEAD_BLOCK, R),
                       dim3(mla::kThreads), smem, static_cast<cudaStream_t>(stream), p));
   return DSA_OK;
+}
+
+int dsa_sparse_mla_partials(const void* q, const void* kv, const int32_t* indices,
+                            const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
+                            int R, int rows_per_seq, int H, int topk_k, int nsplit, float sm_scale,
+                            int64_t kv_seq_stride, int kv_fp8, void* stream) {
+  return mla_partials_launch(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
+                             nsplit, sm_scale, kv_seq_stride, kv_fp8, false, stream);
 }
 
 int dsa_sparse_mla_combine(const float* part_acc, const float* part_m, const float* part_l,
@@ -882,6 +897,17 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
   int rc = dsa_sparse_mla_partials(q, kv, indices, seq_lens, part_acc, part_m, part_l, R,
                                    rows_per_seq, H, topk_k, nsplit, sm_scale, kv_seq_stride, kv_fp8,
                                    stream);
+  if (rc) return rc;
+  return dsa_sparse_mla_combine(part_acc, part_m, part_l, out, R, H, nsplit, stream);
+}
+
+int dsa_sparse_mla_decode_beside(const void* q, const void* kv, const int32_t* indices,
+                                 const int32_t* seq_lens, float* part_acc, float* part_m, float* part_l,
+                                 void* out, int R, int rows_per_seq, int H, int topk_k, int nsplit,
+                                 float sm_scale, int64_t kv_seq_stride, int kv_fp8, void* stream) {
+  DSA_REQUIRE(out && aligned16(out), "sparse MLA: out must be a 16-byte aligned pointer");
+  int rc = mla_partials_launch(q, kv, indices, seq_lens, part_acc, part_m, part_l, R, rows_per_seq, H, topk_k,
+                               nsplit, sm_scale, kv_seq_stride, kv_fp8, true, stream);
   if (rc) return rc;
   return dsa_sparse_mla_combine(part_acc, part_m, part_l, out, R, H, nsplit, stream);
 }

@@ -44,7 +44,7 @@ fused_decode_kernel(const __grid_constant__ CUtensorMap tmap, const scan::Params
     const int split = attn_id % attn_splits;
     const int hg = (attn_id / attn_splits) % attn_hgs;
     const int r = attn_id / (attn_splits * attn_hgs);
-    mla::mla_partials_body(pm, split, hg, r, fused_smem);
+    mla::mla_partials_body<false>(pm, split, hg, r, fused_smem);
   } else {
     scan::scan_tc_body<scan::kStagesTwoPerSm>(&tmap, ps, scan_id % scan_gx, scan_gx, scan_id / scan_gx, fused_smem);
   }

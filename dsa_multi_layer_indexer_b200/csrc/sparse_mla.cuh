@@ -326,6 +326,11 @@ __device__ __forceinline__ void dequant_tile_inplace(uint8_t* s_k, const int* s_
 
 // Body of the split-K partials for CTA (split, hg, r); `smem` is the CTA's
 // dynamic shared memory. Threads 0..127 take part.
+// kBeside: the launch does not depend on the kernel enqueued just before it (under the lagged
+// schedule the attention reads the PREVIOUS layer's selection while this layer's top-k runs), so
+// it releases its own dependents and starts at once, beside that kernel, and waits for it only
+// before it exits: it still completes after it, and the next kernel's wait covers both.
+template <bool kBeside = false>
 __device__ __forceinline__ void mla_partials_body(const Params& p, const int split, const int hg, const int r,
                                                   uint8_t* smem) {
   uint8_t* s_q = smem + SmemLayout::q_off;
@@ -349,7 +354,7 @@ __device__ __forceinline__ void mla_partials_body(const Params& p, const int spl
     mbar_fence_init();
   }
   cta128_sync();
-  pdl_wait();  // the selection, the queries and the lengths may come from the previous kernel
+  if constexpr (!kBeside) pdl_wait();  // the selection, the queries and the lengths may come from the previous kernel
   pdl_launch_dependents();
   // The first tile's selection entries are requested before the row's length is looked at: two
   // loads in flight together instead of two trips to global memory one after the other.
@@ -443,13 +448,20 @@ __device__ __forceinline__ void mla_partials_body(const Params& p, const int spl
     p.part_l[pbase + g] = l_run[0];
     p.part_l[pbase + g + 8] = l_run[1];
   }
+  if constexpr (kBeside) pdl_wait();
   DSA_KTIME_END(2);
 }
 
 __global__ void __launch_bounds__(kThreads)
 sparse_mla_partials_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t mla_smem[];
-  mla_partials_body(p, blockIdx.x, blockIdx.y, blockIdx.z, mla_smem);
+  mla_partials_body<false>(p, blockIdx.x, blockIdx.y, blockIdx.z, mla_smem);
+}
+
+__global__ void __launch_bounds__(kThreads)
+sparse_mla_partials_beside_kernel(const Params p) {
+  extern __shared__ __align__(16) uint8_t mla_smem[];
+  mla_partials_body<true>(p, blockIdx.x, blockIdx.y, blockIdx.z, mla_smem);
 }
 
 // ------------------------------------------------------------------------------

@@ -846,9 +846,12 @@ topk_cluster_kernel(const Params p, const int nk) {
       z[i] = make_uint4(0, 0, 0, 0);
   }
   if (!solo) cluster_arrive();
+  // Dependents are released before the wait: a dependent of the ordinary kind waits for this grid
+  // anyway, and one that runs beside this kernel (the lagged schedule's attention, a host copy)
+  // can then start while the scan before this kernel is still draining.
+  pdl_launch_dependents();
   pdl_wait();
   DSA_STAMP(stamp_cta, 15);
-  pdl_launch_dependents();
   const int R = int(gridDim.y);
   // ---- loads. The CTA's slice (positions slice_base .. + span) comes into shared memory as it
   // lies in global memory, by one bulk copy when the row is 16-byte aligned. Thread (warp, lane)

@@ -86,10 +86,20 @@ class HotPathState:
                         workspace=self.topk_ws)
         return self.indices
 
-    def run_attention(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float) -> torch.Tensor:
-        """Sparse MLA over ``attend`` (any ``[rows, topk]`` int32 selection)."""
+    def run_attention(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float,
+                      beside_previous: bool = False) -> torch.Tensor:
+        """Sparse MLA over ``attend`` (any ``[rows, topk]`` int32 selection). ``beside_previous``:
+        ``attend`` and the queries do not come from the kernel enqueued just before (see
+        :func:`ops.sparse_mla_decode`)."""
         return ops.sparse_mla_decode(self.q, cache.kv, attend, sm_scale, self.seq_lens,
-                                     scratch=self.scratch, out=self.out)
+                                     scratch=self.scratch, out=self.out, beside_previous=beside_previous)
+
+    def run_lagged_chained(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float) -> torch.Tensor:
+        """Lagged order on ONE stream: this layer's scan and top-k, then the attention over
+        ``attend`` (the previous layer's selection) enqueued behind the top-k and running beside
+        it. One chain of programmatic dependents, no second stream and no join."""
+        self.run_indexer(cache)
+        return self.run_attention(cache, attend, sm_scale, beside_previous=True)
 
     def run_lagged_fused(self, cache: LayerCache, attend: torch.Tensor, sm_scale: float) -> torch.Tensor:
         """Lagged order in ONE role-split launch: attention over ``attend`` (the

@@ -295,10 +295,14 @@ def sparse_mla_decode(
     out: Optional[torch.Tensor] = None,
     dense_keys: Optional[int] = None,
     stage: str = "both",
+    beside_previous: bool = False,
 ) -> torch.Tensor:
     """Sparse MLA decode: q ``[R, H, 576]`` bf16, kv ``[n_seq, cap, 576]`` bf16 or
     ``[n_seq, cap, 656]`` uint8 (fp8-packed rows), indices ``[R, topk]`` int32 or
-    None for dense attention over ``dense_keys`` positions. Returns ``[R, H, 512]`` bf16."""
+    None for dense attention over ``dense_keys`` positions. Returns ``[R, H, 512]`` bf16.
+    ``beside_previous``: none of the operands comes from the two kernels enqueued just before
+    this call (the lagged schedule's attention behind this layer's scan and top-k); the attention
+    then runs beside the top-k and completes after it."""
     _cuda_contig(q, "q", (torch.bfloat16,))
     _need(q.dim() == 3 and q.shape[2] == LATENT_DIM, "q must be [R, H, 576]")
     R, H = q.shape[0], q.shape[1]
@@ -329,8 +333,10 @@ def sparse_mla_decode(
     if out is None:
         out = torch.empty(R, H, VALUE_DIM, dtype=torch.bfloat16, device=q.device)
     _out_contig(out, "out", (torch.bfloat16,))
+    _need(not beside_previous or stage == "both", "beside_previous goes with stage='both'")
     if stage == "both":
-        _lib.check(_lib.lib().dsa_sparse_mla_decode(
+        fn = _lib.lib().dsa_sparse_mla_decode_beside if beside_previous else _lib.lib().dsa_sparse_mla_decode
+        _lib.check(fn(
             _ptr(q), _ptr(kv), _ptr(indices), _ptr(seq_lens), _ptr(scratch.acc), _ptr(scratch.m),
             _ptr(scratch.l), _ptr(out), R, rows_per_seq, H, topk, nsplit, float(sm_scale), cap, kv_fp8,
             _stream()))
@@ -483,8 +489,9 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 def copy_bytes(dst: torch.Tensor, src: torch.Tensor, beside_previous: bool = False) -> None:
     """``dst <- src`` (same byte count, a multiple of 16) by a kernel on the current stream.
     Each side is a contiguous CUDA tensor or pinned host memory. With ``beside_previous`` the
-    copy runs beside the kernel enqueued just before it (which must neither write nor read
-    these bytes) and completes after it; what is enqueued next sees both."""
+    copy runs beside the kernel enqueued just before it and completes after it; what is enqueued
+    next sees both. Neither of the two kernels enqueued before it may write or read these bytes
+    (the top-k releases its dependents before it waits for the scan)."""
     for t, name in ((dst, "dst"), (src, "src")):
         _need((t.is_cuda or t.is_pinned()) and t.is_contiguous(), f"{name} must be contiguous CUDA or pinned memory")
     nbytes = dst.numel() * dst.element_size()

@@ -285,6 +285,23 @@ int dsa_sparse_mla_decode(const void* q, const void* kv, const int32_t* indices,
                           int nsplit, float sm_scale, int64_t kv_seq_stride, int kv_fp8,
                           void* stream);
 
+/* dsa_sparse_mla_decode for a launch whose operands do NOT depend on the kernel enqueued just
+ * before it on the stream: under the lagged schedule (inference/modeling/transformer.py:1140-1190)
+ * a layer's attention reads the PREVIOUS layer's selection, so enqueued behind this layer's top-k it
+ * can run beside it (and, because the top-k releases its dependents before it waits for the
+ * scan, beside the end of the scan too: the operands must depend on neither of the two kernels
+ * enqueued before the call). The partials kernel releases its dependents and starts at once, and
+ * waits for the kernel before it only before it exits: it completes after that kernel, and whatever
+ * is enqueued next sees both. The whole lagged layer then stays one chain of programmatic
+ * dependents on one stream (scan -> top-k -> this) instead of two streams and a join. Launches
+ * that the tcgen05 kernel serves run as dsa_sparse_mla_decode does. The kernel before it must be
+ * one of this library's; behind any other work the call behaves like dsa_sparse_mla_decode. */
+int dsa_sparse_mla_decode_beside(const void* q, const void* kv, const int32_t* indices,
+                                 const int32_t* seq_lens, float* part_acc, float* part_m,
+                                 float* part_l, void* out, int R, int rows_per_seq, int H, int topk,
+                                 int nsplit, float sm_scale, int64_t kv_seq_stride, int kv_fp8,
+                                 void* stream);
+
 /* ---- (a6) fused indexer + attention launch -----------------------------------
  * One launch whose first CTAs compute the split-K attention partials over
  * `attend_indices` (under the lagged schedule: the PREVIOUS layer's selection)
@@ -337,9 +354,11 @@ int dsa_add_rmsnorm_bf16(const void* x, const void* delta, const void* weight, v
  * brings from the host. No counterpart in the reference. */
 int dsa_copy_bytes(void* dst, const void* src, int64_t bytes, void* stream);
 /* The same copy, run BESIDE the kernel enqueued just before it on the stream instead of after
- * it: for data that kernel neither writes nor reads (a step's queries arriving from the host
- * while the selection is being computed). The copy still completes after that kernel, and
- * whatever is enqueued next on the stream sees both. It keeps the stream's chain of
+ * it: for data that neither of the two kernels enqueued before it writes or reads (a step's
+ * queries arriving from the host while the selection is being computed; the top-k releases its
+ * dependents before it waits for the scan, so the copy may start while the scan still runs).
+ * The copy still completes after the kernel before it, and whatever is enqueued next on the
+ * stream sees both. It keeps the stream's chain of
  * programmatic dependents intact where a copy on a forked stream would cost a join. The
  * kernel before it must be one of this library's (they release their dependents early);
  * behind any other work it behaves like dsa_copy_bytes. No counterpart in the reference. */

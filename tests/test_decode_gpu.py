@@ -119,6 +119,49 @@ def test_copy_beside_the_previous_kernel_and_copy_with_epoch():
         ops.copy_post_epoch(back[:3], seen[:3], counter, flag)
 
 
+def test_lagged_layer_as_one_chain_equals_the_separate_launches():
+    """The lagged layer on one stream (scan, top-k, then the attention over the PREVIOUS selection
+    enqueued behind the top-k and running beside it) returns bit for bit what the indexer and
+    the attention return when they are launched one after the other, eagerly and from a graph,
+    and what is enqueued after the chain sees the top-k's selection as well as the attention's output."""
+    from dsa_multi_layer_indexer_b200 import _lib
+
+    ops, st, cache, host = make_case(ctx=20000, heads=32, topk=1024, seed=9)
+    sm = 192 ** -0.5
+    st.index_q.copy_(host["iq8"])
+    st.index_w.copy_(host["w"])
+    st.q.copy_(host["q"])
+    torch.manual_seed(4)
+    attend = torch.stack([torch.randperm(20000)[:1024] for _ in range(st.rows)]).int().cuda()
+    st.run_indexer(cache)
+    sel_ref = st.indices.clone()
+    out_ref = st.run_attention(cache, attend, sm).clone()
+    for _ in range(3):
+        st.indices.fill_(-1)
+        st.out.zero_()
+        st.run_lagged_chained(cache, attend, sm)
+        both = torch.cat([st.indices.view(-1), st.out.view(torch.int16).view(-1).int()])  # enqueued after the chain
+        torch.cuda.synchronize()
+        assert torch.equal(st.indices, sel_ref) and torch.equal(st.out, out_ref)
+        assert torch.equal(both[:sel_ref.numel()], sel_ref.view(-1))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        st.run_lagged_chained(cache, attend, sm)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(4):
+            st.run_lagged_chained(cache, attend, sm)
+    for _ in range(3):
+        st.indices.fill_(-1)
+        st.out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(st.indices, sel_ref) and torch.equal(st.out, out_ref)
+    _lib.check_device_status()
+
+
 def test_host_decoder_stream_sync_mode_agrees_with_polling():
     from dsa_multi_layer_indexer_b200.decode import HostDecoder
 
