@@ -826,6 +826,7 @@ def run_mli_stack(args):
             ("baseline_serial", D.ScheduleMode.BASELINE, False, None),
             ("lagged_one_stream", D.ScheduleMode.LAGGED_FUSED, False, None),
             ("lagged_two_streams", D.ScheduleMode.LAGGED_FUSED, True, None),
+            ("lagged_chained_one_stream", D.ScheduleMode.LAGGED_FUSED, "chained", None),
             ("lagged_two_streams_retention_1of4", D.ScheduleMode.LAGGED_FUSED, True, "4"),
             ("lagged_one_indexer_in_8_layers", D.ScheduleMode.LAGGED_FUSED, False, "8")):
         st = fresh_state(retention)
@@ -868,7 +869,7 @@ def run_mli_stack(args):
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     results = dict(zip(sorted(results), vals.tolist()))
-    lag = results["lagged_two_streams"]
+    lag = min(results["lagged_two_streams"], results["lagged_chained_one_stream"])
     idx_us = results["indexer_branch"]
     # attention + MLP of a layer: the stack with ONE indexer in its 8 layers, minus that indexer's share
     attn_mlp_us = results["lagged_one_indexer_in_8_layers"] - idx_us / n_layers
@@ -890,7 +891,11 @@ def run_mli_stack(args):
             "indexer_branch_us": idx_us, "attention_plus_mlp_us": attn_mlp_us, "max_us": max_us,
             "overlapped_us": lag, "overlapped_vs_max_pct": 100.0 * (lag / max_us - 1.0),
             "serial_us": results["baseline_serial"],
-            "note": "one CUDA graph per decode step; per-layer figure = step / 8; projections and MLP are cuBLAS/torch; "
+            "overlapped_form": ("chained_one_stream" if results["lagged_chained_one_stream"] <= results["lagged_two_streams"]
+                                else "two_streams"),
+            "note": "one CUDA graph per decode step; overlapped = the faster of the two lagged realisations (indexer on a "
+                    "second stream; or one stream with the attention enqueued behind the layer's scan and top-k and running "
+                    "beside the top-k); per-layer figure = step / 8; projections and MLP are cuBLAS/torch; "
                     "indexer_branch = scan + top-k of every layer back to back in one graph / 8; attention_plus_mlp = the "
                     "lagged stack with one indexer in its 8 layers minus that indexer's share; target: overlapped within "
                     "10 % of max(indexer_branch, attention_plus_mlp)",

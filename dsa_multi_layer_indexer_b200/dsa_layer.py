@@ -402,13 +402,17 @@ class DSALayer(nn.Module):
             return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value)
         return ops.topk_select(logits, topk, seq_lens, pad_value=pad_value, out_idx=ws.indices, workspace=ws.topk_ws)
 
-    def decode_attention(self, q, cache: LayerDecodeCache, indices, seq_lens) -> torch.Tensor:
-        """Attention hidden output [B, hidden] of the new tokens; indices None = dense."""
+    def decode_attention(self, q, cache: LayerDecodeCache, indices, seq_lens, beside_previous: bool = False) -> torch.Tensor:
+        """Attention hidden output [B, hidden] of the new tokens; indices None = dense.
+        ``beside_previous``: see :func:`ops.sparse_mla_decode` (used only when the queries need no
+        conversion or padding launch in front of the attention)."""
         c = self.config
         if cache.k_scale is not None:
             h = q.shape[1]
+            direct = q.dtype == torch.bfloat16 and h % ops.HEAD_BLOCK == 0 and q.is_contiguous()
             o = ops.sparse_mla_decode(_pad_heads(q.to(torch.bfloat16), ops.HEAD_BLOCK).contiguous(), cache.kv,
-                                      indices, self.sm_scale, seq_lens)[:, :h].to(q.dtype)
+                                      indices, self.sm_scale, seq_lens,
+                                      beside_previous=beside_previous and direct)[:, :h].to(q.dtype)
         else:
             o = ops.sparse_mla_f32(q.float().contiguous(), cache.kv, indices, c.kv_lora_rank, self.sm_scale,
                                    seq_lens).to(q.dtype)

@@ -247,27 +247,33 @@ class DSAModel(nn.Module):
 
     @torch.no_grad()
     def decode_step(self, state: DecodeState, x: torch.Tensor, mode: ScheduleMode,
-                    cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True,
+                    cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap=True,
                     record: Optional[dict] = None, lag_depth: int = 1) -> torch.Tensor:
         """One new token per sequence: x [B,hidden] -> final hidden [B,hidden].
 
         Appends the token's keys to every layer's caches at ``state.positions``
         and advances the device-side lengths. In the lagged modes with
-        ``overlap`` the indexers run on ``state.side_stream``. ``lag_depth`` k >= 2
+        ``overlap`` the indexers run on ``state.side_stream``; with ``overlap="chained"``
+        they stay on the current stream and the attention, which reads the PREVIOUS
+        layer's selection, is enqueued behind the layer's scan and top-k and runs beside
+        the top-k (one chain of programmatic dependents, no second stream). ``lag_depth`` k >= 2
         lets an indexer overlap k refresh spans instead of one (see
         ``_decode_step_depth``). Capturable in a CUDA graph (no host sync, lengths
         stay on the device)."""
         if lag_depth < 1:
             raise ValueError("lag_depth must be >= 1")
+        chained = overlap == "chained"
         if lag_depth > 1:
             if mode is ScheduleMode.BASELINE:
                 raise ValueError("lag_depth > 1 needs a lagged schedule mode")
+            if chained:
+                raise ValueError("the chained overlap is defined for lag_depth 1")
             return self._decode_step_depth(state, x, cold_start, overlap, record, lag_depth)
         types = self.config.resolved_attention_types
         n = len(self.layers)
         lagged = mode is not ScheduleMode.BASELINE
         main = torch.cuda.current_stream()
-        side = state.side_stream if (lagged and overlap) else None
+        side = state.side_stream if (lagged and overlap is True) else None
         state.seq_lens.add_(1)  # the new token sees itself
         carried: Optional[torch.Tensor] = None
         pending = False  # an indexer is in flight on the side stream
@@ -278,6 +284,7 @@ class DSAModel(nn.Module):
             is_dsa = types[li] is AttentionType.DSA
             q, iq, w = layer.decode_project(x_norm, state.rope, state.positions, cache, state.batch_index)
             made = None
+            beside = False
             if not lagged:
                 if is_dsa and state.runs_indexer[li]:
                     carried = made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
@@ -302,7 +309,12 @@ class DSAModel(nn.Module):
                         pending = True
                     else:
                         made = layer.decode_indexer(iq, w, cache, state.seq_lens, ws=state.workspaces[li])
-            attn = layer.decode_attention(q, cache, attend, state.seq_lens)
+                        # The attention may run beside the two launches just enqueued when nothing it
+                        # reads comes from them: the selection is an earlier layer's (li > 0), and the
+                        # indexer call allocated nothing that the attention's scratch could reuse.
+                        beside = (chained and li > 0 and attend is not None and cache.k_scale is not None
+                                  and iq.dtype == torch.uint8 and state.workspaces[li] is not None)
+            attn = layer.decode_attention(q, cache, attend, state.seq_lens, beside_previous=beside)
             x, x_norm = self._residual_tail(li, x, attn)
             if lagged and made is not None:
                 carried = made  # becomes visible to layer li+1 after the join
@@ -405,7 +417,7 @@ class DSAModel(nn.Module):
         return x_norm  # the last layer's tail applied the final norm
 
     def capture_decode(self, state: DecodeState, mode: ScheduleMode,
-                       cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap: bool = True,
+                       cold_start: ColdStartPolicy = ColdStartPolicy.DENSE, overlap=True,
                        lag_depth: int = 1):
         """Captures one decode step in a CUDA graph. Returns (graph, x_in, x_out):
         copy the token's hidden state into x_in, replay, read x_out. The caches

@@ -247,6 +247,54 @@ def test_production_geometry_fp8_bf16_path(D):
     assert min(overlaps) > 0.6 and sum(overlaps) / len(overlaps) > 0.8
 
 
+def test_lagged_chained_on_one_stream_equals_serial(D):
+    """The lagged schedule as one chain on one stream (each layer's attention enqueued behind the
+    layer's scan and top-k and running beside the top-k) returns bit for bit what the serial
+    lagged schedule returns, eagerly and from a captured graph, on the FP8 / bf16 path."""
+    cfg = production_config(D, layers=4)
+    torch.manual_seed(21)
+    model = D.DSAModel(cfg).eval().cuda().to(torch.bfloat16)
+    B, S0, steps = 2, 300, 5
+    prompt = torch.randn(B, S0, cfg.hidden_size, device="cuda").to(torch.bfloat16)
+    toks = torch.randn(steps, B, cfg.hidden_size, device="cuda").to(torch.bfloat16)
+    mode, cold = D.ScheduleMode.LAGGED_FUSED, D.ColdStartPolicy.EAGER
+
+    def run(overlap, graph):
+        st = model.init_decode(B, 320)
+        assert st.fp8
+        model.prefill(st, prompt, mode, cold)
+        outs, sels = [], []
+        if graph:
+            g, x_in, x_out = model.capture_decode(st, mode, cold, overlap=overlap)
+            for t in range(steps):
+                x_in.copy_(toks[t])
+                g.replay()
+                outs.append(x_out.clone())
+        else:
+            for t in range(steps):
+                rec = {}
+                outs.append(model.decode_step(st, toks[t], mode, cold, overlap=overlap, record=rec).clone())
+                sels.append([None if m is None else m.clone() for m in rec["produced"]])
+        torch.cuda.synchronize()
+        return torch.stack(outs), sels
+
+    serial, sel_serial = run(False, False)
+    chained, sel_chained = run("chained", False)
+    graphed, _ = run("chained", True)
+    assert torch.equal(serial, chained)
+    assert torch.equal(serial, graphed)
+    for a, b in zip(sel_serial, sel_chained):
+        for ia, ib in zip(a, b):
+            assert (ia is None) == (ib is None)
+            if ia is not None:
+                assert torch.equal(ia, ib)
+    with pytest.raises(ValueError):
+        st = model.init_decode(B, 320)
+        model.decode_step(st, toks[0], mode, cold, overlap="chained", lag_depth=2)
+    from dsa_multi_layer_indexer_b200 import _lib
+    _lib.check_device_status()
+
+
 def test_full_dimensions_decode_against_the_reference_model(D):
     """Two layers with the full-size dimensions (hidden 7168, 128 MLA heads, q_lora 1536,
     kv_lora 512, indexer 64 x 128, MLP 18432) under the lagged schedule: the bf16 / FP8 decode
