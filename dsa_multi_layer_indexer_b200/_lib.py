@@ -57,7 +57,7 @@ SIGNATURES: Dict[str, Tuple[object, List[object]]] = {
     "dsa_copy_bytes": (_i, [_p, _p, _l, _p]),
     "dsa_copy_bytes_beside": (_i, [_p, _p, _l, _p]),
     "dsa_post_epoch": (_i, [_p, _p, _p]),
-    "dsa_copy_post_epoch": (_i, [_p, _p, _l, _p, _p, _p]),
+    "dsa_copy_post_epoch": (_i, [_p, _p, _l, _p, _p, _i, _p]),
     "dsa_indexer_stage_fp8": (_i, [_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _p, _l, _p, _l,
                                    _i, _i, _l, _i, _i, _f, _f, _p]),
     "dsa_latent_append": (_i, [_p, _p, _f, _p, _p, _p, _p, _p, _i, _l, _l, _i, _i, _i, _p]),

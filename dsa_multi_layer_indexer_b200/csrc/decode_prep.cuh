@@ -204,11 +204,15 @@ __global__ void post_epoch_kernel(uint32_t* __restrict__ counter, volatile uint3
 // stream, a join and the signal. One CTA; the block barrier orders every thread's copy before
 // thread 0's system-wide fence. Launched as a programmatic dependent: it is resident and waiting
 // when the kernel before it retires.
+// With `beside` the bytes do not come from the kernel enqueued just before (the selection, while
+// the merge kernel runs): they are copied first, beside that kernel, and the wait comes after the
+// copy, so that by the time of the fence these writes have long left for the host.
 __global__ void __launch_bounds__(512)
 copy_post_epoch_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, int64_t n16,
-                       uint32_t* __restrict__ counter, volatile uint32_t* __restrict__ host_flag) {
-  pdl_wait();
+                       uint32_t* __restrict__ counter, volatile uint32_t* __restrict__ host_flag, int beside) {
+  if (!beside) pdl_wait();
   for (int64_t i = threadIdx.x; i < n16; i += 512) dst[i] = src[i];
+  if (beside) pdl_wait();
   __syncthreads();
   if (threadIdx.x == 0) {
     const uint32_t e = *counter + 1;

@@ -984,13 +984,13 @@ int dsa_post_epoch(uint32_t* counter, uint32_t* host_flag, void* stream) {
 }
 
 int dsa_copy_post_epoch(void* dst, const void* src, int64_t bytes, uint32_t* counter, uint32_t* host_flag,
-                        void* stream) {
+                        int beside, void* stream) {
   DSA_REQUIRE(dst && src && counter && host_flag, "copy + post epoch: null pointer");
   DSA_REQUIRE(bytes > 0 && bytes <= (int64_t(1) << 20) && bytes % 16 == 0 && aligned16(dst) && aligned16(src),
               "copy + post epoch: at most 1 MiB; size and both pointers must be multiples of 16 bytes");
   DSA_CUDA(launch_pdl(prep::copy_post_epoch_kernel, dim3(1), dim3(512), 0, static_cast<cudaStream_t>(stream),
                       static_cast<uint4*>(dst), static_cast<const uint4*>(src), bytes / 16, counter,
-                      static_cast<volatile uint32_t*>(host_flag)));
+                      static_cast<volatile uint32_t*>(host_flag), beside ? 1 : 0));
   return DSA_OK;
 }
 

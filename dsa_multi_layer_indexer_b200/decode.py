@@ -208,7 +208,8 @@ class HostDecoder:
         ops.sparse_mla_decode(s.q, self.cache.kv, s.indices, sm_scale, s.seq_lens, scratch=s.scratch,
                               out=self.h_out)
         if fused_tail:
-            ops.copy_post_epoch(self.h_indices, s.indices, self._epoch_dev, self._flag)
+            # (the selection was final three launches ago: it travels beside the merge kernel)
+            ops.copy_post_epoch(self.h_indices, s.indices, self._epoch_dev, self._flag, beside_previous=True)
             return
         main.wait_stream(side)
         if self.poll:

@@ -510,9 +510,12 @@ def post_epoch(counter: torch.Tensor, host_flag: torch.Tensor) -> None:
     _lib.check(_lib.lib().dsa_post_epoch(_ptr(counter), _ptr(host_flag), _stream()))
 
 
-def copy_post_epoch(dst: torch.Tensor, src: torch.Tensor, counter: torch.Tensor, host_flag: torch.Tensor) -> None:
+def copy_post_epoch(dst: torch.Tensor, src: torch.Tensor, counter: torch.Tensor, host_flag: torch.Tensor,
+                    beside_previous: bool = False) -> None:
     """:func:`copy_bytes` of at most 1 MiB followed by :func:`post_epoch`, as one launch: the last
-    node of a step when a few KB (the selection) still have to reach the host before the signal."""
+    node of a step when a few KB (the selection) still have to reach the host before the signal.
+    ``beside_previous``: ``src`` does not come from the two kernels enqueued before this call; it is
+    copied beside the last of them and only the signal waits for it."""
     for t, name in ((dst, "dst"), (src, "src")):
         _need((t.is_cuda or t.is_pinned()) and t.is_contiguous(), f"{name} must be contiguous CUDA or pinned memory")
     nbytes = dst.numel() * dst.element_size()
@@ -521,7 +524,8 @@ def copy_post_epoch(dst: torch.Tensor, src: torch.Tensor, counter: torch.Tensor,
     _need(counter.is_cuda and counter.dtype == torch.int32 and counter.numel() == 1, "counter: one CUDA int32")
     _need(host_flag.is_pinned() and host_flag.dtype == torch.int32 and host_flag.numel() == 1,
           "host_flag: one pinned int32")
-    _lib.check(_lib.lib().dsa_copy_post_epoch(_ptr(dst), _ptr(src), nbytes, _ptr(counter), _ptr(host_flag), _stream()))
+    _lib.check(_lib.lib().dsa_copy_post_epoch(_ptr(dst), _ptr(src), nbytes, _ptr(counter), _ptr(host_flag),
+                                              1 if beside_previous else 0, _stream()))
 
 
 def gemv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -372,9 +372,11 @@ int dsa_post_epoch(uint32_t* counter, uint32_t* host_flag, void* stream);
 /* dsa_copy_bytes (at most 1 MiB, by one CTA) followed by dsa_post_epoch in ONE launch: the
  * last node of a step's graph when a few KB (the selection) still have to reach the host
  * before the signal. It starts as a programmatic dependent of the kernel enqueued before
- * it on the stream and runs once that kernel has completed. No counterpart in the reference. */
+ * it on the stream and runs once that kernel has completed. beside != 0: the bytes do not
+ * come from that kernel (nor from the one before it); they are then copied beside it and only
+ * the signal waits for it. No counterpart in the reference. */
 int dsa_copy_post_epoch(void* dst, const void* src, int64_t bytes, uint32_t* counter, uint32_t* host_flag,
-                        void* stream);
+                        int beside, void* stream);
 
 /* y[b, n] = sum_k w[n, k] x[b, k] for a decode batch of 1..4 rows: bf16 operands, fp32
  * accumulation, w [n, k] row-major streamed once (the projection GEMVs of

@@ -92,9 +92,9 @@ def test_bad_arguments_are_rejected_before_any_launch():
     # the host-integration helpers: sizes in 16-byte pieces, the one-CTA copy bounded at 1 MiB
     rc = h.dsa_copy_bytes_beside(addr, addr, 24, None)
     assert rc == -1 and b"multiples of 16" in h.dsa_last_error()
-    rc = h.dsa_copy_post_epoch(addr, addr, 16, None, addr, None)
+    rc = h.dsa_copy_post_epoch(addr, addr, 16, None, addr, 0, None)
     assert rc == -1 and b"null pointer" in h.dsa_last_error()
-    rc = h.dsa_copy_post_epoch(addr, addr, (1 << 20) + 16, addr, addr, None)
+    rc = h.dsa_copy_post_epoch(addr, addr, (1 << 20) + 16, addr, addr, 1, None)
     assert rc == -1 and b"1 MiB" in h.dsa_last_error()
     # the attention that runs beside the kernel before it checks its arguments like the ordinary one
     rc = h.dsa_sparse_mla_decode_beside(addr, addr, addr, None, addr, addr, addr, addr, 1, 1, 24, 64, 1, 0.1, 128, 0, None)
